@@ -1,0 +1,516 @@
+// torch bindings for the sm_100a kernels of dion_b200.  Registered as
+// torch.ops.dion_b200.* by loading the shared library; no Python C-API use.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+#include <torch/torch.h>
+
+#include "gemm.h"
+#include "kernels.h"
+
+namespace {
+
+using at::Tensor;
+
+int gemm_dtype(const Tensor& t, const char* what) {
+  if (t.scalar_type() == at::kBFloat16) return dion::kBF16;
+  if (t.scalar_type() == at::kFloat) return dion::kF32;
+  TORCH_CHECK(false, what, " must be bfloat16 or float32, got ", t.scalar_type());
+}
+
+// Describe a logical (rows x cols) matrix view: returns major + pitch.
+// `contract_last` says whether the contraction (K) dimension is the last logical dim.
+void describe_operand(const Tensor& t, bool contract_last, int* major, int64_t* ld, int64_t* bstride,
+                      const char* what) {
+  TORCH_CHECK(t.dim() == 2 || t.dim() == 3, what, " must be 2-D or 3-D");
+  const int64_t s_row = t.stride(-2), s_col = t.stride(-1);
+  const int64_t rows = t.size(-2), cols = t.size(-1);
+  bool last_contig;
+  if (s_col == 1 && (s_row >= cols || rows == 1)) {
+    last_contig = true;
+    *ld = rows == 1 ? std::max<int64_t>(s_row, cols) : s_row;
+  } else if (s_row == 1 && (s_col >= rows || cols == 1)) {
+    last_contig = false;
+    *ld = cols == 1 ? std::max<int64_t>(s_col, rows) : s_col;
+  } else {
+    TORCH_CHECK(false, what, " needs a unit stride in one of its last two dimensions; strides = ", t.strides());
+  }
+  // K-major means the contraction dimension is the contiguous one.
+  *major = (last_contig == contract_last) ? dion::kMajorK : dion::kMajorMN;
+  *bstride = t.dim() == 3 ? t.stride(0) : 0;
+}
+
+void check_out(const Tensor& t, int64_t batch, int64_t M, int64_t N, const char* what) {
+  TORCH_CHECK(t.is_cuda(), what, " must be a CUDA tensor");
+  TORCH_CHECK(t.dim() == 2 || t.dim() == 3, what, " must be 2-D or 3-D");
+  TORCH_CHECK(t.size(-2) == M && t.size(-1) == N, what, " has shape ", t.sizes(), ", expected (.., ", M, ", ", N, ")");
+  TORCH_CHECK((t.dim() == 3 ? t.size(0) : 1) == batch, what, " batch mismatch");
+  TORCH_CHECK(t.stride(-1) == 1, what, " must be row-major");
+}
+
+// d = act(alpha * a @ b) + beta * c   (a: [B,]M,K   b: [B,]K,N, any transposed views)
+void gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, Tensor d,
+          const std::optional<Tensor>& d2, const std::optional<Tensor>& c_ptrs,
+          const std::optional<Tensor>& d_ptrs, const std::optional<Tensor>& d2_ptrs, double alpha, double beta,
+          int64_t act, int64_t epilogue, int64_t split_k, bool symmetric, int64_t block_n,
+          const std::optional<Tensor>& status) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda(), "gemm operands must be CUDA tensors");
+  TORCH_CHECK(a.scalar_type() == b.scalar_type(), "gemm operands must share a dtype");
+  TORCH_CHECK(a.dim() == b.dim(), "gemm operands must both be 2-D or both 3-D");
+  const c10::cuda::CUDAGuard guard(a.device());
+  dion::GemmArgs g;
+  g.ab_dtype = gemm_dtype(a, "a");
+  g.M = (int)a.size(-2);
+  g.K = (int)a.size(-1);
+  g.N = (int)b.size(-1);
+  TORCH_CHECK(b.size(-2) == g.K, "gemm inner dimensions differ: ", a.sizes(), " x ", b.sizes());
+  g.batch = a.dim() == 3 ? (int)a.size(0) : 1;
+  if (a.dim() == 3) TORCH_CHECK(b.size(0) == g.batch, "gemm batch sizes differ");
+  describe_operand(a, /*contract_last=*/true, &g.a_major, &g.lda, &g.a_batch_stride, "a");
+  describe_operand(b, /*contract_last=*/false, &g.b_major, &g.ldb, &g.b_batch_stride, "b");
+  g.A = a.data_ptr();
+  g.B = b.data_ptr();
+  g.alpha = (float)alpha;
+  g.beta = (float)beta;
+  g.act = (int)act;
+  g.epilogue = (int)epilogue;
+  g.split_k = (int)split_k;
+  g.symmetric = symmetric ? 1 : 0;
+  g.block_n = (int)block_n;
+
+  // Per-batch pointer arrays (int64 CUDA tensors) describe outputs that are separate
+  // allocations; `d` / `c` then only supply dtype, shape and pitch of one element.
+  if (d_ptrs.has_value()) {
+    TORCH_CHECK(d_ptrs->scalar_type() == at::kLong && d_ptrs->is_cuda() && d_ptrs->numel() >= g.batch);
+    TORCH_CHECK(d.dim() == 2 && d.size(0) == g.M && d.size(1) == g.N && d.stride(1) == 1);
+    g.d_ptrs = reinterpret_cast<void* const*>(d_ptrs->data_ptr<int64_t>());
+  } else {
+    check_out(d, g.batch, g.M, g.N, "d");
+    g.d_batch_stride = d.dim() == 3 ? d.stride(0) : 0;
+  }
+  g.D = d.data_ptr();
+  g.d_dtype = gemm_dtype(d, "d");
+  g.ldd = d.stride(-2);
+  if (c.has_value()) {
+    const Tensor& ct = *c;
+    if (c_ptrs.has_value()) {
+      TORCH_CHECK(c_ptrs->scalar_type() == at::kLong && c_ptrs->is_cuda() && c_ptrs->numel() >= g.batch);
+      g.c_ptrs = reinterpret_cast<const void* const*>(c_ptrs->data_ptr<int64_t>());
+    } else {
+      check_out(ct, g.batch, g.M, g.N, "c");
+      g.c_batch_stride = ct.dim() == 3 ? ct.stride(0) : 0;
+    }
+    g.C = ct.data_ptr();
+    g.c_dtype = gemm_dtype(ct, "c");
+    g.ldc = ct.stride(-2);
+  }
+  if (d2.has_value()) {
+    const Tensor& t = *d2;
+    TORCH_CHECK(t.scalar_type() == at::kBFloat16, "d2 must be bfloat16");
+    if (d2_ptrs.has_value()) {
+      TORCH_CHECK(d2_ptrs->scalar_type() == at::kLong && d2_ptrs->is_cuda() && d2_ptrs->numel() >= g.batch);
+      g.d2_ptrs = reinterpret_cast<void* const*>(d2_ptrs->data_ptr<int64_t>());
+    } else {
+      check_out(t, g.batch, g.M, g.N, "d2");
+      g.d2_batch_stride = t.dim() == 3 ? t.stride(0) : 0;
+    }
+    g.D2 = t.data_ptr();
+    g.ldd2 = t.stride(-2);
+  }
+  if (status.has_value()) {
+    TORCH_CHECK(status->scalar_type() == at::kInt && status->is_cuda());
+    g.status = status->data_ptr<int>();
+  }
+  cudaError_t e = dion::gemm_launch(g, at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "dion_b200 gemm launch failed: ", cudaGetErrorString(e), " ",
+              dion::gemm_last_error());
+}
+
+
+// ----------------------------------------------------------------------------- multi-tensor helpers
+
+int elem_type(const Tensor& t, const char* what) {
+  if (t.scalar_type() == at::kFloat) return dion::kElemF32;
+  if (t.scalar_type() == at::kBFloat16) return dion::kElemBF16;
+  TORCH_CHECK(false, what, " must be float32 or bfloat16, got ", t.scalar_type());
+}
+
+void check_list(at::TensorList ref, at::TensorList other, const char* what) {
+  TORCH_CHECK(ref.size() == other.size(), what, ": list length mismatch");
+  for (size_t i = 0; i < ref.size(); ++i) {
+    TORCH_CHECK(other[i].is_cuda() && other[i].is_contiguous(), what, ": tensors must be contiguous CUDA tensors");
+    TORCH_CHECK(other[i].numel() == ref[i].numel(), what, ": element count mismatch at index ", i);
+    TORCH_CHECK(other[i].scalar_type() == other[0].scalar_type(), what, ": mixed dtypes in one list");
+  }
+}
+
+// Calls fn(chunk, first_tensor_index) for consecutive groups of tensors.
+template <typename Fn>
+void for_each_chunk(std::initializer_list<std::pair<int, at::TensorList>> lists, Fn fn) {
+  const at::TensorList& ref = lists.begin()->second;
+  const int64_t n = (int64_t)ref.size();
+  const int block_elems = dion::multi_tensor_block_elems();
+  int64_t i = 0;
+  while (i < n) {
+    dion::TensorListChunk c;
+    memset(&c, 0, sizeof(c));
+    int k = 0;
+    int blocks = 0;
+    const int64_t first = i;
+    while (i < n && k < dion::kMaxTensorsPerLaunch) {
+      const int64_t numel = ref[i].numel();
+      for (const auto& l : lists) c.ptrs[l.first][k] = l.second[i].data_ptr();
+      c.numel[k] = numel;
+      c.block_start[k] = blocks;
+      blocks += (int)((numel + block_elems - 1) / block_elems);
+      ++k;
+      ++i;
+    }
+    c.block_start[k] = blocks;
+    c.num_tensors = k;
+    fn(c, first);
+  }
+}
+
+#define DION_CUDA_CHECK(expr)                                                           \
+  do {                                                                                  \
+    cudaError_t _e = (expr);                                                            \
+    TORCH_CHECK(_e == cudaSuccess, "dion_b200 kernel launch failed: ", cudaGetErrorString(_e)); \
+  } while (0)
+
+void adamw_multi(at::TensorList X, at::TensorList G, at::TensorList M, at::TensorList V, at::TensorList shadow,
+                 double lr, double beta1, double beta2, double weight_decay, double eps, int64_t step) {
+  if (X.empty()) return;
+  const c10::cuda::CUDAGuard guard(X[0].device());
+  check_list(X, X, "X");
+  check_list(X, G, "G");
+  check_list(X, M, "M");
+  check_list(X, V, "V");
+  TORCH_CHECK(X[0].scalar_type() == at::kFloat, "adamw_multi updates float32 parameters");
+  const bool has_shadow = !shadow.empty();
+  if (has_shadow) {
+    check_list(X, shadow, "shadow");
+    TORCH_CHECK(shadow[0].scalar_type() == at::kBFloat16);
+  }
+  dion::AdamWHyper h;
+  h.lr = (float)lr;
+  h.beta1 = (float)beta1;
+  h.beta2 = (float)beta2;
+  h.weight_decay = (float)weight_decay;
+  h.eps = (float)eps;
+  h.bias_correction1 = (float)(1.0 - std::pow(beta1, (double)step));
+  h.bias_correction2_sqrt = (float)std::sqrt(1.0 - std::pow(beta2, (double)step));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int gt = elem_type(G[0], "G"), mt = elem_type(M[0], "M"), vt = elem_type(V[0], "V");
+  auto run = [&](const dion::TensorListChunk& c, int64_t) {
+    DION_CUDA_CHECK(dion::adamw_multi_launch(c, gt, mt, vt, has_shadow, h, stream));
+  };
+  if (has_shadow) for_each_chunk({{0, X}, {1, G}, {2, M}, {3, V}, {4, shadow}}, run);
+  else for_each_chunk({{0, X}, {1, G}, {2, M}, {3, V}}, run);
+}
+
+void lion_multi(at::TensorList X, at::TensorList G, at::TensorList M, at::TensorList shadow, double lr,
+                double beta1, double beta2, double weight_decay) {
+  if (X.empty()) return;
+  const c10::cuda::CUDAGuard guard(X[0].device());
+  check_list(X, X, "X");
+  check_list(X, G, "G");
+  check_list(X, M, "M");
+  TORCH_CHECK(X[0].scalar_type() == at::kFloat, "lion_multi updates float32 parameters");
+  const bool has_shadow = !shadow.empty();
+  if (has_shadow) {
+    check_list(X, shadow, "shadow");
+    TORCH_CHECK(shadow[0].scalar_type() == at::kBFloat16);
+  }
+  dion::LionHyper h{(float)lr, (float)beta1, (float)beta2, (float)weight_decay};
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int gt = elem_type(G[0], "G"), mt = elem_type(M[0], "M");
+  auto run = [&](const dion::TensorListChunk& c, int64_t) {
+    DION_CUDA_CHECK(dion::lion_multi_launch(c, gt, mt, has_shadow, h, stream));
+  };
+  if (has_shadow) for_each_chunk({{0, X}, {1, G}, {2, M}, {4, shadow}}, run);
+  else for_each_chunk({{0, X}, {1, G}, {2, M}}, run);
+}
+
+void muon_pre_multi(at::TensorList G, at::TensorList M, at::TensorList U, double mu, bool nesterov,
+                    const std::optional<Tensor>& sumsq) {
+  if (G.empty()) return;
+  const c10::cuda::CUDAGuard guard(G[0].device());
+  check_list(G, G, "G");
+  check_list(G, M, "M");
+  check_list(G, U, "U");
+  TORCH_CHECK(M[0].scalar_type() == at::kFloat && U[0].scalar_type() == at::kBFloat16);
+  float* ss = nullptr;
+  if (sumsq.has_value()) {
+    TORCH_CHECK(sumsq->scalar_type() == at::kFloat && sumsq->is_cuda() && sumsq->numel() >= (int64_t)G.size());
+    ss = sumsq->data_ptr<float>();
+  }
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int gt = elem_type(G[0], "G");
+  for_each_chunk({{0, G}, {1, M}, {2, U}}, [&](const dion::TensorListChunk& c, int64_t first) {
+    DION_CUDA_CHECK(dion::muon_pre_multi_launch(c, gt, (float)mu, nesterov, ss ? ss + first : nullptr, stream));
+  });
+}
+
+void muon_post_multi(at::TensorList X, at::TensorList U, at::TensorList shadow, double decay, double step) {
+  if (X.empty()) return;
+  const c10::cuda::CUDAGuard guard(X[0].device());
+  check_list(X, X, "X");
+  check_list(X, U, "U");
+  TORCH_CHECK(X[0].scalar_type() == at::kFloat && U[0].scalar_type() == at::kBFloat16);
+  const bool has_shadow = !shadow.empty();
+  if (has_shadow) check_list(X, shadow, "shadow");
+  auto stream = at::cuda::getCurrentCUDAStream();
+  auto run = [&](const dion::TensorListChunk& c, int64_t) {
+    DION_CUDA_CHECK(dion::muon_post_multi_launch(c, has_shadow, (float)decay, (float)step, stream));
+  };
+  if (has_shadow) for_each_chunk({{0, X}, {1, U}, {4, shadow}}, run);
+  else for_each_chunk({{0, X}, {1, U}}, run);
+}
+
+void dion_accum_multi(at::TensorList G, at::TensorList M, const std::optional<Tensor>& nonzero) {
+  if (G.empty()) return;
+  const c10::cuda::CUDAGuard guard(G[0].device());
+  check_list(G, G, "G");
+  check_list(G, M, "M");
+  int* nz = nullptr;
+  if (nonzero.has_value()) {
+    TORCH_CHECK(nonzero->scalar_type() == at::kInt && nonzero->is_cuda() && nonzero->numel() >= (int64_t)G.size());
+    nz = nonzero->data_ptr<int>();
+  }
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int gt = elem_type(G[0], "G"), mt = elem_type(M[0], "M");
+  for_each_chunk({{0, G}, {1, M}}, [&](const dion::TensorListChunk& c, int64_t first) {
+    DION_CUDA_CHECK(dion::dion_accum_multi_launch(c, gt, mt, nz ? nz + first : nullptr, stream));
+  });
+}
+
+void cast_multi(at::TensorList src, at::TensorList dst) {
+  if (src.empty()) return;
+  const c10::cuda::CUDAGuard guard(src[0].device());
+  check_list(src, src, "src");
+  check_list(src, dst, "dst");
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int st = elem_type(src[0], "src"), dt = elem_type(dst[0], "dst");
+  for_each_chunk({{0, src}, {1, dst}}, [&](const dion::TensorListChunk& c, int64_t) {
+    DION_CUDA_CHECK(dion::cast_multi_launch(c, st, dt, stream));
+  });
+}
+
+// ----------------------------------------------------------------------------- model kernels
+
+void check_bf16(const Tensor& t, const char* what) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.is_contiguous(), what,
+              " must be a contiguous CUDA bfloat16 tensor");
+}
+
+void rmsnorm_fwd(const Tensor& x, const std::optional<Tensor>& residual, const std::optional<Tensor>& x_out,
+                 Tensor y, Tensor rstd, double eps) {
+  check_bf16(x, "x");
+  check_bf16(y, "y");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int dim = (int)x.size(-1);
+  const int64_t rows = x.numel() / dim;
+  TORCH_CHECK(rstd.scalar_type() == at::kFloat && rstd.numel() == rows);
+  const void* res = nullptr;
+  void* xo = nullptr;
+  if (residual.has_value()) {
+    check_bf16(*residual, "residual");
+    res = residual->data_ptr();
+  }
+  if (x_out.has_value()) {
+    check_bf16(*x_out, "x_out");
+    xo = x_out->data_ptr();
+  }
+  DION_CUDA_CHECK(dion::rmsnorm_fwd_launch(x.data_ptr(), res, xo, y.data_ptr(), rstd.data_ptr<float>(), rows, dim,
+                                           (float)eps, at::cuda::getCurrentCUDAStream()));
+}
+
+void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& rstd, const std::optional<Tensor>& dx_add,
+                 Tensor dx) {
+  check_bf16(dy, "dy");
+  check_bf16(x, "x");
+  check_bf16(dx, "dx");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int dim = (int)x.size(-1);
+  const int64_t rows = x.numel() / dim;
+  const void* add = nullptr;
+  if (dx_add.has_value()) {
+    check_bf16(*dx_add, "dx_add");
+    add = dx_add->data_ptr();
+  }
+  DION_CUDA_CHECK(dion::rmsnorm_bwd_launch(dy.data_ptr(), x.data_ptr(), rstd.data_ptr<float>(), add, dx.data_ptr(),
+                                           rows, dim, at::cuda::getCurrentCUDAStream()));
+}
+
+// q, k: [tokens, heads * head_dim] (row pitch = stride(0)); outputs contiguous [tokens, heads, head_dim]
+void rope_qknorm_fwd(const Tensor& q, const Tensor& k, Tensor q_out, Tensor k_out, const Tensor& cos,
+                     const Tensor& sin, int64_t seq_len, int64_t heads, int64_t head_dim, double eps) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(q.dim() == 2 && k.dim() == 2 && q.stride(1) == 1 && k.stride(1) == 1 && q.stride(0) == k.stride(0));
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16);
+  check_bf16(q_out, "q_out");
+  check_bf16(k_out, "k_out");
+  check_bf16(cos, "cos");
+  check_bf16(sin, "sin");
+  const int64_t tokens = q.size(0);
+  TORCH_CHECK(q.size(1) == heads * head_dim && cos.size(-1) == head_dim / 2 && cos.numel() >= seq_len * head_dim / 2);
+  DION_CUDA_CHECK(dion::rope_qknorm_fwd_launch(q.data_ptr(), k.data_ptr(), q_out.data_ptr(), k_out.data_ptr(),
+                                               cos.data_ptr(), sin.data_ptr(), tokens, (int)seq_len, (int)heads,
+                                               (int)head_dim, q.stride(0), heads * head_dim, (float)eps,
+                                               at::cuda::getCurrentCUDAStream()));
+}
+
+void rope_qknorm_bwd(const Tensor& dq_out, const Tensor& dk_out, const Tensor& q, const Tensor& k, Tensor dq,
+                     Tensor dk, const Tensor& cos, const Tensor& sin, int64_t seq_len, int64_t heads,
+                     int64_t head_dim, double eps) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(q.dim() == 2 && k.dim() == 2 && q.stride(1) == 1 && k.stride(1) == 1 && q.stride(0) == k.stride(0));
+  TORCH_CHECK(dq.dim() == 2 && dk.dim() == 2 && dq.stride(1) == 1 && dk.stride(1) == 1 &&
+              dq.stride(0) == q.stride(0) && dk.stride(0) == q.stride(0));
+  check_bf16(dq_out, "dq_out");
+  check_bf16(dk_out, "dk_out");
+  const int64_t tokens = q.size(0);
+  DION_CUDA_CHECK(dion::rope_qknorm_bwd_launch(dq_out.data_ptr(), dk_out.data_ptr(), q.data_ptr(), k.data_ptr(),
+                                               dq.data_ptr(), dk.data_ptr(), cos.data_ptr(), sin.data_ptr(), tokens,
+                                               (int)seq_len, (int)heads, (int)head_dim, q.stride(0),
+                                               heads * head_dim, (float)eps, at::cuda::getCurrentCUDAStream()));
+}
+
+void relu2_fwd(const Tensor& x, Tensor h) {
+  check_bf16(x, "x");
+  check_bf16(h, "h");
+  const c10::cuda::CUDAGuard guard(x.device());
+  DION_CUDA_CHECK(dion::relu2_fwd_launch(x.data_ptr(), h.data_ptr(), x.numel(), at::cuda::getCurrentCUDAStream()));
+}
+void relu2_bwd(const Tensor& dh, const Tensor& x, Tensor dx) {
+  check_bf16(dh, "dh");
+  check_bf16(x, "x");
+  check_bf16(dx, "dx");
+  const c10::cuda::CUDAGuard guard(x.device());
+  DION_CUDA_CHECK(dion::relu2_bwd_launch(dh.data_ptr(), x.data_ptr(), dx.data_ptr(), x.numel(),
+                                         at::cuda::getCurrentCUDAStream()));
+}
+
+void cross_entropy_fwd_bwd(Tensor logits, const Tensor& targets, Tensor row_loss, const std::optional<Tensor>& scale,
+                           double grad_scale, int64_t ignore_index, bool write_grad) {
+  const c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.scalar_type() == at::kBFloat16 && logits.stride(1) == 1);
+  TORCH_CHECK(targets.is_cuda() && targets.scalar_type() == at::kLong && targets.is_contiguous() &&
+              targets.numel() == logits.size(0));
+  TORCH_CHECK(row_loss.scalar_type() == at::kFloat && row_loss.numel() == logits.size(0) && row_loss.is_contiguous());
+  const float* sp = nullptr;
+  if (scale.has_value()) {
+    TORCH_CHECK(scale->scalar_type() == at::kFloat && scale->is_cuda());
+    sp = scale->data_ptr<float>();
+  }
+  DION_CUDA_CHECK(dion::cross_entropy_fwd_bwd_launch(logits.data_ptr(), (const long long*)targets.data_ptr<int64_t>(),
+                                                     row_loss.data_ptr<float>(), sp, logits.size(0),
+                                                     (int)logits.size(1), logits.stride(0), (float)grad_scale,
+                                                     ignore_index, write_grad, at::cuda::getCurrentCUDAStream()));
+}
+
+void embedding_fwd(const Tensor& table, const Tensor& idx, Tensor out) {
+  const c10::cuda::CUDAGuard guard(table.device());
+  TORCH_CHECK(table.is_cuda() && table.is_contiguous() && table.dim() == 2);
+  TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kLong && idx.is_contiguous());
+  check_bf16(out, "out");
+  DION_CUDA_CHECK(dion::embedding_fwd_launch(table.data_ptr(), elem_type(table, "table"),
+                                             (const long long*)idx.data_ptr<int64_t>(), out.data_ptr(), idx.numel(),
+                                             (int)table.size(1), at::cuda::getCurrentCUDAStream()));
+}
+void embedding_bwd(const Tensor& dout, const Tensor& idx, Tensor dtable) {
+  const c10::cuda::CUDAGuard guard(dout.device());
+  check_bf16(dout, "dout");
+  TORCH_CHECK(dtable.is_cuda() && dtable.scalar_type() == at::kFloat && dtable.is_contiguous());
+  DION_CUDA_CHECK(dion::embedding_bwd_launch(dout.data_ptr(), (const long long*)idx.data_ptr<int64_t>(),
+                                             dtable.data_ptr<float>(), idx.numel(), (int)dtable.size(1),
+                                             at::cuda::getCurrentCUDAStream()));
+}
+
+// ----------------------------------------------------------------------------- linear algebra
+
+void chol_inverse(const Tensor& G, Tensor Z, Tensor work, Tensor info, double pivot_floor) {
+  const c10::cuda::CUDAGuard guard(G.device());
+  TORCH_CHECK(G.is_cuda() && G.scalar_type() == at::kFloat && G.dim() == 3 && G.size(1) == G.size(2) &&
+              G.stride(2) == 1);
+  const int batch = (int)G.size(0), r = (int)G.size(1);
+  TORCH_CHECK(Z.is_contiguous() && Z.scalar_type() == at::kFloat && Z.numel() == (int64_t)batch * r * r);
+  TORCH_CHECK(work.is_contiguous() && work.scalar_type() == at::kFloat && work.numel() >= (int64_t)batch * r * r);
+  TORCH_CHECK(info.scalar_type() == at::kInt && info.numel() >= batch);
+  cudaError_t e = dion::chol_inverse_launch(G.data_ptr<float>(), Z.data_ptr<float>(), work.data_ptr<float>(),
+                                            info.data_ptr<int>(), batch, r, G.stride(1), G.stride(0),
+                                            (float)pivot_floor, at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "chol_inverse launch failed (rank ", r, "): ", cudaGetErrorString(e));
+}
+
+void col_sumsq(const Tensor& X, Tensor out) {
+  const c10::cuda::CUDAGuard guard(X.device());
+  TORCH_CHECK(X.is_cuda() && X.dim() == 3 && X.stride(2) == 1);
+  TORCH_CHECK(out.scalar_type() == at::kFloat && out.is_contiguous() && out.numel() == X.size(0) * X.size(2));
+  DION_CUDA_CHECK(dion::col_sumsq_launch(X.data_ptr(), elem_type(X, "X"), out.data_ptr<float>(), (int)X.size(0),
+                                         X.size(1), (int)X.size(2), X.stride(1), X.stride(0),
+                                         at::cuda::getCurrentCUDAStream()));
+}
+
+}  // namespace
+
+TORCH_LIBRARY(dion_b200, m) {
+  m.def(
+      "gemm(Tensor a, Tensor b, Tensor? c, Tensor(a!) d, Tensor(b!)? d2, Tensor? c_ptrs, Tensor? d_ptrs, "
+      "Tensor? d2_ptrs, float alpha, float beta, int act, int epilogue, int split_k, bool symmetric, "
+      "int block_n, Tensor? status) -> ()");
+  m.def(
+      "adamw_multi(Tensor(a!)[] X, Tensor[] G, Tensor(b!)[] M, Tensor(c!)[] V, Tensor(d!)[] shadow, float lr, "
+      "float beta1, float beta2, float weight_decay, float eps, int step) -> ()");
+  m.def(
+      "lion_multi(Tensor(a!)[] X, Tensor[] G, Tensor(b!)[] M, Tensor(c!)[] shadow, float lr, float beta1, "
+      "float beta2, float weight_decay) -> ()");
+  m.def("muon_pre_multi(Tensor[] G, Tensor(a!)[] M, Tensor(b!)[] U, float mu, bool nesterov, Tensor(c!)? sumsq) -> ()");
+  m.def("muon_post_multi(Tensor(a!)[] X, Tensor[] U, Tensor(b!)[] shadow, float decay, float step) -> ()");
+  m.def("dion_accum_multi(Tensor[] G, Tensor(a!)[] M, Tensor(b!)? nonzero) -> ()");
+  m.def("cast_multi(Tensor[] src, Tensor(a!)[] dst) -> ()");
+  m.def("rmsnorm_fwd(Tensor x, Tensor? residual, Tensor(a!)? x_out, Tensor(b!) y, Tensor(c!) rstd, float eps) -> ()");
+  m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor rstd, Tensor? dx_add, Tensor(a!) dx) -> ()");
+  m.def(
+      "rope_qknorm_fwd(Tensor q, Tensor k, Tensor(a!) q_out, Tensor(b!) k_out, Tensor cos, Tensor sin, int seq_len, "
+      "int heads, int head_dim, float eps) -> ()");
+  m.def(
+      "rope_qknorm_bwd(Tensor dq_out, Tensor dk_out, Tensor q, Tensor k, Tensor(a!) dq, Tensor(b!) dk, Tensor cos, "
+      "Tensor sin, int seq_len, int heads, int head_dim, float eps) -> ()");
+  m.def("relu2_fwd(Tensor x, Tensor(a!) h) -> ()");
+  m.def("relu2_bwd(Tensor dh, Tensor x, Tensor(a!) dx) -> ()");
+  m.def(
+      "cross_entropy_fwd_bwd(Tensor(a!) logits, Tensor targets, Tensor(b!) row_loss, Tensor? scale, float grad_scale, "
+      "int ignore_index, bool write_grad) -> ()");
+  m.def("embedding_fwd(Tensor table, Tensor idx, Tensor(a!) out) -> ()");
+  m.def("embedding_bwd(Tensor dout, Tensor idx, Tensor(a!) dtable) -> ()");
+  m.def("chol_inverse(Tensor G, Tensor(a!) Z, Tensor(b!) work, Tensor(c!) info, float pivot_floor) -> ()");
+  m.def("col_sumsq(Tensor X, Tensor(a!) out) -> ()");
+}
+
+TORCH_LIBRARY_IMPL(dion_b200, CUDA, m) {
+  m.impl("gemm", &gemm);
+  m.impl("rmsnorm_fwd", &rmsnorm_fwd);
+  m.impl("rmsnorm_bwd", &rmsnorm_bwd);
+  m.impl("rope_qknorm_fwd", &rope_qknorm_fwd);
+  m.impl("rope_qknorm_bwd", &rope_qknorm_bwd);
+  m.impl("relu2_fwd", &relu2_fwd);
+  m.impl("relu2_bwd", &relu2_bwd);
+  m.impl("cross_entropy_fwd_bwd", &cross_entropy_fwd_bwd);
+  m.impl("embedding_fwd", &embedding_fwd);
+  m.impl("embedding_bwd", &embedding_bwd);
+  m.impl("chol_inverse", &chol_inverse);
+  m.impl("col_sumsq", &col_sumsq);
+}
+
+// Ops whose arguments are tensor lists have no dispatch key to select on when a list
+// is empty, so they are registered for every backend and check devices themselves.
+TORCH_LIBRARY_IMPL(dion_b200, CompositeExplicitAutograd, m) {
+  m.impl("adamw_multi", &adamw_multi);
+  m.impl("lion_multi", &lion_multi);
+  m.impl("muon_pre_multi", &muon_pre_multi);
+  m.impl("muon_post_multi", &muon_post_multi);
+  m.impl("dion_accum_multi", &dion_accum_multi);
+  m.impl("cast_multi", &cast_multi);
+}

@@ -1,0 +1,69 @@
+// Host interface of the tcgen05 GEMM.  Plain C++/CUDA types only, so that the
+// same entry points serve the torch bindings and C callers.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace dion {
+
+enum GemmDType : int { kBF16 = 0, kF32 = 1 };  // kF32 operands run as TF32 on the tensor cores
+enum GemmMajor : int { kMajorK = 0, kMajorMN = 1 };
+enum GemmEpilogue : int {
+  kEpiStore = 0,      // D = act(alpha * acc) + beta * C
+  kEpiAtomicAdd = 1,  // D += alpha * acc   (fp32 D, red.global.add; used with split-K)
+};
+enum GemmAct : int { kActNone = 0, kActRelu2 = 1 };
+
+// D[b] = alpha * op(A[b]) * op(B[b]) (+ beta * C[b]),  op(A) is M x K, op(B) is K x N.
+//
+// Operand storage:
+//   a_major == kMajorK  : A is stored M x K row-major (K contiguous), row pitch lda
+//   a_major == kMajorMN : A is stored K x M row-major (M contiguous), row pitch lda
+//   b_major == kMajorK  : B is stored N x K row-major (K contiguous), row pitch ldb
+//   b_major == kMajorMN : B is stored K x N row-major (N contiguous), row pitch ldb
+// Pitches and batch strides are in elements.  Base pointers must be 16-byte
+// aligned and pitches a multiple of 16 bytes (TMA requirement).
+struct GemmArgs {
+  const void* A = nullptr;
+  const void* B = nullptr;
+  int ab_dtype = kBF16;
+  int a_major = kMajorK;
+  int b_major = kMajorK;
+  int64_t lda = 0, ldb = 0;
+  int64_t a_batch_stride = 0, b_batch_stride = 0;
+  int M = 0, N = 0, K = 0, batch = 1;
+  int split_k = 1;  // > 1 requires kEpiAtomicAdd
+
+  float alpha = 1.f, beta = 0.f;
+  // C (optional addend) and D (output); row-major M x N with pitches ldc / ldd.
+  const void* C = nullptr;
+  int c_dtype = kF32;
+  int64_t ldc = 0, c_batch_stride = 0;
+  const void* const* c_ptrs = nullptr;  // optional device array of per-batch C pointers
+  void* D = nullptr;
+  int d_dtype = kF32;
+  int64_t ldd = 0, d_batch_stride = 0;
+  void* const* d_ptrs = nullptr;  // optional device array of per-batch D pointers
+  // Optional second output: bf16 copy of what was stored to D.
+  void* D2 = nullptr;
+  int64_t ldd2 = 0, d2_batch_stride = 0;
+  void* const* d2_ptrs = nullptr;
+
+  int epilogue = kEpiStore;
+  int act = kActNone;
+  // Symmetric mode (M == N, result known symmetric, e.g. X * X^T): only tiles on or
+  // above the diagonal are computed and each off-diagonal tile is also stored transposed.
+  int symmetric = 0;
+  int block_n = 0;  // 0 = choose automatically (64 / 128 / 256)
+  int max_ctas = 0;  // 0 = one CTA per SM
+
+  int* status = nullptr;  // device int, set to a non-zero code on a device-side failure
+};
+
+// Returns cudaSuccess or the launch error; argument errors return cudaErrorInvalidValue
+// and write a message retrievable with gemm_last_error().
+cudaError_t gemm_launch(const GemmArgs& args, cudaStream_t stream);
+const char* gemm_last_error();
+
+}  // namespace dion

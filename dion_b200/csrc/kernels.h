@@ -1,0 +1,105 @@
+// Host launchers of the non-GEMM sm_100a kernels (plain CUDA types only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace dion {
+
+enum ElemType : int { kElemF32 = 0, kElemBF16 = 1 };
+
+// ---------------------------------------------------------------------------
+// Multi-tensor launches: up to kMaxTensorsPerLaunch tensors travel in the kernel
+// parameter block (no device-side tables, no host-to-device copies).
+// ---------------------------------------------------------------------------
+constexpr int kMaxTensorsPerLaunch = 40;
+constexpr int kMaxLists = 5;
+
+struct TensorListChunk {
+  void* ptrs[kMaxLists][kMaxTensorsPerLaunch];
+  long long numel[kMaxTensorsPerLaunch];
+  int block_start[kMaxTensorsPerLaunch + 1];  // prefix sum of thread blocks per tensor
+  int num_tensors;
+};
+
+struct AdamWHyper {
+  float lr, beta1, beta2, weight_decay, eps;
+  float bias_correction1, bias_correction2_sqrt;
+};
+struct LionHyper {
+  float lr, beta1, beta2, weight_decay;
+};
+
+// lists: 0 = X (fp32), 1 = G, 2 = M, 3 = V, 4 = optional bf16 shadow of X
+cudaError_t adamw_multi_launch(const TensorListChunk& tl, int g_type, int m_type, int v_type, bool has_shadow,
+                               const AdamWHyper& h, cudaStream_t s);
+// lists: 0 = X (fp32), 1 = G, 2 = M, 4 = optional bf16 shadow of X
+cudaError_t lion_multi_launch(const TensorListChunk& tl, int g_type, int m_type, bool has_shadow,
+                              const LionHyper& h, cudaStream_t s);
+// Muon momentum: M = mu*M + G; U = nesterov ? mu*M + G : M  (bf16 out); sumsq[t] += sum(U^2)
+// lists: 0 = G, 1 = M (fp32), 2 = U (bf16);  sumsq: fp32[num_tensors] or null
+cudaError_t muon_pre_multi_launch(const TensorListChunk& tl, int g_type, float mu, bool nesterov, float* sumsq,
+                                  cudaStream_t s);
+// Muon apply: X = decay * X - step * U ; lists: 0 = X (fp32), 1 = U (bf16), 4 = optional bf16 shadow
+cudaError_t muon_post_multi_launch(const TensorListChunk& tl, bool has_shadow, float decay, float step,
+                                   cudaStream_t s);
+// Dion momentum accumulate: M += G; nonzero[t] |= any(M != 0)
+// lists: 0 = G, 1 = M ; nonzero: int[num_tensors] or null
+cudaError_t dion_accum_multi_launch(const TensorListChunk& tl, int g_type, int m_type, int* nonzero,
+                                    cudaStream_t s);
+// dst = (dst_type) src ; lists: 0 = src, 1 = dst
+cudaError_t cast_multi_launch(const TensorListChunk& tl, int src_type, int dst_type, cudaStream_t s);
+
+int multi_tensor_block_elems();
+
+// ---------------------------------------------------------------------------
+// Model kernels (bf16 activations, fp32 math)
+// ---------------------------------------------------------------------------
+// y = x * rsqrt(mean(x^2) + eps)  over the last dim (weightless RMSNorm); rstd saved for backward.
+// When `residual` is given: x_out = x + residual is written first and normalised.
+cudaError_t rmsnorm_fwd_launch(const void* x, const void* residual, void* x_out, void* y, float* rstd,
+                               long long rows, int dim, float eps, cudaStream_t s);
+// dx = rstd * (dy - y_hat * mean(dy * y_hat)) (+ dx_add when given), y_hat = x * rstd
+cudaError_t rmsnorm_bwd_launch(const void* dy, const void* x, const float* rstd, const void* dx_add, void* dx,
+                               long long rows, int dim, cudaStream_t s);
+// Rotary embedding (half-split) followed by RMS norm over head_dim, for q and k together.
+// in/out: [tokens, heads, head_dim] bf16 rows with arbitrary row pitch; cos/sin: [seq, head_dim/2] bf16.
+cudaError_t rope_qknorm_fwd_launch(const void* q, const void* k, void* q_out, void* k_out, const void* cos,
+                                   const void* sin, long long tokens, int seq_len, int heads, int head_dim,
+                                   long long in_pitch, long long out_pitch, float eps, cudaStream_t s);
+cudaError_t rope_qknorm_bwd_launch(const void* dq_out, const void* dk_out, const void* q, const void* k, void* dq,
+                                   void* dk, const void* cos, const void* sin, long long tokens, int seq_len,
+                                   int heads, int head_dim, long long in_pitch, long long out_pitch, float eps,
+                                   cudaStream_t s);
+// h = relu(x)^2 ; dx = dh * 2 * relu(x)
+cudaError_t relu2_fwd_launch(const void* x, void* h, long long n, cudaStream_t s);
+cudaError_t relu2_bwd_launch(const void* dh, const void* x, void* dx, long long n, cudaStream_t s);
+// Softmax cross-entropy over bf16 logits [rows, vocab] with row pitch `pitch`:
+//   row_loss[i] = lse_i - logit_i[target_i]  (0 for rows whose target == ignore_index)
+//   when write_grad: logits are overwritten with grad_scale * (*scale_ptr) * (softmax - onehot)
+//   (zero for ignored rows); scale_ptr is an optional device scalar, e.g. 1 / valid rows.
+cudaError_t cross_entropy_fwd_bwd_launch(void* logits, const long long* targets, float* row_loss,
+                                         const float* scale_ptr, long long rows, int vocab, long long pitch,
+                                         float grad_scale, long long ignore_index, bool write_grad, cudaStream_t s);
+// out[t, :] = (bf16) table[idx[t], :]   (table fp32 or bf16)
+cudaError_t embedding_fwd_launch(const void* table, int table_type, const long long* idx, void* out,
+                                 long long tokens, int dim, cudaStream_t s);
+// dtable[idx[t], :] += dout[t, :]  (fp32 atomic accumulation)
+cudaError_t embedding_bwd_launch(const void* dout, const long long* idx, float* dtable, long long tokens, int dim,
+                                 cudaStream_t s);
+
+// ---------------------------------------------------------------------------
+// Dense linear algebra on small matrices (one CTA per matrix, fp32)
+// ---------------------------------------------------------------------------
+// For each of `batch` symmetric positive (semi-)definite r x r matrices G (row-major,
+// pitch ldg): computes the upper Cholesky factor R (G = R^T R) with pivot clamping and
+// writes Rinv = R^{-1} (upper triangular, zeros below the diagonal).
+// `info[b]` counts clamped pivots.  `work` is scratch of batch * r * r floats.
+cudaError_t chol_inverse_launch(const float* G, float* Rinv, float* work, int* info, int batch, int r,
+                                long long ldg, long long g_batch_stride, float pivot_floor_rel, cudaStream_t s);
+
+// Column sums of squares: out[b, j] = sum_i X[b, i, j]^2  (X fp32/bf16, row-major [batch, rows, cols])
+cudaError_t col_sumsq_launch(const void* X, int x_type, float* out, int batch, long long rows, int cols,
+                             long long ldx, long long batch_stride, cudaStream_t s);
+
+}  // namespace dion

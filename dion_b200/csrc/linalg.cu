@@ -1,0 +1,290 @@
+// Small dense factorizations that the Dion orthonormalisation needs, one CTA per
+// matrix, fp32 throughout.
+//
+// chol_inverse: for a symmetric positive semi-definite Gram matrix G = P^T P it
+// produces Z = L^{-1} with G ~= L L^T, after a Jacobi (unit-diagonal) scaling of G,
+// so that P * Z^T has orthonormal columns.  It is the device-side replacement for the
+// cuSOLVER geqrf / potrf + cuBLAS trsm sequence of the reference
+// (dion/dion.py:1284-1303, 1366-1406).  A pivot that is not safely positive is
+// clamped instead of failing; the count of clamped pivots is reported per matrix.
+//
+// Algorithm (right-looking, block size NB): per block column k
+//   1. factor the NB x NB diagonal block in shared memory, invert it (Linv)
+//   2. Z[k,:]   = Linv * B[k,:]                (B starts as the identity)
+//   3. panel    = A[k+1:, k] * Linv^T          (kept transposed in shared memory)
+//   4. A[k+1:, k+1:] -= panel * panel^T        (lower triangle, 64x64 register tiles)
+//      B[k+1:, :]    -= panel * Z[k,:]
+#include <cuda_bf16.h>
+
+#include "kernels.h"
+
+namespace dion {
+
+namespace {
+
+constexpr int kCholThreads = 256;
+
+// out[row0 + i][col0 + j] -= sum_a At[a][i] * Bt[a][j]   for a 64 x 64 tile; each of the
+// 256 threads owns a 4 x 4 sub-tile.  At / Bt are shared-memory arrays indexed [a][.]
+// whose rows are 16-byte aligned and the offsets multiples of 4.
+template <int NB>
+__device__ __forceinline__ void tile_update(float* __restrict__ out, long long ld, int row0, int col0,
+                                            const float* __restrict__ At, int a_stride,
+                                            const float* __restrict__ Bt, int b_stride, int row_end, int col_end) {
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  const int i0 = ty * 4, j0 = tx * 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll 8
+  for (int a = 0; a < NB; ++a) {
+    const float4 av = *reinterpret_cast<const float4*>(At + (long long)a * a_stride + i0);
+    const float4 bv = *reinterpret_cast<const float4*>(Bt + (long long)a * b_stride + j0);
+    const float ar[4] = {av.x, av.y, av.z, av.w};
+    const float br[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(ar[i], br[j], acc[i][j]);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = row0 + i0 + i;
+    if (r >= row_end) continue;
+    float* o = out + (long long)r * ld + col0 + j0;
+    if (col0 + j0 + 3 < col_end && ((ld & 3) == 0)) {
+      float4 v = *reinterpret_cast<float4*>(o);
+      v.x -= acc[i][0];
+      v.y -= acc[i][1];
+      v.z -= acc[i][2];
+      v.w -= acc[i][3];
+      *reinterpret_cast<float4*>(o) = v;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (col0 + j0 + j < col_end) o[j] -= acc[i][j];
+    }
+  }
+}
+
+template <int NB>
+__global__ void __launch_bounds__(kCholThreads, 1)
+chol_inverse_kernel(const float* __restrict__ Gall, float* __restrict__ Zall, float* __restrict__ Wall,
+                    int* __restrict__ info, int r, long long ldg, long long g_batch_stride, int rp,
+                    float pivot_floor) {
+  extern __shared__ __align__(16) float sm[];
+  // rp = r rounded up to a multiple of 64 (+4 pad keeps rows 16-byte aligned)
+  float* panelT = sm;                         // [NB][rp]   panel, transposed
+  float* zrow = panelT + (size_t)NB * rp;     // [NB][rp]   current block row of Z
+  float* dblk = zrow + (size_t)NB * rp;       // [NB][NB+1]
+  float* linv = dblk + NB * (NB + 1);         // [NB][NB+1]
+  float* dscale = linv + NB * (NB + 1);       // [rp] Jacobi scaling 1/sqrt(G_ii)
+  __shared__ int clamp_count;
+
+  const int b = blockIdx.x;
+  const float* G = Gall + (long long)b * g_batch_stride;
+  float* Z = Zall + (long long)b * r * r;
+  float* W = Wall + (long long)b * r * r;
+  const int tid = threadIdx.x;
+
+  if (tid == 0) clamp_count = 0;
+  for (int i = tid; i < rp; i += kCholThreads) {
+    float d = 0.f;
+    if (i < r) {
+      const float g = G[(long long)i * ldg + i];
+      d = (g > 1e-30f) ? rsqrtf(g) : 0.f;
+    }
+    dscale[i] = d;
+  }
+  __syncthreads();
+  // W = D G D (lower triangle is what gets used), Z = I
+  for (long long e = tid; e < (long long)r * r; e += kCholThreads) {
+    const int i = (int)(e / r), j = (int)(e - (long long)i * r);
+    W[e] = G[(long long)i * ldg + j] * dscale[i] * dscale[j];
+    Z[e] = (i == j) ? 1.f : 0.f;
+  }
+  __syncthreads();
+
+  for (int k0 = 0; k0 < r; k0 += NB) {
+    const int nb = min(NB, r - k0);
+    // ---- 1. diagonal block -> shared, unblocked Cholesky with pivot clamping
+    for (int e = tid; e < NB * NB; e += kCholThreads) {
+      const int i = e / NB, j = e - i * NB;
+      float v = 0.f;
+      if (i < nb && j < nb && j <= i) v = W[(long long)(k0 + i) * r + k0 + j];
+      dblk[i * (NB + 1) + j] = v;
+    }
+    __syncthreads();
+    for (int j = 0; j < nb; ++j) {
+      if (tid == 0) {
+        float d = dblk[j * (NB + 1) + j];
+        if (!(d > pivot_floor)) {
+          d = pivot_floor;
+          ++clamp_count;
+        }
+        dblk[j * (NB + 1) + j] = sqrtf(d);
+      }
+      __syncthreads();
+      const float piv = dblk[j * (NB + 1) + j];
+      for (int i = j + 1 + tid; i < nb; i += kCholThreads) dblk[i * (NB + 1) + j] /= piv;
+      __syncthreads();
+      // rank-1 update of the remaining lower triangle
+      const int rem = nb - j - 1;
+      for (int e = tid; e < rem * rem; e += kCholThreads) {
+        const int ii = e / rem, jj = e - ii * rem;
+        if (jj <= ii) {
+          const int i = j + 1 + ii, c = j + 1 + jj;
+          dblk[i * (NB + 1) + c] -= dblk[i * (NB + 1) + j] * dblk[c * (NB + 1) + j];
+        }
+      }
+      __syncthreads();
+    }
+    // ---- inverse of the diagonal factor: column c of Linv by forward substitution
+    for (int e = tid; e < NB * (NB + 1); e += kCholThreads) linv[e] = 0.f;
+    __syncthreads();
+    if (tid < nb) {
+      const int c = tid;
+      for (int i = c; i < nb; ++i) {
+        float s = (i == c) ? 1.f : 0.f;
+        for (int k = c; k < i; ++k) s -= dblk[i * (NB + 1) + k] * linv[k * (NB + 1) + c];
+        linv[i * (NB + 1) + c] = s / dblk[i * (NB + 1) + i];
+      }
+    }
+    __syncthreads();
+
+    // ---- 2. Z[k,:] = Linv * B[k,:] for columns < k0 + nb
+    const int zc = k0 + nb;
+    for (int c = tid; c < rp; c += kCholThreads) {
+      float bcol[NB];
+#pragma unroll
+      for (int a = 0; a < NB; ++a) bcol[a] = (a < nb && c < zc) ? Z[(long long)(k0 + a) * r + c] : 0.f;
+#pragma unroll
+      for (int a = 0; a < NB; ++a) {
+        float s = 0.f;
+#pragma unroll
+        for (int bb = 0; bb < NB; ++bb)
+          if (bb <= a) s = fmaf(linv[a * (NB + 1) + bb], bcol[bb], s);
+        zrow[(size_t)a * rp + c] = s;
+        if (a < nb && c < zc) Z[(long long)(k0 + a) * r + c] = s;
+      }
+    }
+    // ---- 3. panel = A[k+1:, k] * Linv^T, stored transposed: panelT[a][i - p0]
+    const int p0 = k0 + nb;  // first trailing row
+    const int tr = r - p0;   // trailing rows
+    for (int ii = tid; ii < rp; ii += kCholThreads) {
+      float arow[NB];
+      const bool live = ii < tr;
+#pragma unroll
+      for (int a = 0; a < NB; ++a) arow[a] = (live && a < nb) ? W[(long long)(p0 + ii) * r + k0 + a] : 0.f;
+#pragma unroll
+      for (int a = 0; a < NB; ++a) {
+        float s = 0.f;
+#pragma unroll
+        for (int bb = 0; bb < NB; ++bb)
+          if (bb <= a) s = fmaf(arow[bb], linv[a * (NB + 1) + bb], s);
+        panelT[(size_t)a * rp + ii] = s;
+      }
+    }
+    __syncthreads();
+    if (tr <= 0) break;
+
+    // ---- 4. trailing updates with 64 x 64 tiles
+    const int nt = (tr + 63) / 64;
+    for (int ti = 0; ti < nt; ++ti) {
+      // Gram part: lower-triangular tiles only
+      for (int tj = 0; tj <= ti; ++tj)
+        tile_update<NB>(W, r, p0 + ti * 64, p0 + tj * 64, panelT + ti * 64, rp, panelT + tj * 64, rp, r, r);
+      // right-hand-side part: columns < zc
+      const int nc = (zc + 63) / 64;
+      for (int tc = 0; tc < nc; ++tc)
+        tile_update<NB>(Z, r, p0 + ti * 64, tc * 64, panelT + ti * 64, rp, zrow + tc * 64, rp, r, zc);
+    }
+    __syncthreads();
+  }
+
+  // undo the Jacobi scaling: G = D^-1 L' L'^T D^-1  =>  L^{-1} = L'^{-1} D, i.e. scale column j by d_j
+  __syncthreads();
+  for (long long e = tid; e < (long long)r * r; e += kCholThreads) {
+    const int i = (int)(e / r), j = (int)(e - (long long)i * r);
+    Z[e] = (j <= i) ? Z[e] * dscale[j] : 0.f;
+  }
+  if (tid == 0 && info) info[b] = clamp_count;
+}
+
+// One block per (batch, 32 columns): out[b][j] = sum_i X[b][i][j]^2
+__global__ void __launch_bounds__(256) col_sumsq_kernel(const void* __restrict__ X, int x_type,
+                                                       float* __restrict__ out, long long rows, int cols,
+                                                       long long ldx, long long batch_stride) {
+  __shared__ float red[8][33];
+  const int b = blockIdx.y;
+  const int col = blockIdx.x * 32 + (threadIdx.x & 31);
+  const int rlane = threadIdx.x >> 5;  // 8 row lanes
+  float s = 0.f;
+  if (col < cols) {
+    if (x_type == kElemF32) {
+      const float* x = reinterpret_cast<const float*>(X) + (long long)b * batch_stride;
+      for (long long i = rlane; i < rows; i += 8) {
+        const float v = x[i * ldx + col];
+        s = fmaf(v, v, s);
+      }
+    } else {
+      const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(X) + (long long)b * batch_stride;
+      for (long long i = rlane; i < rows; i += 8) {
+        const float v = __bfloat162float(x[i * ldx + col]);
+        s = fmaf(v, v, s);
+      }
+    }
+  }
+  red[rlane][threadIdx.x & 31] = s;
+  __syncthreads();
+  if (rlane == 0 && col < cols) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][threadIdx.x & 31];
+    out[(long long)b * cols + col] = t;
+  }
+}
+
+}  // namespace
+
+cudaError_t chol_inverse_launch(const float* G, float* Z, float* work, int* info, int batch, int r, long long ldg,
+                                long long g_batch_stride, float pivot_floor, cudaStream_t s) {
+  if (batch == 0 || r == 0) return cudaSuccess;
+  const int rp = ((r + 63) / 64) * 64;
+  auto smem_for = [&](int nb) { return (size_t)(2 * nb * rp + 2 * nb * (nb + 1) + rp) * sizeof(float); };
+  cudaError_t e;
+  if (smem_for(32) <= 227 * 1024) {
+    static bool set32 = false;
+    if (!set32) {
+      e = cudaFuncSetAttribute(chol_inverse_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      if (e != cudaSuccess) return e;
+      set32 = true;
+    }
+    chol_inverse_kernel<32><<<batch, kCholThreads, smem_for(32), s>>>(G, Z, work, info, r, ldg, g_batch_stride, rp,
+                                                                     pivot_floor);
+  } else if (smem_for(16) <= 227 * 1024) {
+    static bool set16 = false;
+    if (!set16) {
+      e = cudaFuncSetAttribute(chol_inverse_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      if (e != cudaSuccess) return e;
+      set16 = true;
+    }
+    chol_inverse_kernel<16><<<batch, kCholThreads, smem_for(16), s>>>(G, Z, work, info, r, ldg, g_batch_stride, rp,
+                                                                     pivot_floor);
+  } else {
+    return cudaErrorInvalidValue;  // caller falls back to the library path for very large ranks
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t col_sumsq_launch(const void* X, int x_type, float* out, int batch, long long rows, int cols,
+                             long long ldx, long long batch_stride, cudaStream_t s) {
+  if (batch == 0 || cols == 0) return cudaSuccess;
+  dim3 grid((cols + 31) / 32, batch);
+  col_sumsq_kernel<<<grid, 256, 0, s>>>(X, x_type, out, rows, cols, ldx, batch_stride);
+  return cudaGetLastError();
+}
+
+}  // namespace dion

@@ -1,0 +1,495 @@
+// Bandwidth-bound model kernels: RMSNorm, rotary + QK-norm, ReLU^2, softmax
+// cross-entropy (forward and gradient in one pass) and the embedding gather/scatter.
+// bf16 activations, fp32 math.  They stand in for the Inductor-generated kernels the
+// reference gets from model.compile() (models/gpt_model.py:54-61, 86-89, 106-112,
+// 115-124, 171-179).
+#include <cuda_bf16.h>
+
+#include "kernels.h"
+
+namespace dion {
+
+namespace {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ void unpack8(const uint4& q, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = __bfloat1622float2(h[j]);
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 q;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+  return q;
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One warp per row; the row is kept in registers between the two passes.
+constexpr int kNormMaxVec = 16;  // 16 * 32 lanes * 8 elements = 4096 columns at most
+
+__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res,
+                                                         bf16* __restrict__ x_out, bf16* __restrict__ y,
+                                                         float* __restrict__ rstd, long long rows, int dim,
+                                                         float eps) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int nvec = dim >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * dim);
+  const uint4* rr = res ? reinterpret_cast<const uint4*>(res + row * dim) : nullptr;
+  uint4* xo = x_out ? reinterpret_cast<uint4*>(x_out + row * dim) : nullptr;
+  uint4* yr = reinterpret_cast<uint4*>(y + row * dim);
+  uint4 keep[kNormMaxVec];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < kNormMaxVec; ++i) {
+    const int v = lane + i * 32;
+    if (v < nvec) {
+      uint4 q = xr[v];
+      float f[8];
+      unpack8(q, f);
+      if (rr) {
+        float g[8];
+        unpack8(rr[v], g);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] += g[j];
+        q = pack8(f);
+        unpack8(q, f);  // normalise exactly what is stored as the new residual stream
+        if (xo) xo[v] = q;
+      }
+      keep[i] = q;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+    }
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)dim + eps);
+  if (lane == 0 && rstd) rstd[row] = r;
+#pragma unroll
+  for (int i = 0; i < kNormMaxVec; ++i) {
+    const int v = lane + i * 32;
+    if (v < nvec) {
+      float f[8];
+      unpack8(keep[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] *= r;
+      yr[v] = pack8(f);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
+                                                         const float* __restrict__ rstd,
+                                                         const bf16* __restrict__ dx_add, bf16* __restrict__ dx,
+                                                         long long rows, int dim) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int nvec = dim >> 3;
+  const uint4* dyr = reinterpret_cast<const uint4*>(dy + row * dim);
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * dim);
+  const uint4* ar = dx_add ? reinterpret_cast<const uint4*>(dx_add + row * dim) : nullptr;
+  uint4* dxr = reinterpret_cast<uint4*>(dx + row * dim);
+  const float r = rstd[row];
+  float dot = 0.f;
+  for (int v = lane; v < nvec; v += 32) {
+    float a[8], b[8];
+    unpack8(dyr[v], a);
+    unpack8(xr[v], b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dot += a[j] * b[j];
+  }
+  dot = warp_sum(dot);
+  // dx = r * dy - x * r^3 * mean(dy * x)
+  const float c = r * r * r * dot / (float)dim;
+  for (int v = lane; v < nvec; v += 32) {
+    float a[8], b[8], o[8];
+    unpack8(dyr[v], a);
+    unpack8(xr[v], b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = r * a[j] - c * b[j];
+    if (ar) {
+      float e[8];
+      unpack8(ar[v], e);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] += e[j];
+    }
+    dxr[v] = pack8(o);
+  }
+}
+
+// ------------------------------------------------------------------ rotary + QK norm
+// One warp per (token, head) row of q and of k.  HD is 64 or 128; a lane owns the
+// rotation pairs (p, p + HD/2) for p = lane (+32).
+template <int HD>
+__global__ void __launch_bounds__(256) rope_qknorm_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
+                                                             bf16* __restrict__ qo, bf16* __restrict__ ko,
+                                                             const bf16* __restrict__ cosb,
+                                                             const bf16* __restrict__ sinb, long long tokens,
+                                                             int seq_len, int heads, long long in_pitch,
+                                                             long long out_pitch, float eps) {
+  constexpr int HALF = HD / 2;
+  constexpr int PPL = HALF / 32;  // pairs per lane
+  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const long long nrows = tokens * heads * 2;
+  if (wid >= nrows) return;
+  const int lane = threadIdx.x & 31;
+  const int which = (int)(wid & 1);  // 0 = q, 1 = k
+  const long long th = wid >> 1;
+  const long long tok = th / heads;
+  const int head = (int)(th - tok * heads);
+  const int pos = (int)(tok % seq_len);
+  const bf16* src = (which ? k : q) + tok * in_pitch + (long long)head * HD;
+  bf16* dst = (which ? ko : qo) + tok * out_pitch + (long long)head * HD;
+  float y1[PPL], y2[PPL];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < PPL; ++i) {
+    const int p = lane + i * 32;
+    const float x1 = __bfloat162float(src[p]);
+    const float x2 = __bfloat162float(src[p + HALF]);
+    const float c = __bfloat162float(cosb[(long long)pos * HALF + p]);
+    const float s = __bfloat162float(sinb[(long long)pos * HALF + p]);
+    y1[i] = x1 * c + x2 * s;
+    y2[i] = x2 * c - x1 * s;
+    ss += y1[i] * y1[i] + y2[i] * y2[i];
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)HD + eps);
+#pragma unroll
+  for (int i = 0; i < PPL; ++i) {
+    const int p = lane + i * 32;
+    dst[p] = __float2bfloat16(y1[i] * r);
+    dst[p + HALF] = __float2bfloat16(y2[i] * r);
+  }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(256) rope_qknorm_bwd_kernel(const bf16* __restrict__ dqo,
+                                                             const bf16* __restrict__ dko,
+                                                             const bf16* __restrict__ q, const bf16* __restrict__ k,
+                                                             bf16* __restrict__ dq, bf16* __restrict__ dk,
+                                                             const bf16* __restrict__ cosb,
+                                                             const bf16* __restrict__ sinb, long long tokens,
+                                                             int seq_len, int heads, long long in_pitch,
+                                                             long long out_pitch, float eps) {
+  constexpr int HALF = HD / 2;
+  constexpr int PPL = HALF / 32;
+  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const long long nrows = tokens * heads * 2;
+  if (wid >= nrows) return;
+  const int lane = threadIdx.x & 31;
+  const int which = (int)(wid & 1);
+  const long long th = wid >> 1;
+  const long long tok = th / heads;
+  const int head = (int)(th - tok * heads);
+  const int pos = (int)(tok % seq_len);
+  const bf16* src = (which ? k : q) + tok * in_pitch + (long long)head * HD;
+  const bf16* gsrc = (which ? dko : dqo) + tok * out_pitch + (long long)head * HD;
+  bf16* gdst = (which ? dk : dq) + tok * in_pitch + (long long)head * HD;
+  float y1[PPL], y2[PPL], g1[PPL], g2[PPL], cs[PPL], sn[PPL];
+  float ss = 0.f, dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < PPL; ++i) {
+    const int p = lane + i * 32;
+    const float x1 = __bfloat162float(src[p]);
+    const float x2 = __bfloat162float(src[p + HALF]);
+    cs[i] = __bfloat162float(cosb[(long long)pos * HALF + p]);
+    sn[i] = __bfloat162float(sinb[(long long)pos * HALF + p]);
+    y1[i] = x1 * cs[i] + x2 * sn[i];
+    y2[i] = x2 * cs[i] - x1 * sn[i];
+    g1[i] = __bfloat162float(gsrc[p]);
+    g2[i] = __bfloat162float(gsrc[p + HALF]);
+    ss += y1[i] * y1[i] + y2[i] * y2[i];
+    dot += g1[i] * y1[i] + g2[i] * y2[i];
+  }
+  ss = warp_sum(ss);
+  dot = warp_sum(dot);
+  const float r = rsqrtf(ss / (float)HD + eps);
+  const float c3 = r * r * r * dot / (float)HD;
+#pragma unroll
+  for (int i = 0; i < PPL; ++i) {
+    const int p = lane + i * 32;
+    const float d1 = r * g1[i] - c3 * y1[i];  // grad w.r.t. rotated values
+    const float d2 = r * g2[i] - c3 * y2[i];
+    gdst[p] = __float2bfloat16(d1 * cs[i] - d2 * sn[i]);
+    gdst[p + HALF] = __float2bfloat16(d1 * sn[i] + d2 * cs[i]);
+  }
+}
+
+// ------------------------------------------------------------------ ReLU^2
+__global__ void __launch_bounds__(256) relu2_fwd_kernel(const uint4* __restrict__ x, uint4* __restrict__ h,
+                                                       long long nvec) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= nvec) return;
+  float f[8];
+  unpack8(x[i], f);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float r = fmaxf(f[j], 0.f);
+    f[j] = r * r;
+  }
+  h[i] = pack8(f);
+}
+__global__ void __launch_bounds__(256) relu2_bwd_kernel(const uint4* __restrict__ dh, const uint4* __restrict__ x,
+                                                       uint4* __restrict__ dx, long long nvec) {
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= nvec) return;
+  float f[8], g[8];
+  unpack8(x[i], f);
+  unpack8(dh[i], g);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) g[j] = g[j] * 2.f * fmaxf(f[j], 0.f);
+  dx[i] = pack8(g);
+}
+
+// ------------------------------------------------------------------ cross entropy
+// One 1024-thread block per row; the bf16 row lives in registers (<= 131072 columns).
+constexpr int kCeThreads = 1024;
+constexpr int kCeMaxVec = 16;
+
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float* red) {
+  v = is_max ? warp_max(v) : warp_sum(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = red[threadIdx.x & 31];
+  r = is_max ? warp_max(r) : warp_sum(r);
+  return r;
+}
+
+__global__ void __launch_bounds__(kCeThreads) cross_entropy_kernel(bf16* __restrict__ logits,
+                                                                  const long long* __restrict__ targets,
+                                                                  float* __restrict__ row_loss,
+                                                                  const float* __restrict__ scale_ptr,
+                                                                  int vocab, long long pitch, float grad_scale,
+                                                                  long long ignore_index, int write_grad) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const long long tgt = targets[row];
+  uint4* lr = reinterpret_cast<uint4*>(logits + row * pitch);
+  const int nvec = vocab >> 3;
+  if (tgt == ignore_index) {
+    if (threadIdx.x == 0) row_loss[row] = 0.f;
+    if (write_grad) {
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (int v = threadIdx.x; v < nvec; v += kCeThreads) lr[v] = z;
+    }
+    return;
+  }
+  uint4 keep[kCeMaxVec];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kCeMaxVec; ++i) {
+    const int v = threadIdx.x + i * kCeThreads;
+    if (v < nvec) {
+      keep[i] = lr[v];
+      float f[8];
+      unpack8(keep[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, f[j]);
+    }
+  }
+  mx = block_reduce(mx, true, red);
+  float se = 0.f;
+#pragma unroll
+  for (int i = 0; i < kCeMaxVec; ++i) {
+    const int v = threadIdx.x + i * kCeThreads;
+    if (v < nvec) {
+      float f[8];
+      unpack8(keep[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) se += __expf(f[j] - mx);
+    }
+  }
+  se = block_reduce(se, false, red);
+  const float lse = mx + __logf(se);
+  if (threadIdx.x == 0) {
+    const float tl = __bfloat162float(logits[row * pitch + tgt]);
+    row_loss[row] = lse - tl;
+  }
+  if (!write_grad) return;
+  __syncthreads();  // the target logit was read before any thread overwrites the row
+  const float gs = grad_scale * (scale_ptr ? *scale_ptr : 1.f);
+  const float inv = 1.f / se;
+#pragma unroll
+  for (int i = 0; i < kCeMaxVec; ++i) {
+    const int v = threadIdx.x + i * kCeThreads;
+    if (v < nvec) {
+      float f[8];
+      unpack8(keep[i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float p = __expf(f[j] - mx) * inv;
+        if ((long long)v * 8 + j == tgt) p -= 1.f;
+        f[j] = p * gs;
+      }
+      lr[v] = pack8(f);
+    }
+  }
+}
+
+// ------------------------------------------------------------------ embedding
+__global__ void __launch_bounds__(256) embedding_fwd_kernel(const void* __restrict__ table, int table_type,
+                                                           const long long* __restrict__ idx, bf16* __restrict__ out,
+                                                           long long tokens, int dim) {
+  const long long tok = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (tok >= tokens) return;
+  const int lane = threadIdx.x & 31;
+  const long long id = idx[tok];
+  bf16* o = out + tok * dim;
+  if (table_type == kElemF32) {
+    const float* t = reinterpret_cast<const float*>(table) + id * dim;
+    for (int c = lane * 4; c < dim; c += 128) {
+      const float4 f = *reinterpret_cast<const float4*>(t + c);
+      uint2 q;
+      *reinterpret_cast<__nv_bfloat162*>(&q.x) = __floats2bfloat162_rn(f.x, f.y);
+      *reinterpret_cast<__nv_bfloat162*>(&q.y) = __floats2bfloat162_rn(f.z, f.w);
+      *reinterpret_cast<uint2*>(o + c) = q;
+    }
+  } else {
+    const bf16* t = reinterpret_cast<const bf16*>(table) + id * dim;
+    for (int c = lane * 8; c < dim; c += 256) *reinterpret_cast<uint4*>(o + c) = *reinterpret_cast<const uint4*>(t + c);
+  }
+}
+
+__global__ void __launch_bounds__(256) embedding_bwd_kernel(const bf16* __restrict__ dout,
+                                                           const long long* __restrict__ idx,
+                                                           float* __restrict__ dtable, long long tokens, int dim) {
+  const long long tok = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (tok >= tokens) return;
+  const int lane = threadIdx.x & 31;
+  const long long id = idx[tok];
+  const bf16* g = dout + tok * dim;
+  float* t = dtable + id * dim;
+  for (int c = lane * 2; c < dim; c += 64) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g + c));
+    atomicAdd(t + c, f.x);
+    atomicAdd(t + c + 1, f.y);
+  }
+}
+
+}  // namespace
+
+cudaError_t rmsnorm_fwd_launch(const void* x, const void* residual, void* x_out, void* y, float* rstd,
+                               long long rows, int dim, float eps, cudaStream_t s) {
+  if (rows == 0) return cudaSuccess;
+  if (dim % 8 != 0 || dim > kNormMaxVec * 256) return cudaErrorInvalidValue;
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  rmsnorm_fwd_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const bf16*>(x), reinterpret_cast<const bf16*>(residual),
+                                          reinterpret_cast<bf16*>(x_out), reinterpret_cast<bf16*>(y), rstd, rows,
+                                          dim, eps);
+  return cudaGetLastError();
+}
+cudaError_t rmsnorm_bwd_launch(const void* dy, const void* x, const float* rstd, const void* dx_add, void* dx,
+                               long long rows, int dim, cudaStream_t s) {
+  if (rows == 0) return cudaSuccess;
+  if (dim % 8 != 0) return cudaErrorInvalidValue;
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  rmsnorm_bwd_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const bf16*>(dy), reinterpret_cast<const bf16*>(x), rstd,
+                                          reinterpret_cast<const bf16*>(dx_add), reinterpret_cast<bf16*>(dx), rows,
+                                          dim);
+  return cudaGetLastError();
+}
+
+cudaError_t rope_qknorm_fwd_launch(const void* q, const void* k, void* q_out, void* k_out, const void* cos,
+                                   const void* sin, long long tokens, int seq_len, int heads, int head_dim,
+                                   long long in_pitch, long long out_pitch, float eps, cudaStream_t s) {
+  const long long nrows = tokens * heads * 2;
+  if (nrows == 0) return cudaSuccess;
+  const unsigned grid = (unsigned)((nrows + 7) / 8);
+#define DION_ROPE_FWD(HD)                                                                                         \
+  rope_qknorm_fwd_kernel<HD><<<grid, 256, 0, s>>>(                                                                \
+      reinterpret_cast<const bf16*>(q), reinterpret_cast<const bf16*>(k), reinterpret_cast<bf16*>(q_out),         \
+      reinterpret_cast<bf16*>(k_out), reinterpret_cast<const bf16*>(cos), reinterpret_cast<const bf16*>(sin),     \
+      tokens, seq_len, heads, in_pitch, out_pitch, eps)
+  if (head_dim == 64) DION_ROPE_FWD(64);
+  else if (head_dim == 128) DION_ROPE_FWD(128);
+  else return cudaErrorInvalidValue;
+#undef DION_ROPE_FWD
+  return cudaGetLastError();
+}
+cudaError_t rope_qknorm_bwd_launch(const void* dq_out, const void* dk_out, const void* q, const void* k, void* dq,
+                                   void* dk, const void* cos, const void* sin, long long tokens, int seq_len,
+                                   int heads, int head_dim, long long in_pitch, long long out_pitch, float eps,
+                                   cudaStream_t s) {
+  const long long nrows = tokens * heads * 2;
+  if (nrows == 0) return cudaSuccess;
+  const unsigned grid = (unsigned)((nrows + 7) / 8);
+#define DION_ROPE_BWD(HD)                                                                                         \
+  rope_qknorm_bwd_kernel<HD><<<grid, 256, 0, s>>>(                                                                \
+      reinterpret_cast<const bf16*>(dq_out), reinterpret_cast<const bf16*>(dk_out),                               \
+      reinterpret_cast<const bf16*>(q), reinterpret_cast<const bf16*>(k), reinterpret_cast<bf16*>(dq),            \
+      reinterpret_cast<bf16*>(dk), reinterpret_cast<const bf16*>(cos), reinterpret_cast<const bf16*>(sin),        \
+      tokens, seq_len, heads, in_pitch, out_pitch, eps)
+  if (head_dim == 64) DION_ROPE_BWD(64);
+  else if (head_dim == 128) DION_ROPE_BWD(128);
+  else return cudaErrorInvalidValue;
+#undef DION_ROPE_BWD
+  return cudaGetLastError();
+}
+
+cudaError_t relu2_fwd_launch(const void* x, void* h, long long n, cudaStream_t s) {
+  if (n == 0) return cudaSuccess;
+  if (n % 8 != 0) return cudaErrorInvalidValue;
+  const long long nvec = n / 8;
+  relu2_fwd_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, s>>>(reinterpret_cast<const uint4*>(x),
+                                                                 reinterpret_cast<uint4*>(h), nvec);
+  return cudaGetLastError();
+}
+cudaError_t relu2_bwd_launch(const void* dh, const void* x, void* dx, long long n, cudaStream_t s) {
+  if (n == 0) return cudaSuccess;
+  if (n % 8 != 0) return cudaErrorInvalidValue;
+  const long long nvec = n / 8;
+  relu2_bwd_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, s>>>(
+      reinterpret_cast<const uint4*>(dh), reinterpret_cast<const uint4*>(x), reinterpret_cast<uint4*>(dx), nvec);
+  return cudaGetLastError();
+}
+
+cudaError_t cross_entropy_fwd_bwd_launch(void* logits, const long long* targets, float* row_loss,
+                                         const float* scale_ptr, long long rows, int vocab, long long pitch,
+                                         float grad_scale, long long ignore_index, bool write_grad, cudaStream_t s) {
+  if (rows == 0) return cudaSuccess;
+  if (vocab % 8 != 0 || pitch % 8 != 0 || vocab > kCeThreads * kCeMaxVec * 8) return cudaErrorInvalidValue;
+  cross_entropy_kernel<<<(unsigned)rows, kCeThreads, 0, s>>>(reinterpret_cast<bf16*>(logits), targets, row_loss,
+                                                            scale_ptr, vocab, pitch, grad_scale, ignore_index,
+                                                            write_grad ? 1 : 0);
+  return cudaGetLastError();
+}
+
+cudaError_t embedding_fwd_launch(const void* table, int table_type, const long long* idx, void* out,
+                                 long long tokens, int dim, cudaStream_t s) {
+  if (tokens == 0) return cudaSuccess;
+  if (dim % 8 != 0) return cudaErrorInvalidValue;
+  embedding_fwd_kernel<<<(unsigned)((tokens + 7) / 8), 256, 0, s>>>(table, table_type, idx,
+                                                                   reinterpret_cast<bf16*>(out), tokens, dim);
+  return cudaGetLastError();
+}
+cudaError_t embedding_bwd_launch(const void* dout, const long long* idx, float* dtable, long long tokens, int dim,
+                                 cudaStream_t s) {
+  if (tokens == 0) return cudaSuccess;
+  if (dim % 2 != 0) return cudaErrorInvalidValue;
+  embedding_bwd_kernel<<<(unsigned)((tokens + 7) / 8), 256, 0, s>>>(reinterpret_cast<const bf16*>(dout), idx, dtable,
+                                                                   tokens, dim);
+  return cudaGetLastError();
+}
+
+}  // namespace dion

@@ -1,0 +1,110 @@
+"""tcgen05 GEMM front end: ``gemm(a, b)`` computes ``alpha * a @ b (+ beta * c)`` for
+bf16 or fp32 (TF32) operands given as arbitrary row/column-major 2-D or 3-D views.
+
+On CPU tensors (tests, host-side logic) the same call runs a plain PyTorch
+implementation of identical semantics, which is also the numerical reference of the
+GPU tests.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import runtime
+
+_ACT = {None: 0, "none": 0, "relu2": 1}
+
+
+def _apply_act(x: torch.Tensor, act) -> torch.Tensor:
+    if act in (None, "none"):
+        return x
+    if act == "relu2":
+        return torch.relu(x).square()
+    raise ValueError(f"unknown activation {act!r}")
+
+
+def gemm_reference(a, b, *, c=None, out=None, alpha=1.0, beta=0.0, act=None, out_dtype=None, accumulate=False,
+                   shadow=None, compute_dtype=torch.float32):
+    """PyTorch implementation with the semantics of :func:`gemm` (fp32 accumulate)."""
+    acc = torch.matmul(a.to(compute_dtype), b.to(compute_dtype)).float() * alpha
+    if c is not None and beta != 0.0:
+        acc = acc + beta * c.float()
+    res = _apply_act(acc, act)
+    if out is None:
+        out = torch.empty(acc.shape, dtype=out_dtype or a.dtype, device=a.device)
+        accumulate = False
+    if accumulate:
+        out.add_(res.to(out.dtype))
+    else:
+        out.copy_(res.to(out.dtype))
+    if shadow is not None:
+        shadow.copy_(out.to(shadow.dtype))
+    return out
+
+
+def _tma_ok(t: torch.Tensor) -> bool:
+    es = t.element_size()
+    if t.data_ptr() % 16:
+        return False
+    s_row, s_col = t.stride(-2), t.stride(-1)
+    rows, cols = t.shape[-2], t.shape[-1]
+    if s_col == 1 and (s_row >= cols or rows == 1):
+        ld = s_row if rows > 1 else max(s_row, cols)
+    elif s_row == 1 and (s_col >= rows or cols == 1):
+        ld = s_col if cols > 1 else max(s_col, rows)
+    else:
+        return False
+    if (ld * es) % 16:
+        return False
+    if t.dim() == 3 and t.shape[0] > 1 and (t.stride(0) * es) % 16:
+        return False
+    return True
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, c: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+         alpha: float = 1.0, beta: float = 0.0, act: Optional[str] = None, out_dtype: Optional[torch.dtype] = None,
+         accumulate: bool = False, split_k: int = 1, symmetric: bool = False, shadow: Optional[torch.Tensor] = None,
+         block_n: int = 0, out_ptrs: Optional[torch.Tensor] = None, c_ptrs: Optional[torch.Tensor] = None,
+         shadow_ptrs: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out = act(alpha * a @ b + beta * c)``.
+
+    a: ``[B,] M, K``; b: ``[B,] K, N``; each may be a transposed view (one unit stride in
+    the last two dims).  ``accumulate=True`` adds ``alpha * a @ b`` into an fp32 ``out``
+    with atomics (needed for ``split_k > 1``).  ``symmetric=True`` promises that the
+    result is symmetric (e.g. ``x @ x.T``) and computes only half of the tiles.
+    ``shadow`` receives a bf16 copy of ``out``.  ``*_ptrs`` are int64 CUDA tensors with
+    one device address per batch element, for outputs that are separate allocations.
+    """
+    if a.dim() not in (2, 3) or a.dim() != b.dim():
+        raise ValueError("gemm expects two 2-D or two 3-D operands")
+    if a.dtype != b.dtype:
+        raise ValueError(f"operand dtypes differ: {a.dtype} vs {b.dtype}")
+    M, N = a.shape[-2], b.shape[-1]
+    if out is None:
+        if accumulate:
+            raise ValueError("accumulate=True needs an existing output")
+        shape = (*a.shape[:-2], M, N)
+        out = torch.empty(shape, dtype=out_dtype or a.dtype, device=a.device)
+
+    if not runtime.use_cuda_kernels(a):
+        if out_ptrs is not None or c_ptrs is not None or shadow_ptrs is not None:
+            raise ValueError("pointer-array outputs need CUDA tensors")
+        return gemm_reference(a, b, c=c, out=out, alpha=alpha, beta=beta, act=act, accumulate=accumulate,
+                              shadow=shadow)
+
+    if a.dtype not in (torch.bfloat16, torch.float32) or not (_tma_ok(a) and _tma_ok(b)) or out.stride(-1) != 1:
+        # shapes TMA cannot address (pitch not a multiple of 16 bytes): library GEMM
+        if out_ptrs is not None or c_ptrs is not None or shadow_ptrs is not None:
+            raise ValueError("unaligned operands cannot be combined with pointer-array outputs")
+        cd = torch.float32 if a.dtype == torch.float32 else a.dtype
+        return gemm_reference(a, b, c=c, out=out, alpha=alpha, beta=beta, act=act, accumulate=accumulate,
+                              shadow=shadow, compute_dtype=cd)
+
+    if split_k > 1 and not accumulate:
+        raise ValueError("split_k > 1 needs accumulate=True")
+    torch.ops.dion_b200.gemm(a, b, c, out, shadow, c_ptrs, out_ptrs, shadow_ptrs, float(alpha), float(beta),
+                             _ACT[act], 1 if accumulate else 0, int(split_k), bool(symmetric), int(block_n),
+                             runtime.status_tensor(a.device))
+    return out

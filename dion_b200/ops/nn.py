@@ -1,0 +1,382 @@
+"""Differentiable model ops backed by the sm_100a kernels.
+
+Every public function has two paths with the same semantics:
+  * CUDA bf16 tensors -> ``torch.autograd.Function`` wrappers around the in-tree kernels
+    (tcgen05 GEMM for the Linear layers, fused elementwise kernels for the rest);
+  * anything else (CPU tests, fp32 debugging) -> plain differentiable PyTorch.
+
+The math mirrors the reference model (models/gpt_model.py:54-61 rotary, 86-89 QK norm,
+106-112 ReLU^2 MLP, 115-124 weight-less RMSNorm, 171-179 fp32 cross-entropy).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from . import runtime
+from .gemm import gemm
+from .multi_tensor import cast_copy
+
+RMS_EPS = 1.1920929e-07  # torch.finfo(torch.float32).eps, what F.rms_norm(eps=None) uses
+
+
+def _fast(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype == torch.bfloat16 and runtime.use_cuda_kernels(x)
+
+
+# --------------------------------------------------------------------------- weights in bf16
+
+def bf16_weight(w: torch.Tensor) -> torch.Tensor:
+    """bf16 copy of a (usually fp32) parameter, cached on the parameter and refreshed when
+    the parameter changed.  Optimizers of this package write the copy in their update
+    kernels and call :func:`mark_shadow_fresh`; any other in-place update is detected
+    through the tensor version counter."""
+    if w.dtype == torch.bfloat16:
+        return w.detach()
+    sh = getattr(w, "_bf16_shadow", None)
+    if sh is None or sh.shape != w.shape or sh.device != w.device:
+        sh = torch.empty_like(w, dtype=torch.bfloat16)
+        w._bf16_shadow = sh
+        w._bf16_shadow_version = None
+    if w._bf16_shadow_version != w._version:
+        cast_copy([w.detach()], [sh])
+        w._bf16_shadow_version = w._version
+    return sh
+
+
+def refresh_bf16_weights(params) -> None:
+    """Refresh all stale bf16 copies with a single multi-tensor launch."""
+    src, dst, todo = [], [], []
+    for w in params:
+        if w.dtype == torch.bfloat16 or not w.is_cuda:
+            continue
+        sh = getattr(w, "_bf16_shadow", None)
+        if sh is None or sh.shape != w.shape or sh.device != w.device:
+            sh = torch.empty_like(w, dtype=torch.bfloat16)
+            w._bf16_shadow = sh
+            w._bf16_shadow_version = None
+        if w._bf16_shadow_version != w._version:
+            src.append(w.detach())
+            dst.append(sh)
+            todo.append(w)
+    if src:
+        cast_copy(src, dst)
+        for w in todo:
+            w._bf16_shadow_version = w._version
+
+
+def shadow_for_update(w: torch.Tensor) -> Optional[torch.Tensor]:
+    """The bf16 copy an optimizer kernel should write together with the fp32 update."""
+    return getattr(w, "_bf16_shadow", None)
+
+
+def mark_shadow_fresh(w: torch.Tensor) -> None:
+    if getattr(w, "_bf16_shadow", None) is not None:
+        w._bf16_shadow_version = w._version
+
+
+def mark_shadow_stale(w: torch.Tensor) -> None:
+    if getattr(w, "_bf16_shadow", None) is not None:
+        w._bf16_shadow_version = None
+
+
+# --------------------------------------------------------------------------- Linear
+
+def _split_k_for(M: int, N: int, K: int) -> int:
+    """Split the contraction so that a skinny weight-gradient GEMM fills the GPU."""
+    tiles = ((M + 127) // 128) * ((N + 127) // 128)
+    if tiles >= 148 or K < 2048:
+        return 1
+    want = max(1, (2 * 148 + tiles - 1) // tiles)
+    return int(max(1, min(want, K // 512, 32)))
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = x @ W^T (+ residual); x: [T, K] bf16, W: [N, K] fp32 master or bf16."""
+
+    @staticmethod
+    def forward(ctx, x, weight, residual, act):
+        wb = bf16_weight(weight)
+        pre = None
+        if act is not None:
+            pre = torch.empty(x.shape[0], wb.shape[0], device=x.device, dtype=torch.bfloat16)
+            gemm(x, wb.t(), out=pre)
+            y = torch.empty_like(pre)
+            torch.ops.dion_b200.relu2_fwd(pre, y)
+        else:
+            y = torch.empty(x.shape[0], wb.shape[0], device=x.device, dtype=torch.bfloat16)
+            if residual is not None:
+                gemm(x, wb.t(), c=residual, beta=1.0, out=y)
+            else:
+                gemm(x, wb.t(), out=y)
+        ctx.save_for_backward(x, weight, pre)
+        ctx.has_residual = residual is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight, pre = ctx.saved_tensors
+        wb = bf16_weight(weight)
+        dy = dy.contiguous()
+        if pre is not None:
+            dpre = torch.empty_like(pre)
+            torch.ops.dion_b200.relu2_bwd(dy, pre, dpre)
+            dy_lin = dpre
+        else:
+            dy_lin = dy
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x)
+            gemm(dy_lin, wb, out=dx)  # [T, N] @ [N, K]
+        if ctx.needs_input_grad[1]:
+            N, K = wb.shape
+            T = x.shape[0]
+            sk = _split_k_for(N, K, T)
+            if sk > 1:
+                dw32 = torch.zeros(N, K, device=x.device, dtype=torch.float32)
+                gemm(dy_lin.t(), x, out=dw32, accumulate=True, split_k=sk)
+            else:
+                dw32 = torch.empty(N, K, device=x.device, dtype=torch.float32)
+                gemm(dy_lin.t(), x, out=dw32)
+            dw = dw32 if weight.dtype == torch.float32 else dw32.to(weight.dtype)
+        dres = dy if ctx.has_residual else None
+        return dx, dw, dres, None
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tensor] = None,
+           act: Optional[str] = None) -> torch.Tensor:
+    """``act(x @ weight.T) (+ residual)`` over the last dim of x.  ``act`` in {None, "relu2"}."""
+    if _fast(x):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        r2 = residual.reshape(-1, weight.shape[0]) if residual is not None else None
+        if act is not None and residual is not None:
+            raise ValueError("activation and residual cannot be combined")
+        y = _LinearFn.apply(x2, weight, r2, act)
+        return y.view(*shp[:-1], weight.shape[0])
+    y = F.linear(x, weight.to(x.dtype))
+    if act == "relu2":
+        y = torch.relu(y).square()
+    if residual is not None:
+        y = y + residual
+    return y
+
+
+# --------------------------------------------------------------------------- RMSNorm
+
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, eps):
+        x2 = x.reshape(-1, x.shape[-1])
+        y = torch.empty_like(x2)
+        rstd = torch.empty(x2.shape[0], device=x.device, dtype=torch.float32)
+        torch.ops.dion_b200.rmsnorm_fwd(x2, None, None, y, rstd, eps)
+        ctx.save_for_backward(x2, rstd)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, rstd = ctx.saved_tensors
+        dy2 = dy.contiguous().view(x2.shape)
+        dx = torch.empty_like(x2)
+        torch.ops.dion_b200.rmsnorm_bwd(dy2, x2, rstd, None, dx)
+        return dx.view(dy.shape), None
+
+
+def rms_norm(x: torch.Tensor, eps: float = RMS_EPS) -> torch.Tensor:
+    """Weight-less RMSNorm over the last dim."""
+    if _fast(x) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 4096 and x.is_contiguous():
+        return _RMSNormFn.apply(x, eps)
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)).to(x.dtype)
+
+
+# --------------------------------------------------------------------------- rotary + QK norm
+
+def rotary_tables(seq_len: int, head_dim: int, device, base: float = 10000.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin tables [seq_len, head_dim/2] cached in bf16 (models/gpt_model.py:36-51)."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, head_dim, 2, device=device).float() / head_dim))
+    t = torch.arange(seq_len, device=device).float()
+    freqs = torch.outer(t, inv_freq)
+    return freqs.cos().bfloat16().contiguous(), freqs.sin().bfloat16().contiguous()
+
+
+def _rope_qknorm_torch(q, k, cos, sin, eps):
+    # q, k: [B, T, H, Dh]
+    def rot(x):
+        d = x.shape[-1] // 2
+        x1, x2 = x[..., :d].float(), x[..., d:].float()
+        c = cos[None, : x.shape[1], None, :].float()
+        s = sin[None, : x.shape[1], None, :].float()
+        y = torch.cat([x1 * c + x2 * s, x2 * c - x1 * s], dim=-1)
+        y = y * torch.rsqrt(y.square().mean(-1, keepdim=True) + eps)
+        return y.to(x.dtype)
+
+    return rot(q), rot(k)
+
+
+class _RopeQKNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, cos, sin, seq_len, heads, head_dim, eps):
+        # q, k: [tokens, heads*head_dim] (possibly column slices of one fused buffer)
+        qo = torch.empty(q.shape[0], heads * head_dim, device=q.device, dtype=q.dtype)
+        ko = torch.empty_like(qo)
+        torch.ops.dion_b200.rope_qknorm_fwd(q, k, qo, ko, cos, sin, seq_len, heads, head_dim, eps)
+        ctx.save_for_backward(q, k, cos, sin)
+        ctx.cfg = (seq_len, heads, head_dim, eps)
+        return qo, ko
+
+    @staticmethod
+    def backward(ctx, dqo, dko):
+        q, k, cos, sin = ctx.saved_tensors
+        seq_len, heads, head_dim, eps = ctx.cfg
+        if q.stride(0) == q.shape[1] and k.stride(0) == k.shape[1]:
+            dq = torch.empty_like(q)
+            dk = torch.empty_like(k)
+        else:
+            dq = torch.empty(q.shape, device=q.device, dtype=q.dtype)
+            dk = torch.empty(k.shape, device=k.device, dtype=k.dtype)
+        if dq.stride(0) != q.stride(0):
+            q = q.contiguous()
+            k = k.contiguous()
+        torch.ops.dion_b200.rope_qknorm_bwd(dqo.contiguous(), dko.contiguous(), q, k, dq, dk, cos, sin, seq_len,
+                                            heads, head_dim, eps)
+        return dq, dk, None, None, None, None, None, None
+
+
+def rope_qknorm(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+                eps: float = RMS_EPS) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Rotary embedding followed by RMS norm over head_dim.  q, k: [B, T, H, Dh]."""
+    B, T, H, Dh = q.shape
+    if _fast(q) and Dh in (64, 128) and q.is_contiguous() and k.is_contiguous():
+        qo, ko = _RopeQKNormFn.apply(q.view(B * T, H * Dh), k.view(B * T, H * Dh), cos, sin, T, H, Dh, eps)
+        return qo.view(B, T, H, Dh), ko.view(B, T, H, Dh)
+    return _rope_qknorm_torch(q, k, cos, sin, eps)
+
+
+# --------------------------------------------------------------------------- ReLU^2
+
+class _Relu2Fn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        h = torch.empty_like(x)
+        torch.ops.dion_b200.relu2_fwd(x, h)
+        ctx.save_for_backward(x)
+        return h
+
+    @staticmethod
+    def backward(ctx, dh):
+        (x,) = ctx.saved_tensors
+        dx = torch.empty_like(x)
+        torch.ops.dion_b200.relu2_bwd(dh.contiguous(), x, dx)
+        return dx
+
+
+def relu2(x: torch.Tensor) -> torch.Tensor:
+    if _fast(x) and x.is_contiguous() and x.numel() % 8 == 0:
+        return _Relu2Fn.apply(x)
+    return torch.relu(x).square()
+
+
+# --------------------------------------------------------------------------- embedding
+
+class _EmbeddingFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, idx, table):
+        out = torch.empty(idx.numel(), table.shape[1], device=table.device, dtype=torch.bfloat16)
+        torch.ops.dion_b200.embedding_fwd(table.detach(), idx.reshape(-1).contiguous(), out)
+        ctx.save_for_backward(idx)
+        ctx.table_shape = table.shape
+        ctx.table_dtype = table.dtype
+        return out.view(*idx.shape, table.shape[1])
+
+    @staticmethod
+    def backward(ctx, dout):
+        (idx,) = ctx.saved_tensors
+        dt = torch.zeros(ctx.table_shape, device=dout.device, dtype=torch.float32)
+        torch.ops.dion_b200.embedding_bwd(dout.contiguous().view(-1, dout.shape[-1]), idx.reshape(-1).contiguous(), dt)
+        return None, dt if ctx.table_dtype == torch.float32 else dt.to(ctx.table_dtype)
+
+
+def embedding(idx: torch.Tensor, table: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Token embedding gather producing bf16 activations from an fp32 (or bf16) table."""
+    if table.is_cuda and out_dtype == torch.bfloat16 and runtime.use_cuda_kernels(table) and \
+            table.dtype in (torch.float32, torch.bfloat16) and table.shape[1] % 8 == 0 and table.is_contiguous():
+        return _EmbeddingFn.apply(idx, table)
+    return F.embedding(idx, table).to(out_dtype)
+
+
+# --------------------------------------------------------------------------- lm_head + cross entropy
+
+class _LinearCrossEntropyFn(torch.autograd.Function):
+    """loss = mean CE(x @ W^T, targets) without keeping the logits: the token dimension is
+    processed in chunks; each chunk's logits are turned into their gradient in place by the
+    cross-entropy kernel and immediately contracted into dX and dW."""
+
+    @staticmethod
+    def forward(ctx, x, weight, targets, ignore_index, chunk_tokens):
+        wb = bf16_weight(weight)
+        T, K = x.shape
+        V = wb.shape[0]
+        need_grad = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)
+        valid = (targets != ignore_index).sum().clamp_min(1).to(torch.float32)
+        inv_valid = valid.reciprocal()
+        row_loss = torch.empty(T, device=x.device, dtype=torch.float32)
+        dx = torch.empty_like(x) if need_grad else None
+        dw = torch.zeros(V, K, device=x.device, dtype=torch.float32) if need_grad else None
+        chunk = min(chunk_tokens, T)
+        logits = torch.empty(chunk, V, device=x.device, dtype=torch.bfloat16)
+        for t0 in range(0, T, chunk):
+            t1 = min(t0 + chunk, T)
+            n = t1 - t0
+            lg = logits[:n]
+            gemm(x[t0:t1], wb.t(), out=lg)
+            torch.ops.dion_b200.cross_entropy_fwd_bwd(lg, targets[t0:t1], row_loss[t0:t1], inv_valid, 1.0,
+                                                      ignore_index, need_grad)
+            if need_grad:
+                gemm(lg, wb, out=dx[t0:t1])  # [n, V] @ [V, K]
+                gemm(lg.t(), x[t0:t1], out=dw, accumulate=True, split_k=1)  # [V, n] @ [n, K]
+        loss = row_loss.sum() * inv_valid
+        if need_grad:
+            ctx.save_for_backward(dx, dw)
+            ctx.w_dtype = weight.dtype
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        dx, dw = ctx.saved_tensors
+        dxo = dx * dloss.to(dx.dtype) if ctx.needs_input_grad[0] else None
+        dwo = None
+        if ctx.needs_input_grad[1]:
+            dwo = dw * dloss
+            if ctx.w_dtype != torch.float32:
+                dwo = dwo.to(ctx.w_dtype)
+        return dxo, dwo, None, None, None
+
+
+def linear_cross_entropy(x: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, ignore_index: int = -1,
+                         chunk_tokens: int = 8192) -> torch.Tensor:
+    """Mean cross-entropy of ``x @ weight.T`` against ``targets`` (fp32 softmax math)."""
+    x2 = x.reshape(-1, x.shape[-1])
+    t1 = targets.reshape(-1)
+    V = weight.shape[0]
+    if _fast(x2) and V % 8 == 0 and V <= 131072 and t1.dtype == torch.long:
+        return _LinearCrossEntropyFn.apply(x2.contiguous(), weight, t1.contiguous(), ignore_index, chunk_tokens)
+    logits = F.linear(x2, weight.to(x2.dtype)).float()
+    return F.cross_entropy(logits, t1, ignore_index=ignore_index)
+
+
+# --------------------------------------------------------------------------- attention
+
+def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """Causal self-attention; q, k, v: [B, T, H, Dh] -> [B, T, H*Dh].  Supports grouped
+    KV heads (H_kv dividing H)."""
+    B, T, H, Dh = q.shape
+    Hkv = k.shape[2]
+    qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    y = F.scaled_dot_product_attention(qt, kt, vt, is_causal=True, enable_gqa=(Hkv != H))
+    return y.transpose(1, 2).reshape(B, T, H * Dh)

@@ -1,0 +1,144 @@
+"""tcgen05 GEMM against a plain fp32 PyTorch reference of the same op."""
+import pytest
+import torch
+
+from dion_b200.ops.gemm import gemm, gemm_reference
+
+
+def _operand(rows, cols, dtype, transposed, batch=None, device="cuda"):
+    """Logical [rows, cols] matrix, stored row-major or as the transpose of a row-major one."""
+    shape = (cols, rows) if transposed else (rows, cols)
+    if batch is not None:
+        shape = (batch, *shape)
+    t = torch.randn(shape, device=device, dtype=torch.float32).to(dtype)
+    return t.transpose(-1, -2) if transposed else t
+
+
+def _rel_err(x, ref):
+    return ((x.float() - ref.float()).abs().max() / ref.float().abs().max().clamp_min(1e-20)).item()
+
+
+def test_reference_semantics_cpu():
+    a = torch.randn(5, 7)
+    b = torch.randn(7, 3)
+    c = torch.randn(5, 3)
+    out = gemm(a, b, c=c, alpha=0.5, beta=2.0)
+    torch.testing.assert_close(out, 0.5 * a @ b + 2.0 * c)
+    out2 = torch.ones(5, 3)
+    gemm(a, b, out=out2, accumulate=True)
+    torch.testing.assert_close(out2, 1 + a @ b)
+    out3 = gemm(a, b, act="relu2")
+    torch.testing.assert_close(out3, torch.relu(a @ b) ** 2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("ta", [False, True])
+@pytest.mark.parametrize("tb", [False, True])
+@pytest.mark.parametrize("shape", [(256, 256, 256), (384, 200, 328), (128, 64, 64), (1000, 520, 72)])
+def test_gemm_layouts(dtype, ta, tb, shape):
+    M, N, K = shape
+    a = _operand(M, K, dtype, ta)
+    b = _operand(K, N, dtype, tb)
+    out = gemm(a, b, out_dtype=torch.float32)
+    ref = a.float() @ b.float()
+    tol = 2e-5 if dtype == torch.bfloat16 else 4e-3
+    assert _rel_err(out, ref) < tol
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("block_n", [64, 128, 256])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_gemm_block_n_and_batch(block_n, dtype):
+    a = _operand(300, 192, dtype, False, batch=3)
+    b = _operand(192, 520, dtype, True, batch=3)
+    out = gemm(a, b, out_dtype=torch.float32, block_n=block_n)
+    ref = torch.matmul(a.float(), b.float())
+    assert _rel_err(out, ref) < (2e-5 if dtype == torch.bfloat16 else 4e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("c_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_epilogue_alpha_beta(c_dtype, out_dtype):
+    a = _operand(520, 256, torch.bfloat16, False)
+    b = _operand(256, 392, torch.bfloat16, False)
+    c = torch.randn(520, 392, device="cuda").to(c_dtype)
+    shadow = torch.empty(520, 392, device="cuda", dtype=torch.bfloat16)
+    out = gemm(a, b, c=c, alpha=-0.25, beta=0.75, out_dtype=out_dtype, shadow=shadow)
+    ref = -0.25 * (a.float() @ b.float()) + 0.75 * c.float()
+    assert _rel_err(out, ref) < (1e-2 if out_dtype == torch.bfloat16 else 2e-5)
+    assert torch.equal(shadow, out.to(torch.bfloat16))
+
+
+@pytest.mark.gpu
+def test_gemm_inplace_accumulate_into_c():
+    a = _operand(256, 128, torch.float32, False)
+    b = _operand(128, 256, torch.float32, True)
+    m = torch.randn(256, 256, device="cuda")
+    ref = m - 0.05 * (a @ b)
+    gemm(a, b, c=m, out=m, alpha=-0.05, beta=1.0)
+    assert _rel_err(m, ref) < 1e-3
+
+
+@pytest.mark.gpu
+def test_gemm_relu2():
+    a = _operand(256, 128, torch.bfloat16, False)
+    b = _operand(128, 512, torch.bfloat16, True)
+    out = gemm(a, b, act="relu2", out_dtype=torch.float32)
+    ref = torch.relu(a.float() @ b.float()) ** 2
+    assert _rel_err(out, ref) < 1e-4
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_gemm_symmetric(dtype):
+    x = _operand(640, 328, dtype, False, batch=2)
+    out = gemm(x, x.transpose(-1, -2), out_dtype=torch.float32, symmetric=True)
+    ref = torch.matmul(x.float(), x.float().transpose(-1, -2))
+    assert _rel_err(out, ref) < (2e-5 if dtype == torch.bfloat16 else 4e-3)
+    assert torch.equal(out, out.transpose(-1, -2))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("split_k", [1, 3, 8])
+def test_gemm_split_k_atomic(split_k):
+    a = _operand(256, 4096, torch.bfloat16, True)
+    b = _operand(4096, 384, torch.bfloat16, False)
+    out = torch.ones(256, 384, device="cuda")
+    gemm(a, b, out=out, accumulate=True, split_k=split_k, alpha=0.5)
+    ref = 1 + 0.5 * (a.float() @ b.float())
+    assert _rel_err(out, ref) < 1e-4
+
+
+@pytest.mark.gpu
+def test_gemm_pointer_array_outputs():
+    B = 5
+    a = _operand(256, 96, torch.float32, False, batch=B)
+    b = _operand(96, 384, torch.float32, True, batch=B)
+    xs = [torch.randn(256, 384, device="cuda") for _ in range(B)]
+    sh = [torch.empty(256, 384, device="cuda", dtype=torch.bfloat16) for _ in range(B)]
+    refs = [0.9 * x - 0.1 * (a[i] @ b[i]) for i, x in enumerate(xs)]
+    ptrs = torch.tensor([x.data_ptr() for x in xs], dtype=torch.int64, device="cuda")
+    sptrs = torch.tensor([x.data_ptr() for x in sh], dtype=torch.int64, device="cuda")
+    gemm(a, b, c=xs[0], out=xs[0], c_ptrs=ptrs, out_ptrs=ptrs, shadow=sh[0], shadow_ptrs=sptrs, alpha=-0.1, beta=0.9)
+    for x, r, s in zip(xs, refs, sh):
+        assert _rel_err(x, r) < 2e-3
+        assert torch.equal(s, x.to(torch.bfloat16))
+
+
+@pytest.mark.gpu
+def test_gemm_unaligned_falls_back_to_library():
+    a = torch.randn(33, 17, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(17, 9, device="cuda", dtype=torch.bfloat16)
+    out = gemm(a, b, out_dtype=torch.float32)
+    assert _rel_err(out, a.float() @ b.float()) < 2e-2
+
+
+@pytest.mark.gpu
+def test_gemm_status_word_stays_clear():
+    from dion_b200.ops import runtime
+
+    a = _operand(512, 512, torch.bfloat16, False)
+    gemm(a, a)
+    runtime.check_status()

@@ -1,0 +1,72 @@
+"""Batched Cholesky-inverse kernel and column norms against PyTorch references."""
+import pytest
+import torch
+
+from dion_b200 import ops
+
+
+def _gram(batch, m, r, device, cond=None):
+    P = torch.randn(batch, m, r, device=device)
+    if cond is not None:
+        scale = torch.logspace(0, -cond, r, device=device)
+        P = P * scale
+    return P, P.transpose(-1, -2) @ P
+
+
+def test_chol_inverse_reference_orthonormalises_cpu():
+    P, G = _gram(2, 64, 24, "cpu", cond=2)
+    Z, info = ops.chol_inverse(G)
+    Q = P @ Z.transpose(-1, -2)
+    eye = torch.eye(24).expand(2, 24, 24)
+    assert (Q.transpose(-1, -2) @ Q - eye).abs().max() < 1e-3
+    assert int(info.sum()) == 0
+    # same basis as Householder QR up to column signs
+    Qh, _ = torch.linalg.qr(P)
+    assert ((Q.abs() - Qh.abs()).abs().max()) < 1e-3
+
+
+def test_chol_inverse_reference_zero_matrix_cpu():
+    Z, info = ops.chol_inverse(torch.zeros(1, 8, 8))
+    assert torch.isfinite(Z).all()
+    assert int(info[0]) == 8
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("r", [32, 96, 192, 200, 768, 1024])
+def test_chol_inverse_kernel(r):
+    batch = 3
+    P, G = _gram(batch, 4 * r, r, "cuda", cond=1.5)
+    Z, info = ops.chol_inverse(G)
+    torch.cuda.synchronize()
+    assert int(info.sum()) == 0
+    assert torch.equal(Z, torch.tril(Z))
+    Q = P @ Z.transpose(-1, -2)
+    eye = torch.eye(r, device="cuda")
+    err = (Q.transpose(-1, -2) @ Q - eye).abs().max().item()
+    assert err < 5e-3, err
+    Zr, _ = ops.chol_inverse_reference(G.double())
+    rel = ((Z.double() - Zr.double()).norm() / Zr.double().norm()).item()
+    assert rel < 1e-2, rel
+
+
+@pytest.mark.gpu
+def test_chol_inverse_kernel_rank_deficient_and_zero():
+    P = torch.randn(2, 512, 64, device="cuda")
+    P[0, :, 10] = 0          # a zero column
+    P[0, :, 20] = P[0, :, 5]  # a duplicated column
+    P[1] = 0                 # an all-zero matrix
+    G = P.transpose(-1, -2) @ P
+    Z, info = ops.chol_inverse(G)
+    assert torch.isfinite(Z).all()
+    assert int(info[0]) >= 2 and int(info[1]) == 64
+    Q = P @ Z.transpose(-1, -2)
+    assert torch.isfinite(Q).all()
+    assert Q[1].abs().max() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_col_sumsq_kernel(dtype):
+    X = torch.randn(5, 333, 200, device="cuda").to(dtype)
+    out = ops.col_sumsq(X)
+    torch.testing.assert_close(out, X.float().square().sum(-2), rtol=1e-4, atol=1e-4)

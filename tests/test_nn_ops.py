@@ -1,0 +1,154 @@
+"""Model kernels (norms, rotary, ReLU^2, embedding, fused lm_head + cross-entropy, Linear)
+against fp32 PyTorch references, forward and backward."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from dion_b200.ops import nn as N
+
+
+def _ref_rms(x, eps=N.RMS_EPS):
+    xf = x.float()
+    return xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)
+
+
+def test_cpu_paths_are_differentiable():
+    x = torch.randn(2, 5, 16, requires_grad=True)
+    w = torch.randn(24, 16, requires_grad=True)
+    y = N.linear(N.rms_norm(x), w, act="relu2")
+    y.sum().backward()
+    assert x.grad is not None and w.grad is not None
+    cos, sin = N.rotary_tables(5, 8, "cpu")
+    q = torch.randn(2, 5, 2, 8)
+    qo, ko = N.rope_qknorm(q, q.clone(), cos, sin)
+    assert qo.shape == q.shape
+    torch.testing.assert_close(qo.square().mean(-1), torch.ones(2, 5, 2), rtol=1e-3, atol=1e-3)
+    t = torch.randint(0, 24, (2, 5))
+    loss = N.linear_cross_entropy(torch.randn(2, 5, 16), w, t)
+    assert loss.ndim == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dim", [768, 64, 4096])
+def test_rmsnorm_kernel(dim):
+    x = torch.randn(37, 5, dim, device="cuda").bfloat16().requires_grad_()
+    y = N.rms_norm(x)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    yr = _ref_rms(xr)
+    yr.backward(g.float())
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("head_dim", [64, 128])
+def test_rope_qknorm_kernel(head_dim):
+    B, T, H = 2, 48, 3
+    cos, sin = N.rotary_tables(T, head_dim, "cuda")
+    q = torch.randn(B, T, H, head_dim, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(B, T, H, head_dim, device="cuda").bfloat16().requires_grad_()
+    qo, ko = N.rope_qknorm(q, k, cos, sin)
+    gq, gk = torch.randn_like(qo), torch.randn_like(ko)
+    (qo * gq).sum().backward(retain_graph=True)
+    (ko * gk).sum().backward()
+    qr = q.detach().float().requires_grad_()
+    kr = k.detach().float().requires_grad_()
+    qro, kro = N._rope_qknorm_torch(qr, kr, cos, sin, N.RMS_EPS)
+    ((qro * gq.float()).sum() + (kro * gk.float()).sum()).backward()
+    torch.testing.assert_close(qo.float(), qro, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(ko.float(), kro, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(q.grad.float(), qr.grad, rtol=5e-2, atol=5e-2)
+    torch.testing.assert_close(k.grad.float(), kr.grad, rtol=5e-2, atol=5e-2)
+
+
+@pytest.mark.gpu
+def test_relu2_kernel():
+    x = torch.randn(64, 3072, device="cuda").bfloat16().requires_grad_()
+    h = N.relu2(x)
+    g = torch.randn_like(h)
+    h.backward(g)
+    xr = x.detach().float().requires_grad_()
+    hr = torch.relu(xr).square()
+    hr.backward(g.float())
+    torch.testing.assert_close(h.float(), hr, rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.gpu
+def test_embedding_kernel():
+    table = torch.randn(1000, 768, device="cuda", requires_grad=True)
+    idx = torch.randint(0, 1000, (4, 33), device="cuda")
+    idx[0, :5] = 7  # repeated ids accumulate
+    out = N.embedding(idx, table)
+    g = torch.randn_like(out)
+    out.backward(g)
+    assert torch.equal(out, table.detach()[idx].bfloat16())
+    ref = torch.zeros_like(table)
+    ref.index_put_((idx.reshape(-1),), g.float().view(-1, 768), accumulate=True)
+    torch.testing.assert_close(table.grad, ref, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("residual", [False, True])
+def test_linear_fn(residual):
+    T, K, Nn = 300, 256, 520
+    x = torch.randn(T, K, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(Nn, K, device="cuda") / K ** 0.5).requires_grad_()
+    r = torch.randn(T, Nn, device="cuda").bfloat16().requires_grad_() if residual else None
+    y = N.linear(x, w, residual=r)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().bfloat16().float().requires_grad_()
+    yr = xr @ wr.t() + (r.detach().float() if residual else 0)
+    yr.backward(g.float())
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(w.grad, wr.grad, rtol=2e-2, atol=2e-2)
+    assert w.grad.dtype == torch.float32
+    if residual:
+        assert torch.equal(r.grad, g)
+
+
+@pytest.mark.gpu
+def test_linear_relu2_and_split_k_weight_grad():
+    T, K, Nn = 4096, 128, 256
+    x = torch.randn(T, K, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(Nn, K, device="cuda") / K ** 0.5).requires_grad_()
+    y = N.linear(x, w, act="relu2")
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().bfloat16().float().requires_grad_()
+    pre = (xr @ wr.t()).bfloat16().float()
+    # reference through the same bf16 rounding of the pre-activation
+    yr = torch.relu(xr @ wr.t()).square()
+    yr.backward(g.float())
+    torch.testing.assert_close(y.float(), torch.relu(pre).square(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=5e-2, atol=5e-2)
+    torch.testing.assert_close(w.grad, wr.grad, rtol=5e-2, atol=1e-1)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("vocab", [50304, 1024])
+def test_linear_cross_entropy(vocab):
+    T, K = 700, 256
+    x = torch.randn(T, K, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(vocab, K, device="cuda") / K ** 0.5).requires_grad_()
+    t = torch.randint(0, vocab, (T,), device="cuda")
+    t[:9] = -1
+    loss = N.linear_cross_entropy(x, w, t, ignore_index=-1, chunk_tokens=256)
+    (loss * 0.5).backward()
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().bfloat16().float().requires_grad_()
+    logits = (xr @ wr.t())
+    lr = F.cross_entropy(logits, t, ignore_index=-1)
+    (lr * 0.5).backward()
+    torch.testing.assert_close(loss, lr, rtol=5e-3, atol=5e-3)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=5e-2, atol=2e-4)
+    torch.testing.assert_close(w.grad, wr.grad, rtol=5e-2, atol=2e-4)
+    with torch.no_grad():
+        l2 = N.linear_cross_entropy(x, w, t, ignore_index=-1)
+    torch.testing.assert_close(l2, lr, rtol=5e-3, atol=5e-3)
