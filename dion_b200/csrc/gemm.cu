@@ -71,6 +71,13 @@ struct Cfg {
   static constexpr uint32_t B_LBO = (kBMajor == kMajorK) ? 16u : (uint32_t)BK * 128u;
   static constexpr uint32_t A_KSTEP = (kAMajor == kMajorK) ? 32u : (uint32_t)UMMA_K * 128u;
   static constexpr uint32_t B_KSTEP = (kBMajor == kMajorK) ? 32u : (uint32_t)UMMA_K * 128u;
+  // MN-major fp32 tiles use the 32-byte-atom swizzle: 4 K-rows (512 B) per atom
+  static constexpr bool A_ATOM32 = kTf32 && kAMajor == kMajorMN;
+  static constexpr bool B_ATOM32 = kTf32 && kBMajor == kMajorMN;
+  static constexpr uint32_t A_SBO = A_ATOM32 ? 512u : 1024u;
+  static constexpr uint32_t B_SBO = B_ATOM32 ? 512u : 1024u;
+  static constexpr uint32_t A_LAYOUT = A_ATOM32 ? kLayoutSw128Atom32 : kLayoutSw128;
+  static constexpr uint32_t B_LAYOUT = B_ATOM32 ? kLayoutSw128Atom32 : kLayoutSw128;
 };
 
 struct TileCoord {
@@ -236,8 +243,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           const uint32_t sb = sa + C::A_BYTES;
 #pragma unroll
           for (int j = 0; j < C::KSTEPS; ++j) {
-            const uint64_t da = make_smem_desc(sa + j * C::A_KSTEP, C::A_LBO, 1024);
-            const uint64_t db = make_smem_desc(sb + j * C::B_KSTEP, C::B_LBO, 1024);
+            const uint64_t da = make_smem_desc(sa + j * C::A_KSTEP, C::A_LBO, C::A_SBO, C::A_LAYOUT);
+            const uint64_t db = make_smem_desc(sb + j * C::B_KSTEP, C::B_LBO, C::B_SBO, C::B_LAYOUT);
             umma_ss<kTf32>(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
@@ -461,7 +468,8 @@ EncodeFn get_encode_fn() {
 
 // Tensor map over a row-major [batch][rows][inner] array with a [1][box_rows][box_inner] box.
 bool make_tmap(CUtensorMap* map, const void* base, int dtype, uint64_t inner, uint64_t rows, uint64_t batch,
-               uint64_t row_pitch_elems, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_rows) {
+               uint64_t row_pitch_elems, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_rows,
+               bool atom32) {
   EncodeFn fn = get_encode_fn();
   if (!fn) {
     g_last_error = "cuTensorMapEncodeTiled is not available from this driver";
@@ -480,7 +488,8 @@ bool make_tmap(CUtensorMap* map, const void* base, int dtype, uint64_t inner, ui
   }
   CUresult r = fn(map, dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     char buf[160];
@@ -509,14 +518,14 @@ cudaError_t launch_cfg(const GemmArgs& a, const KernelParams& kp, cudaStream_t s
   const int dt = kTf32 ? kF32 : kBF16;
   bool ok;
   if (kAMajor == kMajorK)
-    ok = make_tmap(&ta, a.A, dt, a.K, a.M, a.batch, a.lda, a.a_batch_stride, C::BK, kBlockM);
+    ok = make_tmap(&ta, a.A, dt, a.K, a.M, a.batch, a.lda, a.a_batch_stride, C::BK, kBlockM, false);
   else
-    ok = make_tmap(&ta, a.A, dt, a.M, a.K, a.batch, a.lda, a.a_batch_stride, C::CH, C::BK);
+    ok = make_tmap(&ta, a.A, dt, a.M, a.K, a.batch, a.lda, a.a_batch_stride, C::CH, C::BK, C::A_ATOM32);
   if (!ok) return cudaErrorInvalidValue;
   if (kBMajor == kMajorK)
-    ok = make_tmap(&tb, a.B, dt, a.K, a.N, a.batch, a.ldb, a.b_batch_stride, C::BK, kBlockN);
+    ok = make_tmap(&tb, a.B, dt, a.K, a.N, a.batch, a.ldb, a.b_batch_stride, C::BK, kBlockN, false);
   else
-    ok = make_tmap(&tb, a.B, dt, a.N, a.K, a.batch, a.ldb, a.b_batch_stride, C::CH, C::BK);
+    ok = make_tmap(&tb, a.B, dt, a.N, a.K, a.batch, a.ldb, a.b_batch_stride, C::CH, C::BK, C::B_ATOM32);
   if (!ok) return cudaErrorInvalidValue;
 
   auto kernel = gemm_kernel<kTf32, kAMajor, kBMajor, kBlockN>;

@@ -81,7 +81,7 @@ chol_inverse_kernel(const float* __restrict__ Gall, float* __restrict__ Zall, fl
   float* dblk = zrow + (size_t)NB * rp;       // [NB][NB+1]
   float* linv = dblk + NB * (NB + 1);         // [NB][NB+1]
   float* dscale = linv + NB * (NB + 1);       // [rp] Jacobi scaling 1/sqrt(G_ii)
-  __shared__ int clamp_count;
+  int& clamp_count = *reinterpret_cast<int*>(dscale + rp);
 
   const int b = blockIdx.x;
   const float* G = Gall + (long long)b * g_batch_stride;
@@ -253,23 +253,24 @@ cudaError_t chol_inverse_launch(const float* G, float* Z, float* work, int* info
                                 long long g_batch_stride, float pivot_floor, cudaStream_t s) {
   if (batch == 0 || r == 0) return cudaSuccess;
   const int rp = ((r + 63) / 64) * 64;
-  auto smem_for = [&](int nb) { return (size_t)(2 * nb * rp + 2 * nb * (nb + 1) + rp) * sizeof(float); };
+  auto smem_for = [&](int nb) { return (size_t)(2 * nb * rp + 2 * nb * (nb + 1) + rp + 4) * sizeof(float); };
+  constexpr size_t kMaxSmem = 227 * 1024;
   cudaError_t e;
-  if (smem_for(32) <= 227 * 1024) {
-    static bool set32 = false;
-    if (!set32) {
-      e = cudaFuncSetAttribute(chol_inverse_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (smem_for(32) <= kMaxSmem) {
+    static size_t granted32 = 48 * 1024;
+    if (smem_for(32) > granted32) {
+      e = cudaFuncSetAttribute(chol_inverse_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem);
       if (e != cudaSuccess) return e;
-      set32 = true;
+      granted32 = kMaxSmem;
     }
     chol_inverse_kernel<32><<<batch, kCholThreads, smem_for(32), s>>>(G, Z, work, info, r, ldg, g_batch_stride, rp,
                                                                      pivot_floor);
-  } else if (smem_for(16) <= 227 * 1024) {
-    static bool set16 = false;
-    if (!set16) {
-      e = cudaFuncSetAttribute(chol_inverse_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  } else if (smem_for(16) <= kMaxSmem) {
+    static size_t granted16 = 48 * 1024;
+    if (smem_for(16) > granted16) {
+      e = cudaFuncSetAttribute(chol_inverse_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem);
       if (e != cudaSuccess) return e;
-      set16 = true;
+      granted16 = kMaxSmem;
     }
     chol_inverse_kernel<16><<<batch, kCholThreads, smem_for(16), s>>>(G, Z, work, info, r, ldg, g_batch_stride, rp,
                                                                      pivot_floor);

@@ -147,20 +147,25 @@ __device__ __forceinline__ void tc_fence_after() {
 //   bits [16,30) leading-dimension byte offset >> 4
 //   bits [32,46) stride-dimension byte offset >> 4
 //   bits [46,48) descriptor version (1 on sm_100)
-//   bits [61,64) layout type (2 = 128-byte swizzle)
+//   bits [61,64) layout type (2 = 128-byte swizzle, 1 = 128-byte swizzle with 32-byte atoms)
 // K-major tile  : rows of 128 B; 8 rows form one 1024 B swizzle atom; SBO is the
 //                 distance between atoms along M/N; LBO is unused.
 // MN-major tile : 128 B rows run along M/N (64 bf16 or 32 fp32); 8 K-rows form an
 //                 atom; SBO is the distance between atoms along K and LBO the
 //                 distance between 128 B-wide chunks along M/N.
+// MN-major tiles of 32-bit elements only exist in the 32-byte-atom flavour of the
+// 128-byte swizzle (address bits [5,7) ^= bits [7,9)): an atom is 4 K-rows = 512 B.
+constexpr uint32_t kLayoutSw128 = 2;
+constexpr uint32_t kLayoutSw128Atom32 = 1;
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
+                                                   uint32_t sbo_bytes,
+                                                   uint32_t layout_type = kLayoutSw128) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
   d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
   d |= 1ull << 46;
-  d |= 2ull << 61;
+  d |= static_cast<uint64_t>(layout_type) << 61;
   return d;
 }
 

@@ -91,7 +91,7 @@ def _split_k_for(M: int, N: int, K: int) -> int:
     tiles = ((M + 127) // 128) * ((N + 127) // 128)
     if tiles >= 148 or K < 2048:
         return 1
-    want = max(1, (2 * 148 + tiles - 1) // tiles)
+    want = max(1, (4 * 148 + tiles - 1) // tiles)
     return int(max(1, min(want, K // 512, 32)))
 
 
@@ -322,7 +322,7 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
         wb = bf16_weight(weight)
         T, K = x.shape
         V = wb.shape[0]
-        need_grad = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad)
+        need_grad = bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[1])
         valid = (targets != ignore_index).sum().clamp_min(1).to(torch.float32)
         inv_valid = valid.reciprocal()
         row_loss = torch.empty(T, device=x.device, dtype=torch.float32)

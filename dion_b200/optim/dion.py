@@ -1,0 +1,665 @@
+"""Dion: distributed orthonormalised updates with low-rank power iteration and error feedback.
+
+Same constructor, parameter-group keys, optimizer-state layout and update rule as the
+reference's ``Dion`` (dion/dion.py:75-739 for the class, 742-1162 for the three update
+functions), executed differently:
+
+* all matrices of one (shape, placements, dtype) class are processed together: their
+  momentum and Q states live in one packed buffer each (``state["momentum"]`` / ``["Q"]``
+  are views into it, so checkpoints look the same), and every stage of the algorithm is
+  one batched kernel launch over the whole class instead of one task per ``world_size``
+  matrices;
+* one local-shard formulation covers the unsharded (DDP), outer-sharded (FSDP2) and
+  inner+outer-sharded (FSDP2 x TP) cases; the only things that differ are which process
+  groups the partial products are reduced over;
+* orthonormalisation is CholeskyQR2 on device (see optim/orthogonalize.py) instead of the
+  sketch + Householder QR + triangular-solve sequence.
+
+Notation: a weight X is m x n; "A" is M (or M^T when transposed) of shape a x b; Q is
+b x r, P = A Q is a x r, R = A^T P is b x r.  The outer (FSDP) mesh shards b, the inner
+(TP) mesh shards a and the columns of Q.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Any, Dict, Generator, List, Optional, Tuple, Union
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+from torch.distributed import ProcessGroup
+from torch.distributed.tensor import DeviceMesh, DTensor, Placement, Replicate, Shard
+from torch.optim.optimizer import Optimizer, ParamsT
+
+from .. import ops
+from ..ops import nn as nn_ops
+from .common import (Scheduler, all_reduce_, group_of, group_rank, group_size, to_local)
+from .orthogonalize import orthonormalize_cholqr
+
+try:  # pragma: no cover - depends on the torch build
+    from torch.distributed.tensor.placement_types import _StridedShard
+except ImportError:  # pragma: no cover
+    _StridedShard = None
+
+
+@dataclass
+class DionMixedPrecisionConfig:
+    """dtypes of the optimizer states; ``None`` keeps the parameter's dtype
+    (dion/dion.py:59-72)."""
+
+    momentum_dtype: Optional[torch.dtype] = None
+    Q_dtype: Optional[torch.dtype] = None
+    variance_dtype: Optional[torch.dtype] = None
+
+
+@dataclass
+class _DionParamConfig:
+    """How one parameter is sharded and which orientation the power iteration uses.
+    Recomputed from the live tensors, never checkpointed (dion/dion.py:33-56, 194-196)."""
+
+    outer_shard_tensor_dim: Optional[int] = None
+    inner_shard_tensor_dim: Optional[int] = None
+    outer_shard_mesh_dim: Optional[int] = None
+    inner_shard_mesh_dim: Optional[int] = None
+    is_transposed: bool = False
+    compressed_all_reduce: bool = False
+    Q_sharded_placements: Optional[Tuple[Placement, ...]] = None
+    Q_inner_unsharded_placements: Optional[Tuple[Placement, ...]] = None
+
+
+def validate_dion_args(lr, mu, betas, weight_decay, rank_fraction, rank_multiple_of):
+    if lr < 0.0:
+        raise ValueError(f"Invalid learning rate: {lr}")
+    if mu < 0.0:
+        raise ValueError(f"Invalid momentum factor (mu): {mu}")
+    if len(betas) != 2 or betas[0] < 0.0 or betas[1] < 0.0:
+        raise ValueError(f"Invalid betas: {betas}")
+    if weight_decay < 0.0:
+        raise ValueError(f"Invalid weight_decay value: {weight_decay}")
+    if rank_fraction <= 0 or rank_fraction > 1:
+        raise ValueError(f"Invalid rank fraction: {rank_fraction}")
+    if rank_multiple_of <= 0:
+        raise ValueError(f"Invalid rank multiple of: {rank_multiple_of}")
+
+
+def validate_dion_meshes(replicate_mesh, outer_shard_mesh, inner_shard_mesh):
+    if replicate_mesh is not None and not isinstance(replicate_mesh, (DeviceMesh, ProcessGroup)):
+        raise TypeError(f"Replicate mesh must be a DeviceMesh or ProcessGroup, but got {type(replicate_mesh)}.")
+    for name, mesh in (("Outer", outer_shard_mesh), ("Inner", inner_shard_mesh)):
+        if mesh is None:
+            continue
+        if not isinstance(mesh, DeviceMesh):
+            raise TypeError(f"{name} shard mesh must be a DeviceMesh, but got {type(mesh)}.")
+        if mesh.ndim != 1:
+            raise ValueError(f"{name} shard mesh must be 1D, but got {mesh.ndim}D. Try using a 1D sub-mesh.")
+        if mesh == replicate_mesh:
+            raise ValueError(f"{name} shard mesh must be different from replicate mesh.")
+    if inner_shard_mesh is not None and inner_shard_mesh == outer_shard_mesh:
+        raise ValueError("Outer and inner shard meshes must be different.")
+
+
+def low_rank_dim(m: int, n: int, rank_fraction: float, rank_multiple_of: int) -> int:
+    """r = rank_fraction * min(m, n), rounded up to a multiple, clamped (dion.py:673-676)."""
+    r = rank_fraction * min(m, n)
+    r = rank_multiple_of * math.ceil(r / rank_multiple_of)
+    return int(min(r, m, n))
+
+
+class _PackedClass:
+    """All Dion parameters of one (shape, placements, dtype, group) class with their states
+    packed into ``M: [B, m_loc, n_loc]`` and ``Q: [B, q_rows_loc, r_loc]``."""
+
+    def __init__(self, params: List[Tensor], cfg: _DionParamConfig, M: Tensor, Q: Tensor):
+        self.params = params
+        self.cfg = cfg
+        self.M = M
+        self.Q = Q
+        self.x_ptrs: Optional[Tensor] = None
+        self.x_ptr_list: Optional[List[int]] = None
+        self.shadow_ptrs: Optional[Tensor] = None
+        self.shadow_ptr_list: Optional[List[int]] = None
+        self.nonzero: Optional[Tensor] = None
+
+
+class Dion(Optimizer):
+    """Distributed Dion optimizer (https://arxiv.org/abs/2504.05295).
+
+    Args mirror the reference: ``replicate_mesh`` (DeviceMesh or ProcessGroup, data-parallel
+    replicas), ``outer_shard_mesh`` (FSDP dimension, replicated during orthogonalisation),
+    ``inner_shard_mesh`` (TP dimension, sharded during orthogonalisation),
+    ``replicate_mesh_grad_sync`` (the optimizer synchronises gradients - compressed to the
+    low-rank factors where that is cheaper), ``rank_fraction`` / ``rank_multiple_of``,
+    ``lr`` (scaled by sqrt(fan_out/fan_in) for matrices), ``mu``, ``betas`` (for the
+    ``adamw`` / ``lion`` parameter groups), ``weight_decay``, ``epsilon``,
+    ``mixed_precision_config``.  Only ``power_iters=1`` and ``qr_method="rcqr"`` are
+    accepted, as in the reference (``cqr_warmup_steps`` and ``rcqr_oversample`` are kept for
+    signature and checkpoint compatibility; the device-side CholeskyQR2 needs neither).
+
+    Parameters are either all DTensors (with DeviceMesh arguments) or all plain tensors
+    (with a ProcessGroup ``replicate_mesh``), sharded uniformly.
+    """
+
+    def __init__(
+        self,
+        params: ParamsT,
+        replicate_mesh: Optional[Union[DeviceMesh, ProcessGroup]] = None,
+        outer_shard_mesh: Optional[DeviceMesh] = None,
+        inner_shard_mesh: Optional[DeviceMesh] = None,
+        replicate_mesh_grad_sync: bool = True,
+        rank_fraction: float = 1.0,
+        rank_multiple_of: int = 1,
+        lr: float = 0.01,
+        mu: float = 0.95,
+        betas: Tuple[float, float] = (0.9, 0.95),
+        weight_decay: float = 0.01,
+        epsilon: float = 1e-8,
+        power_iters: int = 1,
+        qr_method: str = "rcqr",
+        cqr_warmup_steps: int = 150,
+        rcqr_oversample: float = 1.25,
+        mixed_precision_config: Optional[DionMixedPrecisionConfig] = None,
+    ):
+        validate_dion_args(lr, mu, betas, weight_decay, rank_fraction, rank_multiple_of)
+        if power_iters != 1:
+            raise ValueError("Async Dion only supports power_iters=1")
+        if qr_method != "rcqr":
+            raise ValueError("Async Dion only supports qr_method='rcqr'")
+        validate_dion_meshes(replicate_mesh, outer_shard_mesh, inner_shard_mesh)
+
+        defaults = dict(
+            rank_fraction=rank_fraction,
+            rank_multiple_of=rank_multiple_of,
+            lr=lr,
+            mu=mu,
+            beta1=betas[0],
+            beta2=betas[1],
+            weight_decay=weight_decay,
+            epsilon=epsilon,
+            oversample=rcqr_oversample,
+            algorithm="dion",
+            step=0,
+        )
+        super().__init__(params, defaults)
+
+        self._param_config: Dict[Tensor, _DionParamConfig] = {}
+        self._packed: Dict[tuple, _PackedClass] = {}
+        self._replicate_mesh = replicate_mesh
+        self._outer_shard_mesh = outer_shard_mesh
+        self._inner_shard_mesh = inner_shard_mesh
+        self._replicate_mesh_grad_sync = replicate_mesh_grad_sync
+        self._replicate_world_size = group_size(replicate_mesh)
+        self._outer_shard_ranks = (dist.get_process_group_ranks(outer_shard_mesh.get_group())
+                                   if outer_shard_mesh is not None else None)
+        self._inner_shard_ranks = (dist.get_process_group_ranks(inner_shard_mesh.get_group())
+                                   if inner_shard_mesh is not None else None)
+        self._mixed_precision_config = mixed_precision_config or DionMixedPrecisionConfig()
+        # Q factors are drawn from this generator so that every rank draws the same values
+        self._q_seed = 0x0D10
+
+    # ------------------------------------------------------------------ public API
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+
+        dion_groups, lion_groups, adamw_groups = [], [], []
+        for group in self.param_groups:
+            group["step"] += 1
+            algo = group["algorithm"]
+            if algo == "dion":
+                dion_groups.append(group)
+            elif algo == "lion":
+                lion_groups.append(group)
+            elif algo == "adamw":
+                adamw_groups.append(group)
+            else:
+                raise ValueError(f"Unknown algorithm: {algo}")
+
+        def tasks():
+            for group in dion_groups:
+                yield from self._dion_tasks(group)
+            for group in lion_groups:
+                yield lambda g=group: self._scalar_task(g, "lion")
+            for group in adamw_groups:
+                yield lambda g=group: self._scalar_task(g, "adamw")
+
+        Scheduler(tasks(), max_in_flight=3).run()
+        return loss
+
+    @torch.no_grad()
+    def synchronize_for_checkpoint(self):
+        """Average every optimizer-state tensor over the replicate mesh.  With compressed
+        gradient synchronisation the momentum is decoupled across data-parallel replicas, so
+        this must run before a distributed checkpoint is written (dion/dion.py:273-311).  A
+        no-op without a replicate mesh or when the optimizer does not own gradient sync."""
+        if self._replicate_mesh is None or not self._replicate_mesh_grad_sync:
+            return
+        tensors: List[Tensor] = []
+        seen = set()
+        for cls in self._packed.values():
+            for t in (cls.M, cls.Q):
+                tensors.append(t)
+                seen.add(t.untyped_storage().data_ptr())
+        for state in self.state.values():
+            for val in state.values():
+                if isinstance(val, Tensor):
+                    loc = to_local(val)
+                    if loc.untyped_storage().data_ptr() not in seen:
+                        tensors.append(loc)
+        group = group_of(self._replicate_mesh)
+        # bucketed: one collective per ~256 MB
+        bucket, size = [], 0
+        for t in tensors:
+            bucket.append(t)
+            size += t.numel() * t.element_size()
+            if size >= (256 << 20):
+                all_reduce_(bucket, group, average=True)
+                bucket, size = [], 0
+        if bucket:
+            all_reduce_(bucket, group, average=True)
+
+    # ------------------------------------------------------------------ parameter classification
+
+    def _get_dion_param_config(self, x: Tensor) -> _DionParamConfig:
+        """Sharding facts of one parameter (rules of dion/dion.py:498-607)."""
+        cfg = self._param_config.get(x)
+        if cfg is not None:
+            return cfg
+        if x.ndim > 2:
+            raise NotImplementedError(
+                f"Tensors with more than 2 dimensions are not supported. Got {x.ndim}D tensor.")
+        using_device_mesh = any(isinstance(m, DeviceMesh)
+                                for m in (self._replicate_mesh, self._outer_shard_mesh, self._inner_shard_mesh))
+        using_process_group = isinstance(self._replicate_mesh, ProcessGroup)
+        if using_device_mesh and not isinstance(x, DTensor):
+            raise TypeError("When using DeviceMesh, all parameters must be DTensor.")
+        if using_process_group and isinstance(x, DTensor):
+            raise TypeError("When using DTensor parameters, the data parallel group must be specified by a "
+                            "DeviceMesh instead of ProcessGroup.")
+
+        cfg = _DionParamConfig()
+        if x.ndim == 2:
+            m, n = x.shape
+            cfg.is_transposed = m < n
+
+        if isinstance(x, DTensor) and x.ndim == 2:
+            mesh = x.device_mesh
+            placements = x.placements
+            assert len(placements) == mesh.ndim
+            owner_of_dim: List[Optional[int]] = [None, None]
+            for mesh_dim, placement in enumerate(placements):
+                if _StridedShard is not None and isinstance(placement, _StridedShard):
+                    raise NotImplementedError(
+                        "StridedShard is not supported. Ensure that FSDP and TP shard different dimensions of "
+                        "each matrix.")
+                if not placement.is_shard():
+                    continue
+                tdim = placement.dim
+                if owner_of_dim[tdim] is not None:
+                    raise RuntimeError(f"Got double-sharded DTensor for tensor dimension {tdim}.")
+                owner_of_dim[tdim] = mesh_dim
+                ranks = dist.get_process_group_ranks(mesh.get_group(mesh_dim))
+                is_outer = ranks == self._outer_shard_ranks
+                is_inner = ranks == self._inner_shard_ranks
+                if is_outer:
+                    cfg.outer_shard_tensor_dim, cfg.outer_shard_mesh_dim = tdim, mesh_dim
+                if is_inner:
+                    cfg.inner_shard_tensor_dim, cfg.inner_shard_mesh_dim = tdim, mesh_dim
+                if is_outer and is_inner:
+                    raise RuntimeError("Cannot have outer and inner sharding over the same process group.")
+                if mesh.size(mesh_dim) > 1 and not is_outer and not is_inner:
+                    raise RuntimeError(
+                        f"Got DTensor sharded on unrecognized {mesh_dim=}, which does not match outer_shard_mesh "
+                        f"or inner_shard_mesh.")
+            # orthogonalise along the inner-sharded dimension
+            if cfg.inner_shard_tensor_dim == 0 or cfg.outer_shard_tensor_dim == 1:
+                cfg.is_transposed = False
+            if cfg.outer_shard_tensor_dim == 0 or cfg.inner_shard_tensor_dim == 1:
+                cfg.is_transposed = True
+
+        self._param_config[x] = cfg
+        return cfg
+
+    def _split_params_by_sharding(self, params: List[Tensor]) -> Dict[str, List[Tensor]]:
+        out: Dict[str, List[Tensor]] = {"inner_sharded": [], "outer_sharded": [], "non_sharded": []}
+        for p in params:
+            cfg = self._get_dion_param_config(p)
+            if cfg.inner_shard_mesh_dim is not None:
+                out["inner_sharded"].append(p)
+            elif cfg.outer_shard_mesh_dim is not None:
+                out["outer_shard" "ed"].append(p)
+            else:
+                out["non_sharded"].append(p)
+        return out
+
+    # ------------------------------------------------------------------ state
+
+    def _init_opt_state_momentum(self, param: Tensor, state: Dict[str, Any]):
+        state["momentum"] = torch.zeros_like(param, dtype=self._mixed_precision_config.momentum_dtype)
+
+    def _init_opt_state_adam(self, param: Tensor, state: Dict[str, Any]):
+        self._init_opt_state_momentum(param, state)
+        state["variance"] = torch.zeros_like(param, dtype=self._mixed_precision_config.variance_dtype)
+
+    def _draw_q(self, shape: Tuple[int, int], device, dtype) -> Tensor:
+        """Full (unsharded) random Q, identical on every rank: seeded generator on the
+        device, then broadcast from the first rank of the replicate group / world."""
+        gen = torch.Generator(device=device)
+        gen.manual_seed(self._q_seed)
+        self._q_seed += 1
+        q = torch.randn(shape, device=device, dtype=torch.float32, generator=gen).to(dtype)
+        return q
+
+    def _init_opt_state_dion(self, param: Tensor, state: Dict[str, Any], rank_fraction: float,
+                             rank_multiple_of: int):
+        """momentum like the parameter; Q of shape (m, r) if transposed else (n, r), as a
+        DTensor sharded Shard(0) on the outer and Shard(1) on the inner mesh dimension
+        (dion/dion.py:649-721)."""
+        if param.ndim != 2:
+            raise ValueError(
+                f"Expected Dion parameters to be 2D matrix, but got {param.ndim}D. "
+                f"For scalar parameters, set 'algorithm' to 'lion' or 'adamw' when creating param group.")
+        cfg = self._get_dion_param_config(param)
+        self._init_opt_state_momentum(param, state)
+        m, n = param.shape
+        r = low_rank_dim(m, n, rank_fraction, rank_multiple_of)
+        q_shape = (m, r) if cfg.is_transposed else (n, r)
+        if rank_fraction < 1 and (m + n) * r < m * n:
+            cfg.compressed_all_reduce = True
+        q_dtype = self._mixed_precision_config.Q_dtype or param.dtype
+
+        local_param = to_local(param)
+        q_full = self._draw_q(q_shape, local_param.device, q_dtype)
+        if isinstance(param, DTensor):
+            placements: List[Placement] = [Replicate() for _ in range(param.device_mesh.ndim)]
+            if cfg.outer_shard_mesh_dim is not None:
+                placements[cfg.outer_shard_mesh_dim] = Shard(0)
+            if cfg.inner_shard_mesh_dim is not None:
+                placements[cfg.inner_shard_mesh_dim] = Shard(1)
+            cfg.Q_sharded_placements = tuple(placements)
+            if cfg.inner_shard_mesh_dim is not None:
+                unsharded = list(placements)
+                unsharded[cfg.inner_shard_mesh_dim] = Replicate()
+                cfg.Q_inner_unsharded_placements = tuple(unsharded)
+            else:
+                cfg.Q_inner_unsharded_placements = None
+            if dist.is_initialized():
+                dist.broadcast(q_full, src=0)
+            q_local = q_full
+            mesh = param.device_mesh
+            for mesh_dim, pl in enumerate(placements):
+                if pl.is_shard():
+                    size = mesh.size(mesh_dim)
+                    if q_local.size(pl.dim) % size != 0:
+                        raise ValueError(
+                            f"Q dimension {pl.dim} of size {q_local.size(pl.dim)} is not divisible by the mesh "
+                            f"size {size}; use rank_multiple_of to round the rank.")
+                    idx = mesh.get_local_rank(mesh_dim)
+                    q_local = q_local.chunk(size, dim=pl.dim)[idx]
+            state["Q"] = DTensor.from_local(q_local.contiguous(), device_mesh=mesh, placements=placements,
+                                            run_check=False)
+        else:
+            self._replicate_mesh_broadcast(q_full)
+            state["Q"] = q_full
+
+    def _replicate_mesh_broadcast(self, tensor: Tensor):
+        if self._replicate_mesh is None:
+            return
+        if isinstance(self._replicate_mesh, DeviceMesh):
+            for group in self._replicate_mesh.get_all_groups():
+                dist.broadcast(tensor, group=group, group_src=0)
+        elif isinstance(self._replicate_mesh, ProcessGroup):
+            dist.broadcast(tensor, group=self._replicate_mesh, group_src=0)
+        else:
+            raise TypeError("Data parallel mesh must be either a DeviceMesh or ProcessGroup.")
+
+    def _get_or_initialize_state(self, param: Tensor, group: dict) -> dict:
+        state = self.state[param]
+        if not state:
+            algo = group["algorithm"]
+            if algo == "dion":
+                self._init_opt_state_dion(param, state, group["rank_fraction"], group["rank_multiple_of"])
+            elif algo == "adamw":
+                self._init_opt_state_adam(param, state)
+            elif algo in ("lion", "clion"):
+                self._init_opt_state_momentum(param, state)
+            else:
+                raise ValueError(f"Unknown algorithm: {algo}")
+        return state
+
+    # ------------------------------------------------------------------ packing
+
+    def _pack(self, key: tuple, params: List[Tensor], group: dict) -> _PackedClass:
+        """Make the states of `params` views of two packed buffers (copying current values),
+        reusing the existing pack while membership and storage are unchanged."""
+        cls = self._packed.get(key)
+        states = [self._get_or_initialize_state(p, group) for p in params]
+        cfg = self._get_dion_param_config(params[0])
+        if cls is not None and len(cls.params) == len(params) and all(a is b for a, b in zip(cls.params, params)):
+            intact = True
+            for i, s in enumerate(states):
+                m_loc, q_loc = to_local(s["momentum"]), to_local(s["Q"])
+                if m_loc.data_ptr() != cls.M[i].data_ptr() or q_loc.data_ptr() != cls.Q[i].data_ptr() \
+                        or m_loc.dtype != cls.M.dtype or q_loc.dtype != cls.Q.dtype:
+                    intact = False
+                    break
+            if intact:
+                return cls
+        m0, q0 = to_local(states[0]["momentum"]), to_local(states[0]["Q"])
+        M = torch.empty((len(params), *m0.shape), dtype=m0.dtype, device=m0.device)
+        Q = torch.empty((len(params), *q0.shape), dtype=q0.dtype, device=q0.device)
+        for i, (p, s) in enumerate(zip(params, states)):
+            M[i].copy_(to_local(s["momentum"]))
+            Q[i].copy_(to_local(s["Q"]))
+            mom, q = s["momentum"], s["Q"]
+            if isinstance(mom, DTensor):
+                s["momentum"] = DTensor.from_local(M[i], device_mesh=mom.device_mesh, placements=mom.placements,
+                                                   run_check=False, shape=mom.shape, stride=mom.stride())
+            else:
+                s["momentum"] = M[i]
+            if isinstance(q, DTensor):
+                s["Q"] = DTensor.from_local(Q[i], device_mesh=q.device_mesh, placements=q.placements,
+                                            run_check=False, shape=q.shape, stride=q.stride())
+            else:
+                s["Q"] = Q[i]
+        cls = _PackedClass(list(params), cfg, M, Q)
+        self._packed[key] = cls
+        return cls
+
+    # ------------------------------------------------------------------ Dion update
+
+    def _dion_tasks(self, group: dict):
+        params = [p for p in group["params"] if p.grad is not None]
+        if not params:
+            return
+        classes: Dict[tuple, List[Tensor]] = {}
+        for p in params:
+            placements = tuple(p.placements) if isinstance(p, DTensor) else None
+            classes.setdefault((tuple(p.shape), placements, p.dtype, id(group)), []).append(p)
+        for key, members in classes.items():
+            yield lambda k=key, ms=members: self._dion_update_class(k, ms, group)
+
+    def _mesh_dim_group(self, p: Tensor, mesh_dim: Optional[int]) -> Optional[ProcessGroup]:
+        if mesh_dim is None or not isinstance(p, DTensor):
+            return None
+        g = p.device_mesh.get_group(mesh_dim)
+        return g if dist.get_world_size(g) > 1 else None
+
+    def _dion_update_class(self, key: tuple, params: List[Tensor], group: dict) -> Generator[None, None, None]:
+        cls = self._pack(key, params, group)
+        cfg = cls.cfg
+        p0 = params[0]
+        lr, mu, wd, eps = group["lr"], group["mu"], group["weight_decay"], group["epsilon"]
+        B = len(params)
+        M, Qs = cls.M, cls.Q
+        X = [to_local(p) for p in params]
+        G = [to_local(p.grad) for p in params]
+
+        replicate = group_of(self._replicate_mesh)
+        if replicate is not None and dist.get_world_size(replicate) == 1:
+            replicate = None
+        outer = self._mesh_dim_group(p0, cfg.outer_shard_mesh_dim)
+        inner = self._mesh_dim_group(p0, cfg.inner_shard_mesh_dim)
+        sync = self._replicate_mesh_grad_sync and replicate is not None
+        compressed = sync and cfg.compressed_all_reduce
+
+        # 0. full-gradient synchronisation when compression does not pay (dion.py:785-791)
+        if sync and not compressed:
+            wait = all_reduce_(G, replicate, average=True, async_op=True)
+            yield
+            wait()
+
+        # 1. momentum accumulation, remembering which matrices are entirely zero
+        if cls.nonzero is None:
+            cls.nonzero = torch.zeros(B, dtype=torch.int32, device=M.device)
+        else:
+            cls.nonzero.zero_()
+        ops.dion_accumulate(G, list(M.unbind(0)), cls.nonzero)
+
+        # 2. Q with all of its columns (gathered over the inner mesh), in the momentum dtype
+        if inner is not None:
+            w_in = dist.get_world_size(inner)
+            gathered = torch.empty((w_in, *Qs.shape), dtype=Qs.dtype, device=Qs.device)
+            work = dist.all_gather_into_tensor(gathered, Qs.contiguous(), group=inner, async_op=True)
+            yield
+            work.wait()
+            Q_full = gathered.permute(1, 2, 0, 3).reshape(B, Qs.shape[1], w_in * Qs.shape[2])
+        else:
+            Q_full = Qs
+        Qm = Q_full.to(M.dtype)
+
+        # 3. P = A Q, partial over the outer mesh
+        A = M.transpose(1, 2) if cfg.is_transposed else M
+        P = ops.gemm(A, Qm, out_dtype=torch.float32)
+        if outer is not None:
+            wait = all_reduce_(P, outer, average=False, async_op=True)
+            yield
+            wait()
+        if compressed:
+            wait = all_reduce_(P, replicate, average=True, async_op=True)
+            yield
+            wait()
+
+        # 4. orthonormal basis of range(P); rows of P are sharded over the inner mesh
+        P = orthonormalize_cholqr(P, row_group=inner)
+        Pm = P.to(M.dtype)
+
+        # 5. R = A^T P, partial over the inner mesh
+        R = ops.gemm(A.transpose(1, 2), Pm, out_dtype=torch.float32)
+        if inner is not None:
+            wait = all_reduce_(R, inner, average=False, async_op=True)
+            yield
+            wait()
+        if compressed:
+            wait = all_reduce_(R, replicate, average=True, async_op=True)
+            yield
+            wait()
+
+        # 6. all-zero / NaN guard, shard-local like the reference (dion.py:1416-1444):
+        #    an all-zero momentum gives P = 0 and keeps the previous Q
+        nz = (cls.nonzero != 0).view(B, 1, 1)
+        Pm = torch.where(nz, Pm.nan_to_num(), torch.zeros_like(Pm))
+        R = torch.where(nz, R.nan_to_num(), Qm.float())
+        Rm = R.to(M.dtype)
+
+        # 7. error feedback  M -= (1 - mu) P R^T
+        alpha = -(1.0 - mu)
+        if cfg.is_transposed:
+            ops.gemm(Rm, Pm.transpose(1, 2), c=M, out=M, alpha=alpha, beta=1.0)
+        else:
+            ops.gemm(Pm, Rm.transpose(1, 2), c=M, out=M, alpha=alpha, beta=1.0)
+
+        # 8. new Q: column-normalised R (sum of squares completed over the outer mesh)
+        ss = ops.col_sumsq(R)
+        if outer is not None:
+            wait = all_reduce_(ss, outer, average=False, async_op=True)
+            yield
+            wait()
+        Qn = (R / (ss.sqrt().unsqueeze(1) + eps)).to(M.dtype)
+
+        # 9. weight decay and update  X = (1 - lr wd) X - lr sqrt(fan_out / fan_in) P Qn^T
+        fan_out, fan_in = p0.shape[0], p0.shape[1]
+        scaled_lr = ((fan_out / fan_in) ** 0.5) * lr
+        beta = 1.0 - lr * wd
+        if cfg.is_transposed:
+            a_op, b_op = Qn, Pm.transpose(1, 2)
+        else:
+            a_op, b_op = Pm, Qn.transpose(1, 2)
+        self._apply_update(cls, params, X, a_op, b_op, -scaled_lr, beta)
+
+        # 10. keep this rank's columns of the new Q (dion.py:1533-1561)
+        if inner is not None:
+            r_loc = Qs.shape[2]
+            i0 = dist.get_rank(inner) * r_loc
+            Qs.copy_(Qn[:, :, i0:i0 + r_loc])
+        else:
+            Qs.copy_(Qn)
+
+    def _apply_update(self, cls: _PackedClass, params: List[Tensor], X: List[Tensor], a_op: Tensor, b_op: Tensor,
+                      alpha: float, beta: float) -> None:
+        """X[i] = beta * X[i] + alpha * (a_op @ b_op)[i] for separately allocated X[i]."""
+        x0 = X[0]
+        fast = (x0.is_cuda and x0.dtype == torch.float32 and a_op.dtype in (torch.float32, torch.bfloat16)
+                and all(x.is_contiguous() and x.data_ptr() % 16 == 0 for x in X)
+                and (x0.shape[1] * 4) % 16 == 0)
+        if fast:
+            ptr_list = [x.data_ptr() for x in X]
+            if cls.x_ptr_list != ptr_list:
+                cls.x_ptr_list = ptr_list
+                cls.x_ptrs = torch.tensor(ptr_list, dtype=torch.int64, device=x0.device)
+            shadows = [nn_ops.shadow_for_update(p) for p in params]
+            shadow0, shadow_ptrs = None, None
+            if all(s is not None for s in shadows):
+                sp_list = [s.data_ptr() for s in shadows]
+                if cls.shadow_ptr_list != sp_list:
+                    cls.shadow_ptr_list = sp_list
+                    cls.shadow_ptrs = torch.tensor(sp_list, dtype=torch.int64, device=x0.device)
+                shadow0, shadow_ptrs = shadows[0], cls.shadow_ptrs
+            ops.gemm(a_op, b_op, c=x0, out=x0, c_ptrs=cls.x_ptrs, out_ptrs=cls.x_ptrs, shadow=shadow0,
+                     shadow_ptrs=shadow_ptrs, alpha=alpha, beta=beta)
+            for p in params:
+                if shadow0 is not None:
+                    nn_ops.mark_shadow_fresh(p)
+                else:
+                    nn_ops.mark_shadow_stale(p)
+            return
+        upd = torch.matmul(a_op.float(), b_op.float()) if not a_op.is_cuda else ops.gemm(a_op, b_op,
+                                                                                        out_dtype=torch.float32)
+        for i, x in enumerate(X):
+            x.mul_(beta).add_(upd[i].to(x.dtype), alpha=alpha)
+
+    # ------------------------------------------------------------------ scalar (AdamW / Lion) groups
+
+    def _scalar_task(self, group: dict, algo: str) -> Generator[None, None, None]:
+        params = [p for p in group["params"] if p.grad is not None]
+        if not params:
+            return
+        states = [self._get_or_initialize_state(p, group) for p in params]
+        X = to_local(params)
+        G = to_local([p.grad for p in params])
+        Ms = to_local([s["momentum"] for s in states])
+        replicate = group_of(self._replicate_mesh) if self._replicate_mesh_grad_sync else None
+        if replicate is not None and dist.get_world_size(replicate) > 1:
+            wait = all_reduce_(G, replicate, average=True, async_op=True)
+            yield
+            wait()
+        shadows = [nn_ops.shadow_for_update(p) for p in params]
+        shadow_arg = shadows if all(s is not None for s in shadows) and X[0].is_cuda else None
+        if algo == "adamw":
+            Vs = to_local([s["variance"] for s in states])
+            ops.adamw_update(X, G, Ms, Vs, lr=group["lr"], beta1=group["beta1"], beta2=group["beta2"],
+                             weight_decay=group["weight_decay"], step=group["step"], epsilon=group["epsilon"],
+                             shadow=shadow_arg)
+        else:
+            ops.lion_update(X, G, Ms, lr=group["lr"], beta1=group["beta1"], beta2=group["beta2"],
+                            weight_decay=group["weight_decay"], shadow=shadow_arg)
+        for p in params:
+            if shadow_arg is not None:
+                nn_ops.mark_shadow_fresh(p)
+            else:
+                nn_ops.mark_shadow_stale(p)

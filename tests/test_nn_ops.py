@@ -7,6 +7,13 @@ import torch.nn.functional as F
 from dion_b200.ops import nn as N
 
 
+def _close(x, ref, tol):
+    """max |x - ref| relative to the scale of ref (bf16 intermediates make per-element
+    relative checks meaningless near zero)."""
+    err = ((x.float() - ref.float()).abs().max() / ref.float().abs().max().clamp_min(1e-20)).item()
+    assert err < tol, f"scaled max error {err:.3e} >= {tol}"
+
+
 def _ref_rms(x, eps=N.RMS_EPS):
     xf = x.float()
     return xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)
@@ -126,9 +133,9 @@ def test_linear_relu2_and_split_k_weight_grad():
     # reference through the same bf16 rounding of the pre-activation
     yr = torch.relu(xr @ wr.t()).square()
     yr.backward(g.float())
-    torch.testing.assert_close(y.float(), torch.relu(pre).square(), rtol=2e-2, atol=2e-2)
-    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=5e-2, atol=5e-2)
-    torch.testing.assert_close(w.grad, wr.grad, rtol=5e-2, atol=1e-1)
+    _close(y, torch.relu(pre).square(), 1e-2)
+    _close(x.grad, xr.grad, 2e-2)
+    _close(w.grad, wr.grad, 2e-2)
 
 
 @pytest.mark.gpu
@@ -147,8 +154,8 @@ def test_linear_cross_entropy(vocab):
     lr = F.cross_entropy(logits, t, ignore_index=-1)
     (lr * 0.5).backward()
     torch.testing.assert_close(loss, lr, rtol=5e-3, atol=5e-3)
-    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=5e-2, atol=2e-4)
-    torch.testing.assert_close(w.grad, wr.grad, rtol=5e-2, atol=2e-4)
+    _close(x.grad, xr.grad, 2e-2)
+    _close(w.grad, wr.grad, 2e-2)
     with torch.no_grad():
         l2 = N.linear_cross_entropy(x, w, t, ignore_index=-1)
     torch.testing.assert_close(l2, lr, rtol=5e-3, atol=5e-3)
