@@ -263,6 +263,19 @@ class Dion(Optimizer):
         if bucket:
             all_reduce_(bucket, group, average=True)
 
+    def load_state_dict(self, state_dict) -> None:
+        """torch casts loaded floating-point state to the parameter dtype; restore the dtypes
+        of the mixed-precision configuration afterwards so a resumed run keeps its numerics."""
+        super().load_state_dict(state_dict)
+        self._packed.clear()
+        mp = self._mixed_precision_config
+        wanted = {"momentum": mp.momentum_dtype, "Q": mp.Q_dtype, "variance": mp.variance_dtype}
+        for state in self.state.values():
+            for key, dtype in wanted.items():
+                val = state.get(key)
+                if dtype is not None and isinstance(val, Tensor) and val.dtype != dtype:
+                    state[key] = val.to(dtype)
+
     # ------------------------------------------------------------------ parameter classification
 
     def _get_dion_param_config(self, x: Tensor) -> _DionParamConfig:
@@ -332,7 +345,7 @@ class Dion(Optimizer):
             if cfg.inner_shard_mesh_dim is not None:
                 out["inner_sharded"].append(p)
             elif cfg.outer_shard_mesh_dim is not None:
-                out["outer_shard" "ed"].append(p)
+                out["outer_sharded"].append(p)
             else:
                 out["non_sharded"].append(p)
         return out

@@ -1,0 +1,89 @@
+"""Quintic Newton-Schulz orthogonalisation in bf16 (Muon's ``zeropower``).
+
+Same iteration and coefficient schedule as the reference (dion/muon.py:620-647;
+dion/newton_schulz_triton.py:336-374): ``X <- a X + (b A + c A A) X`` with ``A = X X^T``,
+five steps with per-step coefficients, input scaled to Frobenius norm <= 1.
+
+On CUDA the three products of a step are tcgen05 GEMMs: ``A`` and ``b A + c A A`` are
+symmetric, so only the upper-triangular tiles are computed and mirrored in the epilogue,
+which also fuses the ``b A`` / ``a X`` additions.  Tall inputs are handled by multiplying
+from the right (``A = X^T X``), so nothing is ever transposed in memory.
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Sequence, Tuple
+
+import torch
+from torch import Tensor
+
+from .. import ops
+
+NS_COEFFS: Tuple[Tuple[float, float, float], ...] = (
+    (4.0848, -6.8946, 2.9270),
+    (3.9505, -6.3029, 2.6377),
+    (3.7418, -5.5913, 2.3037),
+    (2.8769, -3.1427, 1.2046),
+    (2.8366, -3.0525, 1.2012),
+)
+
+
+def newton_schulz_torch(G: Tensor, epsilon: float = 1e-7,
+                        coeffs: Sequence[Tuple[float, float, float]] = NS_COEFFS) -> Tensor:
+    """Plain PyTorch statement of the iteration (bf16 matmuls); the numerical reference."""
+    X = G.to(torch.bfloat16)
+    tall = G.size(-2) > G.size(-1)
+    if tall:
+        X = X.mT
+    X = X / (X.norm(dim=(-2, -1), keepdim=True) + epsilon)
+    for a, b, c in coeffs:
+        A = X @ X.mT
+        B = b * A + c * (A @ A)
+        X = a * X + B @ X
+    if tall:
+        X = X.mT
+    return X
+
+
+def newton_schulz(G: Tensor, epsilon: float = 1e-7, coeffs: Sequence[Tuple[float, float, float]] = NS_COEFFS,
+                  sumsq: Optional[Tensor] = None) -> Tensor:
+    """Orthogonalise ``G`` (``[m, n]`` or a batch ``[B, m, n]``); returns bf16 of the same shape.
+
+    ``sumsq`` (fp32 ``[B]``), when given, is the squared Frobenius norm of every matrix,
+    e.g. accumulated by the momentum kernel, so that no extra pass over G is needed."""
+    if not G.is_cuda:
+        return newton_schulz_torch(G, float(epsilon), coeffs)
+    squeeze = G.dim() == 2
+    X = G.unsqueeze(0) if squeeze else G
+    if X.dim() != 3:
+        X = X.flatten(end_dim=-3)
+    X = X.to(torch.bfloat16)
+    if not X.is_contiguous():
+        X = X.contiguous()
+    if sumsq is None:
+        sumsq = X.float().square().sum(dim=(-2, -1))
+    scale = (1.0 / (sumsq.float().sqrt() + float(epsilon))).view(-1, 1, 1)
+    X = (X.float() * scale).to(torch.bfloat16)
+    Bn, m, n = X.shape
+    tall = m > n
+    k = n if tall else m
+    A = torch.empty(Bn, k, k, device=X.device, dtype=torch.bfloat16)
+    Bm = torch.empty_like(A)
+    Y = torch.empty_like(X)
+    for a, b, c in coeffs:
+        if tall:
+            ops.gemm(X.transpose(1, 2), X, out=A, symmetric=True)        # A = X^T X
+            ops.gemm(A, A.transpose(1, 2), c=A, out=Bm, alpha=c, beta=b, symmetric=True)  # b A + c A A
+            ops.gemm(X, Bm, c=X, out=Y, alpha=1.0, beta=a)                # a X + X B
+        else:
+            ops.gemm(X, X.transpose(1, 2), out=A, symmetric=True)        # A = X X^T
+            ops.gemm(A, A.transpose(1, 2), c=A, out=Bm, alpha=c, beta=b, symmetric=True)
+            ops.gemm(Bm, X, c=X, out=Y, alpha=1.0, beta=a)                # a X + B X
+        X, Y = Y, X
+    out = X[0] if squeeze else X
+    return out.view(G.shape)
+
+
+def zeropower_via_newtonschulz5(G: Tensor, epsilon: float = 1e-7) -> Tensor:
+    """Name-compatible entry point (dion/muon.py:620)."""
+    return newton_schulz(G, epsilon)

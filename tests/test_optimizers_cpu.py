@@ -1,0 +1,269 @@
+"""Optimizers on CPU against the reference implementations (state injected so that one
+step is comparable) and against their own contracts."""
+import copy
+
+import pytest
+import torch
+
+import dion_b200
+from dion_b200 import Dion, DionMixedPrecisionConfig, DionReference, DionSimple, Muon, MuonReference
+from dion_b200.optim.newton_schulz import newton_schulz_torch
+
+from _reference import load_reference
+
+ref = load_reference()
+needs_ref = pytest.mark.skipif(ref is None, reason="reference package not importable")
+
+SHAPES = [(64, 32), (32, 64), (48, 48), (64, 32), (96, 24)]
+
+
+def _params(shapes=SHAPES):
+    return [torch.nn.Parameter(torch.randn(s)) for s in shapes]
+
+
+def _clone(ps):
+    return [torch.nn.Parameter(p.detach().clone()) for p in ps]
+
+
+def _set_grads(a, b, scale=1.0):
+    for p, q in zip(a, b):
+        g = torch.randn_like(p) * scale
+        p.grad = g.clone()
+        q.grad = g.clone()
+
+
+def _inject_q(opt, opt_ref, P, Pr):
+    for g in opt.param_groups:
+        for p in g["params"]:
+            if g["algorithm"] == "dion":
+                opt._get_or_initialize_state(p, g)
+    for p, pr in zip(P, Pr):
+        if "Q" in opt.state[p]:
+            opt_ref.state[pr] = {"momentum": torch.zeros_like(pr), "Q": opt.state[p]["Q"].clone()}
+
+
+def test_public_names():
+    for name in ("Dion", "DionMixedPrecisionConfig", "DionSimple", "DionReference", "Muon", "MuonReference"):
+        assert hasattr(dion_b200, name)
+
+
+@needs_ref
+@pytest.mark.parametrize("rank_fraction", [1.0, 0.5, 0.25])
+def test_dion_matches_reference_qr(rank_fraction):
+    P = _params()
+    Pr = _clone(P)
+    opt = Dion(P, lr=0.02, rank_fraction=rank_fraction, weight_decay=0.1)
+    opt_ref = ref.DionReference(Pr, lr=0.02, rank_fraction=rank_fraction, weight_decay=0.1, qr_method="qr")
+    _inject_q(opt, opt_ref, P, Pr)
+    for _ in range(4):
+        _set_grads(P, Pr)
+        opt.step()
+        opt_ref.step()
+        for p, pr in zip(P, Pr):
+            torch.testing.assert_close(p, pr, rtol=1e-4, atol=1e-5)
+            torch.testing.assert_close(opt.state[p]["momentum"], opt_ref.state[pr]["momentum"], rtol=1e-4, atol=1e-4)
+            q, qr = opt.state[p]["Q"], opt_ref.state[pr]["Q"]
+            sign = torch.sign((q * qr).sum(0, keepdim=True))
+            torch.testing.assert_close(q * sign, qr, rtol=1e-3, atol=1e-4)
+
+
+@needs_ref
+def test_dion_matches_reference_async_dion_with_scalar_groups():
+    P = _params()
+    e = torch.nn.Parameter(torch.randn(100, 16))
+    h = torch.nn.Parameter(torch.randn(16, 100))
+    Pr, er, hr = _clone(P), _clone([e])[0], _clone([h])[0]
+    groups = lambda ps, a, b: [dict(params=ps), dict(params=[a], algorithm="lion", lr=0.01, weight_decay=0),
+                               dict(params=[b], algorithm="adamw", lr=0.003, betas=(0.95, 0.98))]
+    opt = Dion(groups(P, e, h), lr=0.02, rank_fraction=0.5)
+    opt_ref = ref.Dion(groups(Pr, er, hr), lr=0.02, rank_fraction=0.5)
+    _inject_q(opt, opt_ref, P, Pr)
+    for _ in range(3):
+        _set_grads(P + [e, h], Pr + [er, hr])
+        opt.step()
+        opt_ref.step()
+    for p, pr in zip(P + [e, h], Pr + [er, hr]):
+        torch.testing.assert_close(p, pr, rtol=1e-4, atol=2e-5)
+    # parameter-group keys and state keys are the reference's
+    assert set(opt.param_groups[0].keys()) == set(opt_ref.param_groups[0].keys())
+    assert set(opt.state[P[0]].keys()) == {"momentum", "Q"}
+    assert set(opt.state[e].keys()) == {"momentum"}
+    assert set(opt.state[h].keys()) == {"momentum", "variance"}
+    assert [g["step"] for g in opt.param_groups] == [3, 3, 3]
+
+
+@needs_ref
+@pytest.mark.parametrize("qr_method", ["qr", "cqr", "rcqr"])
+def test_dion_reference_matches_reference(qr_method):
+    P = _params()
+    Pr = _clone(P)
+    kw = dict(lr=0.02, rank_fraction=0.5, qr_method=qr_method, cqr_warmup_steps=1, power_iters=2)
+    opt = DionReference(P, **kw)
+    opt_ref = ref.DionReference(Pr, **kw)
+    _inject_q(opt, opt_ref, P, Pr)
+    for _ in range(3):
+        _set_grads(P, Pr)
+        opt.step()
+        opt_ref.step()
+    # the sketch is random, so rcqr agrees only up to the basis it spans; X and M are basis independent
+    for p, pr in zip(P, Pr):
+        torch.testing.assert_close(p, pr, rtol=2e-3, atol=2e-4)
+
+
+@needs_ref
+def test_dion_simple_matches_reference():
+    P = _params([(64, 32), (48, 48)])
+    Pr = _clone(P)
+    opt = DionSimple(P, lr=0.02, rank=16)
+    opt_ref = ref.DionSimple(Pr, lr=0.02, rank=16)
+    for g in opt.param_groups:
+        for p in g["params"]:
+            opt._init_state(p, opt.state[p], "dion")
+    for p, pr in zip(P, Pr):
+        opt_ref.state[pr] = {"momentum": torch.zeros_like(pr), "Q": opt.state[p]["Q"].clone()}
+    for _ in range(3):
+        _set_grads(P, Pr)
+        opt.step()
+        opt_ref.step()
+    for p, pr in zip(P, Pr):
+        torch.testing.assert_close(p, pr, rtol=1e-4, atol=1e-5)
+
+
+@needs_ref
+@pytest.mark.parametrize("nesterov", [False, True])
+@pytest.mark.parametrize("adjust_lr", ["spectral_norm", "rms_norm", "keller_muon", None])
+def test_muon_matches_reference(nesterov, adjust_lr):
+    P = _params()
+    Pr = _clone(P)
+    opt = Muon(P, lr=0.02, nesterov=nesterov, adjust_lr=adjust_lr)
+    opt_ref = ref.Muon(Pr, lr=0.02, nesterov=nesterov, adjust_lr=adjust_lr)
+    for _ in range(3):
+        _set_grads(P, Pr)
+        opt.step()
+        opt_ref.step()
+    for p, pr in zip(P, Pr):
+        # bf16 Newton-Schulz: compare updates at bf16 accuracy
+        assert (p - pr).abs().max() < 2e-3
+    assert set(opt.param_groups[0].keys()) == set(opt_ref.param_groups[0].keys())
+    assert set(opt.state[P[0]].keys()) == {"momentum"}
+
+
+@needs_ref
+def test_muon_reference_matches_reference():
+    P = _params([(64, 32), (32, 64)])
+    e = torch.nn.Parameter(torch.randn(50, 8))
+    Pr, er = _clone(P), _clone([e])[0]
+    mk = lambda ps, x: [dict(params=ps), dict(params=[x], algorithm="adamw", lr=0.01)]
+    opt = MuonReference(mk(P, e), lr=0.02)
+    opt_ref = ref.MuonReference(mk(Pr, er), lr=0.02)
+    for _ in range(3):
+        _set_grads(P + [e], Pr + [er])
+        opt.step()
+        opt_ref.step()
+    for p, pr in zip(P + [e], Pr + [er]):
+        assert (p - pr).abs().max() < 2e-3
+    assert set(opt.state[P[0]].keys()) == set(opt_ref.state[Pr[0]].keys())
+    assert set(opt.state[e].keys()) == set(opt_ref.state[er].keys())
+
+
+def test_dion_argument_validation():
+    p = _params([(8, 8)])
+    for bad in (dict(lr=-1), dict(mu=-1), dict(betas=(0.9,)), dict(weight_decay=-1), dict(rank_fraction=0),
+                dict(rank_fraction=1.5), dict(rank_multiple_of=0), dict(power_iters=2), dict(qr_method="qr")):
+        with pytest.raises(ValueError):
+            Dion(p, **bad)
+    with pytest.raises(TypeError):
+        Dion(p, replicate_mesh="mesh")
+    with pytest.raises(ValueError):
+        Muon(p, adjust_lr="bogus")
+    with pytest.raises(TypeError):
+        Muon(p, distributed_mesh=3)
+    opt = Dion([torch.nn.Parameter(torch.randn(4, 4, 4))])
+    opt.param_groups[0]["params"][0].grad = torch.randn(4, 4, 4)
+    with pytest.raises((NotImplementedError, ValueError)):
+        opt.step()
+
+
+def test_dion_rank_rounding_and_transposition():
+    p1 = torch.nn.Parameter(torch.randn(100, 40))
+    p2 = torch.nn.Parameter(torch.randn(40, 100))
+    opt = Dion([p1, p2], rank_fraction=0.3, rank_multiple_of=8)
+    for p in (p1, p2):
+        p.grad = torch.randn_like(p)
+    opt.step()
+    assert opt.state[p1]["Q"].shape == (40, 16)   # 0.3 * 40 = 12 -> 16; Q is (n, r) for tall
+    assert opt.state[p2]["Q"].shape == (40, 16)   # transposed: Q is (m, r)
+    assert opt._param_config[p2].is_transposed and not opt._param_config[p1].is_transposed
+
+
+def test_dion_zero_gradient_zero_lr_step_is_noop_on_weights():
+    """What distributed checkpoint loading does to create states: grads = 0, lr = 0, step()."""
+    P = _params()
+    before = [p.detach().clone() for p in P]
+    e = torch.nn.Parameter(torch.randn(10, 4))
+    opt = Dion([dict(params=P), dict(params=[e], algorithm="adamw")], lr=0.02, rank_fraction=0.5)
+    for g in opt.param_groups:
+        g["lr"] = 0.0
+    for p in P + [e]:
+        p.grad = torch.zeros_like(p)
+    opt.step()
+    for p, b in zip(P, before):
+        assert torch.equal(p, b)
+        st = opt.state[p]
+        assert torch.isfinite(st["Q"]).all() and torch.isfinite(st["momentum"]).all()
+        assert st["momentum"].abs().max() == 0
+    m = Muon(_params([(16, 8)]), lr=0.0)
+    q = m.param_groups[0]["params"][0]
+    q.grad = torch.zeros_like(q)
+    w = q.detach().clone()
+    m.step()
+    assert torch.equal(q, w)
+
+
+def test_dion_mixed_precision_state_dtypes_and_state_dict_roundtrip():
+    P = _params()
+    e = torch.nn.Parameter(torch.randn(10, 4))
+    cfg = DionMixedPrecisionConfig(momentum_dtype=torch.bfloat16, Q_dtype=torch.float32, variance_dtype=torch.bfloat16)
+    mk = lambda ps, x: Dion([dict(params=ps), dict(params=[x], algorithm="adamw")], lr=0.02, rank_fraction=0.5,
+                            mixed_precision_config=cfg)
+    opt = mk(P, e)
+    for _ in range(2):
+        for p in P + [e]:
+            p.grad = torch.randn_like(p)
+        opt.step()
+    assert opt.state[P[0]]["momentum"].dtype == torch.bfloat16
+    assert opt.state[P[0]]["Q"].dtype == torch.float32
+    assert opt.state[e]["variance"].dtype == torch.bfloat16
+    sd = copy.deepcopy(opt.state_dict())
+    P2, e2 = _clone(P), _clone([e])[0]
+    opt2 = mk(P2, e2)
+    opt2.load_state_dict(sd)
+    g = [torch.randn_like(p) for p in P + [e]]
+    for p, q, gg in zip(P + [e], P2 + [e2], g):
+        p.grad = gg.clone()
+        q.grad = gg.clone()
+    opt.step()
+    opt2.step()
+    for p, q in zip(P + [e], P2 + [e2]):
+        torch.testing.assert_close(p, q)
+
+
+def test_newton_schulz_orthogonalises():
+    G = torch.randn(3, 32, 64)
+    X = newton_schulz_torch(G).float()
+    s = torch.linalg.svdvals(X)
+    assert s.max() < 1.3 and s.min() > 0.5
+
+
+def test_muon_custom_newton_schulz_and_flatten():
+    calls = []
+
+    def ns(x, epsilon):
+        calls.append(tuple(x.shape))
+        return newton_schulz_torch(x, epsilon)
+
+    p = torch.nn.Parameter(torch.randn(4, 6, 5))
+    opt = Muon([p], lr=0.01, newton_schulz_func=ns, flatten=True)
+    p.grad = torch.randn_like(p)
+    opt.step()
+    assert calls and calls[0][-2:] == (4, 30)
