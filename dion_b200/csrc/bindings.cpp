@@ -8,9 +8,15 @@
 #include "gemm.h"
 #include "kernels.h"
 
+#include <atomic>
+
 namespace {
 
 using at::Tensor;
+
+// Number of kernel launches issued through this library (for benchmarks and tests).
+std::atomic<long long> g_launches{0};
+int64_t launch_count() { return (int64_t)g_launches.load(); }
 
 int gemm_dtype(const Tensor& t, const char* what) {
   if (t.scalar_type() == at::kBFloat16) return dion::kBF16;
@@ -124,6 +130,7 @@ void gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, Tens
   cudaError_t e = dion::gemm_launch(g, at::cuda::getCurrentCUDAStream());
   TORCH_CHECK(e == cudaSuccess, "dion_b200 gemm launch failed: ", cudaGetErrorString(e), " ",
               dion::gemm_last_error());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
 
@@ -176,6 +183,7 @@ void for_each_chunk(std::initializer_list<std::pair<int, at::TensorList>> lists,
   do {                                                                                  \
     cudaError_t _e = (expr);                                                            \
     TORCH_CHECK(_e == cudaSuccess, "dion_b200 kernel launch failed: ", cudaGetErrorString(_e)); \
+    g_launches.fetch_add(1, std::memory_order_relaxed);                                 \
   } while (0)
 
 void adamw_multi(at::TensorList X, at::TensorList G, at::TensorList M, at::TensorList V, at::TensorList shadow,
@@ -442,6 +450,7 @@ void chol_inverse(const Tensor& G, Tensor Z, Tensor work, Tensor info, double pi
                                             info.data_ptr<int>(), batch, r, G.stride(1), G.stride(0),
                                             (float)pivot_floor, at::cuda::getCurrentCUDAStream());
   TORCH_CHECK(e == cudaSuccess, "chol_inverse launch failed (rank ", r, "): ", cudaGetErrorString(e));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
 void col_sumsq(const Tensor& X, Tensor out) {
@@ -487,6 +496,7 @@ TORCH_LIBRARY(dion_b200, m) {
   m.def("embedding_bwd(Tensor dout, Tensor idx, Tensor(a!) dtable) -> ()");
   m.def("chol_inverse(Tensor G, Tensor(a!) Z, Tensor(b!) work, Tensor(c!) info, float pivot_floor) -> ()");
   m.def("col_sumsq(Tensor X, Tensor(a!) out) -> ()");
+  m.def("launch_count() -> int", &launch_count);
 }
 
 TORCH_LIBRARY_IMPL(dion_b200, CUDA, m) {

@@ -14,4 +14,4 @@ from .multi_tensor import (  # noqa: F401
     muon_apply,
     muon_momentum,
 )
-from .runtime import DionKernelError, check_status  # noqa: F401
+from .runtime import DionKernelError, check_status, launch_count  # noqa: F401

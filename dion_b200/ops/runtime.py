@@ -57,3 +57,10 @@ def check_status(device=None) -> None:
     if code != 0:
         t.zero_()
         raise DionKernelError(f"dion_b200 kernel failure on cuda:{idx}: {_STATUS_NAMES.get(code, code)}")
+
+
+def launch_count() -> int:
+    """Kernel launches issued by this library in this process so far."""
+    if not _ext.load(required=False):
+        return 0
+    return int(torch.ops.dion_b200.launch_count())
