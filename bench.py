@@ -146,7 +146,7 @@ def emit(args, world, tokens_per_step, dev_ms, e2e_ms, clocks, extra):
             "h2d_bytes_per_step": extra.get("h2d_bytes_per_step"),
             "d2h_bytes_per_step": extra.get("d2h_bytes_per_step"),
         }
-    for k in ("gpu_launches", "optimizer_ms", "fwd_bwd_ms", "peak_mem_mib"):
+    for k in ("gpu_launches", "optimizer_ms", "fwd_bwd_ms", "peak_mem_mib", "reference_mode"):
         if k in extra:
             line[k] = extra[k]
     print(json.dumps(line), flush=True)
@@ -201,11 +201,22 @@ def run_ours(args):
     sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
+    marks = []
     for x, y in staged:
         loss = step_fn([(x, y)])
+        if os.environ.get("DION_BENCH_TRACE"):
+            m = torch.cuda.Event(enable_timing=True)
+            m.record()
+            marks.append(m)
     ev1.record()
     barrier_sync()
     clocks = sampler.stop()
+    if marks and rank == 0:
+        prev, per_step = ev0, []
+        for m in marks:
+            per_step.append(round(prev.elapsed_time(m), 2))
+            prev = m
+        print(f"[bench] per-step device ms: {per_step}", file=sys.stderr, flush=True)
     dev_ms = max_over_ranks(ev0.elapsed_time(ev1) / args.steps)
     launches = (ops.launch_count() - launches0) // max(args.steps, 1)
     phases = timers.max_over_ranks()
@@ -242,6 +253,10 @@ def run_reference(args):
     if not os.path.isdir(os.path.join(ref_dir, "dion")) or not os.path.isdir(os.path.join(ref_dir, "models")):
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed on this machine"}))
         return
+    # Inductor compiles small host-side C++ kernels with OpenMP; the first g++ on PATH of
+    # some images lacks libgomp.spec, the distribution compiler has it.
+    if "CXX" not in os.environ and os.path.exists("/usr/bin/g++"):
+        os.environ["CXX"] = "/usr/bin/g++"
     import torch
     import torch.distributed as dist
 
@@ -263,59 +278,81 @@ def run_reference(args):
 
     from dion_b200.utils.clocks import ClockSampler
 
-    torch.manual_seed(1234)
     torch._dynamo.config.cache_size_limit = 100
-    cfg = RefCfg(sequence_len=MODEL["sequence_length"], vocab_size=MODEL["vocab_size"], n_layer=args.layers,
-                 n_head=MODEL["n_head"], n_embd=MODEL["model_dim"])
-    with torch.device("meta"):
-        model = RefGPT(cfg)
-    model.to_empty(device="cuda")
-    model.init_weights()
-    model.compile()
-    raw = model
-    model = DDP(model, device_ids=[local])
-    groups = [
-        dict(params=list(raw.transformer.h.parameters())),
-        dict(params=list(raw.transformer.wte.parameters()), algorithm=HP["scalar_opt"], lr=HP["lr"],
-             betas=(0.95, 0.98), weight_decay=0),
-        dict(params=list(raw.lm_head.parameters()), algorithm=HP["scalar_opt"],
-             lr=HP["lr"] / math.sqrt(MODEL["model_dim"]), betas=(0.95, 0.98), weight_decay=0),
-    ]
-    sync_in_opt = True  # replicate_mesh_grad_sync: true in configs/dion_160m.yaml
-    if args.optimizer == "dion":
-        mp = None if args.fp32_states else RefMP(momentum_dtype=torch.bfloat16, variance_dtype=torch.bfloat16,
-                                                 Q_dtype=torch.bfloat16)
-        opt = RefDion(groups, replicate_mesh=model.process_group, replicate_mesh_grad_sync=sync_in_opt,
-                      rank_fraction=HP["rank_fraction"], lr=HP["lr"], mu=HP["mu"], weight_decay=HP["weight_decay"],
-                      mixed_precision_config=mp)
-    else:
-        sync_in_opt = False
-        opt = RefMuon(groups, distributed_mesh=model.process_group, lr=HP["lr"], mu=HP["mu"],
-                      weight_decay=HP["weight_decay"], nesterov=True, adjust_lr="spectral_norm", use_triton=True)
+    autocast = torch.amp.autocast(device_type="cuda", dtype=torch.bfloat16)
+
+    def build(compiled: bool):
+        """Model, optimizer and step function exactly as the reference trainer sets them up
+        (train.py:674-737, 886-921); `compiled=False` is its --no_compile mode with dynamo off."""
+        torch.manual_seed(1234)
+        cfg = RefCfg(sequence_len=MODEL["sequence_length"], vocab_size=MODEL["vocab_size"], n_layer=args.layers,
+                     n_head=MODEL["n_head"], n_embd=MODEL["model_dim"])
+        with torch.device("meta"):
+            raw = RefGPT(cfg)
+        raw.to_empty(device="cuda")
+        raw.init_weights()
+        if compiled:
+            raw.compile()
+        model = DDP(raw, device_ids=[local])
+        groups = [
+            dict(params=list(raw.transformer.h.parameters())),
+            dict(params=list(raw.transformer.wte.parameters()), algorithm=HP["scalar_opt"], lr=HP["lr"],
+                 betas=(0.95, 0.98), weight_decay=0),
+            dict(params=list(raw.lm_head.parameters()), algorithm=HP["scalar_opt"],
+                 lr=HP["lr"] / math.sqrt(MODEL["model_dim"]), betas=(0.95, 0.98), weight_decay=0),
+        ]
+        sync_in_opt = args.optimizer == "dion"  # replicate_mesh_grad_sync: true in configs/dion_160m.yaml
+        if args.optimizer == "dion":
+            mp = None if args.fp32_states else RefMP(momentum_dtype=torch.bfloat16, variance_dtype=torch.bfloat16,
+                                                     Q_dtype=torch.bfloat16)
+            opt = RefDion(groups, replicate_mesh=model.process_group, replicate_mesh_grad_sync=True,
+                          rank_fraction=HP["rank_fraction"], lr=HP["lr"], mu=HP["mu"],
+                          weight_decay=HP["weight_decay"], mixed_precision_config=mp)
+        else:
+            opt = RefMuon(groups, distributed_mesh=model.process_group, lr=HP["lr"], mu=HP["mu"],
+                          weight_decay=HP["weight_decay"], nesterov=True, adjust_lr="spectral_norm",
+                          use_triton=compiled)
+
+        def step(x, y):
+            model.train()
+            with autocast:
+                loss = model(x, y)
+            out = loss.detach()
+            if sync_in_opt:
+                with model.no_sync():
+                    loss.backward()
+            else:
+                loss.backward()
+            opt.step()
+            model.zero_grad(set_to_none=True)
+            return out
+
+        return step
 
     tokens_per_step = args.device_batch * MODEL["sequence_length"] * world
     total_steps = args.warmup + 2 * args.steps + 2
     data_dir = make_data(args, rank, world, total_steps)
     loader = RefLoader(os.path.join(data_dir, "fineweb_train_*.bin"), args.device_batch, MODEL["sequence_length"],
                        rank, world)
-    autocast = torch.amp.autocast(device_type="cuda", dtype=torch.bfloat16)
+    mode = "torch.compile (reference default)"
+    step = build(compiled=True)
+    first = loader.next_batch()
+    try:
+        loss = step(*first)
+        float(loss.item())
+    except Exception as e:  # the compiler stack is unusable on this machine: run the reference eagerly
+        msg = f"{type(e).__name__}: {str(e).splitlines()[-1] if str(e) else ''}"[:200]
+        import traceback
 
-    def step(x, y):
-        # loop body of the reference trainer (train.py:886-921) without logging
-        model.train()
-        with autocast:
-            loss = model(x, y)
-        out = loss.detach()
-        if sync_in_opt:
-            with model.no_sync():
-                loss.backward()
-        else:
-            loss.backward()
-        opt.step()
-        model.zero_grad(set_to_none=True)
-        return out
-
-    for _ in range(args.warmup):
+        print(f"[bench] torch.compile path failed ({msg}); running the reference with --no_compile semantics",
+              file=sys.stderr, flush=True)
+        print("".join(traceback.format_exception(e))[-6000:], file=sys.stderr, flush=True)
+        torch._dynamo.reset()
+        torch._dynamo.config.disable = True
+        mode = f"eager, dynamo disabled (torch.compile failed here: {msg})"
+        step = build(compiled=False)
+        loss = step(*first)
+    for _ in range(max(args.warmup - 1, 0)):
         loss = step(*loader.next_batch())
     float(loss.item())
     staged = [loader.next_batch() for _ in range(args.steps)]
@@ -340,7 +377,7 @@ def run_reference(args):
         barrier_sync()
         e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1000.0 / args.steps)
     extra = {"h2d_bytes_per_step": 2 * args.device_batch * MODEL["sequence_length"] * 8, "d2h_bytes_per_step": 4,
-             "peak_mem_mib": torch.cuda.max_memory_allocated() // (1 << 20)}
+             "peak_mem_mib": torch.cuda.max_memory_allocated() // (1 << 20), "reference_mode": mode}
     if rank == 0:
         emit(args, world, tokens_per_step, dev_ms, e2e_ms, clocks, extra)
     dist.destroy_process_group()

@@ -462,9 +462,64 @@ void col_sumsq(const Tensor& X, Tensor out) {
                                          at::cuda::getCurrentCUDAStream()));
 }
 
+// ----------------------------------------------------------------------------- symmetric-memory collectives
+
+dion::PeerTable peer_table(at::IntArrayRef peers) {
+  TORCH_CHECK(!peers.empty() && (int)peers.size() <= dion::kMaxPeers, "between 1 and ", dion::kMaxPeers,
+              " peers are supported, got ", peers.size());
+  dion::PeerTable t;
+  memset(&t, 0, sizeof(t));
+  for (size_t i = 0; i < peers.size(); ++i) t.ptrs[i] = reinterpret_cast<void*>(peers[i]);
+  return t;
+}
+
+// `anchor` is any tensor on the device the kernel runs on (it selects the CUDA backend and stream).
+void symm_barrier(const Tensor& anchor, at::IntArrayRef peers, int64_t flag_off, int64_t channel, int64_t rank,
+                  int64_t epoch, Tensor status) {
+  const c10::cuda::CUDAGuard guard(anchor.device());
+  DION_CUDA_CHECK(dion::symm_barrier_launch(peer_table(peers), flag_off, (int)channel, (int)rank, (int)peers.size(),
+                                            (unsigned)epoch, status.data_ptr<int>(),
+                                            at::cuda::getCurrentCUDAStream()));
+}
+
+// In-place all-reduce of `buf`, a view into this rank's arena at byte offset `data_off`.
+void symm_all_reduce(Tensor buf, at::IntArrayRef peers, int64_t flag_off, int64_t data_off, int64_t mc_base,
+                     double scale, int64_t rank, int64_t epoch, Tensor counter, Tensor status) {
+  const c10::cuda::CUDAGuard guard(buf.device());
+  TORCH_CHECK(buf.is_contiguous(), "symm_all_reduce needs a contiguous arena view");
+  TORCH_CHECK(reinterpret_cast<int64_t>(buf.data_ptr()) == peers[rank] + data_off,
+              "buffer is not at the stated offset of this rank's arena");
+  DION_CUDA_CHECK(dion::symm_all_reduce_launch(peer_table(peers), flag_off, data_off,
+                                               reinterpret_cast<void*>(mc_base), elem_type(buf, "buf"), buf.numel(),
+                                               (float)scale, (int)rank, (int)peers.size(), (unsigned)epoch,
+                                               reinterpret_cast<unsigned*>(counter.data_ptr<int>()),
+                                               status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()));
+}
+
+// dst = beta * dst + scale * sum over ranks of `src` (arena view at `data_off`)
+void symm_reduce_into(const Tensor& src, Tensor dst, at::IntArrayRef peers, int64_t flag_off, int64_t data_off,
+                      double scale, double beta, int64_t rank, int64_t epoch, Tensor counter, Tensor status) {
+  const c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.is_contiguous() && dst.is_contiguous() && src.numel() == dst.numel());
+  TORCH_CHECK(reinterpret_cast<int64_t>(src.data_ptr()) == peers[rank] + data_off,
+              "source is not at the stated offset of this rank's arena");
+  DION_CUDA_CHECK(dion::symm_reduce_into_launch(peer_table(peers), flag_off, data_off, elem_type(src, "src"),
+                                                dst.data_ptr(), elem_type(dst, "dst"), src.numel(), (float)scale,
+                                                (float)beta, (int)rank, (int)peers.size(), (unsigned)epoch,
+                                                reinterpret_cast<unsigned*>(counter.data_ptr<int>()),
+                                                status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()));
+}
+
 }  // namespace
 
 TORCH_LIBRARY(dion_b200, m) {
+  m.def("symm_barrier(Tensor anchor, int[] peers, int flag_off, int channel, int rank, int epoch, Tensor(a!) status) -> ()");
+  m.def(
+      "symm_all_reduce(Tensor(a!) buf, int[] peers, int flag_off, int data_off, int mc_base, float scale, int rank, "
+      "int epoch, Tensor(b!) counter, Tensor(c!) status) -> ()");
+  m.def(
+      "symm_reduce_into(Tensor src, Tensor(a!) dst, int[] peers, int flag_off, int data_off, float scale, float beta, "
+      "int rank, int epoch, Tensor(b!) counter, Tensor(c!) status) -> ()");
   m.def(
       "gemm(Tensor a, Tensor b, Tensor? c, Tensor(a!) d, Tensor(b!)? d2, Tensor? c_ptrs, Tensor? d_ptrs, "
       "Tensor? d2_ptrs, float alpha, float beta, int act, int epilogue, int split_k, bool symmetric, "
@@ -512,6 +567,9 @@ TORCH_LIBRARY_IMPL(dion_b200, CUDA, m) {
   m.impl("embedding_bwd", &embedding_bwd);
   m.impl("chol_inverse", &chol_inverse);
   m.impl("col_sumsq", &col_sumsq);
+  m.impl("symm_barrier", &symm_barrier);
+  m.impl("symm_all_reduce", &symm_all_reduce);
+  m.impl("symm_reduce_into", &symm_reduce_into);
 }
 
 // Ops whose arguments are tensor lists have no dispatch key to select on when a list

@@ -1,0 +1,344 @@
+// Collectives written as kernels over symmetric memory (same-offset buffers on every
+// GPU of a group, reachable through NVLink peer pointers and, when the group has an
+// NVSwitch multicast object, through one multicast address).
+//
+//   barrier           - release/acquire flags in every peer's flag block, bounded spin
+//   all_reduce        - in place: every rank reduces one slice (peer loads in rank order,
+//                       or multimem.ld_reduce in the switch) and writes it to every peer
+//                       (peer stores or multimem.st); results are bit-identical everywhere
+//   reduce_into       - one shot: dst (+)= scale * sum_p src_p, every rank reads all peers
+//
+// These stand in for the NCCL all-reduce / reduce-scatter / all-gather calls the reference
+// issues through funcol and DTensor redistribute around its power iteration
+// (dion/dion.py:806-844, 925-960, 1076-1110, 1165-1197).
+//
+// Every wait is bounded (kWaitBudgetNs); a wait that gives up sets the status word and the
+// kernel finishes normally.  Nothing here uses TMA or cluster multicast.
+#include <cuda_bf16.h>
+
+#include "kernels.h"
+#include "umma.cuh"
+
+namespace dion {
+
+namespace {
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Flag block layout (unsigned words): flags[channel * kMaxPeers + source_rank].
+// `signal`: tell every peer that this rank reached `epoch` on `channel`.
+__device__ __forceinline__ void signal_peers(const PeerTable& t, long long flag_off, int channel, int rank, int world,
+                                             unsigned epoch, int lane) {
+  if (lane < world) {
+    unsigned* f = reinterpret_cast<unsigned*>(reinterpret_cast<char*>(t.ptrs[lane]) + flag_off);
+    st_release_sys(f + channel * kMaxPeers + rank, epoch);
+  }
+}
+// `wait`: until every source rank reached `epoch` on `channel` in this rank's flag block.
+// Returns false on timeout.  Epochs only grow, so ">= epoch" also accepts a later one.
+__device__ __forceinline__ bool wait_peers(const PeerTable& t, long long flag_off, int channel, int rank, int world,
+                                           unsigned epoch, int lane) {
+  bool ok = true;
+  if (lane < world) {
+    const unsigned* f = reinterpret_cast<const unsigned*>(reinterpret_cast<const char*>(t.ptrs[rank]) + flag_off) +
+                        channel * kMaxPeers + lane;
+    const unsigned long long t0 = global_timer_ns();
+    while ((int)(ld_acquire_sys(f) - epoch) < 0) {
+      if (global_timer_ns() - t0 > kWaitBudgetNs) {
+        ok = false;
+        break;
+      }
+    }
+  }
+  return ok;
+}
+
+__global__ void barrier_kernel(PeerTable t, long long flag_off, int channel, int rank, int world, unsigned epoch,
+                               int* status) {
+  const int lane = threadIdx.x;
+  __threadfence_system();
+  signal_peers(t, flag_off, channel, rank, world, epoch, lane);
+  if (!wait_peers(t, flag_off, channel, rank, world, epoch, lane) && status) atomicCAS(status, 0, kStatusPeerTimeout);
+}
+
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+
+template <typename T>
+struct Vec16;
+template <>
+struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float (&f)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&f)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  }
+  // sum over the multicast group, performed by the switch
+  static __device__ __forceinline__ void mc_load_reduce(const float* p, float (&f)[4]) {
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(f[0]), "=f"(f[1]), "=f"(f[2]), "=f"(f[3])
+                 : "l"(p)
+                 : "memory");
+  }
+  static __device__ __forceinline__ void mc_store(float* p, const float (&f)[4]) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(f[0]), "f"(f[1]),
+                 "f"(f[2]), "f"(f[3])
+                 : "memory");
+  }
+};
+template <>
+struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&f)[8]) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 v = __bfloat1622float2(h[j]);
+      f[2 * j] = v.x;
+      f[2 * j + 1] = v.y;
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&f)[8]) {
+    uint4 q;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+    *reinterpret_cast<uint4*>(p) = q;
+  }
+  static __device__ __forceinline__ void mc_load_reduce(const __nv_bfloat16* p, float (&f)[8]) {
+    uint4 q;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w)
+                 : "l"(p)
+                 : "memory");
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 v = __bfloat1622float2(h[j]);
+      f[2 * j] = v.x;
+      f[2 * j + 1] = v.y;
+    }
+  }
+  static __device__ __forceinline__ void mc_store(__nv_bfloat16* p, const float (&f)[8]) {
+    uint4 q;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(q.x), "r"(q.y),
+                 "r"(q.z), "r"(q.w)
+                 : "memory");
+  }
+};
+
+// In-place all-reduce of `numel` elements at byte offset `data_off` of every peer's arena.
+// Phase 0: all ranks' inputs are complete (flags, channel 0).
+// Phase 1: rank r reduces elements [r * slice, (r + 1) * slice) and writes the result to
+//          all peers.  Phase 2: all slices are written (flags, channel 1), after which the
+//          kernel retires, so stream order hands complete data to the next kernel.
+template <typename T, bool kMulticast>
+__global__ void __launch_bounds__(512) all_reduce_kernel(PeerTable t, long long flag_off, long long data_off,
+                                                        char* mc_base, long long numel, float scale, int rank,
+                                                        int world, unsigned epoch, unsigned* done_counter,
+                                                        int* status) {
+  using V = Vec16<T>;
+  constexpr int N = V::N;
+  __shared__ int ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      signal_peers(t, flag_off, 0, rank, world, epoch, threadIdx.x);
+    }
+    if (!wait_peers(t, flag_off, 0, rank, world, epoch, threadIdx.x)) {
+      ok_flag = 0;
+      if (status) atomicCAS(status, 0, kStatusPeerTimeout);
+    }
+  }
+  __syncthreads();
+  if (ok_flag) {
+    // slice boundaries in vectors, the last rank also takes the remainder
+    const long long nvec = numel / N;
+    const long long per = (nvec + world - 1) / world;
+    const long long v0 = per * rank;
+    const long long v1 = min(v0 + per, nvec);
+    for (long long v = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; v < v1;
+         v += (long long)gridDim.x * blockDim.x) {
+      float acc[N];
+      if (kMulticast) {
+        V::mc_load_reduce(reinterpret_cast<const T*>(mc_base + data_off) + v * N, acc);
+      } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[j] = 0.f;
+        for (int p = 0; p < world; ++p) {
+          float f[N];
+          V::load(reinterpret_cast<const T*>(reinterpret_cast<const char*>(t.ptrs[p]) + data_off) + v * N, f);
+#pragma unroll
+          for (int j = 0; j < N; ++j) acc[j] += f[j];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < N; ++j) acc[j] *= scale;
+      if (kMulticast) {
+        V::mc_store(reinterpret_cast<T*>(mc_base + data_off) + v * N, acc);
+      } else {
+        for (int p = 0; p < world; ++p)
+          V::store(reinterpret_cast<T*>(reinterpret_cast<char*>(t.ptrs[p]) + data_off) + v * N, acc);
+      }
+    }
+    // scalar tail (numel not a multiple of the vector width): rank 0 handles it with peer accesses
+    if (rank == 0 && blockIdx.x == 0) {
+      for (long long i = nvec * N + threadIdx.x; i < numel; i += blockDim.x) {
+        float a = 0.f;
+        for (int p = 0; p < world; ++p)
+          a += to_f(reinterpret_cast<const T*>(reinterpret_cast<const char*>(t.ptrs[p]) + data_off)[i]);
+        a *= scale;
+        for (int p = 0; p < world; ++p)
+          reinterpret_cast<T*>(reinterpret_cast<char*>(t.ptrs[p]) + data_off)[i] = from_f<T>(a);
+      }
+    }
+  }
+  // the last CTA of this rank to finish announces it and waits for the other ranks
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int is_last;
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(done_counter, 1u);
+    is_last = (prev == gridDim.x - 1);
+    if (is_last) *done_counter = 0;  // ready for the next launch on this stream
+  }
+  __syncthreads();
+  if (is_last && threadIdx.x < 32) {
+    __threadfence_system();
+    signal_peers(t, flag_off, 1, rank, world, epoch, threadIdx.x);
+    if (!wait_peers(t, flag_off, 1, rank, world, epoch, threadIdx.x) && status)
+      atomicCAS(status, 0, kStatusPeerTimeout);
+  }
+}
+
+// dst[i] = beta * dst[i] + scale * sum_p src_p[i]; src at `data_off` of every peer's arena,
+// dst an ordinary local fp32 / bf16 buffer.  Channel 2 says "inputs complete", channel 3
+// "this rank finished reading", so the sources may be overwritten once the kernel retired.
+template <typename T, typename D>
+__global__ void __launch_bounds__(512) reduce_into_kernel(PeerTable t, long long flag_off, long long data_off,
+                                                         D* __restrict__ dst, long long numel, float scale,
+                                                         float beta, int rank, int world, unsigned epoch,
+                                                         unsigned* done_counter, int* status) {
+  __shared__ int ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      signal_peers(t, flag_off, 2, rank, world, epoch, threadIdx.x);
+    }
+    if (!wait_peers(t, flag_off, 2, rank, world, epoch, threadIdx.x)) {
+      ok_flag = 0;
+      if (status) atomicCAS(status, 0, kStatusPeerTimeout);
+    }
+  }
+  __syncthreads();
+  if (ok_flag) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < numel;
+         i += (long long)gridDim.x * blockDim.x) {
+      float a = 0.f;
+      for (int p = 0; p < world; ++p)
+        a += to_f(reinterpret_cast<const T*>(reinterpret_cast<const char*>(t.ptrs[p]) + data_off)[i]);
+      a *= scale;
+      if (beta != 0.f) a += beta * to_f(dst[i]);
+      dst[i] = from_f<D>(a);
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int is_last;
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(done_counter, 1u);
+    is_last = (prev == gridDim.x - 1);
+    if (is_last) *done_counter = 0;
+  }
+  __syncthreads();
+  if (is_last && threadIdx.x < 32) {
+    signal_peers(t, flag_off, 3, rank, world, epoch, threadIdx.x);
+    if (!wait_peers(t, flag_off, 3, rank, world, epoch, threadIdx.x) && status)
+      atomicCAS(status, 0, kStatusPeerTimeout);
+  }
+}
+
+int comm_grid(long long work_items, int threads) {
+  long long g = (work_items + threads - 1) / threads;
+  if (g < 1) g = 1;
+  if (g > 64) g = 64;  // a few dozen CTAs saturate NVLink; the rest of the GPU stays free for compute
+  return (int)g;
+}
+
+}  // namespace
+
+cudaError_t symm_barrier_launch(const PeerTable& t, long long flag_off, int channel, int rank, int world,
+                                unsigned epoch, int* status, cudaStream_t s) {
+  if (world > kMaxPeers) return cudaErrorInvalidValue;
+  barrier_kernel<<<1, 32, 0, s>>>(t, flag_off, channel, rank, world, epoch, status);
+  return cudaGetLastError();
+}
+
+cudaError_t symm_all_reduce_launch(const PeerTable& t, long long flag_off, long long data_off, void* mc_base,
+                                   int elem_type, long long numel, float scale, int rank, int world, unsigned epoch,
+                                   unsigned* done_counter, int* status, cudaStream_t s) {
+  if (world > kMaxPeers || (data_off & 15)) return cudaErrorInvalidValue;
+  const int threads = 512;
+  const int vecn = elem_type == kElemF32 ? 4 : 8;
+  const int grid = comm_grid((numel / vecn + world - 1) / world, threads);
+  char* mc = reinterpret_cast<char*>(mc_base);
+  if (elem_type == kElemF32) {
+    if (mc)
+      all_reduce_kernel<float, true><<<grid, threads, 0, s>>>(t, flag_off, data_off, mc, numel, scale, rank, world,
+                                                             epoch, done_counter, status);
+    else
+      all_reduce_kernel<float, false><<<grid, threads, 0, s>>>(t, flag_off, data_off, mc, numel, scale, rank, world,
+                                                              epoch, done_counter, status);
+  } else {
+    if (mc)
+      all_reduce_kernel<__nv_bfloat16, true><<<grid, threads, 0, s>>>(t, flag_off, data_off, mc, numel, scale, rank,
+                                                                     world, epoch, done_counter, status);
+    else
+      all_reduce_kernel<__nv_bfloat16, false><<<grid, threads, 0, s>>>(t, flag_off, data_off, mc, numel, scale,
+                                                                      rank, world, epoch, done_counter, status);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t symm_reduce_into_launch(const PeerTable& t, long long flag_off, long long data_off, int src_type,
+                                    void* dst, int dst_type, long long numel, float scale, float beta, int rank,
+                                    int world, unsigned epoch, unsigned* done_counter, int* status, cudaStream_t s) {
+  if (world > kMaxPeers) return cudaErrorInvalidValue;
+  const int threads = 512;
+  const int grid = comm_grid(numel, threads);
+#define DION_RI(T, D)                                                                                            \
+  reduce_into_kernel<T, D><<<grid, threads, 0, s>>>(t, flag_off, data_off, reinterpret_cast<D*>(dst), numel, scale, \
+                                                    beta, rank, world, epoch, done_counter, status)
+  if (src_type == kElemF32 && dst_type == kElemF32) DION_RI(float, float);
+  else if (src_type == kElemF32 && dst_type == kElemBF16) DION_RI(float, __nv_bfloat16);
+  else if (src_type == kElemBF16 && dst_type == kElemF32) DION_RI(__nv_bfloat16, float);
+  else DION_RI(__nv_bfloat16, __nv_bfloat16);
+#undef DION_RI
+  return cudaGetLastError();
+}
+
+}  // namespace dion

@@ -102,4 +102,27 @@ cudaError_t chol_inverse_launch(const float* G, float* Rinv, float* work, int* i
 cudaError_t col_sumsq_launch(const void* X, int x_type, float* out, int batch, long long rows, int cols,
                              long long ldx, long long batch_stride, cudaStream_t s);
 
+// ---------------------------------------------------------------------------
+// Collectives over symmetric memory (one arena per process group; the same offset names
+// the same logical buffer on every rank).  `PeerTable` holds the arena base address of
+// every rank as seen from this GPU; `flag_off` is the byte offset of the arena's flag
+// block (4 channels x kMaxPeers unsigned words, zeroed at creation); epochs grow by one
+// per collective on a channel.
+// ---------------------------------------------------------------------------
+constexpr int kMaxPeers = 8;
+struct PeerTable {
+  void* ptrs[kMaxPeers];
+};
+cudaError_t symm_barrier_launch(const PeerTable& t, long long flag_off, int channel, int rank, int world,
+                                unsigned epoch, int* status, cudaStream_t s);
+// In-place sum (times `scale`) over all ranks of `numel` elements at `data_off`; `mc_base`
+// is the multicast address of the arena or null for plain peer loads and stores.
+cudaError_t symm_all_reduce_launch(const PeerTable& t, long long flag_off, long long data_off, void* mc_base,
+                                   int elem_type, long long numel, float scale, int rank, int world, unsigned epoch,
+                                   unsigned* done_counter, int* status, cudaStream_t s);
+// dst = beta * dst + scale * sum over ranks of the buffer at `data_off`; dst is local memory.
+cudaError_t symm_reduce_into_launch(const PeerTable& t, long long flag_off, long long data_off, int src_type,
+                                    void* dst, int dst_type, long long numel, float scale, float beta, int rank,
+                                    int world, unsigned epoch, unsigned* done_counter, int* status, cudaStream_t s);
+
 }  // namespace dion

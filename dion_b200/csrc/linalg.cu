@@ -22,7 +22,7 @@ namespace dion {
 
 namespace {
 
-constexpr int kCholThreads = 256;
+constexpr int kCholThreads = 1024;  // four 256-thread groups, each updating its own 64 x 64 tile
 
 // out[row0 + i][col0 + j] -= sum_a At[a][i] * Bt[a][j]   for a 64 x 64 tile; each of the
 // 256 threads owns a 4 x 4 sub-tile.  At / Bt are shared-memory arrays indexed [a][.]
@@ -31,8 +31,18 @@ template <int NB>
 __device__ __forceinline__ void tile_update(float* __restrict__ out, long long ld, int row0, int col0,
                                             const float* __restrict__ At, int a_stride,
                                             const float* __restrict__ Bt, int b_stride, int row_end, int col_end) {
-  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;
+  const int t = threadIdx.x & 255;
+  const int ty = t >> 4, tx = t & 15;
   const int i0 = ty * 4, j0 = tx * 4;
+  const bool vec = (col0 + j0 + 3 < col_end) && ((ld & 3) == 0);
+  // fetch the output tile first so that its latency hides behind the multiply loop
+  float4 cur[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = row0 + i0 + i;
+    cur[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < row_end && vec) cur[i] = *reinterpret_cast<const float4*>(out + (long long)r * ld + col0 + j0);
+  }
   float acc[4][4];
 #pragma unroll
   for (int i = 0; i < 4; ++i)
@@ -54,8 +64,8 @@ __device__ __forceinline__ void tile_update(float* __restrict__ out, long long l
     const int r = row0 + i0 + i;
     if (r >= row_end) continue;
     float* o = out + (long long)r * ld + col0 + j0;
-    if (col0 + j0 + 3 < col_end && ((ld & 3) == 0)) {
-      float4 v = *reinterpret_cast<float4*>(o);
+    if (vec) {
+      float4 v = cur[i];
       v.x -= acc[i][0];
       v.y -= acc[i][1];
       v.z -= acc[i][2];
@@ -190,16 +200,26 @@ chol_inverse_kernel(const float* __restrict__ Gall, float* __restrict__ Zall, fl
     __syncthreads();
     if (tr <= 0) break;
 
-    // ---- 4. trailing updates with 64 x 64 tiles
+    // ---- 4. trailing updates with 64 x 64 tiles, one tile per 256-thread group at a time:
+    //         first the lower-triangular tiles of the Gram part, then the right-hand side
     const int nt = (tr + 63) / 64;
-    for (int ti = 0; ti < nt; ++ti) {
-      // Gram part: lower-triangular tiles only
-      for (int tj = 0; tj <= ti; ++tj)
+    const int nc = (zc + 63) / 64;
+    const int gram_tiles = nt * (nt + 1) / 2;
+    const int total_tiles = gram_tiles + nt * nc;
+    for (int idx = tid >> 8; idx < total_tiles; idx += kCholThreads / 256) {
+      if (idx < gram_tiles) {
+        int ti = 0, rem = idx;
+        while (rem > ti) {  // row ti of the lower triangle holds ti + 1 tiles
+          rem -= ti + 1;
+          ++ti;
+        }
+        const int tj = rem;
         tile_update<NB>(W, r, p0 + ti * 64, p0 + tj * 64, panelT + ti * 64, rp, panelT + tj * 64, rp, r, r);
-      // right-hand-side part: columns < zc
-      const int nc = (zc + 63) / 64;
-      for (int tc = 0; tc < nc; ++tc)
+      } else {
+        const int q = idx - gram_tiles;
+        const int ti = q / nc, tc = q - ti * nc;
         tile_update<NB>(Z, r, p0 + ti * 64, tc * 64, panelT + ti * 64, rp, zrow + tc * 64, rp, r, zc);
+      }
     }
     __syncthreads();
   }

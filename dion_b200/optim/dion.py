@@ -35,8 +35,9 @@ from torch.optim.optimizer import Optimizer, ParamsT
 
 from .. import ops
 from ..ops import nn as nn_ops
+from ..parallel import symm
 from .common import (Scheduler, all_reduce_, group_of, group_rank, group_size, to_local)
-from .orthogonalize import orthonormalize_cholqr
+from .orthogonalize import orthonormalize_many
 
 try:  # pragma: no cover - depends on the torch build
     from torch.distributed.tensor.placement_types import _StridedShard
@@ -121,6 +122,12 @@ class _PackedClass:
         self.shadow_ptrs: Optional[Tensor] = None
         self.shadow_ptr_list: Optional[List[int]] = None
         self.nonzero: Optional[Tensor] = None
+
+
+class _ClassWork:
+    """Per-step working set of one parameter class between the two phases of the update."""
+
+    __slots__ = ("cls", "params", "group", "replicate", "outer", "inner", "sync", "compressed", "A", "Qm", "P")
 
 
 class Dion(Optimizer):
@@ -220,15 +227,31 @@ class Dion(Optimizer):
             else:
                 raise ValueError(f"Unknown algorithm: {algo}")
 
-        def tasks():
-            for group in dion_groups:
-                yield from self._dion_tasks(group)
+        # The update of every (shape, placements, dtype) class runs in two phases around one
+        # joint orthonormalisation, so that the Gram matrices of all classes are factorised
+        # by a single kernel launch.  Within a phase the classes are interleaved by the
+        # scheduler: while one waits for a collective, the others issue their kernels.
+        work: List[_ClassWork] = []
+        for group in dion_groups:
+            work.extend(self._dion_classes(group))
+
+        def phase1():
+            for w in work:
+                yield lambda w=w: self._dion_phase1(w)
             for group in lion_groups:
                 yield lambda g=group: self._scalar_task(g, "lion")
             for group in adamw_groups:
                 yield lambda g=group: self._scalar_task(g, "adamw")
 
-        Scheduler(tasks(), max_in_flight=3).run()
+        if work:
+            groups = {g for w in work for g in (w.outer, w.inner, w.replicate if w.compressed else None) if g is not None}
+            symm.begin_step(sorted(groups, key=lambda g: g.group_name), work[0].cls.M.device)
+        Scheduler(phase1(), max_in_flight=3).run()
+        if work:
+            ortho = orthonormalize_many([w.P for w in work], [w.inner for w in work])
+            for w, P in zip(work, ortho):
+                w.P = P
+            Scheduler((lambda w=w: self._dion_phase2(w) for w in work), max_in_flight=3).run()
         return loss
 
     @torch.no_grad()
@@ -486,16 +509,41 @@ class Dion(Optimizer):
 
     # ------------------------------------------------------------------ Dion update
 
-    def _dion_tasks(self, group: dict):
+    def _dion_classes(self, group: dict) -> List["_ClassWork"]:
+        """Parameters of `group` that have gradients, split into classes of identical
+        (shape, placements, dtype) with their packed states and process groups resolved."""
         params = [p for p in group["params"] if p.grad is not None]
-        if not params:
-            return
         classes: Dict[tuple, List[Tensor]] = {}
         for p in params:
             placements = tuple(p.placements) if isinstance(p, DTensor) else None
-            classes.setdefault((tuple(p.shape), placements, p.dtype, id(group)), []).append(p)
+            transposed = self._get_dion_param_config(p).is_transposed
+            classes.setdefault((tuple(p.shape), placements, p.dtype, id(group), transposed), []).append(p)
+        replicate = group_of(self._replicate_mesh)
+        if replicate is not None and dist.get_world_size(replicate) == 1:
+            replicate = None
+        out = []
         for key, members in classes.items():
-            yield lambda k=key, ms=members: self._dion_update_class(k, ms, group)
+            cls = self._pack(key, members, group)
+            w = _ClassWork()
+            w.cls, w.params, w.group = cls, members, group
+            w.replicate = replicate
+            w.outer = self._mesh_dim_group(members[0], cls.cfg.outer_shard_mesh_dim)
+            w.inner = self._mesh_dim_group(members[0], cls.cfg.inner_shard_mesh_dim)
+            w.sync = self._replicate_mesh_grad_sync and replicate is not None
+            w.compressed = w.sync and cls.cfg.compressed_all_reduce
+            out.append(w)
+        return out
+
+    @staticmethod
+    def _reduce(t: Tensor, group: ProcessGroup, average: bool):
+        """All-reduce `t` over `group`.  Buffers that live in the group's symmetric arena are
+        reduced by the in-tree kernel on the current stream (returns None); anything else
+        starts the library collective asynchronously and returns its wait() callable."""
+        arena = symm.arena_for(group)
+        if arena is not None and t.is_cuda and arena.offset_of(t) is not None:
+            symm.all_reduce(t, group, average=average)
+            return None
+        return all_reduce_(t, group, average=average, async_op=True)
 
     def _mesh_dim_group(self, p: Tensor, mesh_dim: Optional[int]) -> Optional[ProcessGroup]:
         if mesh_dim is None or not isinstance(p, DTensor):
@@ -503,27 +551,16 @@ class Dion(Optimizer):
         g = p.device_mesh.get_group(mesh_dim)
         return g if dist.get_world_size(g) > 1 else None
 
-    def _dion_update_class(self, key: tuple, params: List[Tensor], group: dict) -> Generator[None, None, None]:
-        cls = self._pack(key, params, group)
-        cfg = cls.cfg
-        p0 = params[0]
-        lr, mu, wd, eps = group["lr"], group["mu"], group["weight_decay"], group["epsilon"]
-        B = len(params)
+    def _dion_phase1(self, w: "_ClassWork") -> Generator[None, None, None]:
+        """Gradient sync, momentum accumulation and P = A Q reduced over the meshes."""
+        cls, cfg = w.cls, w.cls.cfg
+        B = len(w.params)
         M, Qs = cls.M, cls.Q
-        X = [to_local(p) for p in params]
-        G = [to_local(p.grad) for p in params]
-
-        replicate = group_of(self._replicate_mesh)
-        if replicate is not None and dist.get_world_size(replicate) == 1:
-            replicate = None
-        outer = self._mesh_dim_group(p0, cfg.outer_shard_mesh_dim)
-        inner = self._mesh_dim_group(p0, cfg.inner_shard_mesh_dim)
-        sync = self._replicate_mesh_grad_sync and replicate is not None
-        compressed = sync and cfg.compressed_all_reduce
+        G = [to_local(p.grad) for p in w.params]
 
         # 0. full-gradient synchronisation when compression does not pay (dion.py:785-791)
-        if sync and not compressed:
-            wait = all_reduce_(G, replicate, average=True, async_op=True)
+        if w.sync and not w.compressed:
+            wait = all_reduce_(G, w.replicate, average=True, async_op=True)
             yield
             wait()
 
@@ -535,43 +572,62 @@ class Dion(Optimizer):
         ops.dion_accumulate(G, list(M.unbind(0)), cls.nonzero)
 
         # 2. Q with all of its columns (gathered over the inner mesh), in the momentum dtype
-        if inner is not None:
-            w_in = dist.get_world_size(inner)
-            gathered = torch.empty((w_in, *Qs.shape), dtype=Qs.dtype, device=Qs.device)
-            work = dist.all_gather_into_tensor(gathered, Qs.contiguous(), group=inner, async_op=True)
+        if w.inner is not None:
+            w_in = dist.get_world_size(w.inner)
+            gathered = torch.empty((w_in * B, Qs.shape[1], Qs.shape[2]), dtype=Qs.dtype, device=Qs.device)
+            work = dist.all_gather_into_tensor(gathered, Qs.contiguous(), group=w.inner, async_op=True)
             yield
             work.wait()
-            Q_full = gathered.permute(1, 2, 0, 3).reshape(B, Qs.shape[1], w_in * Qs.shape[2])
+            Q_full = gathered.view(w_in, B, Qs.shape[1], Qs.shape[2]).permute(1, 2, 0, 3).reshape(
+                B, Qs.shape[1], w_in * Qs.shape[2])
         else:
             Q_full = Qs
-        Qm = Q_full.to(M.dtype)
+        w.Qm = Q_full.to(M.dtype)
 
         # 3. P = A Q, partial over the outer mesh
-        A = M.transpose(1, 2) if cfg.is_transposed else M
-        P = ops.gemm(A, Qm, out_dtype=torch.float32)
-        if outer is not None:
-            wait = all_reduce_(P, outer, average=False, async_op=True)
-            yield
-            wait()
-        if compressed:
-            wait = all_reduce_(P, replicate, average=True, async_op=True)
-            yield
-            wait()
+        w.A = M.transpose(1, 2) if cfg.is_transposed else M
+        a_loc = w.A.shape[1]
+        first = w.outer if w.outer is not None else (w.replicate if w.compressed else None)
+        # the GEMM writes straight into the symmetric arena of the group that reduces P first
+        P = symm.empty(first, (B, a_loc, w.Qm.shape[2]), torch.float32, M.device)
+        ops.gemm(w.A, w.Qm, out=P)
+        if w.outer is not None:
+            wait = self._reduce(P, w.outer, average=False)
+            if wait is not None:
+                yield
+                wait()
+        if w.compressed:
+            wait = self._reduce(P, w.replicate, average=True)
+            if wait is not None:
+                yield
+                wait()
+        w.P = P  # 4. is the joint orthonormalisation in step()
 
-        # 4. orthonormal basis of range(P); rows of P are sharded over the inner mesh
-        P = orthonormalize_cholqr(P, row_group=inner)
-        Pm = P.to(M.dtype)
+    def _dion_phase2(self, w: "_ClassWork") -> Generator[None, None, None]:
+        """R = A^T P, error feedback, new Q and the weight update."""
+        cls, cfg, group = w.cls, w.cls.cfg, w.group
+        params = w.params
+        p0 = params[0]
+        lr, mu, wd, eps = group["lr"], group["mu"], group["weight_decay"], group["epsilon"]
+        B = len(params)
+        M, Qs, A, Qm = cls.M, cls.Q, w.A, w.Qm
+        X = [to_local(p) for p in params]
+        Pm = w.P.to(M.dtype)
 
         # 5. R = A^T P, partial over the inner mesh
-        R = ops.gemm(A.transpose(1, 2), Pm, out_dtype=torch.float32)
-        if inner is not None:
-            wait = all_reduce_(R, inner, average=False, async_op=True)
-            yield
-            wait()
-        if compressed:
-            wait = all_reduce_(R, replicate, average=True, async_op=True)
-            yield
-            wait()
+        first = w.inner if w.inner is not None else (w.replicate if w.compressed else None)
+        R = symm.empty(first, (B, A.shape[2], Pm.shape[2]), torch.float32, M.device)
+        ops.gemm(A.transpose(1, 2), Pm, out=R)
+        if w.inner is not None:
+            wait = self._reduce(R, w.inner, average=False)
+            if wait is not None:
+                yield
+                wait()
+        if w.compressed:
+            wait = self._reduce(R, w.replicate, average=True)
+            if wait is not None:
+                yield
+                wait()
 
         # 6. all-zero / NaN guard, shard-local like the reference (dion.py:1416-1444):
         #    an all-zero momentum gives P = 0 and keeps the previous Q
@@ -588,11 +644,12 @@ class Dion(Optimizer):
             ops.gemm(Pm, Rm.transpose(1, 2), c=M, out=M, alpha=alpha, beta=1.0)
 
         # 8. new Q: column-normalised R (sum of squares completed over the outer mesh)
-        ss = ops.col_sumsq(R)
-        if outer is not None:
-            wait = all_reduce_(ss, outer, average=False, async_op=True)
-            yield
-            wait()
+        ss = ops.col_sumsq(R, out=symm.empty(w.outer, (B, R.shape[2]), torch.float32, M.device))
+        if w.outer is not None:
+            wait = self._reduce(ss, w.outer, average=False)
+            if wait is not None:
+                yield
+                wait()
         Qn = (R / (ss.sqrt().unsqueeze(1) + eps)).to(M.dtype)
 
         # 9. weight decay and update  X = (1 - lr wd) X - lr sqrt(fan_out / fan_in) P Qn^T
@@ -606,12 +663,13 @@ class Dion(Optimizer):
         self._apply_update(cls, params, X, a_op, b_op, -scaled_lr, beta)
 
         # 10. keep this rank's columns of the new Q (dion.py:1533-1561)
-        if inner is not None:
+        if w.inner is not None:
             r_loc = Qs.shape[2]
-            i0 = dist.get_rank(inner) * r_loc
+            i0 = dist.get_rank(w.inner) * r_loc
             Qs.copy_(Qn[:, :, i0:i0 + r_loc])
         else:
             Qs.copy_(Qn)
+        w.A = w.Qm = w.P = None
 
     def _apply_update(self, cls: _PackedClass, params: List[Tensor], X: List[Tensor], a_op: Tensor, b_op: Tensor,
                       alpha: float, beta: float) -> None:

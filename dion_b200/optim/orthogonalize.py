@@ -26,6 +26,7 @@ import torch.distributed as dist
 from torch import Tensor
 
 from .. import ops
+from ..parallel import symm
 
 # "3xtf32" splits fp32 operands into two tf32 halves (three tensor-core passes, ~fp32
 # accuracy); "tf32" is a single pass.
@@ -38,15 +39,17 @@ def _split_tf32(x: Tensor):
     return hi, x - hi
 
 
-def gram(P: Tensor) -> Tensor:
-    """``P^T P`` in fp32 for a batch ``[B, a, r]`` (fp32 input)."""
+def gram(P: Tensor, reduce_group=None) -> Tensor:
+    """``P^T P`` in fp32 for a batch ``[B, a, r]`` (fp32 input).  When the result will be
+    summed over `reduce_group`, it is produced in that group's symmetric arena."""
     Pt = P.transpose(-1, -2)
     if not P.is_cuda:
         return Pt @ P
+    out = symm.empty(reduce_group, (P.shape[0], P.shape[2], P.shape[2]), torch.float32, P.device)
     if GRAM_PRECISION == "tf32":
-        return ops.gemm(Pt, P, symmetric=True)
+        return ops.gemm(Pt, P, out=out, symmetric=True)
     hi, lo = _split_tf32(P)
-    G = ops.gemm(hi.transpose(-1, -2), hi, symmetric=True)
+    G = ops.gemm(hi.transpose(-1, -2), hi, out=out, symmetric=True)
     # cross terms lo^T hi + hi^T lo; lo^T lo is below fp32 resolution
     ops.gemm(lo.transpose(-1, -2), hi, c=G, out=G, beta=1.0)
     ops.gemm(hi.transpose(-1, -2), lo, c=G, out=G, beta=1.0)
@@ -88,6 +91,55 @@ def orthonormalize_cholqr(P: Tensor, row_group: Optional[dist.ProcessGroup] = No
         Z, _ = ops.chol_inverse(G, pivot_floor)
         X = apply_right(X, Z)
     return X.to(out_dtype)
+
+
+def _refine(X: Tensor, row_group: Optional[dist.ProcessGroup]) -> Tensor:
+    """One triangular Newton correction of an almost orthonormal X: with the column-scaled
+    Gram matrix D G D = I + E, the Cholesky factor's inverse is I - stril(E) to first order,
+    so X <- (X D) (I - stril(E))^T squares the orthogonality error while keeping the column
+    spans nested exactly like a QR factorisation does."""
+    G = gram(X, row_group)
+    if row_group is not None and dist.get_world_size(row_group) > 1:
+        symm.all_reduce(G, row_group)
+    diag = torch.diagonal(G, dim1=-2, dim2=-1)
+    d = torch.where(diag > 1e-30, diag.clamp_min(1e-30).rsqrt(), torch.zeros_like(diag))
+    C = torch.tril(G * d.unsqueeze(-1) * d.unsqueeze(-2), diagonal=-1)  # stril(E)
+    Xs = X * d.unsqueeze(-2)
+    # the correction term is small, a single tensor-core pass keeps it far below fp32 resolution
+    corr = ops.gemm(Xs, C.transpose(-1, -2)) if X.is_cuda else Xs @ C.transpose(-1, -2)
+    return Xs - corr
+
+
+def orthonormalize_many(Ps, row_groups=None, refine_passes: int = 2,
+                        pivot_floor: float = ops.linalg.DEFAULT_PIVOT_FLOOR):
+    """Orthonormalise several batches ``P_i: [B_i, a_i, r_i]`` at once.  All Gram matrices of
+    the same rank are factorised by a single launch of the Cholesky kernel (one CTA per
+    matrix), whatever their row counts; the remaining loss of orthogonality is removed by
+    `refine_passes` triangular Newton corrections, which are plain tensor-core GEMMs.
+    ``row_groups[i]`` is the process group sharding the rows of ``P_i`` (or None)."""
+    n = len(Ps)
+    if row_groups is None:
+        row_groups = [None] * n
+    dtypes = [P.dtype for P in Ps]
+    Xs = [P.float() for P in Ps]
+    Gs = [gram(X, g) for X, g in zip(Xs, row_groups)]
+    for G, g in zip(Gs, row_groups):
+        if g is not None and dist.get_world_size(g) > 1:
+            symm.all_reduce(G, g)
+    by_rank = {}
+    for i, G in enumerate(Gs):
+        by_rank.setdefault(G.shape[-1], []).append(i)
+    for r, idxs in by_rank.items():
+        Gcat = Gs[idxs[0]] if len(idxs) == 1 else torch.cat([Gs[i] for i in idxs], dim=0)
+        Z, _ = ops.chol_inverse(Gcat, pivot_floor)
+        off = 0
+        for i in idxs:
+            b = Gs[i].shape[0]
+            Xs[i] = apply_right(Xs[i], Z[off:off + b])
+            off += b
+    for _ in range(refine_passes):
+        Xs = [_refine(X, g) for X, g in zip(Xs, row_groups)]
+    return [X.to(dt) for X, dt in zip(Xs, dtypes)]
 
 
 def orthogonalize_reference(P: Tensor, qr_method: str = "rcqr", oversample: float = 1.25,

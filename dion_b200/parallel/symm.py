@@ -1,0 +1,189 @@
+"""Symmetric-memory arenas and the collectives that run on them.
+
+One arena per process group: a symmetric allocation (same size on every rank, peers mapped
+over NVLink, optionally bound to an NVSwitch multicast object) with a flag block in front.
+Buffers handed out by :func:`empty` are views into the arena; :func:`all_reduce` on such a
+view runs the in-tree all-reduce kernel (peer loads / stores or ``multimem`` instructions
+issued by the kernel itself), anything else falls back to the process group's own
+collective (NCCL on GPUs, gloo on CPUs), so call sites do not care which path is taken.
+
+Sizing is lazy and symmetric: a step that needs more than the arena holds is served from
+ordinary memory (library collectives) and the arena grows at the next :func:`begin_step`,
+which every rank reaches with the same request history.
+
+Environment: ``DION_B200_SYMM=0`` disables the arenas, ``DION_B200_MULTICAST=0`` keeps the
+kernels on plain peer loads and stores.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import runtime
+
+_FLAG_BYTES = 4096
+_ALIGN = 256
+_MIN_ARENA = 8 << 20
+
+
+def _enabled() -> bool:
+    return os.environ.get("DION_B200_SYMM", "1") != "0"
+
+
+class SymmetricArena:
+    def __init__(self, group: dist.ProcessGroup, nbytes: int, device: torch.device):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group
+        self.device = device
+        self.capacity = int(nbytes)
+        self.buf = symm_mem.empty(self.capacity + _FLAG_BYTES, dtype=torch.uint8, device=device)
+        self.buf.zero_()
+        self.hdl = symm_mem.rendezvous(self.buf, group)
+        self.rank = int(self.hdl.rank)
+        self.world = int(self.hdl.world_size)
+        self.peers = [int(p) for p in self.hdl.buffer_ptrs]
+        mc = 0
+        if os.environ.get("DION_B200_MULTICAST", "1") != "0":
+            try:
+                mc = int(self.hdl.multicast_ptr or 0)
+            except Exception:  # pragma: no cover - depends on driver / fabric
+                mc = 0
+        self.mc_base = mc
+        self.counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = 0
+        self.cursor = 0
+        self.high_water = 0
+        self._views: Dict[int, int] = {}  # data_ptr -> byte offset inside the arena (flag block included)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # every rank's flag block is zero before anyone signals
+
+    # -- allocation
+    def reset(self) -> None:
+        self.cursor = 0
+        self._views.clear()
+
+    def alloc(self, shape, dtype) -> Optional[torch.Tensor]:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        start = (self.cursor + _ALIGN - 1) // _ALIGN * _ALIGN
+        self.high_water = max(self.high_water, start + nbytes)
+        if start + nbytes > self.capacity:
+            return None
+        self.cursor = start + nbytes
+        off = _FLAG_BYTES + start
+        t = self.buf[off:off + nbytes].view(dtype).view(*shape)
+        self._views[t.data_ptr()] = off
+        return t
+
+    def offset_of(self, t: torch.Tensor) -> Optional[int]:
+        return self._views.get(t.data_ptr())
+
+    # -- collectives (stream ordered on the current stream)
+    def all_reduce(self, t: torch.Tensor, off: int, average: bool) -> None:
+        self.epoch += 1
+        torch.ops.dion_b200.symm_all_reduce(t, self.peers, 0, off, self.mc_base,
+                                            (1.0 / self.world) if average else 1.0, self.rank, self.epoch,
+                                            self.counter, runtime.status_tensor(self.device))
+
+    def reduce_into(self, src: torch.Tensor, off: int, dst: torch.Tensor, scale: float = 1.0, beta: float = 0.0) -> None:
+        self.epoch += 1
+        torch.ops.dion_b200.symm_reduce_into(src, dst, self.peers, 0, off, scale, beta, self.rank, self.epoch,
+                                             self.counter, runtime.status_tensor(self.device))
+
+    def barrier(self, channel: int = 0) -> None:
+        self.epoch += 1
+        torch.ops.dion_b200.symm_barrier(self.counter, self.peers, 0, channel, self.rank, self.epoch,
+                                         runtime.status_tensor(self.device))
+
+
+_arenas: Dict[str, SymmetricArena] = {}
+_wanted: Dict[str, int] = {}
+_failed = False
+
+
+def _key(group: dist.ProcessGroup) -> str:
+    return getattr(group, "group_name", None) or str(id(group))
+
+
+def _usable(group: Optional[dist.ProcessGroup], device: torch.device) -> bool:
+    if group is None or _failed or not _enabled() or device.type != "cuda":
+        return False
+    try:
+        if dist.get_backend(group) != "nccl":
+            return False
+    except Exception:
+        return False
+    w = dist.get_world_size(group)
+    return 1 < w <= 8
+
+
+def begin_step(groups, device: torch.device) -> None:
+    """Reset (and if necessary create or grow) the arenas of `groups`.  Collective: every rank
+    calls it at the same point of every optimizer step."""
+    global _failed
+    for g in groups:
+        if not _usable(g, device):
+            continue
+        k = _key(g)
+        arena = _arenas.get(k)
+        want = max(_wanted.get(k, 0), arena.high_water if arena else 0)
+        if arena is None or want > arena.capacity:
+            size = max(_MIN_ARENA, int(want * 1.25))
+            try:
+                _arenas[k] = SymmetricArena(g, size, device)
+            except Exception as e:  # pragma: no cover - machine dependent
+                _failed = True
+                if dist.get_rank() == 0:
+                    print(f"[dion_b200] symmetric memory unavailable ({type(e).__name__}: {e}); using library collectives")
+                return
+        else:
+            arena.reset()
+
+
+def empty(group: Optional[dist.ProcessGroup], shape, dtype, device) -> torch.Tensor:
+    """Buffer that will be reduced over `group`: from the group's arena when it has room."""
+    device = torch.device(device)
+    if _usable(group, device):
+        arena = _arenas.get(_key(group))
+        if arena is not None:
+            t = arena.alloc(shape, dtype)
+            if t is not None:
+                return t
+            _wanted[_key(group)] = arena.high_water
+        else:
+            n = 1
+            for s in shape:
+                n *= int(s)
+            _wanted[_key(group)] = _wanted.get(_key(group), 0) + n * 4 + _ALIGN
+    return torch.empty(tuple(shape), dtype=dtype, device=device)
+
+
+def all_reduce(t: torch.Tensor, group: Optional[dist.ProcessGroup], average: bool = False) -> None:
+    """In-place all-reduce (sum or mean) of `t` over `group`, blocking in stream order."""
+    if group is None or dist.get_world_size(group) == 1:
+        return
+    arena = _arenas.get(_key(group)) if t.is_cuda else None
+    if arena is not None:
+        off = arena.offset_of(t)
+        if off is not None and t.is_contiguous() and t.dtype in (torch.float32, torch.bfloat16):
+            arena.all_reduce(t, off, average)
+            return
+    world = dist.get_world_size(group)
+    nccl = t.is_cuda and dist.get_backend(group) == "nccl"
+    if average and nccl:
+        dist.all_reduce(t, op=dist.ReduceOp.AVG, group=group)
+    else:
+        dist.all_reduce(t, group=group)
+        if average:
+            t.div_(world)
+
+
+def arena_for(group: Optional[dist.ProcessGroup]) -> Optional[SymmetricArena]:
+    return _arenas.get(_key(group)) if group is not None else None

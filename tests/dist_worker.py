@@ -1,0 +1,326 @@
+"""Multi-process test cases, launched by tests/test_distributed.py through torchrun.
+Each case runs on every rank (CUDA + NCCL when GPUs are available, CPU + gloo otherwise)
+and compares against a single-process computation of the same thing.  Exit code 0 = pass."""
+import os
+import sys
+
+os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch
+import torch.distributed as dist
+
+CUDA = torch.cuda.is_available() and os.environ.get("DION_TEST_FORCE_CPU", "0") != "1"
+RANK = int(os.environ["RANK"])
+WORLD = int(os.environ["WORLD_SIZE"])
+LOCAL = int(os.environ.get("LOCAL_RANK", "0"))
+DEV = torch.device("cuda", LOCAL) if CUDA else torch.device("cpu")
+
+SHAPES = [(64, 32), (32, 64), (64, 64), (64, 32), (32, 64), (64, 64), (128, 32)]
+
+
+def init():
+    if CUDA:
+        torch.cuda.set_device(LOCAL)
+        dist.init_process_group("nccl", device_id=DEV)
+    else:
+        dist.init_process_group("gloo")
+
+
+def check(name, a, b, tol):
+    err = ((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-12)).item()
+    ok = err < tol
+    if RANK == 0 or not ok:
+        print(f"[rank {RANK}] {name}: scaled max err {err:.3e} (tol {tol}) {'ok' if ok else 'FAIL'}", flush=True)
+    if not ok:
+        raise SystemExit(1)
+
+
+def make_params(seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.nn.Parameter(torch.randn(s, generator=g).to(DEV)) for s in SHAPES]
+
+
+def rank_grads(step, shapes=SHAPES):
+    """Per-rank gradients (deterministic) and their mean over ranks."""
+    out = []
+    for r in range(WORLD):
+        g = torch.Generator().manual_seed(1000 * step + r)
+        out.append([torch.randn(s, generator=g) for s in shapes])
+    mean = [sum(out[r][i] for r in range(WORLD)) / WORLD for i in range(len(shapes))]
+    return [t.to(DEV) for t in out[RANK]], [t.to(DEV) for t in mean]
+
+
+# ------------------------------------------------------------------------------------------ cases
+
+def case_symm():
+    """Symmetric-memory barrier / all-reduce / reduce-into kernels against torch sums."""
+    if not CUDA:
+        print("symm kernels need GPUs; skipped")
+        return
+    from dion_b200 import ops
+    from dion_b200.parallel import symm
+
+    group = dist.group.WORLD
+    symm.begin_step([group], DEV)   # first call creates the arena
+    arena = symm.arena_for(group)
+    assert arena is not None, "arena was not created"
+    for dtype, n in ((torch.float32, 1 << 20), (torch.float32, 1003), (torch.bfloat16, 1 << 18), (torch.bfloat16, 777)):
+        symm.begin_step([group], DEV)
+        t = symm.empty(group, (n,), dtype, DEV)
+        assert arena.offset_of(t) is not None
+        gen = torch.Generator().manual_seed(5)
+        full = [torch.randn(n, generator=gen) for _ in range(WORLD)]
+        t.copy_(full[RANK].to(dtype))
+        ref = sum(f.to(dtype).float() for f in full) / WORLD
+        symm.all_reduce(t, group, average=True)
+        check(f"symm all_reduce {dtype} n={n}", t, ref, 1e-5 if dtype == torch.float32 else 1e-2)
+        # every rank must hold bit-identical results
+        gathered = [torch.empty_like(t) for _ in range(WORLD)]
+        dist.all_gather(gathered, t)
+        assert all(torch.equal(gathered[0], g) for g in gathered), "all-reduce results differ between ranks"
+        # one-shot reduce into a local buffer
+        src = symm.empty(group, (n,), dtype, DEV)
+        src.copy_(full[RANK].to(dtype))
+        dst = torch.ones(n, device=DEV, dtype=torch.float32)
+        arena.reduce_into(src, arena.offset_of(src), dst, scale=0.5, beta=2.0)
+        check(f"symm reduce_into {dtype} n={n}", dst, 2.0 + 0.5 * sum(f.to(dtype).float() for f in full), 1e-2)
+    arena.barrier()
+    torch.cuda.synchronize()
+    ops.check_status(DEV)
+
+
+def _single_process_dion(rank_fraction, steps):
+    from dion_b200 import Dion
+
+    P = make_params()
+    opt = Dion(P, lr=0.02, rank_fraction=rank_fraction, weight_decay=0.1)
+    for s in range(steps):
+        _, mean = rank_grads(s)
+        for p, g in zip(P, mean):
+            p.grad = g.clone()
+        opt.step()
+    return P, opt
+
+
+def case_dion_ddp():
+    """Dion with a ProcessGroup replicate mesh, gradient sync owned by the optimizer:
+    full-gradient path (rank_fraction 1) and compressed P/R path (rank_fraction 0.25)."""
+    from dion_b200 import Dion
+
+    for rf in (1.0, 0.25):
+        P = make_params()
+        opt = Dion(P, replicate_mesh=dist.group.WORLD, replicate_mesh_grad_sync=True, lr=0.02, rank_fraction=rf,
+                   weight_decay=0.1)
+        steps = 3
+        for s in range(steps):
+            mine, _ = rank_grads(s)
+            for p, g in zip(P, mine):
+                p.grad = g.clone()
+            opt.step()
+        Pref, optref = _single_process_dion(rf, steps)
+        tol = 2e-3 if CUDA else 1e-4
+        for i, (p, q) in enumerate(zip(P, Pref)):
+            check(f"dion ddp rf={rf} X[{i}]", p, q, tol)
+        # momentum is decoupled per rank when compressed; its mean follows the single-process run
+        opt.synchronize_for_checkpoint()
+        for i, (p, q) in enumerate(zip(P, Pref)):
+            check(f"dion ddp rf={rf} M[{i}] after synchronize_for_checkpoint", opt.state[p]["momentum"],
+                  optref.state[q]["momentum"], 5e-3 if CUDA else 1e-4)
+
+
+def case_muon_ddp():
+    """Muon with a ProcessGroup: matrices are split over ranks and all-gathered."""
+    from dion_b200 import Muon
+
+    P = make_params()
+    Pref = make_params()
+    opt = Muon(P, distributed_mesh=dist.group.WORLD, lr=0.02, nesterov=True)
+    optref = Muon(Pref, lr=0.02, nesterov=True)
+    for s in range(3):
+        _, mean = rank_grads(s)
+        for p, q, g in zip(P, Pref, mean):
+            p.grad = g.clone()
+            q.grad = g.clone()
+        opt.step()
+        optref.step()
+    for i, (p, q) in enumerate(zip(P, Pref)):
+        check(f"muon ddp X[{i}]", p, q, 2e-2)
+
+
+def _tiny_gpt():
+    from dion_b200.models import GPT, GPTConfig
+
+    torch.manual_seed(0)
+    m = GPT(GPTConfig(sequence_len=64, vocab_size=512, n_layer=2, n_head=4, n_embd=64))
+    m.init_weights()
+    return m
+
+
+def _full(t):
+    from torch.distributed.tensor import DTensor
+
+    return t.full_tensor() if isinstance(t, DTensor) else t
+
+
+def _train(model, opt, steps, data_rank=None, data_world=None):
+    losses = []
+    for s in range(steps):
+        g = torch.Generator().manual_seed(77 + s)
+        idx = torch.randint(0, 512, (4 * WORLD, 64), generator=g)
+        tgt = torch.randint(0, 512, (4 * WORLD, 64), generator=g)
+        if data_rank is not None:
+            idx, tgt = idx[data_rank::data_world], tgt[data_rank::data_world]
+        loss = model(idx.to(DEV), tgt.to(DEV))
+        loss.backward()
+        opt.step()
+        model.zero_grad(set_to_none=True)
+        losses.append(loss.detach().float())
+    return torch.stack(losses)
+
+
+def case_fsdp():
+    """GPT under FSDP2 (fs = world) with Dion (outer mesh) and with Muon, against a
+    single-process run on the full batch."""
+    from torch.distributed.device_mesh import init_device_mesh
+
+    from dion_b200 import Dion, Muon
+    from dion_b200.models.gpt import parallelize_gpt_model
+
+    for name in ("dion", "muon"):
+        mesh = init_device_mesh("cuda" if CUDA else "cpu", (1, WORLD, 1), mesh_dim_names=("dp", "fs", "tp"))
+        ref = _tiny_gpt().to(DEV)
+        model = _tiny_gpt().to(DEV)
+        parallelize_gpt_model(model, mesh, dp_name=None, fs_name="fs", tp_name="tp")
+        mk = lambda m: [dict(params=list(m.transformer.h.parameters())),
+                        dict(params=list(m.transformer.wte.parameters()) + list(m.lm_head.parameters()),
+                             algorithm="adamw", lr=0.002)]
+        if name == "dion":
+            opt = Dion(mk(model), replicate_mesh=mesh["dp"], outer_shard_mesh=mesh["fs"], lr=0.02, rank_fraction=0.5)
+            optref = Dion(mk(ref), lr=0.02, rank_fraction=0.5)
+            # same Q on both sides
+            for g in opt.param_groups[:1]:
+                for p in g["params"]:
+                    opt._get_or_initialize_state(p, g)
+            for (n1, p1), (n2, p2) in zip(model.transformer.h.named_parameters(), ref.transformer.h.named_parameters()):
+                optref.state[p2] = {"momentum": torch.zeros_like(p2), "Q": _full(opt.state[p1]["Q"]).clone()}
+                # the sharding decides the orientation of the power iteration; mirror it
+                optref._get_dion_param_config(p2).is_transposed = opt._param_config[p1].is_transposed
+        else:
+            opt = Muon(mk(model), distributed_mesh=mesh["fs"], lr=0.02, nesterov=True)
+            optref = Muon(mk(ref), lr=0.02, nesterov=True)
+        l1 = _train(model, opt, 3, data_rank=RANK, data_world=WORLD)
+        l2 = _train(ref, optref, 3)
+        dist.all_reduce(l1, op=dist.ReduceOp.SUM)
+        l1 /= WORLD
+        check(f"fsdp {name} losses", l1, l2, 3e-2 if CUDA else 2e-3)
+        for (n1, p1), (n2, p2) in zip(model.named_parameters(), ref.named_parameters()):
+            # embedding / lm_head use a sign-like update in the first steps, where tiny
+            # gradient differences flip whole entries by 2 * lr
+            loose = "wte" in n1 or "lm_head" in n1
+            check(f"fsdp {name} {n1}", _full(p1.detach()), p2.detach(), 6e-2 if (CUDA or loose) else 5e-3)
+
+
+def case_tp():
+    """GPT with tensor parallelism (tp = world): loss and a Dion step (inner mesh) against a
+    single-process run."""
+    from torch.distributed.device_mesh import init_device_mesh
+
+    from dion_b200 import Dion
+    from dion_b200.models.gpt import parallelize_gpt_model
+
+    mesh = init_device_mesh("cuda" if CUDA else "cpu", (1, 1, WORLD), mesh_dim_names=("dp", "fs", "tp"))
+    ref = _tiny_gpt().to(DEV)
+    model = _tiny_gpt().to(DEV)
+    parallelize_gpt_model(model, mesh, dp_name=None, fs_name="fs", tp_name="tp")
+    mk = lambda m: [dict(params=list(m.transformer.h.parameters())),
+                    dict(params=list(m.transformer.wte.parameters()) + list(m.lm_head.parameters()),
+                         algorithm="adamw", lr=0.002)]
+    opt = Dion(mk(model), replicate_mesh=mesh["dp"], outer_shard_mesh=mesh["fs"], inner_shard_mesh=mesh["tp"],
+               lr=0.02, rank_fraction=0.5, rank_multiple_of=WORLD)
+    optref = Dion(mk(ref), lr=0.02, rank_fraction=0.5, rank_multiple_of=WORLD)
+    for g in opt.param_groups[:1]:
+        for p in g["params"]:
+            opt._get_or_initialize_state(p, g)
+    for (n1, p1), (n2, p2) in zip(model.transformer.h.named_parameters(), ref.transformer.h.named_parameters()):
+        optref.state[p2] = {"momentum": torch.zeros_like(p2), "Q": _full(opt.state[p1]["Q"]).clone()}
+        optref._get_dion_param_config(p2).is_transposed = opt._param_config[p1].is_transposed
+    l1 = _train(model, opt, 3)           # tensor-parallel ranks see the same data
+    l2 = _train(ref, optref, 3)
+    check("tp losses", l1, l2, 3e-2 if CUDA else 2e-3)
+    for (n1, p1), (n2, p2) in zip(model.named_parameters(), ref.named_parameters()):
+        loose = "wte" in n1 or "lm_head" in n1
+        check(f"tp {n1}", _full(p1.detach()), p2.detach(), 6e-2 if (CUDA or loose) else 5e-3)
+
+
+def case_checkpoint():
+    """Distributed checkpoint round trip of model + Dion state through CheckpointManager."""
+    import tempfile
+
+    from dion_b200 import Dion
+    from dion_b200.models.data import DistributedDataLoader, write_synthetic_shards
+    from dion_b200.training import CheckpointManager
+
+    box = [None]
+    if RANK == 0:
+        box[0] = tempfile.mkdtemp(prefix="dion_ckpt_")
+        write_synthetic_shards(box[0], 512, train_tokens=200_000, val_tokens=50_000)
+    dist.broadcast_object_list(box, src=0)
+    root = box[0]
+
+    def build():
+        m = _tiny_gpt().to(DEV)
+        o = Dion([dict(params=list(m.transformer.h.parameters())),
+                  dict(params=list(m.transformer.wte.parameters()) + list(m.lm_head.parameters()),
+                       algorithm="adamw", lr=0.002)], replicate_mesh=dist.group.WORLD, lr=0.02, rank_fraction=0.25)
+        tl = DistributedDataLoader(os.path.join(root, "fineweb_train_*.bin"), 2, 64, RANK, WORLD, device=DEV)
+        vl = DistributedDataLoader(os.path.join(root, "fineweb_val_*.bin"), 2, 64, RANK, WORLD, device=DEV)
+        return m, o, tl, vl
+
+    def steps(m, o, tl, n):
+        out = []
+        for _ in range(n):
+            x, y = tl.next_batch()
+            loss = m(x, y)
+            loss.backward()
+            o.step()
+            m.zero_grad(set_to_none=True)
+            out.append(loss.detach().float())
+        return torch.stack(out)
+
+    m, o, tl, vl = build()
+    steps(m, o, tl, 2)
+    o.synchronize_for_checkpoint()
+    mgr = CheckpointManager(os.path.join(root, "ckpt"), m, o, tl, vl)
+    mgr.save(step=2)
+    after = steps(m, o, tl, 2)
+
+    m2, o2, tl2, vl2 = build()
+    mgr2 = CheckpointManager(os.path.join(root, "ckpt"), m2, o2, tl2, vl2)
+    mgr2.load()
+    assert mgr2.step == 2
+    resumed = steps(m2, o2, tl2, 2)
+    check("losses after resume", resumed, after, 2e-2 if CUDA else 1e-4)
+    keys = set(o2.state_dict()["param_groups"][0].keys())
+    assert {"algorithm", "beta1", "beta2", "epsilon", "lr", "mu", "oversample", "params", "rank_fraction",
+            "rank_multiple_of", "step", "weight_decay"} <= keys, keys
+
+
+CASES = {k[5:]: v for k, v in list(globals().items()) if k.startswith("case_")}
+
+if __name__ == "__main__":
+    init()
+    try:
+        for name in sys.argv[1:]:
+            if RANK == 0:
+                print(f"=== case {name}", flush=True)
+            CASES[name]()
+            dist.barrier()
+        if CUDA:
+            from dion_b200 import ops
+
+            ops.check_status(DEV)
+    finally:
+        dist.destroy_process_group()
+    if RANK == 0:
+        print("ALL OK", flush=True)

@@ -1,0 +1,42 @@
+"""Multi-process tests: host-side distributed logic on CPU (gloo, 2 ranks) and the same
+cases plus the symmetric-memory kernels on GPUs (NCCL).  Every case runs in child
+processes launched through torchrun; a rank that fails makes the launcher exit non-zero."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _launch(cases, nproc, force_cpu, timeout=600):
+    env = dict(os.environ)
+    env["DION_TEST_FORCE_CPU"] = "1" if force_cpu else "0"
+    env.setdefault("TORCHDYNAMO_DISABLE", "1")
+    # in-tree kernels on plain peer loads / stores and NCCL without NVLS: a rank that dies
+    # must not leave multicast bindings behind
+    env["DION_B200_MULTICAST"] = "0"
+    env["NCCL_NVLS_ENABLE"] = "0"
+    env["OMP_NUM_THREADS"] = "2"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29600 + (os.getpid() % 300)),
+           os.path.join(HERE, "dist_worker.py"), *cases]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    tail = (res.stdout[-3000:] + "\n" + res.stderr[-3000:])
+    assert res.returncode == 0 and "ALL OK" in res.stdout, tail
+
+
+@pytest.mark.parametrize("case", ["dion_ddp", "muon_ddp", "fsdp", "tp", "checkpoint"])
+def test_cpu_two_ranks(case):
+    _launch([case], nproc=2, force_cpu=True)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", ["symm", "dion_ddp", "muon_ddp", "fsdp", "tp", "checkpoint"])
+def test_gpu_ranks(case):
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    _launch([case], nproc=min(n, 4), force_cpu=False)
