@@ -255,8 +255,26 @@ def run_reference(args):
         return
     # Inductor compiles small host-side C++ kernels with OpenMP; the first g++ on PATH of
     # some images lacks libgomp.spec, the distribution compiler has it.
-    if "CXX" not in os.environ and os.path.exists("/usr/bin/g++"):
-        os.environ["CXX"] = "/usr/bin/g++"
+    import shutil
+    import subprocess
+
+    def can_openmp(cxx: str) -> bool:
+        try:
+            with tempfile.TemporaryDirectory() as d:
+                src = os.path.join(d, "t.cpp")
+                with open(src, "w") as f:
+                    f.write("int main() { return 0; }\n")
+                return subprocess.run([cxx, "-fopenmp", src, "-o", os.path.join(d, "t")],
+                                      capture_output=True, timeout=60).returncode == 0
+        except Exception:
+            return False
+
+    current = os.environ.get("CXX") or shutil.which("g++") or ""
+    if not (current and can_openmp(current)):
+        for cand in ("/usr/bin/g++", "/usr/bin/clang++"):
+            if os.path.exists(cand) and can_openmp(cand):
+                os.environ["CXX"] = cand
+                break
     import torch
     import torch.distributed as dist
 

@@ -134,6 +134,50 @@ void gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, Tens
 }
 
 
+// out-of-place product whose result tiles are scattered to per-destination blocks:
+//   mode 1: block k = rows [k*block, (k+1)*block), mode 2: block k = columns [k*block, (k+1)*block).
+// `block_like` gives dtype and row pitch of one block; `scatter_ptrs` holds batch * dests addresses.
+void gemm_scatter(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, const Tensor& block_like,
+                  const Tensor& scatter_ptrs, int64_t mode, int64_t block, int64_t dests, double alpha, double beta,
+                  const std::optional<Tensor>& status) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == b.scalar_type() && a.dim() == b.dim());
+  const c10::cuda::CUDAGuard guard(a.device());
+  dion::GemmArgs g;
+  g.ab_dtype = gemm_dtype(a, "a");
+  g.M = (int)a.size(-2);
+  g.K = (int)a.size(-1);
+  g.N = (int)b.size(-1);
+  TORCH_CHECK(b.size(-2) == g.K, "gemm inner dimensions differ");
+  g.batch = a.dim() == 3 ? (int)a.size(0) : 1;
+  describe_operand(a, true, &g.a_major, &g.lda, &g.a_batch_stride, "a");
+  describe_operand(b, false, &g.b_major, &g.ldb, &g.b_batch_stride, "b");
+  g.A = a.data_ptr();
+  g.B = b.data_ptr();
+  g.alpha = (float)alpha;
+  g.beta = (float)beta;
+  if (c.has_value()) {
+    check_out(*c, g.batch, g.M, g.N, "c");
+    g.C = c->data_ptr();
+    g.c_dtype = gemm_dtype(*c, "c");
+    g.ldc = c->stride(-2);
+    g.c_batch_stride = c->dim() == 3 ? c->stride(0) : 0;
+  }
+  TORCH_CHECK(block_like.dim() == 2 && block_like.stride(1) == 1);
+  g.d_dtype = gemm_dtype(block_like, "block_like");
+  g.ldd = block_like.stride(0);
+  TORCH_CHECK(scatter_ptrs.scalar_type() == at::kLong && scatter_ptrs.is_cuda() &&
+              scatter_ptrs.numel() >= (int64_t)g.batch * dests);
+  g.scatter_ptrs = reinterpret_cast<void* const*>(scatter_ptrs.data_ptr<int64_t>());
+  g.scatter_mode = (int)mode;
+  g.scatter_block = (int)block;
+  g.scatter_dests = (int)dests;
+  if (status.has_value()) g.status = status->data_ptr<int>();
+  cudaError_t e = dion::gemm_launch(g, at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "dion_b200 gemm_scatter launch failed: ", cudaGetErrorString(e), " ",
+              dion::gemm_last_error());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
 // ----------------------------------------------------------------------------- multi-tensor helpers
 
 int elem_type(const Tensor& t, const char* what) {
@@ -513,6 +557,9 @@ void symm_reduce_into(const Tensor& src, Tensor dst, at::IntArrayRef peers, int6
 }  // namespace
 
 TORCH_LIBRARY(dion_b200, m) {
+  m.def(
+      "gemm_scatter(Tensor a, Tensor b, Tensor? c, Tensor block_like, Tensor scatter_ptrs, int mode, int block, "
+      "int dests, float alpha, float beta, Tensor? status) -> ()");
   m.def("symm_barrier(Tensor anchor, int[] peers, int flag_off, int channel, int rank, int epoch, Tensor(a!) status) -> ()");
   m.def(
       "symm_all_reduce(Tensor(a!) buf, int[] peers, int flag_off, int data_off, int mc_base, float scale, int rank, "
@@ -567,6 +614,7 @@ TORCH_LIBRARY_IMPL(dion_b200, CUDA, m) {
   m.impl("embedding_bwd", &embedding_bwd);
   m.impl("chol_inverse", &chol_inverse);
   m.impl("col_sumsq", &col_sumsq);
+  m.impl("gemm_scatter", &gemm_scatter);
   m.impl("symm_barrier", &symm_barrier);
   m.impl("symm_all_reduce", &symm_all_reduce);
   m.impl("symm_reduce_into", &symm_reduce_into);

@@ -49,6 +49,8 @@ struct KernelParams {
   long long ldd2, d2_batch_stride;
   void* const* d2_ptrs;
   int epilogue, act, symmetric;
+  int scatter_mode, scatter_block, scatter_dests;  // D tiles go to per-destination buffers (peer memory)
+  void* const* scatter_ptrs;
   int vec_c, vec_d, vec_d2;  // 16-byte vector access allowed
   int* status;
 };
@@ -363,10 +365,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               }
             }
           }
-          // store D
+          // store D; in scatter mode the destination buffer depends on the row (mode 1) or
+          // on the column chunk (mode 2): element (row, col) of batch b lands in
+          // scatter_ptrs[b * dests + k] at local (row - k * block, col) resp. (row, col - k * block)
+          char* dd_base = d_base;
+          long long drow = row;
+          int dcol0 = col0;
+          if (p.scatter_mode == 1 && row_ok) {
+            const int k = row / p.scatter_block;
+            dd_base = reinterpret_cast<char*>(p.scatter_ptrs[(long long)t.batch * p.scatter_dests + k]);
+            drow = row - (long long)k * p.scatter_block;
+          } else if (p.scatter_mode == 2) {
+            const int k = col0 / p.scatter_block;
+            dd_base = reinterpret_cast<char*>(p.scatter_ptrs[(long long)t.batch * p.scatter_dests + k]);
+            dcol0 = col0 - k * p.scatter_block;
+          }
           if (row_ok) {
             if (p.d_is_bf16) {
-              __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(d_base) + (long long)row * p.ldd + col0;
+              __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(dd_base) + drow * p.ldd + dcol0;
               if (full_cols && p.vec_d) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
@@ -381,7 +397,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                   if (col0 + i < p.N) dp[i] = __float2bfloat16(v[i]);
               }
             } else {
-              float* dp = reinterpret_cast<float*>(d_base) + (long long)row * p.ldd + col0;
+              float* dp = reinterpret_cast<float*>(dd_base) + drow * p.ldd + dcol0;
               if (full_cols && p.vec_d) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 4)
@@ -586,9 +602,17 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
     g_last_error = "symmetric mode needs M == N";
     return cudaErrorInvalidValue;
   }
-  if (!a.D && !a.d_ptrs) {
+  if (!a.D && !a.d_ptrs && !a.scatter_ptrs) {
     g_last_error = "GEMM output missing";
     return cudaErrorInvalidValue;
+  }
+  if (a.scatter_mode != 0) {
+    if (!a.scatter_ptrs || a.scatter_block <= 0 || a.scatter_dests <= 0 || a.symmetric ||
+        a.epilogue != kEpiStore || (a.scatter_mode == 2 && a.scatter_block % 32 != 0) ||
+        (long long)a.scatter_block * a.scatter_dests < (a.scatter_mode == 1 ? a.M : a.N)) {
+      g_last_error = "invalid scatter epilogue (mode 2 needs a block that is a multiple of 32 columns)";
+      return cudaErrorInvalidValue;
+    }
   }
   const bool tf32 = a.ab_dtype == kF32;
   const int es = tf32 ? 4 : 2;
@@ -650,12 +674,17 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   kp.epilogue = a.epilogue;
   kp.act = a.act;
   kp.symmetric = a.symmetric;
+  kp.scatter_mode = a.scatter_mode;
+  kp.scatter_block = a.scatter_block;
+  kp.scatter_dests = a.scatter_dests;
+  kp.scatter_ptrs = a.scatter_ptrs;
   kp.status = a.status;
   // Vector access needs aligned bases and pitches; per-batch pointer arrays are
   // required to satisfy this by contract (checked by the Python wrapper).
   const int ces = kp.c_is_bf16 ? 2 : 4, des = kp.d_is_bf16 ? 2 : 4;
   kp.vec_c = (a.c_ptrs || aligned16(a.C, a.ldc, ces)) && ((a.c_batch_stride * ces) % 16 == 0);
   kp.vec_d = (a.d_ptrs || aligned16(a.D, a.ldd, des)) && ((a.d_batch_stride * des) % 16 == 0);
+  if (a.scatter_mode != 0) kp.vec_d = ((a.ldd * des) % 16 == 0);  // block bases are 16-byte aligned by contract
   kp.vec_d2 = (a.d2_ptrs || aligned16(a.D2, a.ldd2, 2)) && ((a.d2_batch_stride * 2) % 16 == 0);
 
   return tf32 ? launch_major<true>(a, kp, bn, stream) : launch_major<false>(a, kp, bn, stream);

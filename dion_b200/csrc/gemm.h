@@ -55,6 +55,16 @@ struct GemmArgs {
   // Symmetric mode (M == N, result known symmetric, e.g. X * X^T): only tiles on or
   // above the diagonal are computed and each off-diagonal tile is also stored transposed.
   int symmetric = 0;
+  // Scatter epilogue: D is not one matrix but `scatter_dests` blocks per batch element, each
+  // in its own buffer (typically another GPU's memory, written with peer stores):
+  //   mode 1: block k holds rows    [k * scatter_block, (k + 1) * scatter_block)
+  //   mode 2: block k holds columns [k * scatter_block, (k + 1) * scatter_block)  (multiple of 32)
+  // `scatter_ptrs` is a device array of batch * scatter_dests base pointers; ldd is the row
+  // pitch inside a block; d_dtype its element type.
+  int scatter_mode = 0;
+  int scatter_block = 0;
+  int scatter_dests = 0;
+  void* const* scatter_ptrs = nullptr;
   int block_n = 0;  // 0 = choose automatically (64 / 128 / 256)
   int max_ctas = 0;  // 0 = one CTA per SM
 

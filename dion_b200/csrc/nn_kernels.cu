@@ -137,8 +137,26 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const bf16* __restrict
 }
 
 // ------------------------------------------------------------------ rotary + QK norm
-// One warp per (token, head) row of q and of k.  HD is 64 or 128; a lane owns the
-// rotation pairs (p, p + HD/2) for p = lane (+32).
+// HD / 8 lanes share one (token, head) row of q or k: every lane owns four consecutive
+// rotation pairs (p, p + HD/2), i.e. one 8-byte load from each half of the row.
+__device__ __forceinline__ void unpack4(const uint2& q, float (&f)[4]) {
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.y));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+__device__ __forceinline__ uint2 pack4(const float (&f)[4]) {
+  uint2 q;
+  *reinterpret_cast<__nv_bfloat162*>(&q.x) = __floats2bfloat162_rn(f[0], f[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&q.y) = __floats2bfloat162_rn(f[2], f[3]);
+  return q;
+}
+template <int LPR>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
 template <int HD>
 __global__ void __launch_bounds__(256) rope_qknorm_fwd_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
                                                              bf16* __restrict__ qo, bf16* __restrict__ ko,
@@ -147,38 +165,43 @@ __global__ void __launch_bounds__(256) rope_qknorm_fwd_kernel(const bf16* __rest
                                                              int seq_len, int heads, long long in_pitch,
                                                              long long out_pitch, float eps) {
   constexpr int HALF = HD / 2;
-  constexpr int PPL = HALF / 32;  // pairs per lane
-  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  constexpr int LPR = HD / 8;  // lanes per row
+  const long long gid = (long long)blockIdx.x * 256 + threadIdx.x;
+  const long long rid = gid / LPR;
+  const int sub = (int)(gid - rid * LPR);
   const long long nrows = tokens * heads * 2;
-  if (wid >= nrows) return;
-  const int lane = threadIdx.x & 31;
-  const int which = (int)(wid & 1);  // 0 = q, 1 = k
-  const long long th = wid >> 1;
+  const bool live = rid < nrows;
+  const long long r = live ? rid : 0;
+  const int which = (int)(r & 1);  // 0 = q, 1 = k
+  const long long th = r >> 1;
   const long long tok = th / heads;
   const int head = (int)(th - tok * heads);
   const int pos = (int)(tok % seq_len);
+  const int p = sub * 4;
   const bf16* src = (which ? k : q) + tok * in_pitch + (long long)head * HD;
-  bf16* dst = (which ? ko : qo) + tok * out_pitch + (long long)head * HD;
-  float y1[PPL], y2[PPL];
+  float x1[4], x2[4], c[4], sn[4], y1[4], y2[4];
+  unpack4(*reinterpret_cast<const uint2*>(src + p), x1);
+  unpack4(*reinterpret_cast<const uint2*>(src + p + HALF), x2);
+  unpack4(*reinterpret_cast<const uint2*>(cosb + (long long)pos * HALF + p), c);
+  unpack4(*reinterpret_cast<const uint2*>(sinb + (long long)pos * HALF + p), sn);
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < PPL; ++i) {
-    const int p = lane + i * 32;
-    const float x1 = __bfloat162float(src[p]);
-    const float x2 = __bfloat162float(src[p + HALF]);
-    const float c = __bfloat162float(cosb[(long long)pos * HALF + p]);
-    const float s = __bfloat162float(sinb[(long long)pos * HALF + p]);
-    y1[i] = x1 * c + x2 * s;
-    y2[i] = x2 * c - x1 * s;
+  for (int i = 0; i < 4; ++i) {
+    y1[i] = x1[i] * c[i] + x2[i] * sn[i];
+    y2[i] = x2[i] * c[i] - x1[i] * sn[i];
     ss += y1[i] * y1[i] + y2[i] * y2[i];
   }
-  ss = warp_sum(ss);
-  const float r = rsqrtf(ss / (float)HD + eps);
+  ss = group_sum<LPR>(ss);
+  const float rs = rsqrtf(ss / (float)HD + eps);
 #pragma unroll
-  for (int i = 0; i < PPL; ++i) {
-    const int p = lane + i * 32;
-    dst[p] = __float2bfloat16(y1[i] * r);
-    dst[p + HALF] = __float2bfloat16(y2[i] * r);
+  for (int i = 0; i < 4; ++i) {
+    y1[i] *= rs;
+    y2[i] *= rs;
+  }
+  if (live) {
+    bf16* dst = (which ? ko : qo) + tok * out_pitch + (long long)head * HD;
+    *reinterpret_cast<uint2*>(dst + p) = pack4(y1);
+    *reinterpret_cast<uint2*>(dst + p + HALF) = pack4(y2);
   }
 }
 
@@ -192,46 +215,52 @@ __global__ void __launch_bounds__(256) rope_qknorm_bwd_kernel(const bf16* __rest
                                                              int seq_len, int heads, long long in_pitch,
                                                              long long out_pitch, float eps) {
   constexpr int HALF = HD / 2;
-  constexpr int PPL = HALF / 32;
-  const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  constexpr int LPR = HD / 8;
+  const long long gid = (long long)blockIdx.x * 256 + threadIdx.x;
+  const long long rid = gid / LPR;
+  const int sub = (int)(gid - rid * LPR);
   const long long nrows = tokens * heads * 2;
-  if (wid >= nrows) return;
-  const int lane = threadIdx.x & 31;
-  const int which = (int)(wid & 1);
-  const long long th = wid >> 1;
+  const bool live = rid < nrows;
+  const long long r = live ? rid : 0;
+  const int which = (int)(r & 1);
+  const long long th = r >> 1;
   const long long tok = th / heads;
   const int head = (int)(th - tok * heads);
   const int pos = (int)(tok % seq_len);
+  const int p = sub * 4;
   const bf16* src = (which ? k : q) + tok * in_pitch + (long long)head * HD;
   const bf16* gsrc = (which ? dko : dqo) + tok * out_pitch + (long long)head * HD;
-  bf16* gdst = (which ? dk : dq) + tok * in_pitch + (long long)head * HD;
-  float y1[PPL], y2[PPL], g1[PPL], g2[PPL], cs[PPL], sn[PPL];
+  float x1[4], x2[4], c[4], sn[4], y1[4], y2[4], g1[4], g2[4];
+  unpack4(*reinterpret_cast<const uint2*>(src + p), x1);
+  unpack4(*reinterpret_cast<const uint2*>(src + p + HALF), x2);
+  unpack4(*reinterpret_cast<const uint2*>(cosb + (long long)pos * HALF + p), c);
+  unpack4(*reinterpret_cast<const uint2*>(sinb + (long long)pos * HALF + p), sn);
+  unpack4(*reinterpret_cast<const uint2*>(gsrc + p), g1);
+  unpack4(*reinterpret_cast<const uint2*>(gsrc + p + HALF), g2);
   float ss = 0.f, dot = 0.f;
 #pragma unroll
-  for (int i = 0; i < PPL; ++i) {
-    const int p = lane + i * 32;
-    const float x1 = __bfloat162float(src[p]);
-    const float x2 = __bfloat162float(src[p + HALF]);
-    cs[i] = __bfloat162float(cosb[(long long)pos * HALF + p]);
-    sn[i] = __bfloat162float(sinb[(long long)pos * HALF + p]);
-    y1[i] = x1 * cs[i] + x2 * sn[i];
-    y2[i] = x2 * cs[i] - x1 * sn[i];
-    g1[i] = __bfloat162float(gsrc[p]);
-    g2[i] = __bfloat162float(gsrc[p + HALF]);
+  for (int i = 0; i < 4; ++i) {
+    y1[i] = x1[i] * c[i] + x2[i] * sn[i];
+    y2[i] = x2[i] * c[i] - x1[i] * sn[i];
     ss += y1[i] * y1[i] + y2[i] * y2[i];
     dot += g1[i] * y1[i] + g2[i] * y2[i];
   }
-  ss = warp_sum(ss);
-  dot = warp_sum(dot);
-  const float r = rsqrtf(ss / (float)HD + eps);
-  const float c3 = r * r * r * dot / (float)HD;
+  ss = group_sum<LPR>(ss);
+  dot = group_sum<LPR>(dot);
+  const float rs = rsqrtf(ss / (float)HD + eps);
+  const float c3 = rs * rs * rs * dot / (float)HD;
+  float o1[4], o2[4];
 #pragma unroll
-  for (int i = 0; i < PPL; ++i) {
-    const int p = lane + i * 32;
-    const float d1 = r * g1[i] - c3 * y1[i];  // grad w.r.t. rotated values
-    const float d2 = r * g2[i] - c3 * y2[i];
-    gdst[p] = __float2bfloat16(d1 * cs[i] - d2 * sn[i]);
-    gdst[p + HALF] = __float2bfloat16(d1 * sn[i] + d2 * cs[i]);
+  for (int i = 0; i < 4; ++i) {
+    const float d1 = rs * g1[i] - c3 * y1[i];  // gradient w.r.t. the rotated values
+    const float d2 = rs * g2[i] - c3 * y2[i];
+    o1[i] = d1 * c[i] - d2 * sn[i];
+    o2[i] = d1 * sn[i] + d2 * c[i];
+  }
+  if (live) {
+    bf16* gdst = (which ? dk : dq) + tok * in_pitch + (long long)head * HD;
+    *reinterpret_cast<uint2*>(gdst + p) = pack4(o1);
+    *reinterpret_cast<uint2*>(gdst + p + HALF) = pack4(o2);
   }
 }
 
@@ -262,18 +291,20 @@ __global__ void __launch_bounds__(256) relu2_bwd_kernel(const uint4* __restrict_
 }
 
 // ------------------------------------------------------------------ cross entropy
-// One 1024-thread block per row; the bf16 row lives in registers (<= 131072 columns).
-constexpr int kCeThreads = 1024;
-constexpr int kCeMaxVec = 16;
+// One 256-thread block per row.  Pass 1 streams the bf16 row once and keeps an online
+// (max, sum-exp) pair per thread; pass 2 re-reads the row (it is still in L2) and writes the
+// gradient in place.  Nothing is kept in registers, so any vocabulary size works and eight
+// rows are resident per SM.
+constexpr int kCeThreads = 256;
 
-__device__ __forceinline__ float block_reduce(float v, bool is_max, float* red) {
-  v = is_max ? warp_max(v) : warp_sum(v);
-  __syncthreads();
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
-  __syncthreads();
-  float r = red[threadIdx.x & 31];
-  r = is_max ? warp_max(r) : warp_sum(r);
-  return r;
+__device__ __forceinline__ void online_merge(float& m, float& s, float m2, float s2) {
+  const float mx = fmaxf(m, m2);
+  if (mx == -INFINITY) {
+    s = 0.f;
+  } else {
+    s = s * __expf(m - mx) + s2 * __expf(m2 - mx);
+  }
+  m = mx;
 }
 
 __global__ void __launch_bounds__(kCeThreads) cross_entropy_kernel(bf16* __restrict__ logits,
@@ -282,7 +313,7 @@ __global__ void __launch_bounds__(kCeThreads) cross_entropy_kernel(bf16* __restr
                                                                   const float* __restrict__ scale_ptr,
                                                                   int vocab, long long pitch, float grad_scale,
                                                                   long long ignore_index, int write_grad) {
-  __shared__ float red[32];
+  __shared__ float red_m[kCeThreads / 32], red_s[kCeThreads / 32];
   const long long row = blockIdx.x;
   const long long tgt = targets[row];
   uint4* lr = reinterpret_cast<uint4*>(logits + row * pitch);
@@ -295,55 +326,51 @@ __global__ void __launch_bounds__(kCeThreads) cross_entropy_kernel(bf16* __restr
     }
     return;
   }
-  uint4 keep[kCeMaxVec];
-  float mx = -INFINITY;
+  // pass 1: online softmax statistics
+  float m = -INFINITY, ssum = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += kCeThreads) {
+    float f[8];
+    unpack8(lr[v], f);
+    float mv = f[0];
 #pragma unroll
-  for (int i = 0; i < kCeMaxVec; ++i) {
-    const int v = threadIdx.x + i * kCeThreads;
-    if (v < nvec) {
-      keep[i] = lr[v];
-      float f[8];
-      unpack8(keep[i], f);
+    for (int j = 1; j < 8; ++j) mv = fmaxf(mv, f[j]);
+    const float mx = fmaxf(m, mv);
+    float acc = ssum * __expf(m - mx);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) mx = fmaxf(mx, f[j]);
-    }
+    for (int j = 0; j < 8; ++j) acc += __expf(f[j] - mx);
+    ssum = acc;
+    m = mx;
   }
-  mx = block_reduce(mx, true, red);
-  float se = 0.f;
 #pragma unroll
-  for (int i = 0; i < kCeMaxVec; ++i) {
-    const int v = threadIdx.x + i * kCeThreads;
-    if (v < nvec) {
-      float f[8];
-      unpack8(keep[i], f);
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o);
+    const float s2 = __shfl_xor_sync(0xffffffffu, ssum, o);
+    online_merge(m, ssum, m2, s2);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    red_m[threadIdx.x >> 5] = m;
+    red_s[threadIdx.x >> 5] = ssum;
+  }
+  __syncthreads();
+  m = red_m[0];
+  ssum = red_s[0];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) se += __expf(f[j] - mx);
-    }
-  }
-  se = block_reduce(se, false, red);
-  const float lse = mx + __logf(se);
-  if (threadIdx.x == 0) {
-    const float tl = __bfloat162float(logits[row * pitch + tgt]);
-    row_loss[row] = lse - tl;
-  }
+  for (int w = 1; w < kCeThreads / 32; ++w) online_merge(m, ssum, red_m[w], red_s[w]);
+  const float tl = __bfloat162float(logits[row * pitch + tgt]);
+  if (threadIdx.x == 0) row_loss[row] = m + __logf(ssum) - tl;
   if (!write_grad) return;
-  __syncthreads();  // the target logit was read before any thread overwrites the row
+  __syncthreads();  // every thread has read the target logit before the row is overwritten
+  // pass 2: gradient, in place
   const float gs = grad_scale * (scale_ptr ? *scale_ptr : 1.f);
-  const float inv = 1.f / se;
+  const float inv = gs / ssum;
+  const int tv = (int)(tgt >> 3), tj = (int)(tgt & 7);
+  for (int v = threadIdx.x; v < nvec; v += kCeThreads) {
+    float f[8];
+    unpack8(lr[v], f);
 #pragma unroll
-  for (int i = 0; i < kCeMaxVec; ++i) {
-    const int v = threadIdx.x + i * kCeThreads;
-    if (v < nvec) {
-      float f[8];
-      unpack8(keep[i], f);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float p = __expf(f[j] - mx) * inv;
-        if ((long long)v * 8 + j == tgt) p -= 1.f;
-        f[j] = p * gs;
-      }
-      lr[v] = pack8(f);
-    }
+    for (int j = 0; j < 8; ++j) f[j] = __expf(f[j] - m) * inv;
+    if (v == tv) f[tj] -= gs;
+    lr[v] = pack8(f);
   }
 }
 
@@ -415,7 +442,8 @@ cudaError_t rope_qknorm_fwd_launch(const void* q, const void* k, void* q_out, vo
                                    long long in_pitch, long long out_pitch, float eps, cudaStream_t s) {
   const long long nrows = tokens * heads * 2;
   if (nrows == 0) return cudaSuccess;
-  const unsigned grid = (unsigned)((nrows + 7) / 8);
+  if (in_pitch % 4 != 0 || out_pitch % 4 != 0) return cudaErrorInvalidValue;
+  const unsigned grid = (unsigned)((nrows * (head_dim / 8) + 255) / 256);
 #define DION_ROPE_FWD(HD)                                                                                         \
   rope_qknorm_fwd_kernel<HD><<<grid, 256, 0, s>>>(                                                                \
       reinterpret_cast<const bf16*>(q), reinterpret_cast<const bf16*>(k), reinterpret_cast<bf16*>(q_out),         \
@@ -433,7 +461,8 @@ cudaError_t rope_qknorm_bwd_launch(const void* dq_out, const void* dk_out, const
                                    cudaStream_t s) {
   const long long nrows = tokens * heads * 2;
   if (nrows == 0) return cudaSuccess;
-  const unsigned grid = (unsigned)((nrows + 7) / 8);
+  if (in_pitch % 4 != 0 || out_pitch % 4 != 0) return cudaErrorInvalidValue;
+  const unsigned grid = (unsigned)((nrows * (head_dim / 8) + 255) / 256);
 #define DION_ROPE_BWD(HD)                                                                                         \
   rope_qknorm_bwd_kernel<HD><<<grid, 256, 0, s>>>(                                                                \
       reinterpret_cast<const bf16*>(dq_out), reinterpret_cast<const bf16*>(dk_out),                               \
@@ -468,7 +497,7 @@ cudaError_t cross_entropy_fwd_bwd_launch(void* logits, const long long* targets,
                                          const float* scale_ptr, long long rows, int vocab, long long pitch,
                                          float grad_scale, long long ignore_index, bool write_grad, cudaStream_t s) {
   if (rows == 0) return cudaSuccess;
-  if (vocab % 8 != 0 || pitch % 8 != 0 || vocab > kCeThreads * kCeMaxVec * 8) return cudaErrorInvalidValue;
+  if (vocab % 8 != 0 || pitch % 8 != 0) return cudaErrorInvalidValue;
   cross_entropy_kernel<<<(unsigned)rows, kCeThreads, 0, s>>>(reinterpret_cast<bf16*>(logits), targets, row_loss,
                                                             scale_ptr, vocab, pitch, grad_scale, ignore_index,
                                                             write_grad ? 1 : 0);

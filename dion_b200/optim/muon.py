@@ -24,6 +24,7 @@ from torch.optim.optimizer import Optimizer, ParamsT
 
 from .. import ops
 from ..ops import nn as nn_ops
+from ..parallel import symm
 from .common import Scheduler, to_local
 from .newton_schulz import newton_schulz, newton_schulz_torch, zeropower_via_newtonschulz5  # noqa: F401
 
@@ -65,6 +66,10 @@ def _exchange(out: Tensor, inp: Tensor, group: ProcessGroup) -> None:
     chunk = inp.shape[0] // world
     for s in range(world):
         out[s * chunk:(s + 1) * chunk].copy_(gathered[s][rank * chunk:(rank + 1) * chunk])
+
+
+class _ArenaTooSmall(Exception):
+    """The symmetric arena cannot hold this step's exchange buffers yet."""
 
 
 class Muon(Optimizer):
@@ -157,6 +162,11 @@ class Muon(Optimizer):
             else:
                 raise ValueError(f"Unknown algorithm: {algo}")
 
+        if muon_groups and self._process_group is not None and self._world_size > 1:
+            first = next((p for g in muon_groups for p in g["params"] if p.grad is not None), None)
+            if first is not None:
+                symm.begin_step([self._process_group], to_local(first).device)
+
         def tasks():
             for group in muon_groups:
                 yield from self._muon_tasks(group)
@@ -248,10 +258,18 @@ class Muon(Optimizer):
         sumsq = torch.zeros(Bp, dtype=torch.float32, device=X[0].device) if use_sumsq else None
         ops.muon_momentum(G, M, mu=mu, nesterov=nesterov, U=list(U[:B].unbind(0)), sumsq=sumsq)
 
+        if distributed and shard_dim is not None and params[0].size(shard_dim) % W != 0:
+            raise AssertionError(
+                f"Shard dimension {shard_dim} size {params[0].size(shard_dim)} is not divisible by world size {W}.")
+        if distributed and shard_dim is not None and self._fused_exchange_ok(params[0], X[0], shard_dim):
+            # shards travel by peer stores issued from the momentum kernel and from the epilogue of
+            # the last Newton-Schulz product; see _muon_update_class_fused
+            try:
+                self._muon_update_class_fused(params, X, G, M, group, shard_dim, per, Bp)
+                return
+            except _ArenaTooSmall:
+                pass  # the arena grows at the next step; this step uses the library collectives
         if distributed and shard_dim is not None:
-            if params[0].size(shard_dim) % W != 0:
-                raise AssertionError(
-                    f"Shard dimension {shard_dim} size {params[0].size(shard_dim)} is not divisible by world size {W}.")
             # shards of the matrices a rank owns travel to it: [W, per, *local] by source rank
             if sumsq is not None:
                 work_n = dist.all_reduce(sumsq, group=pg, async_op=True)
@@ -288,6 +306,74 @@ class Muon(Optimizer):
         shadows = [nn_ops.shadow_for_update(p) for p in params]
         shadow_arg = shadows if all(s is not None for s in shadows) and X[0].is_cuda else None
         ops.muon_apply(X, list(U[:B].unbind(0)), decay=1.0 - lr * wd, step=adjusted_lr, shadow=shadow_arg)
+        for p in params:
+            if shadow_arg is not None:
+                nn_ops.mark_shadow_fresh(p)
+            else:
+                nn_ops.mark_shadow_stale(p)
+
+    def _fused_exchange_ok(self, p: Tensor, x_local: Tensor, shard_dim: int) -> bool:
+        if self._custom_ns or not x_local.is_cuda or x_local.dim() != 2 or x_local.dtype != torch.float32:
+            return False
+        arena = symm.arena_for(self._process_group)
+        if arena is None:
+            return False
+        # column blocks must be whole 32-column chunks of the epilogue; pitches 16-byte aligned
+        if shard_dim == 1 and x_local.shape[1] % 32 != 0:
+            return False
+        return (x_local.shape[1] * 2) % 16 == 0
+
+    def _muon_update_class_fused(self, params, X, G, M, group, shard_dim: int, per: int, Bp: int) -> None:
+        """Sharded Muon update whose two all-to-alls are peer stores issued by the kernels that
+        produce the data (dion/muon.py:404-435 does them as NCCL all_to_all calls):
+          1. the momentum kernel writes every bf16 shard directly into the receive buffer of the
+             rank that owns the matrix;
+          2. after a flag barrier the owner runs Newton-Schulz on its whole matrices;
+          3. the epilogue of the last product stores each row/column block of the result into the
+             update buffer of the rank that holds that shard;
+          4. after a second barrier every rank applies its shards."""
+        lr, mu, wd, eps = group["lr"], group["mu"], group["weight_decay"], group["epsilon"]
+        W, rank, pg = self._world_size, self._device_rank, self._process_group
+        arena = symm.arena_for(pg)
+        B = len(params)
+        local_shape = tuple(X[0].shape)
+        full_shape = tuple(params[0].shape)
+        dev = X[0].device
+        recv = symm.empty(pg, (per, W, *local_shape), torch.bfloat16, dev)   # [owned matrix, source rank]
+        upd = symm.empty(pg, (Bp, *local_shape), torch.bfloat16, dev)        # [matrix of the class]
+        if arena.offset_of(recv) is None or arena.offset_of(upd) is None:
+            raise _ArenaTooSmall()
+        # 1. momentum + Nesterov + bf16 cast, stored into the owners' receive buffers
+        peer_recv = [arena.peer_view(d, recv) for d in range(W)]
+        U = [peer_recv[i // per][i % per, rank] for i in range(B)]
+        ops.muon_momentum(G, M, mu=mu, nesterov=group["nesterov"], U=U, sumsq=None)
+        arena.barrier()
+        # 2./3. Newton-Schulz on the matrices this rank owns, result scattered to the shard holders
+        cnt = max(0, min(per, B - rank * per))
+        if cnt > 0:
+            if shard_dim == 0:
+                whole = recv[:cnt].reshape(cnt, *full_shape)                  # row blocks are already in place
+                mode, block = 1, local_shape[0]
+            else:
+                whole = recv[:cnt].permute(0, 2, 1, 3).reshape(cnt, *full_shape)
+                mode, block = 2, local_shape[1]
+            shard_bytes = X[0].numel() * 2
+            key = (arena.peers[0], arena.offset_of(upd), cnt, per, rank)
+            cache = getattr(self, "_scatter_cache", None)
+            if cache is None:
+                cache = self._scatter_cache = {}
+            ptrs = cache.get(key)
+            if ptrs is None:
+                addr = [[arena.peer_address(s, upd) + (rank * per + j) * shard_bytes for s in range(W)]
+                        for j in range(cnt)]
+                ptrs = cache[key] = torch.tensor(addr, dtype=torch.int64, device=dev).view(-1)
+            newton_schulz(whole, eps, scatter=dict(ptrs=ptrs, mode=mode, block=block, dests=W, block_like=upd[0]))
+        arena.barrier()
+        # 4. apply
+        adjusted_lr = _ADJUST[group["adjust_lr"]](lr, params[0].shape)
+        shadows = [nn_ops.shadow_for_update(p) for p in params]
+        shadow_arg = shadows if all(s is not None for s in shadows) else None
+        ops.muon_apply(X, list(upd[:B].unbind(0)), decay=1.0 - lr * wd, step=adjusted_lr, shadow=shadow_arg)
         for p in params:
             if shadow_arg is not None:
                 nn_ops.mark_shadow_fresh(p)

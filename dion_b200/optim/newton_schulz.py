@@ -46,11 +46,18 @@ def newton_schulz_torch(G: Tensor, epsilon: float = 1e-7,
 
 
 def newton_schulz(G: Tensor, epsilon: float = 1e-7, coeffs: Sequence[Tuple[float, float, float]] = NS_COEFFS,
-                  sumsq: Optional[Tensor] = None) -> Tensor:
+                  sumsq: Optional[Tensor] = None, scatter: Optional[dict] = None) -> Optional[Tensor]:
     """Orthogonalise ``G`` (``[m, n]`` or a batch ``[B, m, n]``); returns bf16 of the same shape.
 
     ``sumsq`` (fp32 ``[B]``), when given, is the squared Frobenius norm of every matrix,
-    e.g. accumulated by the momentum kernel, so that no extra pass over G is needed."""
+    e.g. accumulated by the momentum kernel, so that no extra pass over G is needed.
+
+    ``scatter`` (CUDA only) makes the last product write its result tiles straight into
+    per-destination blocks instead of one output tensor - the all-to-all that returns the
+    shards of every orthogonalised matrix to their owners, done by the GEMM epilogue with
+    peer stores.  Keys: ``ptrs`` (int64 CUDA tensor, B * dests block addresses), ``mode``
+    (1 = row blocks, 2 = column blocks), ``block``, ``dests``, ``block_like`` (a tensor with
+    the dtype and row pitch of one block).  Nothing is returned in that case."""
     if not G.is_cuda:
         return newton_schulz_torch(G, float(epsilon), coeffs)
     squeeze = G.dim() == 2
@@ -70,15 +77,22 @@ def newton_schulz(G: Tensor, epsilon: float = 1e-7, coeffs: Sequence[Tuple[float
     A = torch.empty(Bn, k, k, device=X.device, dtype=torch.bfloat16)
     Bm = torch.empty_like(A)
     Y = torch.empty_like(X)
-    for a, b, c in coeffs:
+    for it, (a, b, c) in enumerate(coeffs):
+        last = it == len(coeffs) - 1
         if tall:
             ops.gemm(X.transpose(1, 2), X, out=A, symmetric=True)        # A = X^T X
             ops.gemm(A, A.transpose(1, 2), c=A, out=Bm, alpha=c, beta=b, symmetric=True)  # b A + c A A
-            ops.gemm(X, Bm, c=X, out=Y, alpha=1.0, beta=a)                # a X + X B
+            lhs, rhs = X, Bm                                              # a X + X B
         else:
             ops.gemm(X, X.transpose(1, 2), out=A, symmetric=True)        # A = X X^T
             ops.gemm(A, A.transpose(1, 2), c=A, out=Bm, alpha=c, beta=b, symmetric=True)
-            ops.gemm(Bm, X, c=X, out=Y, alpha=1.0, beta=a)                # a X + B X
+            lhs, rhs = Bm, X                                              # a X + B X
+        if last and scatter is not None:
+            torch.ops.dion_b200.gemm_scatter(lhs, rhs, X, scatter["block_like"], scatter["ptrs"], scatter["mode"],
+                                             scatter["block"], scatter["dests"], 1.0, float(a),
+                                             ops.runtime.status_tensor(X.device))
+            return None
+        ops.gemm(lhs, rhs, c=X, out=Y, alpha=1.0, beta=a)
         X, Y = Y, X
     out = X[0] if squeeze else X
     return out.view(G.shape)

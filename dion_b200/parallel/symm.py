@@ -38,6 +38,9 @@ class SymmetricArena:
     def __init__(self, group: dist.ProcessGroup, nbytes: int, device: torch.device):
         import torch.distributed._symmetric_memory as symm_mem
 
+        from ..ops import _ext
+
+        _ext.load(required=True)
         self.group = group
         self.device = device
         self.capacity = int(nbytes)
@@ -84,6 +87,15 @@ class SymmetricArena:
 
     def offset_of(self, t: torch.Tensor) -> Optional[int]:
         return self._views.get(t.data_ptr())
+
+    def peer_view(self, rank: int, t: torch.Tensor) -> torch.Tensor:
+        """The buffer of `rank` that sits where `t` sits in this rank's arena (same shape and
+        dtype); writing to it stores into that GPU's memory over NVLink."""
+        off = self._views[t.data_ptr()]
+        return self.hdl.get_buffer(rank, tuple(t.shape), t.dtype, off // t.element_size())
+
+    def peer_address(self, rank: int, t: torch.Tensor) -> int:
+        return self.peers[rank] + self._views[t.data_ptr()]
 
     # -- collectives (stream ordered on the current stream)
     def all_reduce(self, t: torch.Tensor, off: int, average: bool) -> None:
