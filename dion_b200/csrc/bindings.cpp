@@ -429,6 +429,30 @@ void rope_qknorm_bwd(const Tensor& dq_out, const Tensor& dk_out, const Tensor& q
                                                heads * head_dim, (float)eps, at::cuda::getCurrentCUDAStream()));
 }
 
+// rotary embedding of one tensor [tokens, heads * head_dim], no normalisation
+void rope_fwd(const Tensor& x, Tensor out, const Tensor& cos, const Tensor& sin, int64_t seq_len, int64_t heads,
+              int64_t head_dim) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.scalar_type() == at::kBFloat16 && x.size(1) == heads * head_dim);
+  check_bf16(out, "out");
+  check_bf16(cos, "cos");
+  check_bf16(sin, "sin");
+  DION_CUDA_CHECK(dion::rope_qknorm_fwd_launch(x.data_ptr(), nullptr, out.data_ptr(), nullptr, cos.data_ptr(),
+                                               sin.data_ptr(), x.size(0), (int)seq_len, (int)heads, (int)head_dim,
+                                               x.stride(0), heads * head_dim, -1.f,
+                                               at::cuda::getCurrentCUDAStream()));
+}
+void rope_bwd(const Tensor& dout, const Tensor& x, Tensor dx, const Tensor& cos, const Tensor& sin, int64_t seq_len,
+              int64_t heads, int64_t head_dim) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && dx.dim() == 2 && dx.stride(1) == 1 && dx.stride(0) == x.stride(0));
+  check_bf16(dout, "dout");
+  DION_CUDA_CHECK(dion::rope_qknorm_bwd_launch(dout.data_ptr(), nullptr, x.data_ptr(), nullptr, dx.data_ptr(),
+                                               nullptr, cos.data_ptr(), sin.data_ptr(), x.size(0), (int)seq_len,
+                                               (int)heads, (int)head_dim, x.stride(0), heads * head_dim, -1.f,
+                                               at::cuda::getCurrentCUDAStream()));
+}
+
 void relu2_fwd(const Tensor& x, Tensor h) {
   check_bf16(x, "x");
   check_bf16(h, "h");
@@ -589,6 +613,8 @@ TORCH_LIBRARY(dion_b200, m) {
   m.def(
       "rope_qknorm_bwd(Tensor dq_out, Tensor dk_out, Tensor q, Tensor k, Tensor(a!) dq, Tensor(b!) dk, Tensor cos, "
       "Tensor sin, int seq_len, int heads, int head_dim, float eps) -> ()");
+  m.def("rope_fwd(Tensor x, Tensor(a!) out, Tensor cos, Tensor sin, int seq_len, int heads, int head_dim) -> ()");
+  m.def("rope_bwd(Tensor dout, Tensor x, Tensor(a!) dx, Tensor cos, Tensor sin, int seq_len, int heads, int head_dim) -> ()");
   m.def("relu2_fwd(Tensor x, Tensor(a!) h) -> ()");
   m.def("relu2_bwd(Tensor dh, Tensor x, Tensor(a!) dx) -> ()");
   m.def(
@@ -607,6 +633,8 @@ TORCH_LIBRARY_IMPL(dion_b200, CUDA, m) {
   m.impl("rmsnorm_bwd", &rmsnorm_bwd);
   m.impl("rope_qknorm_fwd", &rope_qknorm_fwd);
   m.impl("rope_qknorm_bwd", &rope_qknorm_bwd);
+  m.impl("rope_fwd", &rope_fwd);
+  m.impl("rope_bwd", &rope_bwd);
   m.impl("relu2_fwd", &relu2_fwd);
   m.impl("relu2_bwd", &relu2_bwd);
   m.impl("cross_entropy_fwd_bwd", &cross_entropy_fwd_bwd);

@@ -120,6 +120,60 @@ __device__ __forceinline__ float apply_act(float x, int act) {
   return x;
 }
 
+// 32 consecutive columns of one row, bf16 destination
+__device__ __forceinline__ void store_chunk_bf16(__nv_bfloat16* dp, const float (&v)[32], bool vec, int ncols) {
+  if (vec) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 8) {
+      uint4 q;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
+      *reinterpret_cast<uint4*>(dp + i) = q;
+    }
+  } else {
+    for (int i = 0; i < 32; ++i)
+      if (i < ncols) dp[i] = __float2bfloat16(v[i]);
+  }
+}
+
+// 32 consecutive columns of one row of C (bf16 or fp32) as floats; missing columns read as 0
+__device__ __forceinline__ void load_chunk(const char* base, bool is_bf16, long long elem, float (&c)[32], bool vec,
+                                           int ncols) {
+  if (is_bf16) {
+    const __nv_bfloat16* cp = reinterpret_cast<const __nv_bfloat16*>(base) + elem;
+    if (vec) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        const uint4 q = *reinterpret_cast<const uint4*>(cp + i);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h[j]);
+          c[i + 2 * j] = f.x;
+          c[i + 2 * j + 1] = f.y;
+        }
+      }
+    } else {
+      for (int i = 0; i < 32; ++i) c[i] = i < ncols ? __bfloat162float(cp[i]) : 0.f;
+    }
+  } else {
+    const float* cp = reinterpret_cast<const float*>(base) + elem;
+    if (vec) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        const float4 q = *reinterpret_cast<const float4*>(cp + i);
+        c[i] = q.x;
+        c[i + 1] = q.y;
+        c[i + 2] = q.z;
+        c[i + 3] = q.w;
+      }
+    } else {
+      for (int i = 0; i < 32; ++i) c[i] = i < ncols ? cp[i] : 0.f;
+    }
+  }
+}
+
 template <bool kTf32, int kAMajor, int kBMajor, int kBlockN>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -309,9 +363,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int i = 0; i < 32; ++i) v[i] = 0.f;
         }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = apply_act(p.alpha * v[i], p.act);
+        for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
 
         const bool full_cols = col0 + 32 <= p.N;
+        const int ncols = p.N - col0;  // valid columns of this chunk when it is the ragged last one
+        bool d2_done = false;
+        if (p.act == kActRelu2SavePre) {
+          // D2 keeps the pre-activation (what the backward pass needs), D gets relu(x)^2
+          if (row_ok && d2_base != nullptr)
+            store_chunk_bf16(reinterpret_cast<__nv_bfloat16*>(d2_base) + (long long)row * p.ldd2 + col0, v,
+                             full_cols && p.vec_d2, ncols);
+          d2_done = true;
+        }
+        if (p.act == kActRelu2 || p.act == kActRelu2SavePre) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = apply_act(v[i], kActRelu2);
+        }
         if (p.epilogue == kEpiAtomicAdd) {
           if (row_ok) {
             float* dp = reinterpret_cast<float*>(d_base) + (long long)row * p.ldd + col0;
@@ -327,42 +394,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
           }
         } else {
-          // beta * C
-          if (c_base != nullptr && p.beta != 0.f && row_ok) {
-            if (p.c_is_bf16) {
-              const __nv_bfloat16* cp =
-                  reinterpret_cast<const __nv_bfloat16*>(c_base) + (long long)row * p.ldc + col0;
-              if (full_cols && p.vec_c) {
+          // C operand: added (beta * C) or, for the ReLU^2 backward, multiplied in as 2 * relu(C)
+          if (c_base != nullptr && row_ok && (p.beta != 0.f || p.act == kActMulRelu2Grad)) {
+            float cv[32];
+            load_chunk(c_base, p.c_is_bf16 != 0, (long long)row * p.ldc + col0, cv, full_cols && p.vec_c, ncols);
+            if (p.act == kActMulRelu2Grad) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                  const uint4 q = *reinterpret_cast<const uint4*>(cp + i);
-                  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    const float2 f = __bfloat1622float2(h[j]);
-                    v[i + 2 * j] += p.beta * f.x;
-                    v[i + 2 * j + 1] += p.beta * f.y;
-                  }
-                }
-              } else {
-                for (int i = 0; i < 32; ++i)
-                  if (col0 + i < p.N) v[i] += p.beta * __bfloat162float(cp[i]);
-              }
+              for (int i = 0; i < 32; ++i) v[i] *= 2.f * fmaxf(cv[i], 0.f);
             } else {
-              const float* cp = reinterpret_cast<const float*>(c_base) + (long long)row * p.ldc + col0;
-              if (full_cols && p.vec_c) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                  const float4 q = *reinterpret_cast<const float4*>(cp + i);
-                  v[i] += p.beta * q.x;
-                  v[i + 1] += p.beta * q.y;
-                  v[i + 2] += p.beta * q.z;
-                  v[i + 3] += p.beta * q.w;
-                }
-              } else {
-                for (int i = 0; i < 32; ++i)
-                  if (col0 + i < p.N) v[i] += p.beta * cp[i];
-              }
+              for (int i = 0; i < 32; ++i) v[i] += p.beta * cv[i];
             }
           }
           // store D; in scatter mode the destination buffer depends on the row (mode 1) or
@@ -407,22 +448,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                   if (col0 + i < p.N) dp[i] = v[i];
               }
             }
-            if (d2_base != nullptr) {
-              __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(d2_base) + (long long)row * p.ldd2 + col0;
-              if (full_cols && p.vec_d2) {
-#pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                  uint4 q;
-                  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
-                  *reinterpret_cast<uint4*>(dp + i) = q;
-                }
-              } else {
-                for (int i = 0; i < 32; ++i)
-                  if (col0 + i < p.N) dp[i] = __float2bfloat16(v[i]);
-              }
-            }
+            if (d2_base != nullptr && !d2_done)
+              store_chunk_bf16(reinterpret_cast<__nv_bfloat16*>(d2_base) + (long long)row * p.ldd2 + col0, v,
+                               full_cols && p.vec_d2, ncols);
             if (mirror) {
               // transposed copy of an off-diagonal tile: D[col, row]; lanes hold
               // consecutive rows, so each store instruction is contiguous across the warp

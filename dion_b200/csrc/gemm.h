@@ -13,7 +13,12 @@ enum GemmEpilogue : int {
   kEpiStore = 0,      // D = act(alpha * acc) + beta * C
   kEpiAtomicAdd = 1,  // D += alpha * acc   (fp32 D, red.global.add; used with split-K)
 };
-enum GemmAct : int { kActNone = 0, kActRelu2 = 1 };
+enum GemmAct : int {
+  kActNone = 0,
+  kActRelu2 = 1,         // D = relu(alpha * acc)^2 (+ beta * C)
+  kActRelu2SavePre = 2,  // as kActRelu2, and D2 receives the pre-activation alpha * acc
+  kActMulRelu2Grad = 3,  // D = alpha * acc * 2 * relu(C): backward of ReLU^2 with C the saved pre-activation
+};
 
 // D[b] = alpha * op(A[b]) * op(B[b]) (+ beta * C[b]),  op(A) is M x K, op(B) is K x N.
 //

@@ -63,6 +63,7 @@ cudaError_t rmsnorm_fwd_launch(const void* x, const void* residual, void* x_out,
 cudaError_t rmsnorm_bwd_launch(const void* dy, const void* x, const float* rstd, const void* dx_add, void* dx,
                                long long rows, int dim, cudaStream_t s);
 // Rotary embedding (half-split) followed by RMS norm over head_dim, for q and k together.
+// k (with k_out / dk / dk_out) may be null to process a single tensor; eps < 0 skips the norm.
 // in/out: [tokens, heads, head_dim] bf16 rows with arbitrary row pitch; cos/sin: [seq, head_dim/2] bf16.
 cudaError_t rope_qknorm_fwd_launch(const void* q, const void* k, void* q_out, void* k_out, const void* cos,
                                    const void* sin, long long tokens, int seq_len, int heads, int head_dim,

@@ -169,11 +169,11 @@ __global__ void __launch_bounds__(256) rope_qknorm_fwd_kernel(const bf16* __rest
   const long long gid = (long long)blockIdx.x * 256 + threadIdx.x;
   const long long rid = gid / LPR;
   const int sub = (int)(gid - rid * LPR);
-  const long long nrows = tokens * heads * 2;
+  const long long nrows = tokens * heads * (k ? 2 : 1);
   const bool live = rid < nrows;
   const long long r = live ? rid : 0;
-  const int which = (int)(r & 1);  // 0 = q, 1 = k
-  const long long th = r >> 1;
+  const int which = k ? (int)(r & 1) : 0;  // 0 = q, 1 = k
+  const long long th = k ? (r >> 1) : r;
   const long long tok = th / heads;
   const int head = (int)(th - tok * heads);
   const int pos = (int)(tok % seq_len);
@@ -192,7 +192,7 @@ __global__ void __launch_bounds__(256) rope_qknorm_fwd_kernel(const bf16* __rest
     ss += y1[i] * y1[i] + y2[i] * y2[i];
   }
   ss = group_sum<LPR>(ss);
-  const float rs = rsqrtf(ss / (float)HD + eps);
+  const float rs = eps < 0.f ? 1.f : rsqrtf(ss / (float)HD + eps);  // eps < 0: rotary only, no norm
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     y1[i] *= rs;
@@ -219,11 +219,11 @@ __global__ void __launch_bounds__(256) rope_qknorm_bwd_kernel(const bf16* __rest
   const long long gid = (long long)blockIdx.x * 256 + threadIdx.x;
   const long long rid = gid / LPR;
   const int sub = (int)(gid - rid * LPR);
-  const long long nrows = tokens * heads * 2;
+  const long long nrows = tokens * heads * (k ? 2 : 1);
   const bool live = rid < nrows;
   const long long r = live ? rid : 0;
-  const int which = (int)(r & 1);
-  const long long th = r >> 1;
+  const int which = k ? (int)(r & 1) : 0;
+  const long long th = k ? (r >> 1) : r;
   const long long tok = th / heads;
   const int head = (int)(th - tok * heads);
   const int pos = (int)(tok % seq_len);
@@ -247,8 +247,8 @@ __global__ void __launch_bounds__(256) rope_qknorm_bwd_kernel(const bf16* __rest
   }
   ss = group_sum<LPR>(ss);
   dot = group_sum<LPR>(dot);
-  const float rs = rsqrtf(ss / (float)HD + eps);
-  const float c3 = rs * rs * rs * dot / (float)HD;
+  const float rs = eps < 0.f ? 1.f : rsqrtf(ss / (float)HD + eps);
+  const float c3 = eps < 0.f ? 0.f : rs * rs * rs * dot / (float)HD;
   float o1[4], o2[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -440,7 +440,7 @@ cudaError_t rmsnorm_bwd_launch(const void* dy, const void* x, const float* rstd,
 cudaError_t rope_qknorm_fwd_launch(const void* q, const void* k, void* q_out, void* k_out, const void* cos,
                                    const void* sin, long long tokens, int seq_len, int heads, int head_dim,
                                    long long in_pitch, long long out_pitch, float eps, cudaStream_t s) {
-  const long long nrows = tokens * heads * 2;
+  const long long nrows = tokens * heads * (k ? 2 : 1);
   if (nrows == 0) return cudaSuccess;
   if (in_pitch % 4 != 0 || out_pitch % 4 != 0) return cudaErrorInvalidValue;
   const unsigned grid = (unsigned)((nrows * (head_dim / 8) + 255) / 256);
@@ -459,7 +459,7 @@ cudaError_t rope_qknorm_bwd_launch(const void* dq_out, const void* dk_out, const
                                    void* dk, const void* cos, const void* sin, long long tokens, int seq_len,
                                    int heads, int head_dim, long long in_pitch, long long out_pitch, float eps,
                                    cudaStream_t s) {
-  const long long nrows = tokens * heads * 2;
+  const long long nrows = tokens * heads * (k ? 2 : 1);
   if (nrows == 0) return cudaSuccess;
   if (in_pitch % 4 != 0 || out_pitch % 4 != 0) return cudaErrorInvalidValue;
   const unsigned grid = (unsigned)((nrows * (head_dim / 8) + 255) / 256);

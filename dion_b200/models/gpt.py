@@ -113,10 +113,10 @@ class MLP(nn.Module):
         group, _ = _tp_group(self.c_fc.weight)
         if group is not None:
             h = TP.copy_to_tp_region(h, group)
-        u = K.linear(h, _local(self.c_fc.weight), act="relu2")
         if group is not None:
+            u = K.linear(h, _local(self.c_fc.weight), act="relu2")
             return residual + TP.reduce_from_tp_region(K.linear(u, _local(self.c_proj.weight)), group)
-        return K.linear(u, _local(self.c_proj.weight), residual=residual)
+        return K.mlp(h, _local(self.c_fc.weight), _local(self.c_proj.weight), residual)
 
 
 class Block(nn.Module):
@@ -126,8 +126,10 @@ class Block(nn.Module):
         self.mlp = MLP(config)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        x = self.attn(K.rms_norm(x), x)
-        x = self.mlp(K.rms_norm(x), x)
+        x, h = K.norm_branch(x)
+        x = self.attn(h, x)
+        x, h = K.norm_branch(x)
+        x = self.mlp(h, x)
         return x
 
 

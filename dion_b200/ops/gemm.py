@@ -14,7 +14,7 @@ import torch
 
 from . import runtime
 
-_ACT = {None: 0, "none": 0, "relu2": 1}
+_ACT = {None: 0, "none": 0, "relu2": 1, "relu2_save_pre": 2, "mul_relu2_grad": 3}
 
 
 def _apply_act(x: torch.Tensor, act) -> torch.Tensor:
@@ -29,9 +29,13 @@ def gemm_reference(a, b, *, c=None, out=None, alpha=1.0, beta=0.0, act=None, out
                    shadow=None, compute_dtype=torch.float32):
     """PyTorch implementation with the semantics of :func:`gemm` (fp32 accumulate)."""
     acc = torch.matmul(a.to(compute_dtype), b.to(compute_dtype)).float() * alpha
-    if c is not None and beta != 0.0:
-        acc = acc + beta * c.float()
-    res = _apply_act(acc, act)
+    pre = acc
+    if act == "mul_relu2_grad":
+        res = acc * 2.0 * torch.relu(c.float())
+    else:
+        res = _apply_act(acc, "relu2" if act == "relu2_save_pre" else act)
+        if c is not None and beta != 0.0:
+            res = res + beta * c.float()
     if out is None:
         out = torch.empty(acc.shape, dtype=out_dtype or a.dtype, device=a.device)
         accumulate = False
@@ -40,7 +44,7 @@ def gemm_reference(a, b, *, c=None, out=None, alpha=1.0, beta=0.0, act=None, out
     else:
         out.copy_(res.to(out.dtype))
     if shadow is not None:
-        shadow.copy_(out.to(shadow.dtype))
+        shadow.copy_((pre if act == "relu2_save_pre" else out).to(shadow.dtype))
     return out
 
 

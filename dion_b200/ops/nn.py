@@ -166,6 +166,62 @@ def linear(x: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tenso
     return y
 
 
+class _MLPFn(torch.autograd.Function):
+    """out = residual + relu(x W_fc^T)^2 W_proj^T with the activation fused into the GEMM
+    epilogues: the forward c_fc product writes both the pre-activation and relu^2 of it, the
+    backward c_proj product multiplies its result by 2 relu(pre) on the way out."""
+
+    @staticmethod
+    def forward(ctx, x, w_fc, w_proj, residual):
+        fc, pj = bf16_weight(w_fc), bf16_weight(w_proj)
+        T = x.shape[0]
+        pre = torch.empty(T, fc.shape[0], device=x.device, dtype=torch.bfloat16)
+        h = torch.empty_like(pre)
+        gemm(x, fc.t(), out=h, shadow=pre, act="relu2_save_pre")
+        out = torch.empty(T, pj.shape[0], device=x.device, dtype=torch.bfloat16)
+        gemm(h, pj.t(), c=residual, beta=1.0, out=out)
+        ctx.save_for_backward(x, w_fc, w_proj, pre, h)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w_fc, w_proj, pre, h = ctx.saved_tensors
+        fc, pj = bf16_weight(w_fc), bf16_weight(w_proj)
+        dy = dy.contiguous()
+        T = x.shape[0]
+        dpre = torch.empty_like(pre)
+        gemm(dy, pj, c=pre, out=dpre, act="mul_relu2_grad")          # (dy W_proj) * 2 relu(pre)
+        dw_proj = _weight_grad(dy, h, w_proj) if ctx.needs_input_grad[2] else None
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x)
+            gemm(dpre, fc, out=dx)
+        dw_fc = _weight_grad(dpre, x, w_fc) if ctx.needs_input_grad[1] else None
+        return dx, dw_fc, dw_proj, dy
+
+
+def _weight_grad(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """dW = dy^T x in fp32 (split over the token dimension when the tile grid is small)."""
+    N, K, T = dy.shape[1], x.shape[1], x.shape[0]
+    sk = _split_k_for(N, K, T)
+    if sk > 1:
+        dw = torch.zeros(N, K, device=x.device, dtype=torch.float32)
+        gemm(dy.t(), x, out=dw, accumulate=True, split_k=sk)
+    else:
+        dw = torch.empty(N, K, device=x.device, dtype=torch.float32)
+        gemm(dy.t(), x, out=dw)
+    return dw if weight.dtype == torch.float32 else dw.to(weight.dtype)
+
+
+def mlp(x: torch.Tensor, w_fc: torch.Tensor, w_proj: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+    """``residual + relu(x @ w_fc.T)**2 @ w_proj.T``."""
+    if _fast(x):
+        shp = x.shape
+        out = _MLPFn.apply(x.reshape(-1, shp[-1]), w_fc, w_proj, residual.reshape(-1, w_proj.shape[0]))
+        return out.view(*shp[:-1], w_proj.shape[0])
+    return linear(linear(x, w_fc, act="relu2"), w_proj, residual=residual)
+
+
 # --------------------------------------------------------------------------- RMSNorm
 
 class _RMSNormFn(torch.autograd.Function):
@@ -185,6 +241,35 @@ class _RMSNormFn(torch.autograd.Function):
         dx = torch.empty_like(x2)
         torch.ops.dion_b200.rmsnorm_bwd(dy2, x2, rstd, None, dx)
         return dx.view(dy.shape), None
+
+
+class _NormBranchFn(torch.autograd.Function):
+    """(x, rmsnorm(x)): hands the residual stream through unchanged next to its normalised
+    copy, so that the backward pass adds the two incoming gradients inside the norm kernel."""
+
+    @staticmethod
+    def forward(ctx, x, eps):
+        x2 = x.reshape(-1, x.shape[-1])
+        y = torch.empty_like(x2)
+        rstd = torch.empty(x2.shape[0], device=x.device, dtype=torch.float32)
+        torch.ops.dion_b200.rmsnorm_fwd(x2, None, None, y, rstd, eps)
+        ctx.save_for_backward(x2, rstd)
+        return x.view_as(x), y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dx_pass, dy):
+        x2, rstd = ctx.saved_tensors
+        dx = torch.empty_like(x2)
+        torch.ops.dion_b200.rmsnorm_bwd(dy.contiguous().view(x2.shape), x2, rstd,
+                                        dx_pass.contiguous().view(x2.shape), dx)
+        return dx.view(dy.shape), None
+
+
+def norm_branch(x: torch.Tensor, eps: float = RMS_EPS):
+    """Returns ``(x, rms_norm(x))`` for a pre-norm residual block."""
+    if _fast(x) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 4096 and x.is_contiguous():
+        return _NormBranchFn.apply(x, eps)
+    return x, rms_norm(x, eps)
 
 
 def rms_norm(x: torch.Tensor, eps: float = RMS_EPS) -> torch.Tensor:
@@ -256,6 +341,37 @@ def rope_qknorm(q: torch.Tensor, k: torch.Tensor, cos: torch.Tensor, sin: torch.
         qo, ko = _RopeQKNormFn.apply(q.view(B * T, H * Dh), k.view(B * T, H * Dh), cos, sin, T, H, Dh, eps)
         return qo.view(B, T, H, Dh), ko.view(B, T, H, Dh)
     return _rope_qknorm_torch(q, k, cos, sin, eps)
+
+
+class _RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin, seq_len, heads, head_dim):
+        out = torch.empty(x.shape[0], heads * head_dim, device=x.device, dtype=x.dtype)
+        torch.ops.dion_b200.rope_fwd(x, out, cos, sin, seq_len, heads, head_dim)
+        ctx.save_for_backward(x, cos, sin)
+        ctx.cfg = (seq_len, heads, head_dim)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        x, cos, sin = ctx.saved_tensors
+        seq_len, heads, head_dim = ctx.cfg
+        xc = x.contiguous()
+        dx = torch.empty_like(xc)
+        torch.ops.dion_b200.rope_bwd(dout.contiguous(), xc, dx, cos, sin, seq_len, heads, head_dim)
+        return dx, None, None, None, None, None
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotary embedding (half-split pairs) of ``x: [B, T, H, Dh]`` without normalisation."""
+    B, T, H, Dh = x.shape
+    if _fast(x) and Dh in (64, 128) and x.is_contiguous():
+        return _RopeFn.apply(x.view(B * T, H * Dh), cos, sin, T, H, Dh).view(B, T, H, Dh)
+    d = Dh // 2
+    x1, x2 = x[..., :d].float(), x[..., d:].float()
+    c = cos[None, :T, None, :].float()
+    s = sin[None, :T, None, :].float()
+    return torch.cat([x1 * c + x2 * s, x2 * c - x1 * s], dim=-1).to(x.dtype)
 
 
 # --------------------------------------------------------------------------- ReLU^2

