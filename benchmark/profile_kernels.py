@@ -8,6 +8,9 @@ between) and prints achieved FLOP/s or bytes/s next to the measured peaks of
 MEASURED_PEAKS.json when that file is present.  Under `ncu -k regex:<kernel> -c 1` the same
 command yields one capture of the named kernel.
 
+`--ref` times cuBLAS (torch.matmul / torch.bmm) on the operands of gemm_fwd, gemm_dx, gemm_dw
+and gemm_sym for comparison.
+
 Cases: gemm_fwd, gemm_dx, gemm_dw, gemm_sym, gemm_tf32_mn, gemm_scatter, chol, cross_entropy,
 rope, rmsnorm, lion, adamw, muon_pre, dion_accum, all_reduce (single rank loop-back over
 symmetric memory).
@@ -54,25 +57,37 @@ def _time(fn, iters):
     return tot / iters
 
 
-def case(name: str):
+def case(name: str, ref: bool = False):
+    from dion_b200.ops import _ext
+
+    _ext.load(required=True)  # the raw torch.ops calls below need the library in the process
     dev = "cuda"
     bf, f32 = torch.bfloat16, torch.float32
     r = lambda *s, dt=bf: torch.randn(*s, device=dev, dtype=torch.float32).to(dt)
     if name == "gemm_fwd":        # Linear forward: [T, K] x [N, K]^T, both K-major
         T, N, Kd = 32768, 3072, 768
         x, w, y = r(T, Kd), r(N, Kd), torch.empty(T, N, device=dev, dtype=bf)
+        if ref:
+            return (lambda: torch.matmul(x, w.t(), out=y)), 2.0 * T * N * Kd, (T * Kd + N * Kd + T * N) * 2
         return (lambda: ops.gemm(x, w.t(), out=y)), 2.0 * T * N * Kd, (T * Kd + N * Kd + T * N) * 2
     if name == "gemm_dx":         # input gradient: [T, N] x [N, K], B is MN-major
         T, N, Kd = 32768, 3072, 768
         dy, w, dx = r(T, N), r(N, Kd), torch.empty(T, Kd, device=dev, dtype=bf)
+        if ref:
+            return (lambda: torch.matmul(dy, w, out=dx)), 2.0 * T * N * Kd, (T * N + N * Kd + T * Kd) * 2
         return (lambda: ops.gemm(dy, w, out=dx)), 2.0 * T * N * Kd, (T * N + N * Kd + T * Kd) * 2
     if name == "gemm_dw":         # weight gradient: [N, T] x [T, K], both MN-major, split-K atomics
         T, N, Kd = 65536, 768, 768
         dy, x, dw = r(T, N), r(T, Kd), torch.zeros(N, Kd, device=dev)
+        if ref:
+            dyb, dwb = dy.t(), torch.empty(N, Kd, device=dev, dtype=bf)
+            return (lambda: torch.matmul(dyb, x, out=dwb)), 2.0 * T * N * Kd, (T * N + T * Kd) * 2
         return (lambda: ops.gemm(dy.t(), x, out=dw, accumulate=True, split_k=16)), 2.0 * T * N * Kd, (T * N + T * Kd) * 2
     if name == "gemm_sym":        # Newton-Schulz X X^T, upper-triangular tiles + mirror
         B, m, n = 24, 768, 3072
         x, a = r(B, m, n), torch.empty(B, m, m, device=dev, dtype=bf)
+        if ref:
+            return (lambda: torch.bmm(x, x.transpose(1, 2), out=a)), 2.0 * B * m * m * n, B * (m * n + m * m) * 2
         return (lambda: ops.gemm(x, x.transpose(1, 2), out=a, symmetric=True)), 2.0 * B * m * m * n, B * (m * n + m * m) * 2
     if name == "gemm_tf32_mn":    # Dion R = A^T P on fp32 state: A MN-major (32-byte-atom swizzle)
         B, a, b_, rr = 12, 3072, 768, 768
@@ -147,11 +162,14 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("case")
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--ref", action="store_true",
+                    help="time the library routine (cuBLAS through torch.matmul) on the same operands instead; "
+                         "GEMM cases only")
     a = ap.parse_args()
-    fn, flops, nbytes = case(a.case)
+    fn, flops, nbytes = case(a.case, a.ref)
     ms = _time(fn, a.iters)
     hbm, tf, src = _peaks()
-    line = {"case": a.case, "ms": round(ms, 4)}
+    line = {"case": a.case + (" (library)" if a.ref else ""), "ms": round(ms, 4)}
     if flops:
         line["tflops"] = round(flops / ms / 1e9, 1)
         line[f"frac_of_{src}_bf16_peak"] = round(flops / ms / 1e9 / tf, 3)

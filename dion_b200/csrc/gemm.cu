@@ -18,6 +18,7 @@
 
 #include <cuda.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -30,7 +31,8 @@ namespace dion {
 namespace {
 
 constexpr int kBlockM = 128;
-constexpr int kNumThreads = 192;
+constexpr int kNumEpilogueWarps = 8;  // two per TMEM lane quadrant, each takes half of the tile's columns
+constexpr int kNumThreads = 64 + 32 * kNumEpilogueWarps;
 
 struct KernelParams {
   int M, N, K, batch, split_k;
@@ -52,6 +54,7 @@ struct KernelParams {
   int scatter_mode, scatter_block, scatter_dests;  // D tiles go to per-destination buffers (peer memory)
   void* const* scatter_ptrs;
   int vec_c, vec_d, vec_d2;  // 16-byte vector access allowed
+  int stage;                 // turn epilogue accesses through shared memory (coalesced)
   int* status;
 };
 
@@ -67,7 +70,7 @@ struct Cfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = 196608 / STAGE_BYTES;  // 4 / 6 / 8 stages in 192 KB
   static constexpr int TMEM_COLS = (2 * kBlockN <= 32) ? 32 : 2 * kBlockN;  // power of two
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + 8 * 32 * 128 /*epilogue staging*/;
   // descriptor strides
   static constexpr uint32_t A_LBO = (kAMajor == kMajorK) ? 16u : (uint32_t)BK * 128u;
   static constexpr uint32_t B_LBO = (kBMajor == kMajorK) ? 16u : (uint32_t)BK * 128u;
@@ -174,6 +177,88 @@ __device__ __forceinline__ void load_chunk(const char* base, bool is_bf16, long 
   }
 }
 
+// ---- epilogue staging: one warp turns a 32-row block through shared memory.  A buffer holds 32
+// rows of 128 bytes; the 16-byte segment index is XOR-ed with the row so that both the
+// row-per-lane side and the segment-per-lane side are free of bank conflicts.
+constexpr int kStageBytes = 32 * 128;
+
+__device__ __forceinline__ uint32_t stage_off(int row, int seg) { return row * 128 + ((seg ^ (row & 7)) << 4); }
+
+// lane's own row, 32 bf16 values into segments [seg0, seg0 + 4)
+__device__ __forceinline__ void stage_put_bf16(uint8_t* st, int lane, int seg0, const float (&v)[32]) {
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    uint4 q;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[8 * s + 2 * j], v[8 * s + 2 * j + 1]);
+    *reinterpret_cast<uint4*>(st + stage_off(lane, seg0 + s)) = q;
+  }
+}
+// lane's own row, 32 fp32 values into segments [0, 8)
+__device__ __forceinline__ void stage_put_f32(uint8_t* st, int lane, const float (&v)[32]) {
+#pragma unroll
+  for (int s = 0; s < 8; ++s)
+    *reinterpret_cast<float4*>(st + stage_off(lane, s)) = make_float4(v[4 * s], v[4 * s + 1], v[4 * s + 2], v[4 * s + 3]);
+}
+// lane's own row back as floats: 4 segments of bf16 or 8 segments of fp32
+__device__ __forceinline__ void stage_get(const uint8_t* st, int lane, bool is_bf16, float (&c)[32]) {
+  if (is_bf16) {
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const uint4 q = *reinterpret_cast<const uint4*>(st + stage_off(lane, s));
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        c[8 * s + 2 * j] = f.x;
+        c[8 * s + 2 * j + 1] = f.y;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      const float4 q = *reinterpret_cast<const float4*>(st + stage_off(lane, s));
+      c[4 * s] = q.x;
+      c[4 * s + 1] = q.y;
+      c[4 * s + 2] = q.z;
+      c[4 * s + 3] = q.w;
+    }
+  }
+}
+// Buffer -> global: `nseg` (4 or 8) lanes cover one row, 32 / nseg rows per instruction.
+// row_ptr(grow) is the address of the first staged byte of global row `grow`.
+template <int NSEG, typename RowPtr>
+__device__ __forceinline__ void stage_flush(const uint8_t* st, int lane, int row_first, int M, RowPtr row_ptr) {
+  constexpr int SHIFT = NSEG == 8 ? 3 : 2;
+  const int seg = lane & (NSEG - 1);
+  const int rsub = lane >> SHIFT;
+  uint4 q[NSEG];
+#pragma unroll
+  for (int i = 0; i < NSEG; ++i) q[i] = *reinterpret_cast<const uint4*>(st + stage_off(i * (32 >> SHIFT) + rsub, seg));
+#pragma unroll
+  for (int i = 0; i < NSEG; ++i) {
+    const int r = i * (32 >> SHIFT) + rsub;
+    if (row_first + r < M) *reinterpret_cast<uint4*>(row_ptr(row_first + r) + seg * 16) = q[i];
+  }
+}
+// global -> buffer, same lane mapping; rows past M read as zero
+template <int NSEG, typename RowPtr>
+__device__ __forceinline__ void stage_fetch(uint8_t* st, int lane, int row_first, int M, RowPtr row_ptr) {
+  constexpr int SHIFT = NSEG == 8 ? 3 : 2;
+  const int seg = lane & (NSEG - 1);
+  const int rsub = lane >> SHIFT;
+  uint4 q[NSEG];
+#pragma unroll
+  for (int i = 0; i < NSEG; ++i) {
+    const int r = i * (32 >> SHIFT) + rsub;
+    q[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (row_first + r < M) q[i] = *reinterpret_cast<const uint4*>(row_ptr(row_first + r) + seg * 16);
+  }
+#pragma unroll
+  for (int i = 0; i < NSEG; ++i) *reinterpret_cast<uint4*>(st + stage_off(i * (32 >> SHIFT) + rsub, seg)) = q[i];
+}
+
 template <bool kTf32, int kAMajor, int kBMajor, int kBlockN>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -190,6 +275,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* stage_area = bar_area + 256;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -203,7 +289,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 4);
+      mbar_init(&tmem_empty[a], kNumEpilogueWarps);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -350,8 +436,42 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                             : reinterpret_cast<char*>(p.D2) + (long long)t.batch * p.d2_batch_stride * 2;
       const bool mirror = p.symmetric && (t.m_blk != t.n_blk);
 
+      // After tcgen05.ld every lane holds one row of the tile, so a direct access would touch 32
+      // different lines per instruction.  Tiles that are full width and 16-byte aligned are turned
+      // through this warp's staging buffer instead, so that consecutive lanes move consecutive
+      // bytes (C on its way in, D and the second output D2 on their way out, one after the other).
+      uint8_t* st = stage_area + (warp - 2) * kStageBytes;
+      const int row_first = m0 + quad * 32;
+      const bool full_tile = n0 + kBlockN <= p.N;
+      const bool atomic = p.epilogue == kEpiAtomicAdd;
+      const bool use_c = c_base != nullptr && !atomic && (p.beta != 0.f || p.act == kActMulRelu2Grad);
+      const bool stage_c = p.stage && use_c && full_tile && p.vec_c;
+      const bool stage_d = p.stage && !atomic && full_tile && p.vec_d;
+      const bool stage_d2 = p.stage && d2_base != nullptr && full_tile && p.vec_d2;
+      const int es_c = p.c_is_bf16 ? 2 : 4;
+      const int es_d = p.d_is_bf16 ? 2 : 4;
+
+      // address of element (grow, col) of D with the scatter modes applied
+      auto d_addr = [&](int grow, int col) -> char* {
+        char* base = d_base;
+        long long r = grow;
+        int cc = col;
+        if (p.scatter_mode == 1) {
+          const int k = grow / p.scatter_block;
+          base = reinterpret_cast<char*>(p.scatter_ptrs[(long long)t.batch * p.scatter_dests + k]);
+          r = grow - (long long)k * p.scatter_block;
+        } else if (p.scatter_mode == 2) {
+          const int k = col / p.scatter_block;
+          base = reinterpret_cast<char*>(p.scatter_ptrs[(long long)t.batch * p.scatter_dests + k]);
+          cc = col - k * p.scatter_block;
+        }
+        return base + (r * p.ldd + cc) * es_d;
+      };
+
+      constexpr int kChunksPerWarp = kBlockN / 32 / (kNumEpilogueWarps / 4);
+      const int c_first = ((warp - 2) >> 2) * kChunksPerWarp;
 #pragma unroll 1
-      for (int c = 0; c < kBlockN / 32; ++c) {
+      for (int c = c_first; c < c_first + kChunksPerWarp; ++c) {
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;  // warp-uniform
         float v[32];
@@ -362,24 +482,39 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0.f;
         }
+        if (p.alpha != 1.f) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
+          for (int i = 0; i < 32; ++i) v[i] *= p.alpha;
+        }
 
         const bool full_cols = col0 + 32 <= p.N;
         const int ncols = p.N - col0;  // valid columns of this chunk when it is the ragged last one
+
+        // second output (bf16): staged or direct
+        auto emit_d2 = [&]() {
+          if (stage_d2) {
+            stage_put_bf16(st, lane, 0, v);
+            __syncwarp();
+            stage_flush<4>(st, lane, row_first, p.M,
+                           [&](int grow) { return d2_base + ((long long)grow * p.ldd2 + col0) * 2; });
+            __syncwarp();
+          } else if (row_ok) {
+            store_chunk_bf16(reinterpret_cast<__nv_bfloat16*>(d2_base) + (long long)row * p.ldd2 + col0, v,
+                             full_cols && p.vec_d2, ncols);
+          }
+        };
+
         bool d2_done = false;
         if (p.act == kActRelu2SavePre) {
           // D2 keeps the pre-activation (what the backward pass needs), D gets relu(x)^2
-          if (row_ok && d2_base != nullptr)
-            store_chunk_bf16(reinterpret_cast<__nv_bfloat16*>(d2_base) + (long long)row * p.ldd2 + col0, v,
-                             full_cols && p.vec_d2, ncols);
+          if (d2_base != nullptr) emit_d2();
           d2_done = true;
         }
         if (p.act == kActRelu2 || p.act == kActRelu2SavePre) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = apply_act(v[i], kActRelu2);
         }
-        if (p.epilogue == kEpiAtomicAdd) {
+        if (atomic) {
           if (row_ok) {
             float* dp = reinterpret_cast<float*>(d_base) + (long long)row * p.ldd + col0;
             if (full_cols && p.vec_d) {
@@ -395,9 +530,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
         } else {
           // C operand: added (beta * C) or, for the ReLU^2 backward, multiplied in as 2 * relu(C)
-          if (c_base != nullptr && row_ok && (p.beta != 0.f || p.act == kActMulRelu2Grad)) {
+          if (use_c) {
             float cv[32];
-            load_chunk(c_base, p.c_is_bf16 != 0, (long long)row * p.ldc + col0, cv, full_cols && p.vec_c, ncols);
+            if (stage_c) {
+              auto c_row = [&](int grow) { return c_base + ((long long)grow * p.ldc + col0) * es_c; };
+              if (p.c_is_bf16) stage_fetch<4>(st, lane, row_first, p.M, c_row);
+              else stage_fetch<8>(st, lane, row_first, p.M, c_row);
+              __syncwarp();
+              stage_get(st, lane, p.c_is_bf16 != 0, cv);
+              __syncwarp();
+            } else if (row_ok) {
+              load_chunk(c_base, p.c_is_bf16 != 0, (long long)row * p.ldc + col0, cv, full_cols && p.vec_c, ncols);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) cv[i] = 0.f;
+            }
             if (p.act == kActMulRelu2Grad) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) v[i] *= 2.f * fmaxf(cv[i], 0.f);
@@ -406,39 +553,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               for (int i = 0; i < 32; ++i) v[i] += p.beta * cv[i];
             }
           }
-          // store D; in scatter mode the destination buffer depends on the row (mode 1) or
-          // on the column chunk (mode 2): element (row, col) of batch b lands in
-          // scatter_ptrs[b * dests + k] at local (row - k * block, col) resp. (row, col - k * block)
-          char* dd_base = d_base;
-          long long drow = row;
-          int dcol0 = col0;
-          if (p.scatter_mode == 1 && row_ok) {
-            const int k = row / p.scatter_block;
-            dd_base = reinterpret_cast<char*>(p.scatter_ptrs[(long long)t.batch * p.scatter_dests + k]);
-            drow = row - (long long)k * p.scatter_block;
-          } else if (p.scatter_mode == 2) {
-            const int k = col0 / p.scatter_block;
-            dd_base = reinterpret_cast<char*>(p.scatter_ptrs[(long long)t.batch * p.scatter_dests + k]);
-            dcol0 = col0 - k * p.scatter_block;
-          }
-          if (row_ok) {
+          if (stage_d) {
+            auto d_row = [&](int grow) { return d_addr(grow, col0); };
             if (p.d_is_bf16) {
-              __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(dd_base) + drow * p.ldd + dcol0;
-              if (full_cols && p.vec_d) {
-#pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                  uint4 q;
-                  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(v[i + 2 * j], v[i + 2 * j + 1]);
-                  *reinterpret_cast<uint4*>(dp + i) = q;
-                }
-              } else {
-                for (int i = 0; i < 32; ++i)
-                  if (col0 + i < p.N) dp[i] = __float2bfloat16(v[i]);
-              }
+              stage_put_bf16(st, lane, 0, v);
+              __syncwarp();
+              stage_flush<4>(st, lane, row_first, p.M, d_row);
             } else {
-              float* dp = reinterpret_cast<float*>(dd_base) + drow * p.ldd + dcol0;
+              stage_put_f32(st, lane, v);
+              __syncwarp();
+              stage_flush<8>(st, lane, row_first, p.M, d_row);
+            }
+            __syncwarp();
+          } else if (row_ok) {
+            char* dptr = d_addr(row, col0);
+            if (p.d_is_bf16) {
+              store_chunk_bf16(reinterpret_cast<__nv_bfloat16*>(dptr), v, full_cols && p.vec_d, ncols);
+            } else {
+              float* dp = reinterpret_cast<float*>(dptr);
               if (full_cols && p.vec_d) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 4)
@@ -448,21 +580,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                   if (col0 + i < p.N) dp[i] = v[i];
               }
             }
-            if (d2_base != nullptr && !d2_done)
-              store_chunk_bf16(reinterpret_cast<__nv_bfloat16*>(d2_base) + (long long)row * p.ldd2 + col0, v,
-                               full_cols && p.vec_d2, ncols);
-            if (mirror) {
-              // transposed copy of an off-diagonal tile: D[col, row]; lanes hold
-              // consecutive rows, so each store instruction is contiguous across the warp
-              if (p.d_is_bf16) {
-                __nv_bfloat16* dt = reinterpret_cast<__nv_bfloat16*>(d_base);
-                for (int i = 0; i < 32; ++i)
-                  if (col0 + i < p.N) dt[(long long)(col0 + i) * p.ldd + row] = __float2bfloat16(v[i]);
-              } else {
-                float* dt = reinterpret_cast<float*>(d_base);
-                for (int i = 0; i < 32; ++i)
-                  if (col0 + i < p.N) dt[(long long)(col0 + i) * p.ldd + row] = v[i];
-              }
+          }
+          if (d2_base != nullptr && !d2_done) emit_d2();
+          if (mirror && row_ok) {
+            // transposed copy of an off-diagonal tile: D[col, row]; lanes hold
+            // consecutive rows, so each store instruction is contiguous across the warp
+            if (p.d_is_bf16) {
+              __nv_bfloat16* dt = reinterpret_cast<__nv_bfloat16*>(d_base);
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) dt[(long long)(col0 + i) * p.ldd + row] = __float2bfloat16(v[i]);
+            } else {
+              float* dt = reinterpret_cast<float*>(d_base);
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N) dt[(long long)(col0 + i) * p.ldd + row] = v[i];
             }
           }
         }
@@ -714,6 +844,13 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   kp.vec_d = (a.d_ptrs || aligned16(a.D, a.ldd, des)) && ((a.d_batch_stride * des) % 16 == 0);
   if (a.scatter_mode != 0) kp.vec_d = ((a.ldd * des) % 16 == 0);  // block bases are 16-byte aligned by contract
   kp.vec_d2 = (a.d2_ptrs || aligned16(a.D2, a.ldd2, 2)) && ((a.d2_batch_stride * 2) % 16 == 0);
+  {
+    static const int stage_env = [] {
+      const char* e = getenv("DION_B200_GEMM_STAGE");
+      return (e && e[0] == '0') ? 0 : 1;
+    }();
+    kp.stage = stage_env;
+  }
 
   return tf32 ? launch_major<true>(a, kp, bn, stream) : launch_major<false>(a, kp, bn, stream);
 }
