@@ -58,7 +58,7 @@ void check_out(const Tensor& t, int64_t batch, int64_t M, int64_t N, const char*
 void gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, Tensor d,
           const std::optional<Tensor>& d2, const std::optional<Tensor>& c_ptrs,
           const std::optional<Tensor>& d_ptrs, const std::optional<Tensor>& d2_ptrs, double alpha, double beta,
-          int64_t act, int64_t epilogue, int64_t split_k, bool symmetric, int64_t block_n,
+          int64_t act, int64_t epilogue, int64_t split_k, bool symmetric, int64_t block_n, int64_t pair,
           const std::optional<Tensor>& status) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda(), "gemm operands must be CUDA tensors");
   TORCH_CHECK(a.scalar_type() == b.scalar_type(), "gemm operands must share a dtype");
@@ -83,6 +83,7 @@ void gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, Tens
   g.split_k = (int)split_k;
   g.symmetric = symmetric ? 1 : 0;
   g.block_n = (int)block_n;
+  g.pair = (int)pair;
 
   // Per-batch pointer arrays (int64 CUDA tensors) describe outputs that are separate
   // allocations; `d` / `c` then only supply dtype, shape and pitch of one element.
@@ -594,7 +595,7 @@ TORCH_LIBRARY(dion_b200, m) {
   m.def(
       "gemm(Tensor a, Tensor b, Tensor? c, Tensor(a!) d, Tensor(b!)? d2, Tensor? c_ptrs, Tensor? d_ptrs, "
       "Tensor? d2_ptrs, float alpha, float beta, int act, int epilogue, int split_k, bool symmetric, "
-      "int block_n, Tensor? status) -> ()");
+      "int block_n, int pair, Tensor? status) -> ()");
   m.def(
       "adamw_multi(Tensor(a!)[] X, Tensor[] G, Tensor(b!)[] M, Tensor(c!)[] V, Tensor(d!)[] shadow, float lr, "
       "float beta1, float beta2, float weight_decay, float eps, int step) -> ()");

@@ -58,7 +58,10 @@ struct KernelParams {
   int* status;
 };
 
-template <bool kTf32, int kAMajor, int kBMajor, int kBlockN>
+// kPair: two CTAs of a cluster work on one 256 x kBlockN tile (tcgen05 cta_group::2).  Each CTA
+// loads its own 128 rows of A and half of the tile's B rows, so every byte of B is fetched from
+// L2 once per 256 output rows instead of once per 128.
+template <bool kTf32, int kAMajor, int kBMajor, int kBlockN, bool kPair = false>
 struct Cfg {
   static constexpr int ES = kTf32 ? 4 : 2;
   static constexpr int BK = 128 / ES;      // K elements per stage (one 128B swizzle span)
@@ -66,8 +69,11 @@ struct Cfg {
   static constexpr int UMMA_K = 32 / ES;   // K per tcgen05.mma
   static constexpr int KSTEPS = BK / UMMA_K;
   static constexpr int A_BYTES = kBlockM * 128;
-  static constexpr int B_BYTES = kBlockN * 128;
+  static constexpr int TILE_M = kPair ? 2 * kBlockM : kBlockM;
+  static constexpr int B_ROWS = kPair ? kBlockN / 2 : kBlockN;  // B rows (N) held by one CTA
+  static constexpr int B_BYTES = B_ROWS * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TX_BYTES = kPair ? 2 * STAGE_BYTES : STAGE_BYTES;  // what one full barrier phase receives
   static constexpr int STAGES = 196608 / STAGE_BYTES;  // 4 / 6 / 8 stages in 192 KB
   static constexpr int TMEM_COLS = (2 * kBlockN <= 32) ? 32 : 2 * kBlockN;  // power of two
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + 8 * 32 * 128 /*epilogue staging*/;
@@ -259,11 +265,11 @@ __device__ __forceinline__ void stage_fetch(uint8_t* st, int lane, int row_first
   for (int i = 0; i < NSEG; ++i) *reinterpret_cast<uint4*>(st + stage_off(i * (32 >> SHIFT) + rsub, seg)) = q[i];
 }
 
-template <bool kTf32, int kAMajor, int kBMajor, int kBlockN>
+template <bool kTf32, int kAMajor, int kBMajor, int kBlockN, bool kPair>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const KernelParams p) {
-  using C = Cfg<kTf32, kAMajor, kBMajor, kBlockN>;
+  using C = Cfg<kTf32, kAMajor, kBMajor, kBlockN, kPair>;
   extern __shared__ uint8_t smem_raw[];
   // 128B swizzle atoms need 1024-byte aligned tiles.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -279,6 +285,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // CTA pair: rank 0 leads (issues the MMAs, owns the full / tmem_empty barriers in use)
+  uint32_t cta_rank = 0;
+  if constexpr (kPair) cta_rank = cluster_ctarank();
+  const int worker = kPair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int num_workers = kPair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_a);
@@ -289,17 +300,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], kNumEpilogueWarps);
+      mbar_init(&tmem_empty[a], kPair ? 2 * kNumEpilogueWarps : kNumEpilogueWarps);
     }
     *abort_flag = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, C::TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (kPair) {
+      tmem_alloc_pair(tmem_slot, C::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, C::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (kPair) cluster_sync_all();  // both CTAs' barriers and TMEM exist before either is used
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -311,10 +328,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+      for (int tile = worker; tile < p.total_tiles && ok; tile += num_workers) {
         const TileCoord t = decode_tile(p, tile);
-        const int m0 = t.m_blk * kBlockM;
-        const int n0 = t.n_blk * kBlockN;
+        const int m0 = t.m_blk * C::TILE_M + (int)cta_rank * kBlockM;
+        const int n0 = t.n_blk * kBlockN + (int)cta_rank * (kPair ? C::B_ROWS : 0);
         const int kb0 = t.split * kb_per_split;
         const int kb1 = min(kb0 + kb_per_split, p.kblocks_total);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -324,25 +341,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             if (p.status) atomicCAS(p.status, 0, kStatusProducerTimeout);
             break;
           }
-          mbar_arrive_expect_tx(&full_bar[stage], C::STAGE_BYTES);
+          // the leader's full barrier collects the bytes of both CTAs
+          if (cta_rank == 0) mbar_arrive_expect_tx(&full_bar[stage], C::TX_BYTES);
+          const uint32_t bar = kPair ? mapa_shared(smem_u32(&full_bar[stage]), 0) : smem_u32(&full_bar[stage]);
+          auto load = [&](void* dst, const CUtensorMap* map, int c0, int c1) {
+            if constexpr (kPair) tma_load_3d_pair(dst, map, bar, c0, c1, t.batch);
+            else tma_load_3d(dst, map, &full_bar[stage], c0, c1, t.batch);
+          };
           uint8_t* sa = smem + stage * C::STAGE_BYTES;
           uint8_t* sb = sa + C::A_BYTES;
           const int k0 = kb * C::BK;
           if constexpr (kAMajor == kMajorK) {
-            tma_load_3d(sa, &tmap_a, &full_bar[stage], k0, m0, t.batch);
+            load(sa, &tmap_a, k0, m0);
           } else {
 #pragma unroll
-            for (int c = 0; c < kBlockM / C::CH; ++c)
-              tma_load_3d(sa + c * (C::BK * 128), &tmap_a, &full_bar[stage], m0 + c * C::CH, k0,
-                          t.batch);
+            for (int c = 0; c < kBlockM / C::CH; ++c) load(sa + c * (C::BK * 128), &tmap_a, m0 + c * C::CH, k0);
           }
           if constexpr (kBMajor == kMajorK) {
-            tma_load_3d(sb, &tmap_b, &full_bar[stage], k0, n0, t.batch);
+            load(sb, &tmap_b, k0, n0);
           } else {
 #pragma unroll
-            for (int c = 0; c < kBlockN / C::CH; ++c)
-              tma_load_3d(sb + c * (C::BK * 128), &tmap_b, &full_bar[stage], n0 + c * C::CH, k0,
-                          t.batch);
+            for (int c = 0; c < C::B_ROWS / C::CH; ++c) load(sb + c * (C::BK * 128), &tmap_b, n0 + c * C::CH, k0);
           }
           if (++stage == C::STAGES) {
             stage = 0;
@@ -353,13 +372,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_instr_desc(kTf32 ? 2 : 1, kAMajor, kBMajor, kBlockM, kBlockN);
+    if (lane == 0 && cta_rank == 0) {
+      constexpr uint32_t idesc = make_instr_desc(kTf32 ? 2 : 1, kAMajor, kBMajor, C::TILE_M, kBlockN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++it) {
+      for (int tile = worker; tile < p.total_tiles && ok; tile += num_workers, ++it) {
         const TileCoord t = decode_tile(p, tile);
         const int kb0 = t.split * kb_per_split;
         const int kb1 = min(kb0 + kb_per_split, p.kblocks_total);
@@ -387,15 +406,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           for (int j = 0; j < C::KSTEPS; ++j) {
             const uint64_t da = make_smem_desc(sa + j * C::A_KSTEP, C::A_LBO, C::A_SBO, C::A_LAYOUT);
             const uint64_t db = make_smem_desc(sb + j * C::B_KSTEP, C::B_LBO, C::B_SBO, C::B_LAYOUT);
-            umma_ss<kTf32>(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+            if constexpr (kPair) umma_ss_pair<kTf32>(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+            else umma_ss<kTf32>(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
           }
-          umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
+          // frees the smem stage (of both CTAs) once these MMAs retire
+          if constexpr (kPair) umma_commit_pair(&empty_bar[stage], 3);
+          else umma_commit(&empty_bar[stage]);
           if (++stage == C::STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) umma_commit(&tmem_full[acc]);
+        if (ok) {
+          if constexpr (kPair) umma_commit_pair(&tmem_full[acc], 3);
+          else umma_commit(&tmem_full[acc]);
+        }
       }
     }
   } else {
@@ -403,9 +428,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     int it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++it) {
+    for (int tile = worker; tile < p.total_tiles && ok; tile += num_workers, ++it) {
       const TileCoord t = decode_tile(p, tile);
-      const int m0 = t.m_blk * kBlockM;
+      const int m0 = t.m_blk * C::TILE_M + (int)cta_rank * kBlockM;
       const int n0 = t.n_blk * kBlockN;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -600,7 +625,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       // hand the accumulator buffer back to the MMA warp
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (lane == 0) {
+        if (cta_rank == 0) mbar_arrive(&tmem_empty[acc]);
+        else mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty[acc]), 0));
+      }
     }
   }
 
@@ -612,9 +640,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     while (global_timer_ns() - t0 < 2000000ull) __nanosleep(1000);
     __syncthreads();
   }
+  // a CTA of a pair must outlive its peer's last access to its shared memory, barriers and TMEM
+  if constexpr (kPair) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, C::TMEM_COLS);
+    if constexpr (kPair) tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+    else tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
 }
 
@@ -685,9 +716,9 @@ int num_sms() {
   return n;
 }
 
-template <bool kTf32, int kAMajor, int kBMajor, int kBlockN>
+template <bool kTf32, int kAMajor, int kBMajor, int kBlockN, bool kPair = false>
 cudaError_t launch_cfg(const GemmArgs& a, const KernelParams& kp, cudaStream_t stream) {
-  using C = Cfg<kTf32, kAMajor, kBMajor, kBlockN>;
+  using C = Cfg<kTf32, kAMajor, kBMajor, kBlockN, kPair>;
   CUtensorMap ta, tb;
   const int dt = kTf32 ? kF32 : kBF16;
   bool ok;
@@ -697,12 +728,12 @@ cudaError_t launch_cfg(const GemmArgs& a, const KernelParams& kp, cudaStream_t s
     ok = make_tmap(&ta, a.A, dt, a.M, a.K, a.batch, a.lda, a.a_batch_stride, C::CH, C::BK, C::A_ATOM32);
   if (!ok) return cudaErrorInvalidValue;
   if (kBMajor == kMajorK)
-    ok = make_tmap(&tb, a.B, dt, a.K, a.N, a.batch, a.ldb, a.b_batch_stride, C::BK, kBlockN, false);
+    ok = make_tmap(&tb, a.B, dt, a.K, a.N, a.batch, a.ldb, a.b_batch_stride, C::BK, C::B_ROWS, false);
   else
     ok = make_tmap(&tb, a.B, dt, a.N, a.K, a.batch, a.ldb, a.b_batch_stride, C::CH, C::BK, C::B_ATOM32);
   if (!ok) return cudaErrorInvalidValue;
 
-  auto kernel = gemm_kernel<kTf32, kAMajor, kBMajor, kBlockN>;
+  auto kernel = gemm_kernel<kTf32, kAMajor, kBMajor, kBlockN, kPair>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
@@ -710,13 +741,34 @@ cudaError_t launch_cfg(const GemmArgs& a, const KernelParams& kp, cudaStream_t s
     attr_set = true;
   }
   int grid = a.max_ctas > 0 ? a.max_ctas : num_sms();
-  if (grid > kp.total_tiles) grid = kp.total_tiles;
-  kernel<<<grid, kNumThreads, C::SMEM_BYTES, stream>>>(ta, tb, kp);
-  return cudaGetLastError();
+  if constexpr (kPair) {
+    grid /= 2;  // clusters of two CTAs, one tile per cluster at a time
+    if (grid > kp.total_tiles) grid = kp.total_tiles;
+    if (grid < 1) grid = 1;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(2 * grid, 1, 1);
+    cfg.blockDim = dim3(kNumThreads, 1, 1);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, ta, tb, kp);
+  } else {
+    if (grid > kp.total_tiles) grid = kp.total_tiles;
+    kernel<<<grid, kNumThreads, C::SMEM_BYTES, stream>>>(ta, tb, kp);
+    return cudaGetLastError();
+  }
 }
 
 template <bool kTf32, int kAMajor, int kBMajor>
-cudaError_t launch_bn(const GemmArgs& a, const KernelParams& kp, int bn, cudaStream_t s) {
+cudaError_t launch_bn(const GemmArgs& a, const KernelParams& kp, int bn, bool pair, cudaStream_t s) {
+  if (pair) return launch_cfg<kTf32, kAMajor, kBMajor, 256, true>(a, kp, s);
   switch (bn) {
     case 64: return launch_cfg<kTf32, kAMajor, kBMajor, 64>(a, kp, s);
     case 128: return launch_cfg<kTf32, kAMajor, kBMajor, 128>(a, kp, s);
@@ -725,13 +777,13 @@ cudaError_t launch_bn(const GemmArgs& a, const KernelParams& kp, int bn, cudaStr
 }
 
 template <bool kTf32>
-cudaError_t launch_major(const GemmArgs& a, const KernelParams& kp, int bn, cudaStream_t s) {
+cudaError_t launch_major(const GemmArgs& a, const KernelParams& kp, int bn, bool pair, cudaStream_t s) {
   if (a.a_major == kMajorK) {
-    if (a.b_major == kMajorK) return launch_bn<kTf32, kMajorK, kMajorK>(a, kp, bn, s);
-    return launch_bn<kTf32, kMajorK, kMajorMN>(a, kp, bn, s);
+    if (a.b_major == kMajorK) return launch_bn<kTf32, kMajorK, kMajorK>(a, kp, bn, pair, s);
+    return launch_bn<kTf32, kMajorK, kMajorMN>(a, kp, bn, pair, s);
   }
-  if (a.b_major == kMajorK) return launch_bn<kTf32, kMajorMN, kMajorK>(a, kp, bn, s);
-  return launch_bn<kTf32, kMajorMN, kMajorMN>(a, kp, bn, s);
+  if (a.b_major == kMajorK) return launch_bn<kTf32, kMajorMN, kMajorK>(a, kp, bn, pair, s);
+  return launch_bn<kTf32, kMajorMN, kMajorMN>(a, kp, bn, pair, s);
 }
 
 bool aligned16(const void* p, long long ld, int es) {
@@ -795,6 +847,21 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
     }
   }
 
+  // CTA pairs (256-row tiles, half the B traffic per CTA) for GEMMs with enough 256 x 256 tiles to
+  // keep every pair busy; DION_B200_GEMM_PAIR=0 turns them off, a.pair = 1 / -1 forces / forbids.
+  static const int pair_env = [] {
+    const char* e = getenv("DION_B200_GEMM_PAIR");
+    return (e && e[0] == '0') ? 0 : 1;
+  }();
+  bool pair = false;
+  if (a.pair > 0 && !a.symmetric) bn = 256;
+  if (!a.symmetric && bn == 256 && a.pair >= 0 && (pair_env || a.pair > 0)) {
+    const long long t = (long long)((a.M + 255) / 256) * ((a.N + 255) / 256) * a.batch * a.split_k;
+    // short-K tiles are bound by the epilogue, which a pair does not speed up
+    pair = a.pair > 0 || (t >= 2 * (num_sms() / 2) && a.K / a.split_k >= 1024);
+  }
+  const int tile_m = pair ? 2 * kBlockM : kBlockM;
+
   KernelParams kp;
   memset(&kp, 0, sizeof(kp));
   kp.M = a.M;
@@ -802,7 +869,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   kp.K = a.K;
   kp.batch = a.batch;
   kp.split_k = a.split_k;
-  kp.tiles_m = (a.M + kBlockM - 1) / kBlockM;
+  kp.tiles_m = (a.M + tile_m - 1) / tile_m;
   kp.tiles_n = (a.N + bn - 1) / bn;
   kp.tiles_per_batch = a.symmetric ? kp.tiles_n * (kp.tiles_n + 1) / 2 : kp.tiles_m * kp.tiles_n;
   const long long total = (long long)kp.tiles_per_batch * a.batch * a.split_k;
@@ -852,7 +919,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
     kp.stage = stage_env;
   }
 
-  return tf32 ? launch_major<true>(a, kp, bn, stream) : launch_major<false>(a, kp, bn, stream);
+  return tf32 ? launch_major<true>(a, kp, bn, pair, stream) : launch_major<false>(a, kp, bn, pair, stream);
 }
 
 }  // namespace dion

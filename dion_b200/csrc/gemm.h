@@ -72,6 +72,7 @@ struct GemmArgs {
   void* const* scatter_ptrs = nullptr;
   int block_n = 0;  // 0 = choose automatically (64 / 128 / 256)
   int max_ctas = 0;  // 0 = one CTA per SM
+  int pair = 0;      // CTA pairs (256-row tiles): 0 = choose automatically, 1 = force (needs block_n 256), -1 = never
 
   int* status = nullptr;  // device int, set to a non-zero code on a device-side failure
 };

@@ -70,7 +70,7 @@ def _tma_ok(t: torch.Tensor) -> bool:
 def gemm(a: torch.Tensor, b: torch.Tensor, *, c: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
          alpha: float = 1.0, beta: float = 0.0, act: Optional[str] = None, out_dtype: Optional[torch.dtype] = None,
          accumulate: bool = False, split_k: int = 1, symmetric: bool = False, shadow: Optional[torch.Tensor] = None,
-         block_n: int = 0, out_ptrs: Optional[torch.Tensor] = None, c_ptrs: Optional[torch.Tensor] = None,
+         block_n: int = 0, pair: int = 0, out_ptrs: Optional[torch.Tensor] = None, c_ptrs: Optional[torch.Tensor] = None,
          shadow_ptrs: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``out = act(alpha * a @ b + beta * c)``.
 
@@ -109,6 +109,6 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, c: Optional[torch.Tensor] = None, 
     if split_k > 1 and not accumulate:
         raise ValueError("split_k > 1 needs accumulate=True")
     torch.ops.dion_b200.gemm(a, b, c, out, shadow, c_ptrs, out_ptrs, shadow_ptrs, float(alpha), float(beta),
-                             _ACT[act], 1 if accumulate else 0, int(split_k), bool(symmetric), int(block_n),
+                             _ACT[act], 1 if accumulate else 0, int(split_k), bool(symmetric), int(block_n), int(pair),
                              runtime.status_tensor(a.device))
     return out

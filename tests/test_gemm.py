@@ -160,3 +160,47 @@ def test_gemm_relu2_save_pre_and_backward_multiplier():
     gemm(dy, w, c=pre, out=dpre, act="mul_relu2_grad")
     ref = (dy.float() @ w.float()) * 2 * torch.relu(pre.float())
     assert _rel_err(dpre, ref) < 1e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("ta", [False, True])
+@pytest.mark.parametrize("tb", [False, True])
+@pytest.mark.parametrize("shape", [(512, 512, 256), (640, 296, 200), (200, 1000, 72)])
+def test_gemm_cta_pair_layouts(dtype, ta, tb, shape):
+    """256-row tiles computed by two CTAs of a cluster (tcgen05 cta_group::2), forced on small shapes."""
+    M, N, K = shape
+    a = _operand(M, K, dtype, ta)
+    b = _operand(K, N, dtype, tb)
+    out = gemm(a, b, out_dtype=torch.float32, pair=1)
+    ref = a.float() @ b.float()
+    assert _rel_err(out, ref) < (2e-5 if dtype == torch.bfloat16 else 4e-3)
+
+
+@pytest.mark.gpu
+def test_gemm_cta_pair_epilogues_batch_and_many_tiles():
+    # batched, with C / alpha / beta and the second output; more tiles than CTA pairs so that the
+    # persistent loop and both accumulator buffers wrap around several times
+    a = _operand(1100, 320, torch.bfloat16, False, batch=5)
+    b = _operand(320, 2100, torch.bfloat16, True, batch=5)
+    c = torch.randn(5, 1100, 2100, device="cuda").to(torch.bfloat16)
+    shadow = torch.empty(5, 1100, 2100, device="cuda", dtype=torch.bfloat16)
+    out = gemm(a, b, c=c, alpha=0.5, beta=1.0, out_dtype=torch.float32, shadow=shadow, pair=1)
+    ref = 0.5 * torch.matmul(a.float(), b.float()) + c.float()
+    assert _rel_err(out, ref) < 2e-5
+    assert torch.equal(shadow, out.to(torch.bfloat16))
+    y = gemm(a, b, act="relu2", pair=1)
+    assert _rel_err(y, torch.relu(torch.matmul(a.float(), b.float())) ** 2) < 1e-2
+    # split-K accumulation with atomics
+    acc = torch.zeros(5, 1100, 2100, device="cuda")
+    gemm(a, b, out=acc, accumulate=True, split_k=3, pair=1)
+    assert _rel_err(acc, torch.matmul(a.float(), b.float())) < 2e-5
+
+
+@pytest.mark.gpu
+def test_gemm_cta_pair_matches_single_cta_bitwise():
+    a = _operand(4096, 768, torch.bfloat16, False)
+    b = _operand(768, 3072, torch.bfloat16, True)
+    y1 = gemm(a, b, pair=1)
+    y0 = gemm(a, b, pair=-1)
+    assert torch.equal(y0, y1)
