@@ -579,9 +579,47 @@ void symm_reduce_into(const Tensor& src, Tensor dst, at::IntArrayRef peers, int6
                                                 status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()));
 }
 
+// out (world * n) = concatenation of every rank's `inp` (n), through the staging slot at `slot_off`
+void symm_all_gather(const Tensor& inp, Tensor out, at::IntArrayRef peers, int64_t flag_off, int64_t slot_off,
+                     int64_t rank, int64_t epoch, int64_t channel, Tensor counter, Tensor status, int64_t budget_ns) {
+  const c10::cuda::CUDAGuard guard(inp.device());
+  TORCH_CHECK(inp.is_contiguous() && out.is_contiguous() && inp.scalar_type() == out.scalar_type());
+  TORCH_CHECK(out.numel() == inp.numel() * (int64_t)peers.size(), "all-gather output must hold every rank's input");
+  ++g_launches;
+  DION_CUDA_CHECK(dion::symm_all_gather_launch(peer_table(peers), flag_off, slot_off, inp.data_ptr(), out.data_ptr(),
+                                               inp.numel() * inp.element_size(), (int)rank, (int)peers.size(),
+                                               (unsigned)epoch, (int)channel,
+                                               reinterpret_cast<unsigned*>(counter.data_ptr<int>()),
+                                               status.data_ptr<int>(), budget_ns, at::cuda::getCurrentCUDAStream()));
+}
+
+// out (n) = scale * sum over ranks of slice `rank` of `inp` (world * n, an arena view at `data_off`)
+void symm_reduce_scatter(const Tensor& inp, Tensor out, at::IntArrayRef peers, int64_t flag_off, int64_t data_off,
+                         int64_t mc_base, double scale, int64_t rank, int64_t epoch, int64_t ch_start, int64_t ch_end,
+                         Tensor counter, Tensor status, int64_t budget_ns) {
+  const c10::cuda::CUDAGuard guard(inp.device());
+  TORCH_CHECK(inp.is_contiguous() && out.is_contiguous() && inp.scalar_type() == out.scalar_type());
+  TORCH_CHECK(inp.numel() == out.numel() * (int64_t)peers.size(), "reduce-scatter input must hold one slice per rank");
+  TORCH_CHECK(reinterpret_cast<int64_t>(inp.data_ptr()) == peers[rank] + data_off,
+              "input is not at the stated offset of this rank's arena");
+  ++g_launches;
+  DION_CUDA_CHECK(dion::symm_reduce_scatter_launch(
+      peer_table(peers), flag_off, data_off, reinterpret_cast<void*>(mc_base), elem_type(inp, "input"), out.data_ptr(),
+      out.numel(), (float)scale, (int)rank, (int)peers.size(), (unsigned)epoch, (int)ch_start, (int)ch_end,
+      reinterpret_cast<unsigned*>(counter.data_ptr<int>()), status.data_ptr<int>(), budget_ns,
+      at::cuda::getCurrentCUDAStream()));
+}
+
 }  // namespace
 
 TORCH_LIBRARY(dion_b200, m) {
+  m.def(
+      "symm_all_gather(Tensor inp, Tensor(a!) out, int[] peers, int flag_off, int slot_off, int rank, int epoch, "
+      "int channel, Tensor(b!) counter, Tensor(c!) status, int budget_ns) -> ()");
+  m.def(
+      "symm_reduce_scatter(Tensor inp, Tensor(a!) out, int[] peers, int flag_off, int data_off, int mc_base, "
+      "float scale, int rank, int epoch, int ch_start, int ch_end, Tensor(b!) counter, Tensor(c!) status, "
+      "int budget_ns) -> ()");
   m.def(
       "gemm_scatter(Tensor a, Tensor b, Tensor? c, Tensor block_like, Tensor scatter_ptrs, int mode, int block, "
       "int dests, float alpha, float beta, Tensor? status) -> ()");
@@ -647,6 +685,8 @@ TORCH_LIBRARY_IMPL(dion_b200, CUDA, m) {
   m.impl("symm_barrier", &symm_barrier);
   m.impl("symm_all_reduce", &symm_all_reduce);
   m.impl("symm_reduce_into", &symm_reduce_into);
+  m.impl("symm_all_gather", &symm_all_gather);
+  m.impl("symm_reduce_scatter", &symm_reduce_scatter);
 }
 
 // Ops whose arguments are tensor lists have no dispatch key to select on when a list

@@ -44,20 +44,31 @@ __device__ __forceinline__ void signal_peers(const PeerTable& t, long long flag_
 // `wait`: until every source rank reached `epoch` on `channel` in this rank's flag block.
 // Returns false on timeout.  Epochs only grow, so ">= epoch" also accepts a later one.
 __device__ __forceinline__ bool wait_peers(const PeerTable& t, long long flag_off, int channel, int rank, int world,
-                                           unsigned epoch, int lane) {
+                                           unsigned epoch, int lane, unsigned long long budget_ns = kWaitBudgetNs) {
   bool ok = true;
   if (lane < world) {
     const unsigned* f = reinterpret_cast<const unsigned*>(reinterpret_cast<const char*>(t.ptrs[rank]) + flag_off) +
                         channel * kMaxPeers + lane;
     const unsigned long long t0 = global_timer_ns();
     while ((int)(ld_acquire_sys(f) - epoch) < 0) {
-      if (global_timer_ns() - t0 > kWaitBudgetNs) {
+      if (global_timer_ns() - t0 > budget_ns) {
         ok = false;
         break;
       }
     }
   }
   return ok;
+}
+// one source rank only; every lane of the calling warp polls the same word
+__device__ __forceinline__ bool wait_peer(const PeerTable& t, long long flag_off, int channel, int rank, int src,
+                                          unsigned epoch, unsigned long long budget_ns) {
+  const unsigned* f = reinterpret_cast<const unsigned*>(reinterpret_cast<const char*>(t.ptrs[rank]) + flag_off) +
+                      channel * kMaxPeers + src;
+  const unsigned long long t0 = global_timer_ns();
+  while ((int)(ld_acquire_sys(f) - epoch) < 0) {
+    if (global_timer_ns() - t0 > budget_ns) return false;
+  }
+  return true;
 }
 
 __global__ void barrier_kernel(PeerTable t, long long flag_off, int channel, int rank, int world, unsigned epoch,
@@ -282,6 +293,138 @@ __global__ void __launch_bounds__(512) reduce_into_kernel(PeerTable t, long long
   }
 }
 
+// All-gather for parameter shards (the collective FSDP2 issues before a block runs,
+// models/gpt_model.py:336-376 in the reference).  `out` (world * bytes) and `in` (bytes) are
+// ordinary local buffers; only a staging slot of the arena is symmetric:
+//   1. copy `in` to this rank's staging slot (and to out[rank] unless it already lives there),
+//   2. the last CTA to finish announces it on `channel`,
+//   3. every CTA pulls peer p's slot into out[p] as soon as p announced.
+// Slots alternate with the parity of `epoch`: a rank can only start writing slot e+2 after its
+// launch e+1 saw every peer's announcement e+1, which peers make after their launch e retired,
+// so no closing barrier is needed.  Launches of one arena must be stream-ordered on every rank.
+__global__ void __launch_bounds__(512) all_gather_kernel(PeerTable t, long long flag_off, long long slot_off,
+                                                        const char* __restrict__ in, char* __restrict__ out,
+                                                        long long bytes, int rank, int world, unsigned epoch,
+                                                        int channel, unsigned* done_counter, int* status,
+                                                        unsigned long long budget_ns) {
+  const long long nvec = bytes / 16;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  {
+    const uint4* src = reinterpret_cast<const uint4*>(in);
+    uint4* slot = reinterpret_cast<uint4*>(reinterpret_cast<char*>(t.ptrs[rank]) + slot_off);
+    uint4* own = reinterpret_cast<uint4*>(out + (long long)rank * bytes);
+    const bool copy_own = reinterpret_cast<const char*>(own) != in;
+    for (long long v = tid; v < nvec; v += nthreads) {
+      const uint4 q = src[v];
+      slot[v] = q;
+      if (copy_own) own[v] = q;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(done_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *done_counter = 0;
+      __threadfence_system();
+      for (int p = 0; p < world; ++p) {
+        unsigned* f = reinterpret_cast<unsigned*>(reinterpret_cast<char*>(t.ptrs[p]) + flag_off);
+        st_release_sys(f + channel * kMaxPeers + rank, epoch);
+      }
+    }
+  }
+  __shared__ int ok_flag;
+  for (int i = 1; i < world; ++i) {
+    const int p = (rank + i) % world;
+    if (threadIdx.x == 0) {
+      ok_flag = wait_peer(t, flag_off, channel, rank, p, epoch, budget_ns) ? 1 : 0;
+      if (!ok_flag && status) atomicCAS(status, 0, kStatusPeerTimeout);
+    }
+    __syncthreads();
+    if (ok_flag) {
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(t.ptrs[p]) + slot_off);
+      uint4* dst = reinterpret_cast<uint4*>(out + (long long)p * bytes);
+      for (long long v = tid; v < nvec; v += nthreads) dst[v] = src[v];
+    }
+    __syncthreads();
+  }
+}
+
+// Reduce-scatter for gradients: every rank's input (world * numel elements at `data_off` of its
+// arena) is complete when the kernel starts in stream order; rank r writes
+// out[i] = scale * sum_p in_p[r * numel + i], summing in rank order (or in the switch).  The
+// kernel retires only after every peer finished reading this rank's input, so the input may be
+// overwritten by the next kernel in the stream.
+template <typename T, bool kMulticast>
+__global__ void __launch_bounds__(512) reduce_scatter_kernel(PeerTable t, long long flag_off, long long data_off,
+                                                            char* mc_base, T* __restrict__ out, long long numel,
+                                                            float scale, int rank, int world, unsigned epoch,
+                                                            int ch_start, int ch_end, unsigned* done_counter,
+                                                            int* status, unsigned long long budget_ns) {
+  using V = Vec16<T>;
+  constexpr int N = V::N;
+  __shared__ int ok_flag;
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    if (blockIdx.x == 0) {
+      __threadfence_system();
+      signal_peers(t, flag_off, ch_start, rank, world, epoch, threadIdx.x);
+    }
+    if (!wait_peers(t, flag_off, ch_start, rank, world, epoch, threadIdx.x, budget_ns)) {
+      ok_flag = 0;
+      if (status) atomicCAS(status, 0, kStatusPeerTimeout);
+    }
+  }
+  __syncthreads();
+  if (ok_flag) {
+    const long long slice_off = data_off + (long long)rank * numel * (long long)sizeof(T);
+    const long long nvec = numel / N;
+    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec;
+         v += (long long)gridDim.x * blockDim.x) {
+      float acc[N];
+      if (kMulticast) {
+        V::mc_load_reduce(reinterpret_cast<const T*>(mc_base + slice_off) + v * N, acc);
+      } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[j] = 0.f;
+        for (int p = 0; p < world; ++p) {
+          float f[N];
+          V::load(reinterpret_cast<const T*>(reinterpret_cast<const char*>(t.ptrs[p]) + slice_off) + v * N, f);
+#pragma unroll
+          for (int j = 0; j < N; ++j) acc[j] += f[j];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < N; ++j) acc[j] *= scale;
+      V::store(out + v * N, acc);
+    }
+    if (blockIdx.x == 0) {
+      for (long long i = nvec * N + threadIdx.x; i < numel; i += blockDim.x) {
+        float a = 0.f;
+        for (int p = 0; p < world; ++p)
+          a += to_f(reinterpret_cast<const T*>(reinterpret_cast<const char*>(t.ptrs[p]) + slice_off)[i]);
+        out[i] = from_f<T>(a * scale);
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ int is_last;
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(done_counter, 1u);
+    is_last = (prev == gridDim.x - 1);
+    if (is_last) *done_counter = 0;
+  }
+  __syncthreads();
+  if (is_last && threadIdx.x < 32) {
+    signal_peers(t, flag_off, ch_end, rank, world, epoch, threadIdx.x);
+    if (!wait_peers(t, flag_off, ch_end, rank, world, epoch, threadIdx.x, budget_ns) && status)
+      atomicCAS(status, 0, kStatusPeerTimeout);
+  }
+}
+
 int comm_grid(long long work_items, int threads) {
   long long g = (work_items + threads - 1) / threads;
   if (g < 1) g = 1;
@@ -338,6 +481,46 @@ cudaError_t symm_reduce_into_launch(const PeerTable& t, long long flag_off, long
   else if (src_type == kElemBF16 && dst_type == kElemF32) DION_RI(__nv_bfloat16, float);
   else DION_RI(__nv_bfloat16, __nv_bfloat16);
 #undef DION_RI
+  return cudaGetLastError();
+}
+
+cudaError_t symm_all_gather_launch(const PeerTable& t, long long flag_off, long long slot_off, const void* in,
+                                   void* out, long long bytes, int rank, int world, unsigned epoch, int channel,
+                                   unsigned* done_counter, int* status, long long budget_ns, cudaStream_t s) {
+  if (world > kMaxPeers || (bytes & 15) || (slot_off & 15) || (reinterpret_cast<uintptr_t>(in) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return cudaErrorInvalidValue;
+  const int threads = 512;
+  const int grid = comm_grid(bytes / 16, threads);
+  all_gather_kernel<<<grid, threads, 0, s>>>(t, flag_off, slot_off, reinterpret_cast<const char*>(in),
+                                             reinterpret_cast<char*>(out), bytes, rank, world, epoch, channel,
+                                             done_counter, status, (unsigned long long)budget_ns);
+  return cudaGetLastError();
+}
+
+cudaError_t symm_reduce_scatter_launch(const PeerTable& t, long long flag_off, long long data_off, void* mc_base,
+                                       int elem_type, void* out, long long numel, float scale, int rank, int world,
+                                       unsigned epoch, int ch_start, int ch_end, unsigned* done_counter, int* status,
+                                       long long budget_ns, cudaStream_t s) {
+  const int es = elem_type == kElemF32 ? 4 : 2;
+  if (world > kMaxPeers || (data_off & 15) || ((numel * es) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+    return cudaErrorInvalidValue;
+  const int threads = 512;
+  const int grid = comm_grid(numel / (16 / es), threads);
+  char* mc = reinterpret_cast<char*>(mc_base);
+  const unsigned long long b = (unsigned long long)budget_ns;
+#define DION_RS(T, MC)                                                                                           \
+  reduce_scatter_kernel<T, MC><<<grid, threads, 0, s>>>(t, flag_off, data_off, mc, reinterpret_cast<T*>(out), numel, \
+                                                        scale, rank, world, epoch, ch_start, ch_end, done_counter,   \
+                                                        status, b)
+  if (elem_type == kElemF32) {
+    if (mc) DION_RS(float, true);
+    else DION_RS(float, false);
+  } else {
+    if (mc) DION_RS(__nv_bfloat16, true);
+    else DION_RS(__nv_bfloat16, false);
+  }
+#undef DION_RS
   return cudaGetLastError();
 }
 

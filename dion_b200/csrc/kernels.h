@@ -125,5 +125,15 @@ cudaError_t symm_all_reduce_launch(const PeerTable& t, long long flag_off, long 
 cudaError_t symm_reduce_into_launch(const PeerTable& t, long long flag_off, long long data_off, int src_type,
                                     void* dst, int dst_type, long long numel, float scale, float beta, int rank,
                                     int world, unsigned epoch, unsigned* done_counter, int* status, cudaStream_t s);
+// FSDP-style collectives: all-gather through a double-buffered symmetric staging slot (in / out
+// are ordinary local buffers) and reduce-scatter of a symmetric input into an ordinary output.
+// `budget_ns` bounds every wait on a peer.
+cudaError_t symm_all_gather_launch(const PeerTable& t, long long flag_off, long long slot_off, const void* in,
+                                   void* out, long long bytes, int rank, int world, unsigned epoch, int channel,
+                                   unsigned* done_counter, int* status, long long budget_ns, cudaStream_t s);
+cudaError_t symm_reduce_scatter_launch(const PeerTable& t, long long flag_off, long long data_off, void* mc_base,
+                                       int elem_type, void* out, long long numel, float scale, int rank, int world,
+                                       unsigned epoch, int ch_start, int ch_end, unsigned* done_counter, int* status,
+                                       long long budget_ns, cudaStream_t s);
 
 }  // namespace dion

@@ -298,3 +298,7 @@ def _apply_fsdp(model: GPT, fsdp_mesh: DeviceMesh, reshard_after_forward: bool =
     shard_map = {model.transformer.wte.weight: Shard(1), model.lm_head.weight: Shard(1)}
     fully_shard(model, mesh=fsdp_mesh, mp_policy=mp_policy, shard_placement_fn=lambda p, m=shard_map: m.get(p),
                 reshard_after_forward=False)
+    # all-gather / reduce-scatter as in-tree kernels over symmetric memory where the group allows it
+    from ..parallel import fsdp_comm
+
+    fsdp_comm.install(model)

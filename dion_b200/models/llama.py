@@ -169,3 +169,6 @@ def parallelize_llama_model(model: Llama, fsdp_mesh: DeviceMesh, reshard_after_f
     top = {model.tok_embeddings.weight: Shard(1), model.output.weight: Shard(1)}
     fully_shard(model, mesh=fsdp_mesh, mp_policy=mp, reshard_after_forward=False,
                 shard_placement_fn=lambda p, m=top: m.get(p))
+    from ..parallel import fsdp_comm
+
+    fsdp_comm.install(model)

@@ -219,6 +219,64 @@ def case_fsdp():
             # gradient differences flip whole entries by 2 * lr
             loose = "wte" in n1 or "lm_head" in n1
             check(f"fsdp {name} {n1}", _full(p1.detach()), p2.detach(), 6e-2 if (CUDA or loose) else 5e-3)
+    if CUDA and os.environ.get("DION_B200_SYMM", "1") != "0":
+        from dion_b200.parallel import fsdp_comm
+
+        calls = [(a.kernel_calls, r.kernel_calls) for a, r in fsdp_comm._installed.values()]
+        assert calls and all(a > 0 and r > 0 for a, r in calls), f"FSDP ran on library collectives: {calls}"
+
+
+def case_fsdp_comm():
+    """All-gather / reduce-scatter kernels behind the FSDP2 hooks against the library collectives:
+    several sizes (the arenas regrow), fp32 and bf16, SUM and AVG, slot reuse back to back."""
+    from dion_b200.parallel.fsdp_comm import SymmAllGather, SymmReduceScatter
+
+    g = dist.group.WORLD
+    ag, rs = SymmAllGather(g, DEV), SymmReduceScatter(g, DEV)
+    gen = torch.Generator().manual_seed(7 + RANK)
+    for it, (n, dtype) in enumerate([(4096, torch.bfloat16), (1 << 20, torch.bfloat16), (40, torch.float32),
+                                     (3 << 19, torch.float32), (1 << 20, torch.bfloat16), (8, torch.bfloat16)]):
+        # all-gather, the way FSDP calls it: the input is a view of the output
+        out = ag.allocate((n * WORLD,), dtype=dtype, device=DEV)
+        inp = out.narrow(0, RANK * n, n)
+        inp.copy_(torch.randn(n, generator=gen).to(DEV))
+        want = torch.empty_like(out)
+        dist.all_gather_into_tensor(want, inp.clone(), group=g)
+        ag(out, inp, g)
+        assert torch.equal(out, want), f"all-gather mismatch (n={n}, {dtype})"
+        # separate input buffer
+        inp2 = torch.randn(n, generator=gen).to(DEV).to(dtype)
+        out2 = torch.empty(n * WORLD, dtype=dtype, device=DEV)
+        dist.all_gather_into_tensor(want, inp2, group=g)
+        ag(out2, inp2, g)
+        assert torch.equal(out2, want)
+        # reduce-scatter, input from allocate() then output from allocate()
+        for op in (dist.ReduceOp.AVG, dist.ReduceOp.SUM):
+            rin = rs.allocate((n * WORLD,), dtype=dtype, device=DEV)
+            rin.copy_(torch.randn(n * WORLD, generator=gen).to(DEV))
+            rout = rs.allocate((n,), dtype=dtype, device=DEV)
+            want_r = torch.empty(n, dtype=dtype, device=DEV)
+            if CUDA:
+                dist.reduce_scatter_tensor(want_r, rin.clone(), op=op, group=g)
+            else:
+                full = rin.clone().float()
+                dist.all_reduce(full, group=g)
+                want_r = (full / (WORLD if op == dist.ReduceOp.AVG else 1))[RANK * n:(RANK + 1) * n].to(dtype)
+            if CUDA:
+                rs(rout, rin, g, op)
+            else:
+                # gloo has no reduce-scatter; the object is only exercised for its bookkeeping here
+                rout.copy_(want_r)
+            check(f"reduce-scatter n={n} {dtype} {op}", rout, want_r, 2e-2 if dtype == torch.bfloat16 else 1e-5)
+    if CUDA:
+        from dion_b200 import ops
+
+        ops.check_status()
+        assert ag.kernel_calls > 0 and rs.kernel_calls > 0, (ag.kernel_calls, ag.fallback_calls, rs.kernel_calls,
+                                                              rs.fallback_calls)
+        if RANK == 0:
+            print(f"fsdp_comm: all-gather kernel/fallback {ag.kernel_calls}/{ag.fallback_calls}, "
+                  f"reduce-scatter {rs.kernel_calls}/{rs.fallback_calls}", flush=True)
 
 
 def case_tp():
