@@ -579,6 +579,26 @@ void symm_reduce_into(const Tensor& src, Tensor dst, at::IntArrayRef peers, int6
                                                 status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()));
 }
 
+void split_tf32(const Tensor& x, Tensor hi, Tensor lo) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.scalar_type() == at::kFloat && hi.scalar_type() == at::kFloat && lo.scalar_type() == at::kFloat);
+  TORCH_CHECK(x.is_contiguous() && hi.is_contiguous() && lo.is_contiguous() && hi.numel() == x.numel() &&
+              lo.numel() == x.numel());
+  ++g_launches;
+  DION_CUDA_CHECK(dion::split_tf32_launch(x.data_ptr<float>(), hi.data_ptr<float>(), lo.data_ptr<float>(), x.numel(),
+                                          at::cuda::getCurrentCUDAStream()));
+}
+
+void refine_prep(const Tensor& G, Tensor C, Tensor d) {
+  const c10::cuda::CUDAGuard guard(G.device());
+  TORCH_CHECK(G.scalar_type() == at::kFloat && C.scalar_type() == at::kFloat && d.scalar_type() == at::kFloat);
+  TORCH_CHECK(G.dim() == 3 && G.size(1) == G.size(2) && G.is_contiguous() && C.is_contiguous() && d.is_contiguous());
+  TORCH_CHECK(C.numel() == G.numel() && d.numel() == G.size(0) * G.size(1));
+  ++g_launches;
+  DION_CUDA_CHECK(dion::refine_prep_launch(G.data_ptr<float>(), C.data_ptr<float>(), d.data_ptr<float>(),
+                                           (int)G.size(0), (int)G.size(1), at::cuda::getCurrentCUDAStream()));
+}
+
 // out (world * n) = concatenation of every rank's `inp` (n), through the staging slot at `slot_off`
 void symm_all_gather(const Tensor& inp, Tensor out, at::IntArrayRef peers, int64_t flag_off, int64_t slot_off,
                      int64_t rank, int64_t epoch, int64_t channel, Tensor counter, Tensor status, int64_t budget_ns) {
@@ -663,6 +683,8 @@ TORCH_LIBRARY(dion_b200, m) {
   m.def("embedding_bwd(Tensor dout, Tensor idx, Tensor(a!) dtable) -> ()");
   m.def("chol_inverse(Tensor G, Tensor(a!) Z, Tensor(b!) work, Tensor(c!) info, float pivot_floor) -> ()");
   m.def("col_sumsq(Tensor X, Tensor(a!) out) -> ()");
+  m.def("split_tf32(Tensor x, Tensor(a!) hi, Tensor(b!) lo) -> ()");
+  m.def("refine_prep(Tensor G, Tensor(a!) C, Tensor(b!) d) -> ()");
   m.def("launch_count() -> int", &launch_count);
 }
 
@@ -681,6 +703,8 @@ TORCH_LIBRARY_IMPL(dion_b200, CUDA, m) {
   m.impl("embedding_bwd", &embedding_bwd);
   m.impl("chol_inverse", &chol_inverse);
   m.impl("col_sumsq", &col_sumsq);
+  m.impl("split_tf32", &split_tf32);
+  m.impl("refine_prep", &refine_prep);
   m.impl("gemm_scatter", &gemm_scatter);
   m.impl("symm_barrier", &symm_barrier);
   m.impl("symm_all_reduce", &symm_all_reduce);

@@ -102,6 +102,10 @@ cudaError_t chol_inverse_launch(const float* G, float* Rinv, float* work, int* i
 // Column sums of squares: out[b, j] = sum_i X[b, i, j]^2  (X fp32/bf16, row-major [batch, rows, cols])
 cudaError_t col_sumsq_launch(const void* X, int x_type, float* out, int batch, long long rows, int cols,
                              long long ldx, long long batch_stride, cudaStream_t s);
+// hi / lo halves of fp32 data for 3xTF32 products; all three pointers 16-byte aligned
+cudaError_t split_tf32_launch(const float* x, float* hi, float* lo, long long numel, cudaStream_t s);
+// d = rsqrt(diag G) (0 where the diagonal vanishes), C = strictly lower part of D G D; contiguous [batch, r, r]
+cudaError_t refine_prep_launch(const float* G, float* C, float* d, int batch, int r, cudaStream_t s);
 
 // ---------------------------------------------------------------------------
 // Collectives over symmetric memory (one arena per process group; the same offset names

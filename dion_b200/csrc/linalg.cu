@@ -267,6 +267,56 @@ __global__ void __launch_bounds__(256) col_sumsq_kernel(const void* __restrict__
   }
 }
 
+// x = hi + lo with hi exactly representable in tf32 (low 13 mantissa bits cleared): the two
+// operands of a 3xTF32 product, written in one pass over x.
+__global__ void __launch_bounds__(256) split_tf32_kernel(const float4* __restrict__ x, float4* __restrict__ hi,
+                                                        float4* __restrict__ lo, long long nvec,
+                                                        const float* __restrict__ xs, float* __restrict__ his,
+                                                        float* __restrict__ los, long long ntail) {
+  auto split = [](float v, float& h, float& l) {
+    h = __int_as_float(__float_as_int(v) & 0xffffe000);
+    l = v - h;
+  };
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float4 v = x[i];
+    float4 h, l;
+    split(v.x, h.x, l.x);
+    split(v.y, h.y, l.y);
+    split(v.z, h.z, l.z);
+    split(v.w, h.w, l.w);
+    hi[i] = h;
+    lo[i] = l;
+  }
+  if (blockIdx.x == 0 && threadIdx.x < ntail) split(xs[threadIdx.x], his[threadIdx.x], los[threadIdx.x]);
+}
+
+// Preparation of one triangular Newton correction from a Gram matrix G (r x r per batch entry):
+//   d_i  = G_ii > tiny ? rsqrt(G_ii) : 0
+//   C_ij = i > j ? d_i * G_ij * d_j : 0          (strictly lower part of D G D - I)
+// One block per (row block of 8, batch entry); d is written by the blocks of the first column tile.
+__global__ void __launch_bounds__(256) refine_prep_kernel(const float* __restrict__ G, float* __restrict__ C,
+                                                         float* __restrict__ d, int r) {
+  const long long b = blockIdx.y;
+  const float* g = G + b * (long long)r * r;
+  float* c = C + b * (long long)r * r;
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= r) return;
+  const int lane = threadIdx.x & 31;
+  const float gii = g[(long long)row * r + row];
+  const float di = gii > 1e-30f ? rsqrtf(gii) : 0.f;
+  if (lane == 0) d[b * r + row] = di;
+  for (int j = lane; j < r; j += 32) {
+    float v = 0.f;
+    if (j < row) {
+      const float gjj = g[(long long)j * r + j];
+      const float dj = gjj > 1e-30f ? rsqrtf(gjj) : 0.f;
+      v = di * g[(long long)row * r + j] * dj;
+    }
+    c[(long long)row * r + j] = v;
+  }
+}
+
 }  // namespace
 
 cudaError_t chol_inverse_launch(const float* G, float* Z, float* work, int* info, int batch, int r, long long ldg,
@@ -305,6 +355,27 @@ cudaError_t col_sumsq_launch(const void* X, int x_type, float* out, int batch, l
   if (batch == 0 || cols == 0) return cudaSuccess;
   dim3 grid((cols + 31) / 32, batch);
   col_sumsq_kernel<<<grid, 256, 0, s>>>(X, x_type, out, rows, cols, ldx, batch_stride);
+  return cudaGetLastError();
+}
+
+cudaError_t split_tf32_launch(const float* x, float* hi, float* lo, long long numel, cudaStream_t s) {
+  if (numel == 0) return cudaSuccess;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(hi) | reinterpret_cast<uintptr_t>(lo)) & 15)
+    return cudaErrorInvalidValue;
+  const long long nvec = numel / 4, ntail = numel - nvec * 4;
+  long long grid = (nvec + 255) / 256;
+  if (grid > 148 * 16) grid = 148 * 16;
+  if (grid < 1) grid = 1;
+  split_tf32_kernel<<<(int)grid, 256, 0, s>>>(reinterpret_cast<const float4*>(x), reinterpret_cast<float4*>(hi),
+                                              reinterpret_cast<float4*>(lo), nvec, x + nvec * 4, hi + nvec * 4,
+                                              lo + nvec * 4, ntail);
+  return cudaGetLastError();
+}
+
+cudaError_t refine_prep_launch(const float* G, float* C, float* d, int batch, int r, cudaStream_t s) {
+  if (batch == 0 || r == 0) return cudaSuccess;
+  if (batch > 65535) return cudaErrorInvalidValue;
+  refine_prep_kernel<<<dim3((r + 7) / 8, batch), 256, 0, s>>>(G, C, d, r);
   return cudaGetLastError();
 }
 

@@ -3,7 +3,7 @@ PyTorch implementations of the same semantics (host-side tests and numerical ora
 
 from . import _ext, runtime  # noqa: F401
 from .gemm import gemm, gemm_reference  # noqa: F401
-from .linalg import chol_inverse, chol_inverse_reference, col_sumsq  # noqa: F401
+from .linalg import chol_inverse, chol_inverse_reference, col_sumsq, refine_prep, split_tf32  # noqa: F401
 from .multi_tensor import (  # noqa: F401
     adamw_update,
     adamw_update_reference,

@@ -87,3 +87,27 @@ def col_sumsq(X: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tens
             out.copy_(res.view_as(out))
             res = out
     return res.view(-1) if squeeze else res.view(X3.shape[0], X3.shape[2])
+
+
+def split_tf32(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``x = hi + lo`` with ``hi`` exactly representable in tf32 (low 13 mantissa bits cleared):
+    the operand pair of a 3xTF32 product (three tensor-core passes, close to fp32 accuracy)."""
+    if runtime.use_cuda_kernels(x) and x.dtype == torch.float32 and x.is_contiguous() and x.data_ptr() % 16 == 0:
+        hi, lo = torch.empty_like(x), torch.empty_like(x)
+        torch.ops.dion_b200.split_tf32(x, hi, lo)
+        return hi, lo
+    hi = (x.view(torch.int32) & -8192).view(torch.float32)
+    return hi, x - hi
+
+
+def refine_prep(G: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """From Gram matrices ``G: [B, r, r]``: ``d = rsqrt(diag G)`` (0 where the diagonal vanishes)
+    and ``C = stril(D G D)``, the strictly lower part of the column-scaled Gram matrix."""
+    if runtime.use_cuda_kernels(G) and G.dtype == torch.float32 and G.dim() == 3:
+        G = G.contiguous()
+        C, d = torch.empty_like(G), torch.empty(G.shape[:-1], dtype=torch.float32, device=G.device)
+        torch.ops.dion_b200.refine_prep(G, C, d)
+        return C, d
+    diag = torch.diagonal(G, dim1=-2, dim2=-1)
+    d = torch.where(diag > 1e-30, diag.clamp_min(1e-30).rsqrt(), torch.zeros_like(diag))
+    return torch.tril(G * d.unsqueeze(-1) * d.unsqueeze(-2), diagonal=-1), d

@@ -35,8 +35,7 @@ GRAM_PRECISION = os.environ.get("DION_B200_GRAM_PRECISION", "3xtf32")
 
 def _split_tf32(x: Tensor):
     """x = hi + lo with hi exactly representable in tf32 (low 13 mantissa bits cleared)."""
-    hi = (x.view(torch.int32) & -8192).view(torch.float32)
-    return hi, x - hi
+    return ops.linalg.split_tf32(x)
 
 
 def gram(P: Tensor, reduce_group=None) -> Tensor:
@@ -101,13 +100,12 @@ def _refine(X: Tensor, row_group: Optional[dist.ProcessGroup]) -> Tensor:
     G = gram(X, row_group)
     if row_group is not None and dist.get_world_size(row_group) > 1:
         symm.all_reduce(G, row_group)
-    diag = torch.diagonal(G, dim1=-2, dim2=-1)
-    d = torch.where(diag > 1e-30, diag.clamp_min(1e-30).rsqrt(), torch.zeros_like(diag))
-    C = torch.tril(G * d.unsqueeze(-1) * d.unsqueeze(-2), diagonal=-1)  # stril(E)
+    C, d = ops.linalg.refine_prep(G)  # d = rsqrt(diag G), C = stril(D G D) = stril(E)
     Xs = X * d.unsqueeze(-2)
-    # the correction term is small, a single tensor-core pass keeps it far below fp32 resolution
-    corr = ops.gemm(Xs, C.transpose(-1, -2)) if X.is_cuda else Xs @ C.transpose(-1, -2)
-    return Xs - corr
+    if X.is_cuda:
+        # the correction term is small, a single tensor-core pass keeps it far below fp32 resolution
+        return ops.gemm(Xs, C.transpose(-1, -2), c=Xs, alpha=-1.0, beta=1.0)
+    return Xs - Xs @ C.transpose(-1, -2)
 
 
 def orthonormalize_many(Ps, row_groups=None, refine_passes: int = 2,

@@ -560,11 +560,13 @@ def main(argv=None):
             ops.check_status(device)
 
         if hp.checkpoint_freq > 0 and step % hp.checkpoint_freq == 0 and step > 0:
+            sync()
+            training_time_ms += 1000 * (time.time() - t0)  # checkpoints are not training time
             if hasattr(optimizer, "synchronize_for_checkpoint"):
                 optimizer.synchronize_for_checkpoint()
             ckpt.save(step=step)
-        sync()
-        t0 = time.time()
+            sync()
+            t0 = time.time()
 
     if pbar:
         pbar.close()

@@ -70,3 +70,21 @@ def test_col_sumsq_kernel(dtype):
     X = torch.randn(5, 333, 200, device="cuda").to(dtype)
     out = ops.col_sumsq(X)
     torch.testing.assert_close(out, X.float().square().sum(-2), rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.gpu
+def test_split_tf32_and_refine_prep_match_torch():
+    from dion_b200.ops.linalg import refine_prep, split_tf32
+
+    x = torch.randn(3, 130, 77, device="cuda") * 10
+    hi, lo = split_tf32(x)
+    ref_hi = (x.view(torch.int32) & -8192).view(torch.float32)
+    assert torch.equal(hi, ref_hi) and torch.equal(lo, x - ref_hi)
+    a = torch.randn(5, 200, 72, device="cuda")
+    a[2, :, 7] = 0  # a vanishing column: d = 0, its row and column of C are zero
+    G = a.transpose(1, 2) @ a
+    C, d = refine_prep(G)
+    Cr, dr = refine_prep(G.cpu())
+    torch.testing.assert_close(d.cpu(), dr, rtol=1e-5, atol=0)
+    torch.testing.assert_close(C.cpu(), Cr, rtol=1e-5, atol=1e-7)
+    assert d[2, 7] == 0 and C[2, 7].abs().max() == 0 and C[2, :, 7].abs().max() == 0
