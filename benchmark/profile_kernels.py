@@ -103,7 +103,7 @@ def case(name: str, ref: bool = False):
         fn = lambda: torch.ops.dion_b200.gemm_scatter(bm, x, x, out[0, 0], ptrs, 1, m // W, W, 1.0, 2.8, st)
         return fn, 2.0 * B * m * m * n, B * (m * m + 3 * m * n) * 2
     if name == "chol":            # all Dion Gram matrices of GPT-160M in one launch
-        B, rr = 72, 768
+        B, rr = int(os.environ.get("CHOL_BATCH", "72")), 768
         P = r(B, 1024, rr, dt=f32)
         G = P.transpose(1, 2) @ P
         Z, W_, info = torch.empty_like(G), torch.empty_like(G), torch.empty(B, dtype=torch.int32, device=dev)

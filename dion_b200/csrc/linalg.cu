@@ -15,6 +15,9 @@
 //   4. A[k+1:, k+1:] -= panel * panel^T        (lower triangle, 64x64 register tiles)
 //      B[k+1:, :]    -= panel * Z[k,:]
 #include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include "kernels.h"
 
@@ -267,6 +270,273 @@ __global__ void __launch_bounds__(256) col_sumsq_kernel(const void* __restrict__
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Second-generation kernel: the same algorithm run by a cluster of two CTAs per matrix, so that
+// 72 matrices occupy 144 SMs instead of 72.  Both CTAs factor the diagonal block and build the
+// panel / block row redundantly (a few percent of the work, warp-synchronous in registers for the
+// 32 x 32 factorisation), then share the trailing 128 x 128 tiles, each 256-thread group
+// computing one tile with 8 x 8 register sub-tiles; a cluster barrier (release / acquire) ends
+// every block step so that each CTA sees the other's updates of W and Z in global memory.
+constexpr int kChol2Threads = 512;
+
+__device__ __forceinline__ uint32_t chol_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void chol_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// out[row0 + i][col0 + j] -= sum_a At[a][i] * Bt[a][j] for a 128 x 128 tile; thread t of the
+// 256-thread group owns rows {4 ty .. 4 ty + 3} and {64 + 4 ty ..}, columns likewise with tx.
+template <int NB>
+__device__ __forceinline__ void tile_update128(float* __restrict__ out, long long ld, int row0, int col0,
+                                               const float* __restrict__ At, int a_stride,
+                                               const float* __restrict__ Bt, int b_stride, int row_end,
+                                               int col_end, int t) {
+  const int ty = t >> 4, tx = t & 15;
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+  const float* ap = At + ty * 4;
+  const float* bp = Bt + tx * 4;
+#pragma unroll 4
+  for (int a = 0; a < NB; ++a) {
+    const float4 a0 = *reinterpret_cast<const float4*>(ap + (long long)a * a_stride);
+    const float4 a1 = *reinterpret_cast<const float4*>(ap + (long long)a * a_stride + 64);
+    const float4 b0 = *reinterpret_cast<const float4*>(bp + (long long)a * b_stride);
+    const float4 b1 = *reinterpret_cast<const float4*>(bp + (long long)a * b_stride + 64);
+    const float ar[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    const float br[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(ar[i], br[j], acc[i][j]);
+  }
+  const bool ld_vec = (ld & 3) == 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = row0 + (i >> 2) * 64 + ty * 4 + (i & 3);
+    if (r >= row_end) continue;
+#pragma unroll
+    for (int jh = 0; jh < 2; ++jh) {
+      const int c = col0 + jh * 64 + tx * 4;
+      float* o = out + (long long)r * ld + c;
+      if (ld_vec && c + 3 < col_end) {
+        float4 v = *reinterpret_cast<const float4*>(o);
+        v.x -= acc[i][jh * 4 + 0];
+        v.y -= acc[i][jh * 4 + 1];
+        v.z -= acc[i][jh * 4 + 2];
+        v.w -= acc[i][jh * 4 + 3];
+        *reinterpret_cast<float4*>(o) = v;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (c + j < col_end) o[j] -= acc[i][jh * 4 + j];
+      }
+    }
+  }
+}
+
+// Cholesky factor L of the NB x NB block in `dblk` (lower triangle, row pitch NB + 1) and its
+// inverse, written to `linv` (pitch NB + 1) and `linv_al` (pitch NB, rows 16-byte aligned), upper
+// parts zero.  One warp, lane i owns row i of the block and of the right-hand side in registers;
+// rows >= nb are treated as rows of the identity.  Column step j (a rolled loop, so that this
+// single-warp code is not bound by instruction fetch; everything indexed by a column c inside
+// it is unrolled to keep the rows in registers):
+//   L[:, j] = A[:, j] / sqrt(A_jj);  A[i, c] -= L[i, j] L[c, j]  (c > j)
+//   X[j, :] /= L_jj;                 X[i, :] -= L[i, j] X[j, :]  (i > j), X starting as I
+// Returns the number of clamped pivots (valid in every lane).
+template <int NB>
+__device__ __forceinline__ int warp_factor_block(const float* dblk, float* linv, float* linv_al, int nb,
+                                                 float pivot_floor, int lane) {
+  static_assert(NB <= 32, "one lane per row");
+  constexpr int P = NB + 1;
+  float a[NB], x[NB];
+#pragma unroll
+  for (int c = 0; c < NB; ++c) {
+    float v = (c == lane) ? 1.f : 0.f;
+    if (lane < nb && c < nb) v = dblk[lane * P + c];
+    a[c] = v;
+    x[c] = (c == lane) ? 1.f : 0.f;
+  }
+  int clamped = 0;
+#pragma unroll 1
+  for (int j = 0; j < NB; ++j) {
+    float aj = 0.f;  // A[lane][j]
+#pragma unroll
+    for (int c = 0; c < NB; ++c) aj = (c == j) ? a[c] : aj;
+    float d = __shfl_sync(0xffffffffu, aj, j);
+    if (!(d > pivot_floor)) {
+      d = pivot_floor;
+      if (j < nb) ++clamped;
+    }
+    const float inv_s = rsqrtf(d);
+    const float l = (lane > j) ? aj * inv_s : 0.f;  // L[lane][j] below the diagonal
+#pragma unroll
+    for (int c = 0; c < NB; ++c) {
+      const float lc = __shfl_sync(0xffffffffu, l, c);
+      if (c > j && lane >= c) a[c] = fmaf(-l, lc, a[c]);
+      const float xs = (lane == j) ? x[c] * inv_s : x[c];
+      const float xj = __shfl_sync(0xffffffffu, xs, j);
+      x[c] = (lane > j) ? fmaf(-l, xj, xs) : xs;
+    }
+  }
+  if (lane < NB) {
+#pragma unroll
+    for (int c = 0; c < NB; ++c) {
+      const float v = (c <= lane) ? x[c] : 0.f;
+      linv[lane * P + c] = v;
+      linv_al[lane * NB + c] = v;
+    }
+  }
+  return clamped;
+}
+
+template <int NB>
+__global__ void __launch_bounds__(kChol2Threads, 1)
+chol_inverse_pair_kernel(const float* __restrict__ Gall, float* __restrict__ Zall, float* __restrict__ Wall,
+                         int* __restrict__ info, int r, long long ldg, long long g_batch_stride, int rp,
+                         float pivot_floor) {
+  extern __shared__ __align__(16) float sm[];
+  // rp = r rounded up to a multiple of 128
+  float* panelT = sm;                         // [NB][rp]   panel, transposed
+  float* zrow = panelT + (size_t)NB * rp;     // [NB][rp]   current block row of Z
+  float* dblk = zrow + (size_t)NB * rp;       // [NB][NB+1]
+  float* linv = dblk + NB * (NB + 1);         // [NB][NB+1]
+  float* linv_al = linv + NB * (NB + 1);      // [NB][NB], rows 16-byte aligned (NB * (NB + 1) is a multiple of 4)
+  float* dscale = linv_al + NB * NB;          // [rp] Jacobi scaling 1/sqrt(G_ii)
+
+  const int cta = (int)chol_cluster_rank();
+  const int b = blockIdx.x >> 1;
+  const float* G = Gall + (long long)b * g_batch_stride;
+  float* Z = Zall + (long long)b * r * r;
+  float* W = Wall + (long long)b * r * r;
+  const int tid = threadIdx.x;
+  int clamp_count = 0;  // meaningful in warp 0
+
+  for (int i = tid; i < rp; i += kChol2Threads) {
+    float d = 0.f;
+    if (i < r) {
+      const float g = G[(long long)i * ldg + i];
+      d = (g > 1e-30f) ? rsqrtf(g) : 0.f;
+    }
+    dscale[i] = d;
+  }
+  __syncthreads();
+  // W = D G D (lower triangle is what gets used), Z = I; the two CTAs take alternate rows
+  for (int i = cta; i < r; i += 2) {
+    const float di = dscale[i];
+    for (int j = tid; j < r; j += kChol2Threads) {
+      W[(long long)i * r + j] = G[(long long)i * ldg + j] * di * dscale[j];
+      Z[(long long)i * r + j] = (i == j) ? 1.f : 0.f;
+    }
+  }
+  chol_cluster_sync();
+
+  for (int k0 = 0; k0 < r; k0 += NB) {
+    const int nb = min(NB, r - k0);
+    // ---- 1. diagonal block -> shared, factor and invert it in warp 0
+    for (int e = tid; e < NB * NB; e += kChol2Threads) {
+      const int i = e / NB, j = e - i * NB;
+      float v = 0.f;
+      if (i < nb && j < nb && j <= i) v = W[(long long)(k0 + i) * r + k0 + j];
+      dblk[i * (NB + 1) + j] = v;
+    }
+    __syncthreads();
+    if (tid < 32) clamp_count += warp_factor_block<NB>(dblk, linv, linv_al, nb, pivot_floor, tid);
+    __syncthreads();
+
+    // ---- 2. Z[k,:] = Linv * B[k,:] for columns < k0 + nb (CTA 0 writes it back)
+    const int zc = k0 + nb;
+    for (int c = tid; c < rp; c += kChol2Threads) {
+      float bcol[NB];
+#pragma unroll
+      for (int a = 0; a < NB; ++a) bcol[a] = (a < nb && c < zc) ? Z[(long long)(k0 + a) * r + c] : 0.f;
+#pragma unroll 1
+      for (int a = 0; a < NB; ++a) {
+        const float4* lrow = reinterpret_cast<const float4*>(linv_al + a * NB);  // lower triangular, zeros above
+        float s = 0.f;
+#pragma unroll
+        for (int q = 0; q < NB / 4; ++q) {
+          const float4 lv = lrow[q];
+          s = fmaf(lv.x, bcol[4 * q], s);
+          s = fmaf(lv.y, bcol[4 * q + 1], s);
+          s = fmaf(lv.z, bcol[4 * q + 2], s);
+          s = fmaf(lv.w, bcol[4 * q + 3], s);
+        }
+        zrow[(size_t)a * rp + c] = s;
+        if (cta == 0 && a < nb && c < zc) Z[(long long)(k0 + a) * r + c] = s;
+      }
+    }
+    // ---- 3. panel = A[k+1:, k] * Linv^T, stored transposed: panelT[a][i - p0]
+    const int p0 = k0 + nb;  // first trailing row
+    const int tr = r - p0;   // trailing rows
+    for (int ii = tid; ii < rp; ii += kChol2Threads) {
+      float arow[NB];
+      const bool live = ii < tr;
+#pragma unroll
+      for (int a = 0; a < NB; ++a) arow[a] = (live && a < nb) ? W[(long long)(p0 + ii) * r + k0 + a] : 0.f;
+#pragma unroll 1
+      for (int a = 0; a < NB; ++a) {
+        const float4* lrow = reinterpret_cast<const float4*>(linv_al + a * NB);
+        float s = 0.f;
+#pragma unroll
+        for (int q = 0; q < NB / 4; ++q) {
+          const float4 lv = lrow[q];
+          s = fmaf(arow[4 * q], lv.x, s);
+          s = fmaf(arow[4 * q + 1], lv.y, s);
+          s = fmaf(arow[4 * q + 2], lv.z, s);
+          s = fmaf(arow[4 * q + 3], lv.w, s);
+        }
+        panelT[(size_t)a * rp + ii] = s;
+      }
+    }
+    __syncthreads();
+    if (tr <= 0) break;  // uniform over the cluster
+
+    // ---- 4. trailing updates with 128 x 128 tiles, spread over the four 256-thread groups of
+    //         the cluster: lower-triangular tiles of the Gram part, then the right-hand side
+    const int nt = (tr + 127) / 128;
+    const int nc = (zc + 127) / 128;
+    const int gram_tiles = nt * (nt + 1) / 2;
+    const int total_tiles = gram_tiles + nt * nc;
+    const int t = tid & 255;
+    for (int idx = cta * 2 + (tid >> 8); idx < total_tiles; idx += 4) {
+      if (idx < gram_tiles) {
+        int ti = 0, rem = idx;
+        while (rem > ti) {  // row ti of the lower triangle holds ti + 1 tiles
+          rem -= ti + 1;
+          ++ti;
+        }
+        const int tj = rem;
+        tile_update128<NB>(W, r, p0 + ti * 128, p0 + tj * 128, panelT + ti * 128, rp, panelT + tj * 128, rp, r, r,
+                           t);
+      } else {
+        const int q = idx - gram_tiles;
+        const int ti = q / nc, tc = q - ti * nc;
+        tile_update128<NB>(Z, r, p0 + ti * 128, tc * 128, panelT + ti * 128, rp, zrow + tc * 128, rp, r, zc, t);
+      }
+    }
+    chol_cluster_sync();
+  }
+
+  // undo the Jacobi scaling: G = D^-1 L' L'^T D^-1  =>  L^{-1} = L'^{-1} D, i.e. scale column j by d_j
+  chol_cluster_sync();
+  for (int i = cta; i < r; i += 2) {
+    for (int j = tid; j < r; j += kChol2Threads) {
+      const long long e = (long long)i * r + j;
+      Z[e] = (j <= i) ? Z[e] * dscale[j] : 0.f;
+    }
+  }
+  if (cta == 0 && tid == 0 && info) info[b] = clamp_count;
+}
+
+
 // x = hi + lo with hi exactly representable in tf32 (low 13 mantissa bits cleared): the two
 // operands of a 3xTF32 product, written in one pass over x.
 __global__ void __launch_bounds__(256) split_tf32_kernel(const float4* __restrict__ x, float4* __restrict__ hi,
@@ -322,6 +592,39 @@ __global__ void __launch_bounds__(256) refine_prep_kernel(const float* __restric
 cudaError_t chol_inverse_launch(const float* G, float* Z, float* work, int* info, int batch, int r, long long ldg,
                                 long long g_batch_stride, float pivot_floor, cudaStream_t s) {
   if (batch == 0 || r == 0) return cudaSuccess;
+  {
+    // cluster-pair kernel (two CTAs per matrix); DION_B200_CHOL_PAIR=0 selects the single-CTA one
+    static const int pair_env = [] {
+      const char* e = getenv("DION_B200_CHOL_PAIR");
+      return (e && e[0] == '0') ? 0 : 1;
+    }();
+    const int rp2 = ((r + 127) / 128) * 128;
+    const size_t smem2 = (size_t)(2 * 32 * rp2 + 2 * 32 * 33 + 32 * 32 + rp2 + 4) * sizeof(float);
+    if (pair_env && smem2 <= 227 * 1024) {
+      static bool granted = false;
+      if (!granted) {
+        cudaError_t e2 = cudaFuncSetAttribute(chol_inverse_pair_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              227 * 1024);
+        if (e2 != cudaSuccess) return e2;
+        granted = true;
+      }
+      cudaLaunchConfig_t cfg;
+      memset(&cfg, 0, sizeof(cfg));
+      cfg.gridDim = dim3(2 * batch, 1, 1);
+      cfg.blockDim = dim3(kChol2Threads, 1, 1);
+      cfg.dynamicSmemBytes = smem2;
+      cfg.stream = s;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      return cudaLaunchKernelEx(&cfg, chol_inverse_pair_kernel<32>, G, Z, work, info, r, ldg, g_batch_stride, rp2,
+                                pivot_floor);
+    }
+  }
   const int rp = ((r + 63) / 64) * 64;
   auto smem_for = [&](int nb) { return (size_t)(2 * nb * rp + 2 * nb * (nb + 1) + rp + 4) * sizeof(float); };
   constexpr size_t kMaxSmem = 227 * 1024;
