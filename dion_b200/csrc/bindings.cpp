@@ -579,6 +579,22 @@ void symm_reduce_into(const Tensor& src, Tensor dst, at::IntArrayRef peers, int6
                                                 status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()));
 }
 
+// q [B, T, H, D], k / v [B, T, Hkv, D] (contiguous bf16) -> out [B, T, H, D], lse [B, H, T]
+void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor out, Tensor lse, double scale, Tensor status) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "attention operands must be [B, T, H, D]");
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 &&
+              v.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16 && lse.scalar_type() == at::kFloat);
+  TORCH_CHECK(q.is_contiguous() && k.is_contiguous() && v.is_contiguous() && out.is_contiguous() && lse.is_contiguous());
+  const int64_t B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
+  TORCH_CHECK(k.size(0) == B && k.size(1) == T && k.size(3) == D && v.sizes() == k.sizes() && out.sizes() == q.sizes());
+  TORCH_CHECK(lse.numel() == B * H * T);
+  ++g_launches;
+  DION_CUDA_CHECK(dion::attn_fwd_launch(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr<float>(),
+                                        (int)B, (int)T, (int)H, (int)Hkv, (int)D, (float)scale, status.data_ptr<int>(),
+                                        at::cuda::getCurrentCUDAStream()));
+}
+
 void split_tf32(const Tensor& x, Tensor hi, Tensor lo) {
   const c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.scalar_type() == at::kFloat && hi.scalar_type() == at::kFloat && lo.scalar_type() == at::kFloat);
@@ -684,6 +700,7 @@ TORCH_LIBRARY(dion_b200, m) {
   m.def("chol_inverse(Tensor G, Tensor(a!) Z, Tensor(b!) work, Tensor(c!) info, float pivot_floor) -> ()");
   m.def("col_sumsq(Tensor X, Tensor(a!) out) -> ()");
   m.def("split_tf32(Tensor x, Tensor(a!) hi, Tensor(b!) lo) -> ()");
+  m.def("attn_fwd(Tensor q, Tensor k, Tensor v, Tensor(a!) out, Tensor(b!) lse, float scale, Tensor(c!) status) -> ()");
   m.def("refine_prep(Tensor G, Tensor(a!) C, Tensor(b!) d) -> ()");
   m.def("launch_count() -> int", &launch_count);
 }
@@ -704,6 +721,7 @@ TORCH_LIBRARY_IMPL(dion_b200, CUDA, m) {
   m.impl("chol_inverse", &chol_inverse);
   m.impl("col_sumsq", &col_sumsq);
   m.impl("split_tf32", &split_tf32);
+  m.impl("attn_fwd", &attn_fwd);
   m.impl("refine_prep", &refine_prep);
   m.impl("gemm_scatter", &gemm_scatter);
   m.impl("symm_barrier", &symm_barrier);

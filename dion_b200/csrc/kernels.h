@@ -102,6 +102,11 @@ cudaError_t chol_inverse_launch(const float* G, float* Rinv, float* work, int* i
 // Column sums of squares: out[b, j] = sum_i X[b, i, j]^2  (X fp32/bf16, row-major [batch, rows, cols])
 cudaError_t col_sumsq_launch(const void* X, int x_type, float* out, int batch, long long rows, int cols,
                              long long ldx, long long batch_stride, cudaStream_t s);
+// Causal flash attention forward on tcgen05: q [B*T, H*D], k / v [B*T, Hkv*D], out [B*T, H*D] bf16,
+// lse [B, H, T] fp32 (natural log of the softmax denominator, for the backward pass); D is 64 or 128,
+// T a multiple of 128.
+cudaError_t attn_fwd_launch(const void* q, const void* k, const void* v, void* out, float* lse, int B, int T, int H,
+                            int Hkv, int D, float scale, int* status, cudaStream_t stream);
 // hi / lo halves of fp32 data for 3xTF32 products; all three pointers 16-byte aligned
 cudaError_t split_tf32_launch(const float* x, float* hi, float* lo, long long numel, cudaStream_t s);
 // d = rsqrt(diag G) (0 where the diagonal vanishes), C = strictly lower part of D G D; contiguous [batch, r, r]

@@ -488,6 +488,26 @@ def linear_cross_entropy(x: torch.Tensor, weight: torch.Tensor, targets: torch.T
 
 # --------------------------------------------------------------------------- attention
 
+def flash_attention_forward(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: Optional[float] = None):
+    """Causal attention forward by the tcgen05 kernel.  q: [B, T, H, D], k / v: [B, T, Hkv, D], bf16,
+    contiguous, D in {64, 128}, T a multiple of 128.  Returns (out [B, T, H, D], lse [B, H, T])."""
+    B, T, H, D = q.shape
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    runtime.use_cuda_kernels(q)
+    out = torch.empty_like(q)
+    lse = torch.empty(B, H, T, dtype=torch.float32, device=q.device)
+    torch.ops.dion_b200.attn_fwd(q, k, v, out, lse, float(scale), runtime.status_tensor(q.device))
+    return out, lse
+
+
+def flash_attention_supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> bool:
+    B, T, H, D = q.shape
+    return (q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16
+            and D in (64, 128) and T % 128 == 0 and H % k.shape[2] == 0 and B * H <= 65535
+            and q.is_contiguous() and k.is_contiguous() and v.is_contiguous())
+
+
 def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     """Causal self-attention; q, k, v: [B, T, H, Dh] -> [B, T, H*Dh].  Supports grouped
     KV heads (H_kv dividing H)."""

@@ -198,3 +198,27 @@ def test_norm_branch_adds_both_gradients():
     _close(x.grad, xr.grad + g1.float(), 2e-2)
     assert torch.equal(xp, x)
     _close(gx_pass, g1.float() + 0 * xr.grad, 1e-2) if False else None
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(2, 256, 3, 3, 128), (1, 1024, 4, 2, 128), (3, 384, 2, 2, 64), (2, 128, 2, 1, 64)])
+def test_flash_attention_forward_matches_fp32_reference(shape):
+    from dion_b200 import ops
+    from dion_b200.ops.nn import flash_attention_forward
+
+    B, T, H, Hkv, D = shape
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q = torch.randn(B, T, H, D, device="cuda", generator=g).to(torch.bfloat16)
+    k = torch.randn(B, T, Hkv, D, device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn(B, T, Hkv, D, device="cuda", generator=g).to(torch.bfloat16)
+    out, lse = flash_attention_forward(q, k, v)
+    ops.check_status()
+    qf, kf, vf = (t.float().transpose(1, 2) for t in (q, k, v))
+    kf = kf.repeat_interleave(H // Hkv, dim=1)
+    vf = vf.repeat_interleave(H // Hkv, dim=1)
+    s = (qf @ kf.transpose(-1, -2)) / D ** 0.5
+    s = s.masked_fill(torch.triu(torch.ones(T, T, device="cuda", dtype=torch.bool), 1), float("-inf"))
+    ref = torch.softmax(s, dim=-1) @ vf
+    err = (out.float().transpose(1, 2) - ref).abs().max().item()
+    assert err < 2e-2, err
+    torch.testing.assert_close(lse, torch.logsumexp(s, dim=-1), rtol=1e-3, atol=1e-3)
