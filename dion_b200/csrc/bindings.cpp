@@ -595,6 +595,24 @@ void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor out, Ten
                                         at::cuda::getCurrentCUDAStream()));
 }
 
+void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& d_o, const Tensor& lse,
+              Tensor delta, Tensor dq, Tensor dk, Tensor dv, double scale, Tensor status) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&q, &k, &v, &o, &d_o, &dq, &dk, &dv})
+    TORCH_CHECK(t->dim() == 4 && t->scalar_type() == at::kBFloat16 && t->is_contiguous(),
+                "attention tensors must be contiguous bf16 [B, T, H, D]");
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && delta.scalar_type() == at::kFloat && lse.is_contiguous() &&
+              delta.is_contiguous() && delta.numel() == lse.numel());
+  const int64_t B = q.size(0), T = q.size(1), H = q.size(2), D = q.size(3), Hkv = k.size(2);
+  TORCH_CHECK(o.sizes() == q.sizes() && d_o.sizes() == q.sizes() && dq.sizes() == q.sizes() && v.sizes() == k.sizes() &&
+              dk.sizes() == k.sizes() && dv.sizes() == k.sizes() && lse.numel() == B * H * T);
+  g_launches += 3;
+  DION_CUDA_CHECK(dion::attn_bwd_launch(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(),
+                                        lse.data_ptr<float>(), delta.data_ptr<float>(), dq.data_ptr(), dk.data_ptr(),
+                                        dv.data_ptr(), (int)B, (int)T, (int)H, (int)Hkv, (int)D, (float)scale,
+                                        status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()));
+}
+
 void split_tf32(const Tensor& x, Tensor hi, Tensor lo) {
   const c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.scalar_type() == at::kFloat && hi.scalar_type() == at::kFloat && lo.scalar_type() == at::kFloat);
@@ -701,6 +719,9 @@ TORCH_LIBRARY(dion_b200, m) {
   m.def("col_sumsq(Tensor X, Tensor(a!) out) -> ()");
   m.def("split_tf32(Tensor x, Tensor(a!) hi, Tensor(b!) lo) -> ()");
   m.def("attn_fwd(Tensor q, Tensor k, Tensor v, Tensor(a!) out, Tensor(b!) lse, float scale, Tensor(c!) status) -> ()");
+  m.def(
+      "attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, Tensor lse, Tensor(a!) delta, Tensor(b!) dq, "
+      "Tensor(c!) dk, Tensor(d!) dv, float scale, Tensor(e!) status) -> ()");
   m.def("refine_prep(Tensor G, Tensor(a!) C, Tensor(b!) d) -> ()");
   m.def("launch_count() -> int", &launch_count);
 }
@@ -722,6 +743,7 @@ TORCH_LIBRARY_IMPL(dion_b200, CUDA, m) {
   m.impl("col_sumsq", &col_sumsq);
   m.impl("split_tf32", &split_tf32);
   m.impl("attn_fwd", &attn_fwd);
+  m.impl("attn_bwd", &attn_bwd);
   m.impl("refine_prep", &refine_prep);
   m.impl("gemm_scatter", &gemm_scatter);
   m.impl("symm_barrier", &symm_barrier);

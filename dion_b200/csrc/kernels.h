@@ -107,6 +107,11 @@ cudaError_t col_sumsq_launch(const void* X, int x_type, float* out, int batch, l
 // T a multiple of 128.
 cudaError_t attn_fwd_launch(const void* q, const void* k, const void* v, void* out, float* lse, int B, int T, int H,
                             int Hkv, int D, float scale, int* status, cudaStream_t stream);
+// Backward of the same attention: dq [B*T, H*D], dk / dv [B*T, Hkv*D] (bf16) from q, k, v, the forward's
+// output `o` and log-sum-exp `lse`, and the output gradient `d_o`; `delta` is a [B, H, T] fp32 workspace.
+cudaError_t attn_bwd_launch(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                            const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int T, int H, int Hkv,
+                            int D, float scale, int* status, cudaStream_t stream);
 // hi / lo halves of fp32 data for 3xTF32 products; all three pointers 16-byte aligned
 cudaError_t split_tf32_launch(const float* x, float* hi, float* lo, long long numel, cudaStream_t s);
 // d = rsqrt(diag G) (0 where the diagonal vanishes), C = strictly lower part of D G D; contiguous [batch, r, r]

@@ -12,6 +12,7 @@ The math mirrors the reference model (models/gpt_model.py:54-61 rotary, 86-89 QK
 from __future__ import annotations
 
 import math
+import os
 from typing import List, Optional, Tuple
 
 import torch
@@ -508,11 +509,45 @@ def flash_attention_supported(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor)
             and q.is_contiguous() and k.is_contiguous() and v.is_contiguous())
 
 
+def flash_attention_backward(q, k, v, out, lse, d_out, scale: Optional[float] = None):
+    """Gradients of :func:`flash_attention_forward` by the tcgen05 kernels: (dq, dk, dv)."""
+    B, T, H, D = q.shape
+    if scale is None:
+        scale = 1.0 / math.sqrt(D)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    delta = torch.empty_like(lse)
+    torch.ops.dion_b200.attn_bwd(q, k, v, out, d_out.contiguous(), lse, delta, dq, dk, dv, float(scale),
+                                 runtime.status_tensor(q.device))
+    return dq, dk, dv
+
+
+class _FlashAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v):
+        out, lse = flash_attention_forward(q, k, v)
+        ctx.save_for_backward(q, k, v, out, lse)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        q, k, v, out, lse = ctx.saved_tensors
+        return flash_attention_backward(q, k, v, out, lse, d_out)
+
+
+# "kernel": the in-tree tcgen05 kernels wherever they apply; "library": always
+# F.scaled_dot_product_attention (cuDNN / flash kernels of the framework)
+ATTENTION_IMPL = os.environ.get("DION_B200_ATTENTION", "kernel")
+
+
 def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     """Causal self-attention; q, k, v: [B, T, H, Dh] -> [B, T, H*Dh].  Supports grouped
     KV heads (H_kv dividing H)."""
     B, T, H, Dh = q.shape
     Hkv = k.shape[2]
+    if ATTENTION_IMPL == "kernel" and q.is_cuda:
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        if flash_attention_supported(q, k, v):
+            return _FlashAttnFn.apply(q, k, v).view(B, T, H * Dh)
     qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
     y = F.scaled_dot_product_attention(qt, kt, vt, is_causal=True, enable_gqa=(Hkv != H))
     return y.transpose(1, 2).reshape(B, T, H * Dh)

@@ -222,3 +222,30 @@ def test_flash_attention_forward_matches_fp32_reference(shape):
     err = (out.float().transpose(1, 2) - ref).abs().max().item()
     assert err < 2e-2, err
     torch.testing.assert_close(lse, torch.logsumexp(s, dim=-1), rtol=1e-3, atol=1e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(2, 256, 3, 3, 128), (1, 1024, 4, 2, 128), (3, 384, 2, 2, 64), (2, 128, 4, 1, 64)])
+def test_flash_attention_backward_matches_fp32_reference(shape):
+    from dion_b200 import ops
+    from dion_b200.ops.nn import flash_attention_backward, flash_attention_forward
+
+    B, T, H, Hkv, D = shape
+    g = torch.Generator(device="cuda").manual_seed(11)
+    q = torch.randn(B, T, H, D, device="cuda", generator=g).to(torch.bfloat16)
+    k = torch.randn(B, T, Hkv, D, device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn(B, T, Hkv, D, device="cuda", generator=g).to(torch.bfloat16)
+    d_out = torch.randn(B, T, H, D, device="cuda", generator=g).to(torch.bfloat16)
+    out, lse = flash_attention_forward(q, k, v)
+    dq, dk, dv = flash_attention_backward(q, k, v, out, lse, d_out)
+    ops.check_status()
+    qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+    kr = kf.transpose(1, 2).repeat_interleave(H // Hkv, dim=1)
+    vr = vf.transpose(1, 2).repeat_interleave(H // Hkv, dim=1)
+    s = (qf.transpose(1, 2) @ kr.transpose(-1, -2)) / D ** 0.5
+    s = s.masked_fill(torch.triu(torch.ones(T, T, device="cuda", dtype=torch.bool), 1), float("-inf"))
+    ref = (torch.softmax(s, dim=-1) @ vr).transpose(1, 2)
+    ref.backward(d_out.float())
+    for name, got, want in (("dq", dq, qf.grad), ("dk", dk, kf.grad), ("dv", dv, vf.grad)):
+        err = (got.float() - want).abs().max().item() / want.abs().max().item()
+        assert err < 2e-2, (name, err)
