@@ -77,15 +77,38 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const float (&v)[3
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// D[tmem] (+)= A[tmem] * B[smem]: A (128 rows, one per lane, bf16 pairs along the columns) is read
-// from tensor memory
-__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
-                                        uint32_t accumulate) {
+// The MMA-issuing thread is on the critical path of every kv iteration (tiles are small, so one
+// tcgen05.mma runs for only 30-70 cycles); descriptors are therefore kept as two 32-bit halves and
+// stepped with a single integer add: the start-address field (bits [0,14), units of 16 bytes) never
+// carries because shared-memory offsets stay below 256 KB.
+struct DescHalves {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ DescHalves desc_halves(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  const uint64_t d = make_smem_desc(smem_addr, lbo_bytes, sbo_bytes);
+  return DescHalves{(uint32_t)d, (uint32_t)(d >> 32)};
+}
+// D[tmem] (+)= A[smem] * B[smem], bf16, descriptors given as halves plus byte offsets
+__device__ __forceinline__ void umma_ss_h(uint32_t tmem_d, DescHalves a, uint32_t a_off, DescHalves b, uint32_t b_off,
+                                          uint32_t idesc, uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
+      "r"(a.lo + (a_off >> 4)), "r"(a.hi), "r"(b.lo + (b_off >> 4)), "r"(b.hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_ts_h(uint32_t tmem_d, uint32_t tmem_a, DescHalves b, uint32_t b_off,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "r"(b.lo + (b_off >> 4)), "r"(b.hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 
@@ -190,6 +213,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_instr_desc(1, kMajorK, kMajorK, kBM, kBN);
       constexpr uint32_t idesc_pv = make_instr_desc(1, kMajorK, kMajorMN, kBM, D);
+      const DescHalves dq_ = desc_halves(smem_u32(sQ), 16, 1024);
+      const DescHalves dk0 = desc_halves(smem_u32(sK), 16, 1024), dk1 = desc_halves(smem_u32(sK + C::K_BYTES), 16, 1024);
+      const DescHalves dv0 = desc_halves(smem_u32(sV), kBN * 128, 1024),
+                       dv1 = desc_halves(smem_u32(sV + C::V_BYTES), kBN * 128, 1024);
       bool ok = mbar_wait(q_full, 0, abort_flag);
       // S_j and P_j share tensor-memory columns (P_j overwrites the first half of S_j), and the
       // tensor core executes this thread's MMAs in issue order, so S_{j+2} = Q K_{j+2}^T, issued after
@@ -198,13 +225,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int s = j & 1;
         if (!mbar_wait(&k_full[s], (j >> 1) & 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t a0 = smem_u32(sQ), b0 = smem_u32(sK + s * C::K_BYTES);
+        const DescHalves dk_s = s ? dk1 : dk0;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off_a = (kk >> 2) * (kBM * 128) + (kk & 3) * 32;
           const uint32_t off_b = (kk >> 2) * (kBN * 128) + (kk & 3) * 32;
-          umma_ss<false>(tmem_base + s * C::S_COLS, make_smem_desc(a0 + off_a, 16, 1024),
-                         make_smem_desc(b0 + off_b, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+          umma_ss_h(tmem_base + s * C::S_COLS, dq_, off_a, dk_s, off_b, idesc_qk, kk > 0 ? 1u : 0u);
         }
         umma_commit(&k_empty[s]);
         umma_commit(&s_full[s]);
@@ -219,13 +245,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           break;
         }
         tc_fence_after();
-        const uint32_t b0 = smem_u32(sV + s * C::V_BYTES);
+        const DescHalves dv_s = s ? dv1 : dv0;
 #pragma unroll
         for (int kk = 0; kk < kBN / 16; ++kk) {
           // P from tensor memory: 16 bf16 of a row = 8 columns per step; V: MN-major, PANELS chunks of
           // 64 head columns, 16 kv rows per step
-          umma_ts(tmem_base + C::O_COL, tmem_base + s * C::S_COLS + kk * 8,
-                  make_smem_desc(b0 + kk * (16 * 128), kBN * 128, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          umma_ts_h(tmem_base + C::O_COL, tmem_base + s * C::S_COLS + kk * 8, dv_s, kk * (16 * 128), idesc_pv,
+                    (j > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&v_empty[s]);
         if (j + 2 < n_tiles) ok = issue_qk(j + 2);
@@ -414,24 +440,29 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
                : "memory");
 }
 
-// delta[b, h, t] = sum_d O[b, t, h, d] * dO[b, t, h, d]; one warp per (b, t, h) row
+// delta[b, h, t] = sum_d O[b, t, h, d] * dO[b, t, h, d]; D / 8 lanes per (b, t, h) row, 16 bytes per lane
+template <int D>
 __global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __restrict__ o,
                                                         const __nv_bfloat16* __restrict__ d_o,
-                                                        float* __restrict__ delta, long long rows, int T, int H,
-                                                        int D) {
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);  // index into [B, T, H]
-  if (row >= rows) return;
-  const int lane = threadIdx.x & 31;
-  const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(o + row * D);
-  const __nv_bfloat162* g = reinterpret_cast<const __nv_bfloat162*>(d_o + row * D);
+                                                        float* __restrict__ delta, long long rows, int T, int H) {
+  constexpr int LPR = D / 8;  // lanes per row: 16 (D = 128) or 8 (D = 64)
+  const long long row = ((long long)blockIdx.x * 256 + threadIdx.x) / LPR;  // index into [B, T, H]
+  const int sub = threadIdx.x % LPR;
   float s = 0.f;
-  for (int i = lane; i < D / 2; i += 32) {
-    const float2 x = __bfloat1622float2(a[i]), y = __bfloat1622float2(g[i]);
-    s = fmaf(x.x, y.x, fmaf(x.y, y.y, s));
+  if (row < rows) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + row * D + sub * 8);
+    const uint4 g = *reinterpret_cast<const uint4*>(d_o + row * D + sub * 8);
+    const __nv_bfloat162* ah = reinterpret_cast<const __nv_bfloat162*>(&a);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __bfloat1622float2(ah[i]), y = __bfloat1622float2(gh[i]);
+      s = fmaf(x.x, y.x, fmaf(x.y, y.y, s));
+    }
   }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (lane == 0) {
+  for (int off = LPR / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (sub == 0 && row < rows) {
     const long long bt = row / H;
     const int h = (int)(row - bt * H);
     const long long b = bt / T;
@@ -548,6 +579,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_instr_desc(1, kMajorK, kMajorK, kBM, kBN);
       constexpr uint32_t idesc_dq = make_instr_desc(1, kMajorK, kMajorMN, kBM, D);
+      const DescHalves dq_ = desc_halves(smem_u32(sQ), 16, 1024), ddo_ = desc_halves(smem_u32(sDO), 16, 1024);
+      const DescHalves dk0 = desc_halves(smem_u32(sK), 16, 1024), dk1 = desc_halves(smem_u32(sK + C::K_BYTES), 16, 1024);
+      const DescHalves dv_ = desc_halves(smem_u32(sV), 16, 1024);
+      // K_j once more, read as [64 kv rows (K) x D (N)], MN-major, for dQ += dS K_j
+      const DescHalves dkm0 = desc_halves(smem_u32(sK), kBN * 128, 1024),
+                       dkm1 = desc_halves(smem_u32(sK + C::K_BYTES), kBN * 128, 1024);
       bool ok = mbar_wait(q_full, 0, abort_flag);
       // S_j = Q K_j^T and dP_j = dO V_j^T.  Both overwrite columns the previous dS lives in; they are
       // issued after dS_{j-1} K_{j-1}, which the tensor core therefore finishes first.
@@ -555,20 +592,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         const int s = j & 1;
         if (!mbar_wait(&k_full[s], (j >> 1) & 1, abort_flag) || !mbar_wait(v_full, j & 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t q0 = smem_u32(sQ), do0 = smem_u32(sDO), k0 = smem_u32(sK + s * C::K_BYTES), v0 = smem_u32(sV);
+        const DescHalves dk_s = s ? dk1 : dk0;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off_a = (kk >> 2) * (kBM * 128) + (kk & 3) * 32;
           const uint32_t off_b = (kk >> 2) * (kBN * 128) + (kk & 3) * 32;
-          umma_ss<false>(tmem_base + C::S_COL, make_smem_desc(q0 + off_a, 16, 1024),
-                         make_smem_desc(k0 + off_b, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          umma_ss_h(tmem_base + C::S_COL, dq_, off_a, dk_s, off_b, idesc_s, kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off_a = (kk >> 2) * (kBM * 128) + (kk & 3) * 32;
           const uint32_t off_b = (kk >> 2) * (kBN * 128) + (kk & 3) * 32;
-          umma_ss<false>(tmem_base + C::DP_COL, make_smem_desc(do0 + off_a, 16, 1024),
-                         make_smem_desc(v0 + off_b, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          umma_ss_h(tmem_base + C::DP_COL, ddo_, off_a, dv_, off_b, idesc_s, kk > 0 ? 1u : 0u);
         }
         umma_commit(v_empty);
         umma_commit(sdp_full);
@@ -582,11 +617,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
           break;
         }
         tc_fence_after();
-        const uint32_t k0 = smem_u32(sK + s * C::K_BYTES);
+        const DescHalves dkm_s = s ? dkm1 : dkm0;
 #pragma unroll
         for (int kk = 0; kk < kBN / 16; ++kk)
-          umma_ts(tmem_base + C::DQ_COL, tmem_base + C::S_COL + kk * 8,
-                  make_smem_desc(k0 + kk * (16 * 128), kBN * 128, 1024), idesc_dq, (j > 0 || kk > 0) ? 1u : 0u);
+          umma_ts_h(tmem_base + C::DQ_COL, tmem_base + C::S_COL + kk * 8, dkm_s, kk * (16 * 128), idesc_dq,
+                    (j > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&k_empty[s]);
         if (j + 1 < n_tiles) ok = issue_sdp(j + 1);
       }
@@ -691,7 +726,8 @@ struct BwdKvCfg {
   static constexpr int STAT_BYTES = kBQ * 4;           // lse_i or delta_i
   static constexpr int TILE_BYTES = 2 * Q_BYTES;                   // Q_i and dO_i of one stage
   static constexpr int STAGE_BYTES = TILE_BYTES + 2 * STAT_BYTES;  // what one stage's barrier receives
-  static constexpr int SMEM = 2 * KV_BYTES + 2 * STAGE_BYTES + 256 + 1024;
+  static constexpr int STAGES = 3;                                  // query-side tiles in flight
+  static constexpr int SMEM = 2 * KV_BYTES + STAGES * STAGE_BYTES + 256 + 1024;
   static constexpr int ST_COL = 0;      // two buffers of 64 columns
   static constexpr int DPT_COL = 128;   // two buffers of 64 columns
   static constexpr int DV_COL = 256;
@@ -711,15 +747,15 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   uint8_t* sK = smem;
   uint8_t* sV = sK + C::KV_BYTES;
   uint8_t* sStage = sV + C::KV_BYTES;           // per stage: Q_i, dO_i (1024-byte aligned tiles)
-  uint8_t* sStat = sStage + 2 * C::TILE_BYTES;  // per stage: lse_i, delta_i
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + 4 * C::STAT_BYTES);
+  uint8_t* sStat = sStage + C::STAGES * C::TILE_BYTES;  // per stage: lse_i, delta_i
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sStat + C::STAGES * 2 * C::STAT_BYTES);
   uint64_t* kv_full = bars;          // 1
-  uint64_t* qdo_full = bars + 1;     // 2
-  uint64_t* qdo_empty = bars + 3;    // 2
-  uint64_t* sdp_full = bars + 5;     // 2
-  uint64_t* pds_full = bars + 7;     // 2 (eight warps arrive)
-  uint64_t* acc_full = bars + 9;     // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* qdo_full = bars + 1;     // 3
+  uint64_t* qdo_empty = bars + 4;    // 3
+  uint64_t* sdp_full = bars + 7;     // 2
+  uint64_t* pds_full = bars + 9;     // 2 (eight warps arrive)
+  uint64_t* acc_full = bars + 11;    // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -739,9 +775,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_v);
     mbar_init(kv_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(&qdo_full[s], 1);
       mbar_init(&qdo_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(&sdp_full[s], 1);
       mbar_init(&pds_full[s], 8);
     }
@@ -768,10 +806,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
       bool ok = true;
       for (int it = 0; it < n_it && ok; ++it) {
-        const int s = it & 1;
+        const int s = it % C::STAGES;
         const int g = it / n_q, i = i_first + (it - g * n_q);
         const int h = hk * group + g;
-        if (!mbar_wait(&qdo_empty[s], ((it >> 1) & 1) ^ 1u, abort_flag)) {
+        if (!mbar_wait(&qdo_empty[s], ((it / C::STAGES) & 1) ^ 1u, abort_flag)) {
           ok = false;
           break;
         }
@@ -797,27 +835,30 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_instr_desc(1, kMajorK, kMajorK, kBM, kBQ);
       constexpr uint32_t idesc_acc = make_instr_desc(1, kMajorK, kMajorMN, kBM, D);
+      const DescHalves dk_ = desc_halves(smem_u32(sK), 16, 1024), dv_ = desc_halves(smem_u32(sV), 16, 1024);
+      // stage 0 of the query-side tiles, K-major (for S^T, dP^T) and MN-major (for dV, dK)
+      const DescHalves dq_ = desc_halves(smem_u32(sStage), 16, 1024),
+                       ddo_ = desc_halves(smem_u32(sStage + C::Q_BYTES), 16, 1024);
+      const DescHalves dqm_ = desc_halves(smem_u32(sStage), kBQ * 128, 1024),
+                       ddom_ = desc_halves(smem_u32(sStage + C::Q_BYTES), kBQ * 128, 1024);
       bool ok = mbar_wait(kv_full, 0, abort_flag);
       // S^T = K Q_i^T and dP^T = V dO_i^T into buffer it & 1
       auto issue_sdp = [&](int it) -> bool {
-        const int s = it & 1;
-        if (!mbar_wait(&qdo_full[s], (it >> 1) & 1, abort_flag)) return false;
+        const int s = it & 1, st = it % C::STAGES;
+        if (!mbar_wait(&qdo_full[st], (it / C::STAGES) & 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t k0 = smem_u32(sK), v0 = smem_u32(sV);
-        const uint32_t q0 = smem_u32(sStage + s * C::TILE_BYTES), do0 = q0 + C::Q_BYTES;
+        const uint32_t st_off = st * C::TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off_a = (kk >> 2) * (kBM * 128) + (kk & 3) * 32;
           const uint32_t off_b = (kk >> 2) * (kBQ * 128) + (kk & 3) * 32;
-          umma_ss<false>(tmem_base + C::ST_COL + s * kBQ, make_smem_desc(k0 + off_a, 16, 1024),
-                         make_smem_desc(q0 + off_b, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          umma_ss_h(tmem_base + C::ST_COL + s * kBQ, dk_, off_a, dq_, st_off + off_b, idesc_s, kk > 0 ? 1u : 0u);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off_a = (kk >> 2) * (kBM * 128) + (kk & 3) * 32;
           const uint32_t off_b = (kk >> 2) * (kBQ * 128) + (kk & 3) * 32;
-          umma_ss<false>(tmem_base + C::DPT_COL + s * kBQ, make_smem_desc(v0 + off_a, 16, 1024),
-                         make_smem_desc(do0 + off_b, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+          umma_ss_h(tmem_base + C::DPT_COL + s * kBQ, dv_, off_a, ddo_, st_off + off_b, idesc_s, kk > 0 ? 1u : 0u);
         }
         umma_commit(&sdp_full[s]);
         return true;
@@ -831,17 +872,18 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           break;
         }
         tc_fence_after();
-        const uint32_t q0 = smem_u32(sStage + s * C::TILE_BYTES), do0 = q0 + C::Q_BYTES;
+        const int st = it % C::STAGES;
+        const uint32_t st_off = st * C::TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < kBQ / 16; ++kk) {
           // dV += P^T dO_i and dK += dS^T Q_i: A from tensor memory (bf16 pairs, 8 columns per step),
           // B = the query-side tile read as [64 rows (K) x D (N)], MN-major
-          umma_ts(tmem_base + C::DV_COL, tmem_base + C::ST_COL + s * kBQ + kk * 8,
-                  make_smem_desc(do0 + kk * (16 * 128), kBQ * 128, 1024), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
-          umma_ts(tmem_base + C::DK_COL, tmem_base + C::DPT_COL + s * kBQ + kk * 8,
-                  make_smem_desc(q0 + kk * (16 * 128), kBQ * 128, 1024), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_ts_h(tmem_base + C::DV_COL, tmem_base + C::ST_COL + s * kBQ + kk * 8, ddom_, st_off + kk * (16 * 128),
+                    idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_ts_h(tmem_base + C::DK_COL, tmem_base + C::DPT_COL + s * kBQ + kk * 8, dqm_, st_off + kk * (16 * 128),
+                    idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(&qdo_empty[s]);
+        umma_commit(&qdo_empty[st]);
         if (it + 2 < n_it) ok = issue_sdp(it + 2);
       }
       if (ok) umma_commit(acc_full);
@@ -866,7 +908,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         break;
       }
       tc_fence_after();
-      const float* lse_s = reinterpret_cast<const float*>(sStat + s * 2 * C::STAT_BYTES) + half * 32;
+      const float* lse_s = reinterpret_cast<const float*>(sStat + (it % C::STAGES) * 2 * C::STAT_BYTES) + half * 32;
       const float* dlt_s = lse_s + kBQ;
       float sc[32], dp[32];
       tmem_ld_32x32(lane_base + C::ST_COL + s * kBQ + half * 32, sc);
@@ -1030,9 +1072,8 @@ cudaError_t attn_bwd_launch_d(const void* q, const void* k, const void* v, const
     attr_set = true;
   }
   const long long nrows = (long long)B * T * H;
-  attn_delta_kernel<<<(unsigned)((nrows + 7) / 8), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(o),
-                                                                   reinterpret_cast<const __nv_bfloat16*>(d_o), delta,
-                                                                   nrows, T, H, D);
+  attn_delta_kernel<D><<<(unsigned)((nrows * (D / 8) + 255) / 256), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(o), reinterpret_cast<const __nv_bfloat16*>(d_o), delta, nrows, T, H);
   AttnBwdParams p;
   p.dq = reinterpret_cast<__nv_bfloat16*>(dq);
   p.dk = reinterpret_cast<__nv_bfloat16*>(dk);
