@@ -99,7 +99,7 @@ class CausalSelfAttention(nn.Module):
         q, k = K.rope_qknorm(q, k, cos, sin)
         y = K.causal_attention(q, k, v)
         if group is not None:
-            return residual + TP.reduce_from_tp_region(K.linear(y, _local(self.c_proj.weight)), group)
+            return residual + TP.row_parallel_linear(y, _local(self.c_proj.weight), group)
         return K.linear(y, _local(self.c_proj.weight), residual=residual)
 
 
@@ -112,10 +112,10 @@ class MLP(nn.Module):
     def forward(self, h: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
         group, _ = _tp_group(self.c_fc.weight)
         if group is not None:
-            h = TP.copy_to_tp_region(h, group)
-        if group is not None:
-            u = K.linear(h, _local(self.c_fc.weight), act="relu2")
-            return residual + TP.reduce_from_tp_region(K.linear(u, _local(self.c_proj.weight)), group)
+            # column-parallel c_fc (its input gradient is summed over the group by a fused
+            # GEMM -> all-reduce), row-parallel c_proj (its output likewise)
+            u = K.relu2(TP.column_parallel_linear(h, _local(self.c_fc.weight), group))
+            return residual + TP.row_parallel_linear(u, _local(self.c_proj.weight), group)
         return K.mlp(h, _local(self.c_fc.weight), _local(self.c_proj.weight), residual)
 
 

@@ -15,6 +15,9 @@ import torch.distributed as dist
 import torch.nn.functional as F
 
 from ..ops import nn as K
+from ..ops import runtime
+from ..ops.gemm import gemm
+from . import fsdp_comm, symm
 
 
 class _CopyToRegion(torch.autograd.Function):
@@ -62,6 +65,141 @@ class _GatherFromRegion(torch.autograd.Function):
         world, rank = dist.get_world_size(ctx.group), dist.get_rank(ctx.group)
         n = g.shape[-1] // world
         return g[..., rank * n:(rank + 1) * n].contiguous(), None
+
+
+# ------------------------------------------------------------------ fused GEMM -> all-reduce
+class _TPComm:
+    """Per-group state of the fused row-parallel product: a symmetric receive buffer with two slots
+    (each holds one [world, T / world, N] bf16 block, written by the peers' GEMM epilogues) and the
+    all-gather kernel that redistributes the reduced row blocks."""
+
+    def __init__(self, group, device):
+        self.group, self.device = group, torch.device(device)
+        self.recv = fsdp_comm._Arena(group, self.device)
+        self.gather = fsdp_comm.SymmAllGather(group, self.device)
+        self.calls = 0
+        self._ptr_cache = {}
+
+    def ptrs(self, slot_off: int, block_bytes: int) -> torch.Tensor:
+        """Destination of this rank's partial row block k: slot `rank` of rank k's receive buffer."""
+        ar = self.recv.arena
+        key = (ar.peers[0], slot_off, block_bytes)
+        t = self._ptr_cache.get(key)
+        if t is None:
+            addr = [ar.peers[k] + slot_off + ar.rank * block_bytes for k in range(ar.world)]
+            t = self._ptr_cache[key] = torch.tensor(addr, dtype=torch.int64, device=self.device)
+        return t
+
+
+_tp_comms = {}
+
+
+def _tp_comm(group, device):
+    if not symm._usable(group, torch.device(device)):
+        return None
+    key = symm._key(group)
+    c = _tp_comms.get(key)
+    if c is None:
+        c = _tp_comms[key] = _TPComm(group, device)
+    return c
+
+
+def _matmul_all_reduce(x: torch.Tensor, w_t: torch.Tensor, group) -> torch.Tensor:
+    """``sum over ranks of x_r @ w_t_r`` for x: [T, K] bf16 and w_t: [K, N] (a transposed view of the
+    local weight), identical on every rank.  One GEMM whose epilogue stores row block k of the
+    partial product straight into rank k's receive buffer (peer stores over NVLink, tile by tile
+    while the remaining tiles are still being multiplied), a flag barrier, the sum of the `world`
+    partial blocks each rank received, and an all-gather kernel.  Falls back to GEMM + the process
+    group's all-reduce when the shapes or the group do not fit."""
+    T, N = x.shape[0], w_t.shape[1]
+    comm = _tp_comm(group, x.device) if x.is_cuda else None
+    world = dist.get_world_size(group)
+    ok = (comm is not None and x.dtype == torch.bfloat16 and T % world == 0 and (T // world) % 8 == 0 and N % 8 == 0
+          and comm.recv.ensure(T * N * 2))
+    if not ok:
+        y = gemm(x, w_t) if x.is_cuda else x @ w_t
+        dist.all_reduce(y, group=group)
+        return y
+    ar = comm.recv.arena
+    comm.calls += 1
+    slot = comm.calls & 1
+    slot_off = comm.recv.slot_offset(slot)
+    rows = T // world
+    block_bytes = rows * N * 2
+    recv = ar.buf[slot_off:slot_off + T * N * 2].view(torch.bfloat16).view(world, rows, N)
+    torch.ops.dion_b200.gemm_scatter(x, w_t, None, recv[0], comm.ptrs(slot_off, block_bytes), 1, rows, world, 1.0, 0.0,
+                                     runtime.status_tensor(x.device))
+    ar.barrier()
+    mine = recv.float().sum(dim=0).to(torch.bfloat16)  # fixed summation order
+    out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+    comm.gather(out.view(-1), mine.view(-1), group)
+    return out
+
+
+class _RowParallelLinearFn(torch.autograd.Function):
+    """y = all-reduce(x_local @ W_local^T) for a row-parallel weight W_local: [N, K_local]."""
+
+    @staticmethod
+    def forward(ctx, x, weight, group):
+        wb = K.bf16_weight(weight)
+        ctx.save_for_backward(x, weight)
+        return _matmul_all_reduce(x, wb.t(), group)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        wb = K.bf16_weight(weight)
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy, wb)
+        if ctx.needs_input_grad[1]:
+            dw = K._weight_grad(dy, x, weight)
+        return dx, dw, None
+
+
+class _ColumnParallelInputGradFn(torch.autograd.Function):
+    """y = x @ W_local^T for a column-parallel weight W_local: [N_local, K] with a replicated input;
+    the input gradient sum over ranks of dy_r @ W_r runs through the same fused product."""
+
+    @staticmethod
+    def forward(ctx, x, weight, group):
+        wb = K.bf16_weight(weight)
+        ctx.save_for_backward(x, weight)
+        ctx.group = group
+        return gemm(x, wb.t())
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        wb = K.bf16_weight(weight)
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = _matmul_all_reduce(dy, wb, ctx.group)
+        if ctx.needs_input_grad[1]:
+            dw = K._weight_grad(dy, x, weight)
+        return dx, dw, None
+
+
+def row_parallel_linear(x: torch.Tensor, weight_local: torch.Tensor, group) -> torch.Tensor:
+    """All-reduced output of a row-parallel linear layer (attn.c_proj / mlp.c_proj under the
+    reference's RowwiseParallel plan, models/gpt_model.py:318-327)."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        shp = x.shape
+        y = _RowParallelLinearFn.apply(x.reshape(-1, shp[-1]), weight_local, group)
+        return y.view(*shp[:-1], weight_local.shape[0])
+    return reduce_from_tp_region(K.linear(x, weight_local), group)
+
+
+def column_parallel_linear(x: torch.Tensor, weight_local: torch.Tensor, group) -> torch.Tensor:
+    """Local output columns of a column-parallel linear layer on a replicated input; the backward
+    all-reduces the input gradient."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        shp = x.shape
+        y = _ColumnParallelInputGradFn.apply(x.reshape(-1, shp[-1]), weight_local, group)
+        return y.view(*shp[:-1], weight_local.shape[0])
+    return K.linear(copy_to_tp_region(x, group), weight_local)
 
 
 def copy_to_tp_region(x, group):

@@ -309,6 +309,13 @@ def case_tp():
     for (n1, p1), (n2, p2) in zip(model.named_parameters(), ref.named_parameters()):
         loose = "wte" in n1 or "lm_head" in n1
         check(f"tp {n1}", _full(p1.detach()), p2.detach(), 6e-2 if (CUDA or loose) else 5e-3)
+    if CUDA and os.environ.get("DION_B200_SYMM", "1") != "0":
+        from dion_b200.parallel import tp as TP
+
+        calls = [c.calls for c in TP._tp_comms.values()]
+        assert calls and all(c > 0 for c in calls), f"row-parallel products ran on library collectives: {calls}"
+        if RANK == 0:
+            print(f"tp: fused GEMM -> reduce-scatter / all-gather products: {calls}", flush=True)
 
 
 def case_checkpoint():
