@@ -900,20 +900,24 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const int kv_pos = kv0 + row_in_tile;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
     bool ok = true;
-    for (int it = 0; it < n_it && ok; ++it) {
+    // A failed wait clears `ok` but the loop keeps its shape: both warps of a quadrant must reach
+    // the named barrier the same number of times.
+    for (int it = 0; it < n_it; ++it) {
       const int s = it & 1;
       const int g = it / n_q, i = i_first + (it - g * n_q);
-      if (!mbar_wait(&sdp_full[s], (it >> 1) & 1, abort_flag)) {
-        ok = false;
-        break;
-      }
+      if (ok && !mbar_wait(&sdp_full[s], (it >> 1) & 1, abort_flag)) ok = false;
       tc_fence_after();
       const float* lse_s = reinterpret_cast<const float*>(sStat + (it % C::STAGES) * 2 * C::STAT_BYTES) + half * 32;
       const float* dlt_s = lse_s + kBQ;
       float sc[32], dp[32];
-      tmem_ld_32x32(lane_base + C::ST_COL + s * kBQ + half * 32, sc);
-      tmem_ld_32x32(lane_base + C::DPT_COL + s * kBQ + half * 32, dp);
-      tmem_ld_wait();
+      if (ok) {
+        tmem_ld_32x32(lane_base + C::ST_COL + s * kBQ + half * 32, sc);
+        tmem_ld_32x32(lane_base + C::DPT_COL + s * kBQ + half * 32, dp);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) sc[c] = dp[c] = 0.f;
+      }
       const int qcol0 = i * kBQ + half * 32;           // sequence position of this thread's first column
       const bool diag = qcol0 < kv0 + kBM;             // some query of this block precedes some kv row
       uint32_t pp[16], dd[16];
@@ -939,6 +943,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       // both warps of a quadrant must have read S^T / dP^T before either overwrites its part: the
       // packed halves land in columns [0, 32) of the buffers, which the other warp may still be loading
       asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
+      if (!__all_sync(0xffffffffu, ok)) {
+        ok = false;
+        continue;
+      }
       tmem_st_32x16(lane_base + C::ST_COL + s * kBQ + half * 16, pp);
       tmem_st_32x16(lane_base + C::DPT_COL + s * kBQ + half * 16, dd);
       tmem_st_wait();
