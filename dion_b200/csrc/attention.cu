@@ -112,6 +112,17 @@ __device__ __forceinline__ void umma_ts_h(uint32_t tmem_d, uint32_t tmem_a, Desc
       : "memory");
 }
 
+// barrier of the two warps (64 threads) that share TMEM lane quadrant `quad`; immediate barrier
+// numbers, so that the kernel reserves five named barriers instead of all sixteen
+__device__ __forceinline__ void pair_barrier(int quad) {
+  switch (quad) {
+    case 0: asm volatile("bar.sync 1, 64;" ::: "memory"); break;
+    case 1: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
+    case 2: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
+    default: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
+  }
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -728,15 +739,19 @@ struct BwdKvCfg {
   static constexpr int STAGE_BYTES = TILE_BYTES + 2 * STAT_BYTES;  // what one stage's barrier receives
   static constexpr int STAGES = 3;                                  // query-side tiles in flight
   static constexpr int SMEM = 2 * KV_BYTES + STAGES * STAGE_BYTES + 256 + 1024;
-  static constexpr int ST_COL = 0;      // two buffers of 64 columns
-  static constexpr int DPT_COL = 128;   // two buffers of 64 columns
-  static constexpr int DV_COL = 256;
-  static constexpr int DK_COL = 256 + D;
-  static constexpr int TMEM_COLS = 512;
+  // D = 128: S^T / dP^T double buffered, one CTA per SM (512 columns).  D = 64: single buffers and
+  // 256 columns, so that two CTAs share an SM and cover each other's prologue, epilogue and waits.
+  static constexpr int NBUF = D == 128 ? 2 : 1;
+  static constexpr int ST_COL = 0;                   // NBUF buffers of 64 columns
+  static constexpr int DPT_COL = NBUF * kBQ;         // NBUF buffers of 64 columns
+  static constexpr int DV_COL = 2 * NBUF * kBQ;
+  static constexpr int DK_COL = DV_COL + D;
+  static constexpr int TMEM_COLS = D == 128 ? 512 : 256;
+  static constexpr int CTAS_PER_SM = D == 128 ? 1 : 2;
 };
 
 template <int D>
-__global__ void __launch_bounds__(kKvThreads, 1)
+__global__ void __launch_bounds__(kKvThreads, BwdKvCfg<D>::CTAS_PER_SM)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
                     const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                     const AttnBwdParams p) {
@@ -844,7 +859,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       bool ok = mbar_wait(kv_full, 0, abort_flag);
       // S^T = K Q_i^T and dP^T = V dO_i^T into buffer it & 1
       auto issue_sdp = [&](int it) -> bool {
-        const int s = it & 1, st = it % C::STAGES;
+        const int s = it % C::NBUF, st = it % C::STAGES;
         if (!mbar_wait(&qdo_full[st], (it / C::STAGES) & 1, abort_flag)) return false;
         tc_fence_after();
         const uint32_t st_off = st * C::TILE_BYTES;
@@ -864,10 +879,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         return true;
       };
       if (ok) ok = issue_sdp(0);
-      if (ok && n_it > 1) ok = issue_sdp(1);
+      if (ok && C::NBUF > 1 && n_it > 1) ok = issue_sdp(1);
       for (int it = 0; it < n_it && ok; ++it) {
-        const int s = it & 1;
-        if (!mbar_wait(&pds_full[s], (it >> 1) & 1, abort_flag)) {
+        const int s = it % C::NBUF;
+        if (!mbar_wait(&pds_full[s], (it / C::NBUF) & 1, abort_flag)) {
           ok = false;
           break;
         }
@@ -884,7 +899,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                     idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&qdo_empty[st]);
-        if (it + 2 < n_it) ok = issue_sdp(it + 2);
+        if (it + C::NBUF < n_it) ok = issue_sdp(it + C::NBUF);
       }
       if (ok) umma_commit(acc_full);
       else {
@@ -903,9 +918,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     // A failed wait clears `ok` but the loop keeps its shape: both warps of a quadrant must reach
     // the named barrier the same number of times.
     for (int it = 0; it < n_it; ++it) {
-      const int s = it & 1;
+      const int s = it % C::NBUF;
       const int g = it / n_q, i = i_first + (it - g * n_q);
-      if (ok && !mbar_wait(&sdp_full[s], (it >> 1) & 1, abort_flag)) ok = false;
+      if (ok && !mbar_wait(&sdp_full[s], (it / C::NBUF) & 1, abort_flag)) ok = false;
       tc_fence_after();
       const float* lse_s = reinterpret_cast<const float*>(sStat + (it % C::STAGES) * 2 * C::STAT_BYTES) + half * 32;
       const float* dlt_s = lse_s + kBQ;
@@ -942,7 +957,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
       // both warps of a quadrant must have read S^T / dP^T before either overwrites its part: the
       // packed halves land in columns [0, 32) of the buffers, which the other warp may still be loading
-      asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
+      pair_barrier(quad);
       if (!__all_sync(0xffffffffu, ok)) {
         ok = false;
         continue;
