@@ -92,9 +92,8 @@ class CausalSelfAttention(nn.Module):
         group, _ = _tp_group(self.c_q.weight)
         if group is not None:
             h = TP.copy_to_tp_region(h, group)
-        q = K.linear(h, _local(self.c_q.weight)).view(B, T, -1, self.head_dim)
-        k = K.linear(h, _local(self.c_k.weight)).view(B, T, -1, self.head_dim)
-        v = K.linear(h, _local(self.c_v.weight)).view(B, T, -1, self.head_dim)
+        q, k, v = K.linear_fanout(h, _local(self.c_q.weight), _local(self.c_k.weight), _local(self.c_v.weight))
+        q, k, v = (t.view(B, T, -1, self.head_dim) for t in (q, k, v))
         cos, sin = self.rotary.tables(T, h.device)
         q, k = K.rope_qknorm(q, k, cos, sin)
         y = K.causal_attention(q, k, v)

@@ -167,6 +167,58 @@ def linear(x: torch.Tensor, weight: torch.Tensor, residual: Optional[torch.Tenso
     return y
 
 
+class _LinearFanoutFn(torch.autograd.Function):
+    """(x W_0^T, x W_1^T, ...) for several weights applied to the same input (the q / k / v
+    projections): the backward pass accumulates the input gradient through the GEMM epilogue
+    (``dx += dy_i W_i``) instead of leaving autograd to add three full-size tensors."""
+
+    @staticmethod
+    def forward(ctx, x, *weights):
+        ctx.save_for_backward(x, *weights)
+        outs = []
+        for w in weights:
+            wb = bf16_weight(w)
+            y = torch.empty(x.shape[0], wb.shape[0], device=x.device, dtype=torch.bfloat16)
+            gemm(x, wb.t(), out=y)
+            outs.append(y)
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *dys):
+        x, *weights = ctx.saved_tensors
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x)
+            first = True
+            for w, dy in zip(weights, dys):
+                if dy is None:
+                    continue
+                wb = bf16_weight(w)
+                if first:
+                    gemm(dy.contiguous(), wb, out=dx)
+                    first = False
+                else:
+                    gemm(dy.contiguous(), wb, c=dx, beta=1.0, out=dx)
+            if first:
+                dx.zero_()
+        dws = []
+        for i, (w, dy) in enumerate(zip(weights, dys)):
+            if ctx.needs_input_grad[1 + i] and dy is not None:
+                dws.append(_weight_grad(dy.contiguous(), x, w))
+            else:
+                dws.append(None)
+        return (dx, *dws)
+
+
+def linear_fanout(x: torch.Tensor, *weights: torch.Tensor):
+    """``tuple(x @ w.T for w in weights)`` with a single accumulated input gradient."""
+    if _fast(x):
+        shp = x.shape
+        outs = _LinearFanoutFn.apply(x.reshape(-1, shp[-1]), *weights)
+        return tuple(o.view(*shp[:-1], w.shape[0]) for o, w in zip(outs, weights))
+    return tuple(linear(x, w) for w in weights)
+
+
 class _MLPFn(torch.autograd.Function):
     """out = residual + relu(x W_fc^T)^2 W_proj^T with the activation fused into the GEMM
     epilogues: the forward c_fc product writes both the pre-activation and relu^2 of it, the

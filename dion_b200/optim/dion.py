@@ -244,8 +244,16 @@ class Dion(Optimizer):
                 yield lambda g=group: self._scalar_task(g, "adamw")
 
         if work:
-            groups = {g for w in work for g in (w.outer, w.inner, w.replicate if w.compressed else None) if g is not None}
-            symm.begin_step(sorted(groups, key=lambda g: g.group_name), work[0].cls.M.device)
+            # Arena creation is collective over each group, so every rank must walk its groups in an
+            # order that is consistent across the whole job: by mesh role (replicate, outer, inner),
+            # never by group name, which differs between the sub-groups of one mesh dimension.
+            groups = []
+            for pick in (lambda w: w.replicate if w.compressed else None, lambda w: w.outer, lambda w: w.inner):
+                for w in work:
+                    g = pick(w)
+                    if g is not None and all(g is not h for h in groups):
+                        groups.append(g)
+            symm.begin_step(groups, work[0].cls.M.device)
         Scheduler(phase1(), max_in_flight=3).run()
         if work:
             ortho = orthonormalize_many([w.P for w in work], [w.inner for w in work])

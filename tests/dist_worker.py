@@ -279,6 +279,79 @@ def case_fsdp_comm():
                   f"reduce-scatter {rs.kernel_calls}/{rs.fallback_calls}", flush=True)
 
 
+def case_hybrid():
+    """Meshes with two active dimensions (needs a multiple of four ranks).
+    (a) dp2 x fs: FSDP2 over `fs`, Dion keeps the replicas in step by exchanging only the low-rank
+        P / R factors over `dp` (compressed sync, rank_fraction 0.25, fp32 Q / bf16 momentum); every
+        replica sees different data, yet the parameters must stay identical across `dp`.
+    (b) fs2 x tp: FSDP2 + tensor parallelism, against a single-process run on the full batch."""
+    from torch.distributed.device_mesh import init_device_mesh
+
+    from dion_b200 import Dion, DionMixedPrecisionConfig
+    from dion_b200.models.gpt import parallelize_gpt_model
+
+    if WORLD % 4 != 0:
+        print("hybrid meshes need 4 ranks; skipped")
+        return
+    kind = "cuda" if CUDA else "cpu"
+    mk = lambda m: [dict(params=list(m.transformer.h.parameters())),
+                    dict(params=list(m.transformer.wte.parameters()) + list(m.lm_head.parameters()),
+                         algorithm="adamw", lr=0.002)]
+    def stage(msg):
+        if os.environ.get("DION_TEST_VERBOSE"):
+            print(f"[rank {RANK}] hybrid: {msg}", file=sys.stderr, flush=True)
+
+    # ---- (a)
+    stage("dp x fs: building")
+    mesh = init_device_mesh(kind, (2, WORLD // 2, 1), mesh_dim_names=("dp", "fs", "tp"))
+    model = _tiny_gpt().to(DEV)
+    parallelize_gpt_model(model, mesh, dp_name=None, fs_name="fs", tp_name="tp")
+    opt = Dion(mk(model), replicate_mesh=mesh["dp"], outer_shard_mesh=mesh["fs"], replicate_mesh_grad_sync=True,
+               lr=0.02, rank_fraction=0.25,
+               mixed_precision_config=DionMixedPrecisionConfig(momentum_dtype=torch.bfloat16, Q_dtype=torch.float32))
+    stage("dp x fs: training")
+    losses = _train(model, opt, 4, data_rank=RANK, data_world=WORLD)
+    stage("dp x fs: trained")
+    assert torch.isfinite(losses).all(), losses
+    opt.synchronize_for_checkpoint()
+    stage("dp x fs: synchronised")
+    dp_group = mesh["dp"].get_group()
+    for n, p_ in model.named_parameters():
+        loc = p_.detach().to_local() if hasattr(p_, "to_local") else p_.detach()
+        ref = loc.clone()
+        dist.broadcast(ref, src=dist.get_global_rank(dp_group, 0), group=dp_group)
+        check(f"hybrid dp x fs replica consistency {n}", loc, ref, 1e-6)
+    st = next(iter(opt.state.values()))
+    assert st["momentum"].dtype == torch.bfloat16 and st["Q"].dtype == torch.float32
+    # ---- (b)
+    stage("fs x tp: building")
+    mesh = init_device_mesh(kind, (1, 2, WORLD // 2), mesh_dim_names=("dp", "fs", "tp"))
+    ref = _tiny_gpt().to(DEV)
+    model = _tiny_gpt().to(DEV)
+    parallelize_gpt_model(model, mesh, dp_name=None, fs_name="fs", tp_name="tp")
+    tp = WORLD // 2
+    opt = Dion(mk(model), replicate_mesh=mesh["dp"], outer_shard_mesh=mesh["fs"], inner_shard_mesh=mesh["tp"],
+               lr=0.02, rank_fraction=0.5, rank_multiple_of=tp)
+    optref = Dion(mk(ref), lr=0.02, rank_fraction=0.5, rank_multiple_of=tp)
+    for g in opt.param_groups[:1]:
+        for p_ in g["params"]:
+            opt._get_or_initialize_state(p_, g)
+    for (n1, p1), (n2, p2) in zip(model.transformer.h.named_parameters(), ref.transformer.h.named_parameters()):
+        optref.state[p2] = {"momentum": torch.zeros_like(p2), "Q": _full(opt.state[p1]["Q"]).clone()}
+        optref._get_dion_param_config(p2).is_transposed = opt._param_config[p1].is_transposed
+    fs_rank = mesh["fs"].get_local_rank()
+    stage("fs x tp: training")
+    l1 = _train(model, opt, 3, data_rank=fs_rank, data_world=2)
+    stage("fs x tp: trained")
+    l2 = _train(ref, optref, 3)
+    dist.all_reduce(l1, op=dist.ReduceOp.SUM)
+    l1 /= WORLD
+    check("hybrid fs x tp losses", l1, l2, 3e-2 if CUDA else 2e-3)
+    for (n1, p1), (n2, p2) in zip(model.named_parameters(), ref.named_parameters()):
+        loose = "wte" in n1 or "lm_head" in n1
+        check(f"hybrid fs x tp {n1}", _full(p1.detach()), p2.detach(), 6e-2 if (CUDA or loose) else 5e-3)
+
+
 def case_tp():
     """GPT with tensor parallelism (tp = world): loss and a Dion step (inner mesh) against a
     single-process run."""

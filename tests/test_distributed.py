@@ -33,6 +33,17 @@ def test_cpu_two_ranks(case):
     _launch([case], nproc=2, force_cpu=True)
 
 
+def test_cpu_four_ranks_hybrid_meshes():
+    _launch(["hybrid"], nproc=4, force_cpu=True, timeout=900)
+
+
+@pytest.mark.gpu
+def test_gpu_hybrid_meshes():
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs at least 4 GPUs")
+    _launch(["hybrid"], nproc=4, force_cpu=False, timeout=240)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("case", ["symm", "dion_ddp", "muon_ddp", "fsdp", "fsdp_comm", "tp", "checkpoint"])
 def test_gpu_ranks(case):

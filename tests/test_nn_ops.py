@@ -249,3 +249,24 @@ def test_flash_attention_backward_matches_fp32_reference(shape):
     for name, got, want in (("dq", dq, qf.grad), ("dk", dk, kf.grad), ("dv", dv, vf.grad)):
         err = (got.float() - want).abs().max().item() / want.abs().max().item()
         assert err < 2e-2, (name, err)
+
+
+@pytest.mark.gpu
+def test_linear_fanout_matches_separate_linears():
+    x = torch.randn(640, 256, device="cuda").to(torch.bfloat16).requires_grad_()
+    ws = [torch.nn.Parameter(torch.randn(n, 256, device="cuda") * 0.05) for n in (256, 128, 384)]
+    outs = N.linear_fanout(x, *ws)
+    gs = [torch.randn_like(o) for o in outs]
+    torch.autograd.backward(outs, gs)
+    got = [x.grad.clone()] + [w.grad.clone() for w in ws]
+    x.grad = None
+    for w in ws:
+        w.grad = None
+    ref = [N.linear(x, w) for w in ws]
+    torch.autograd.backward(ref, gs)
+    for o, r in zip(outs, ref):
+        assert torch.equal(o, r)
+    want = [x.grad] + [w.grad for w in ws]
+    for g, w in zip(got, want):
+        err = (g.float() - w.float()).abs().max().item() / w.float().abs().max().item()
+        assert err < 1e-2, err
