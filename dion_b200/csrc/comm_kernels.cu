@@ -190,28 +190,39 @@ __global__ void __launch_bounds__(512) all_reduce_kernel(PeerTable t, long long 
     const long long per = (nvec + world - 1) / world;
     const long long v0 = per * rank;
     const long long v1 = min(v0 + per, nvec);
-    for (long long v = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; v < v1;
-         v += (long long)gridDim.x * blockDim.x) {
-      float acc[N];
-      if (kMulticast) {
-        V::mc_load_reduce(reinterpret_cast<const T*>(mc_base + data_off) + v * N, acc);
-      } else {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long vb = v0 + (long long)blockIdx.x * blockDim.x + threadIdx.x; vb < v1; vb += 4 * stride) {
+      float acc[4][N];
+      // up to four vectors per thread, so that several peer / switch loads are in flight
 #pragma unroll
-        for (int j = 0; j < N; ++j) acc[j] = 0.f;
-        for (int p = 0; p < world; ++p) {
-          float f[N];
-          V::load(reinterpret_cast<const T*>(reinterpret_cast<const char*>(t.ptrs[p]) + data_off) + v * N, f);
+      for (int u = 0; u < 4; ++u) {
+        const long long v = vb + u * stride;
+        if (v >= v1) break;
+        if (kMulticast) {
+          V::mc_load_reduce(reinterpret_cast<const T*>(mc_base + data_off) + v * N, acc[u]);
+        } else {
 #pragma unroll
-          for (int j = 0; j < N; ++j) acc[j] += f[j];
+          for (int j = 0; j < N; ++j) acc[u][j] = 0.f;
+          for (int p = 0; p < world; ++p) {
+            float f[N];
+            V::load(reinterpret_cast<const T*>(reinterpret_cast<const char*>(t.ptrs[p]) + data_off) + v * N, f);
+#pragma unroll
+            for (int j = 0; j < N; ++j) acc[u][j] += f[j];
+          }
         }
       }
 #pragma unroll
-      for (int j = 0; j < N; ++j) acc[j] *= scale;
-      if (kMulticast) {
-        V::mc_store(reinterpret_cast<T*>(mc_base + data_off) + v * N, acc);
-      } else {
-        for (int p = 0; p < world; ++p)
-          V::store(reinterpret_cast<T*>(reinterpret_cast<char*>(t.ptrs[p]) + data_off) + v * N, acc);
+      for (int u = 0; u < 4; ++u) {
+        const long long v = vb + u * stride;
+        if (v >= v1) break;
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[u][j] *= scale;
+        if (kMulticast) {
+          V::mc_store(reinterpret_cast<T*>(mc_base + data_off) + v * N, acc[u]);
+        } else {
+          for (int p = 0; p < world; ++p)
+            V::store(reinterpret_cast<T*>(reinterpret_cast<char*>(t.ptrs[p]) + data_off) + v * N, acc[u]);
+        }
       }
     }
     // scalar tail (numel not a multiple of the vector width): rank 0 handles it with peer accesses
@@ -315,10 +326,17 @@ __global__ void __launch_bounds__(512) all_gather_kernel(PeerTable t, long long 
     uint4* slot = reinterpret_cast<uint4*>(reinterpret_cast<char*>(t.ptrs[rank]) + slot_off);
     uint4* own = reinterpret_cast<uint4*>(out + (long long)rank * bytes);
     const bool copy_own = reinterpret_cast<const char*>(own) != in;
-    for (long long v = tid; v < nvec; v += nthreads) {
-      const uint4 q = src[v];
-      slot[v] = q;
-      if (copy_own) own[v] = q;
+    for (long long v = tid; v < nvec; v += 4 * nthreads) {
+      uint4 q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v + u * nthreads < nvec) q[u] = src[v + u * nthreads];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v + u * nthreads < nvec) {
+          slot[v + u * nthreads] = q[u];
+          if (copy_own) own[v + u * nthreads] = q[u];
+        }
     }
   }
   __threadfence_system();
@@ -345,7 +363,16 @@ __global__ void __launch_bounds__(512) all_gather_kernel(PeerTable t, long long 
     if (ok_flag) {
       const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(t.ptrs[p]) + slot_off);
       uint4* dst = reinterpret_cast<uint4*>(out + (long long)p * bytes);
-      for (long long v = tid; v < nvec; v += nthreads) dst[v] = src[v];
+      // four independent 16-byte peer loads in flight per thread
+      for (long long v = tid; v < nvec; v += 4 * nthreads) {
+        uint4 q[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (v + u * nthreads < nvec) q[u] = src[v + u * nthreads];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (v + u * nthreads < nvec) dst[v + u * nthreads] = q[u];
+      }
     }
     __syncthreads();
   }
@@ -381,24 +408,35 @@ __global__ void __launch_bounds__(512) reduce_scatter_kernel(PeerTable t, long l
   if (ok_flag) {
     const long long slice_off = data_off + (long long)rank * numel * (long long)sizeof(T);
     const long long nvec = numel / N;
-    for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec;
-         v += (long long)gridDim.x * blockDim.x) {
-      float acc[N];
-      if (kMulticast) {
-        V::mc_load_reduce(reinterpret_cast<const T*>(mc_base + slice_off) + v * N, acc);
-      } else {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long v0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; v0 < nvec; v0 += 4 * stride) {
+      float acc[4][N];
+      // up to four vectors per thread: their peer loads are independent and overlap
 #pragma unroll
-        for (int j = 0; j < N; ++j) acc[j] = 0.f;
-        for (int p = 0; p < world; ++p) {
-          float f[N];
-          V::load(reinterpret_cast<const T*>(reinterpret_cast<const char*>(t.ptrs[p]) + slice_off) + v * N, f);
+      for (int u = 0; u < 4; ++u) {
+        const long long v = v0 + u * stride;
+        if (v >= nvec) break;
+        if (kMulticast) {
+          V::mc_load_reduce(reinterpret_cast<const T*>(mc_base + slice_off) + v * N, acc[u]);
+        } else {
 #pragma unroll
-          for (int j = 0; j < N; ++j) acc[j] += f[j];
+          for (int j = 0; j < N; ++j) acc[u][j] = 0.f;
+          for (int p = 0; p < world; ++p) {
+            float f[N];
+            V::load(reinterpret_cast<const T*>(reinterpret_cast<const char*>(t.ptrs[p]) + slice_off) + v * N, f);
+#pragma unroll
+            for (int j = 0; j < N; ++j) acc[u][j] += f[j];
+          }
         }
       }
 #pragma unroll
-      for (int j = 0; j < N; ++j) acc[j] *= scale;
-      V::store(out + v * N, acc);
+      for (int u = 0; u < 4; ++u) {
+        const long long v = v0 + u * stride;
+        if (v >= nvec) break;
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[u][j] *= scale;
+        V::store(out + v * N, acc[u]);
+      }
     }
     if (blockIdx.x == 0) {
       for (long long i = nvec * N + threadIdx.x; i < numel; i += blockDim.x) {
@@ -428,7 +466,7 @@ __global__ void __launch_bounds__(512) reduce_scatter_kernel(PeerTable t, long l
 int comm_grid(long long work_items, int threads) {
   long long g = (work_items + threads - 1) / threads;
   if (g < 1) g = 1;
-  if (g > 64) g = 64;  // a few dozen CTAs saturate NVLink; the rest of the GPU stays free for compute
+  if (g > 96) g = 96;  // enough CTAs to keep NVLink busy; the rest of the GPU stays free for compute
   return (int)g;
 }
 

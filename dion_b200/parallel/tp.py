@@ -130,7 +130,7 @@ def _matmul_all_reduce(x: torch.Tensor, w_t: torch.Tensor, group) -> torch.Tenso
     torch.ops.dion_b200.gemm_scatter(x, w_t, None, recv[0], comm.ptrs(slot_off, block_bytes), 1, rows, world, 1.0, 0.0,
                                      runtime.status_tensor(x.device))
     ar.barrier()
-    mine = recv.float().sum(dim=0).to(torch.bfloat16)  # fixed summation order
+    mine = torch.sum(recv, dim=0, dtype=torch.float32).to(torch.bfloat16)  # fp32 accumulation, fixed order
     out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
     comm.gather(out.view(-1), mine.view(-1), group)
     return out

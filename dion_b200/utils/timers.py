@@ -13,12 +13,16 @@ import torch.distributed as dist
 
 
 class PhaseTimers:
-    def __init__(self, enabled: bool = True):
+    def __init__(self, enabled: bool = True, nvtx: bool = False):
         self.enabled = enabled and torch.cuda.is_available()
+        # NVTX ranges around the same phases, for timeline tools; off by default
+        self.nvtx = nvtx and torch.cuda.is_available()
         self._open: Dict[str, torch.cuda.Event] = {}
         self._pairs: Dict[str, List[Tuple[torch.cuda.Event, torch.cuda.Event]]] = defaultdict(list)
 
     def start(self, name: str) -> None:
+        if self.nvtx:
+            torch.cuda.nvtx.range_push(name)
         if not self.enabled:
             return
         ev = torch.cuda.Event(enable_timing=True)
@@ -26,6 +30,8 @@ class PhaseTimers:
         self._open[name] = ev
 
     def stop(self, name: str) -> None:
+        if self.nvtx:
+            torch.cuda.nvtx.range_pop()
         if not self.enabled:
             return
         ev = torch.cuda.Event(enable_timing=True)
