@@ -8,7 +8,11 @@ _ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def load_reference():
-    for cand in (os.path.join(_ROOT, "baseline", "_ref"), "/root/reference"):
+    # the install made for the benchmark's reference arm, or a checkout named by DION_REFERENCE_PATH
+    cands = [os.path.join(_ROOT, "baseline", "_ref")]
+    if os.environ.get("DION_REFERENCE_PATH"):
+        cands.append(os.environ["DION_REFERENCE_PATH"])
+    for cand in cands:
         if os.path.isdir(os.path.join(cand, "dion")):
             # a different package called `dion` may be installed in site-packages
             if cand in sys.path:
