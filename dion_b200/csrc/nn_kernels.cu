@@ -42,9 +42,12 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 }
 
 // ------------------------------------------------------------------ RMSNorm
-// One warp per row; the row is kept in registers between the two passes.
+// One warp per row; the row is kept in registers between the two passes.  kVec = 16-byte vectors
+// per lane (dim <= kVec * 256): instantiated for 4, 8 and 16 so that narrow rows do not pay the
+// registers, and with them the occupancy, of the widest case.
 constexpr int kNormMaxVec = 16;  // 16 * 32 lanes * 8 elements = 4096 columns at most
 
+template <int kVec>
 __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res,
                                                          bf16* __restrict__ x_out, bf16* __restrict__ y,
                                                          float* __restrict__ rstd, long long rows, int dim,
@@ -57,10 +60,10 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const bf16* __restrict
   const uint4* rr = res ? reinterpret_cast<const uint4*>(res + row * dim) : nullptr;
   uint4* xo = x_out ? reinterpret_cast<uint4*>(x_out + row * dim) : nullptr;
   uint4* yr = reinterpret_cast<uint4*>(y + row * dim);
-  uint4 keep[kNormMaxVec];
+  uint4 keep[kVec];
   float ss = 0.f;
 #pragma unroll
-  for (int i = 0; i < kNormMaxVec; ++i) {
+  for (int i = 0; i < kVec; ++i) {
     const int v = lane + i * 32;
     if (v < nvec) {
       uint4 q = xr[v];
@@ -84,7 +87,7 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const bf16* __restrict
   const float r = rsqrtf(ss / (float)dim + eps);
   if (lane == 0 && rstd) rstd[row] = r;
 #pragma unroll
-  for (int i = 0; i < kNormMaxVec; ++i) {
+  for (int i = 0; i < kVec; ++i) {
     const int v = lane + i * 32;
     if (v < nvec) {
       float f[8];
@@ -96,6 +99,7 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const bf16* __restrict
   }
 }
 
+template <int kVec>
 __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x,
                                                          const float* __restrict__ rstd,
                                                          const bf16* __restrict__ dx_add, bf16* __restrict__ dx,
@@ -109,30 +113,47 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const bf16* __restrict
   const uint4* ar = dx_add ? reinterpret_cast<const uint4*>(dx_add + row * dim) : nullptr;
   uint4* dxr = reinterpret_cast<uint4*>(dx + row * dim);
   const float r = rstd[row];
-  float dot = 0.f;
-  for (int v = lane; v < nvec; v += 32) {
-    float a[8], b[8];
-    unpack8(dyr[v], a);
-    unpack8(xr[v], b);
+  // all loads of the row are issued before the first use
+  uint4 kdy[kVec], kx[kVec];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) dot += a[j] * b[j];
+  for (int i = 0; i < kVec; ++i) {
+    const int v = lane + i * 32;
+    if (v < nvec) {
+      kdy[i] = dyr[v];
+      kx[i] = xr[v];
+    }
+  }
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < kVec; ++i) {
+    if (lane + i * 32 < nvec) {
+      float a[8], b[8];
+      unpack8(kdy[i], a);
+      unpack8(kx[i], b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) dot += a[j] * b[j];
+    }
   }
   dot = warp_sum(dot);
   // dx = r * dy - x * r^3 * mean(dy * x)
   const float c = r * r * r * dot / (float)dim;
-  for (int v = lane; v < nvec; v += 32) {
-    float a[8], b[8], o[8];
-    unpack8(dyr[v], a);
-    unpack8(xr[v], b);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = r * a[j] - c * b[j];
-    if (ar) {
-      float e[8];
-      unpack8(ar[v], e);
+  for (int i = 0; i < kVec; ++i) {
+    const int v = lane + i * 32;
+    if (v < nvec) {
+      float a[8], b[8], o[8];
+      unpack8(kdy[i], a);
+      unpack8(kx[i], b);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] += e[j];
+      for (int j = 0; j < 8; ++j) o[j] = r * a[j] - c * b[j];
+      if (ar) {
+        float e[8];
+        unpack8(ar[v], e);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] += e[j];
+      }
+      dxr[v] = pack8(o);
     }
-    dxr[v] = pack8(o);
   }
 }
 
@@ -421,19 +442,28 @@ cudaError_t rmsnorm_fwd_launch(const void* x, const void* residual, void* x_out,
   if (rows == 0) return cudaSuccess;
   if (dim % 8 != 0 || dim > kNormMaxVec * 256) return cudaErrorInvalidValue;
   const unsigned grid = (unsigned)((rows + 7) / 8);
-  rmsnorm_fwd_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const bf16*>(x), reinterpret_cast<const bf16*>(residual),
-                                          reinterpret_cast<bf16*>(x_out), reinterpret_cast<bf16*>(y), rstd, rows,
-                                          dim, eps);
+#define DION_NORM_FWD(V)                                                                                          \
+  rmsnorm_fwd_kernel<V><<<grid, 256, 0, s>>>(reinterpret_cast<const bf16*>(x), reinterpret_cast<const bf16*>(residual), \
+                                             reinterpret_cast<bf16*>(x_out), reinterpret_cast<bf16*>(y), rstd, rows, \
+                                             dim, eps)
+  if (dim <= 4 * 256) DION_NORM_FWD(4);
+  else if (dim <= 8 * 256) DION_NORM_FWD(8);
+  else DION_NORM_FWD(16);
+#undef DION_NORM_FWD
   return cudaGetLastError();
 }
 cudaError_t rmsnorm_bwd_launch(const void* dy, const void* x, const float* rstd, const void* dx_add, void* dx,
                                long long rows, int dim, cudaStream_t s) {
   if (rows == 0) return cudaSuccess;
-  if (dim % 8 != 0) return cudaErrorInvalidValue;
+  if (dim % 8 != 0 || dim > kNormMaxVec * 256) return cudaErrorInvalidValue;
   const unsigned grid = (unsigned)((rows + 7) / 8);
-  rmsnorm_bwd_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const bf16*>(dy), reinterpret_cast<const bf16*>(x), rstd,
-                                          reinterpret_cast<const bf16*>(dx_add), reinterpret_cast<bf16*>(dx), rows,
-                                          dim);
+#define DION_NORM_BWD(V)                                                                                          \
+  rmsnorm_bwd_kernel<V><<<grid, 256, 0, s>>>(reinterpret_cast<const bf16*>(dy), reinterpret_cast<const bf16*>(x), rstd, \
+                                             reinterpret_cast<const bf16*>(dx_add), reinterpret_cast<bf16*>(dx), rows, dim)
+  if (dim <= 4 * 256) DION_NORM_BWD(4);
+  else if (dim <= 8 * 256) DION_NORM_BWD(8);
+  else DION_NORM_BWD(16);
+#undef DION_NORM_BWD
   return cudaGetLastError();
 }
 

@@ -296,9 +296,15 @@ class Muon(Optimizer):
             lo = self._device_rank * per
             mine = sumsq[lo:lo + per] if sumsq is not None else None
             ortho = self._orthogonalize(U[lo:lo + per], mine, flatten, eps)
-            work = dist.all_gather_into_tensor(U, ortho.contiguous(), group=pg, async_op=True)
-            yield
-            work.wait()
+            gather = self._symm_gather(ortho.device)
+            if gather is not None:
+                # all-gather kernel over symmetric memory (falls back to the group's own by itself)
+                gather(U.view(-1), ortho.contiguous().view(-1), pg)
+                yield
+            else:
+                work = dist.all_gather_into_tensor(U, ortho.contiguous(), group=pg, async_op=True)
+                yield
+                work.wait()
         else:
             U = self._orthogonalize(U, sumsq, flatten, eps)
 
@@ -379,6 +385,20 @@ class Muon(Optimizer):
                 nn_ops.mark_shadow_fresh(p)
             else:
                 nn_ops.mark_shadow_stale(p)
+
+    def _symm_gather(self, device):
+        """All-gather object for the unsharded path (updates computed by their owners are
+        distributed to every rank), or None where symmetric memory does not apply."""
+        if device.type != "cuda" or self._process_group is None:
+            return None
+        g = getattr(self, "_gather_obj", None)
+        if g is None:
+            from ..parallel.fsdp_comm import SymmAllGather, _usable
+
+            if not _usable(self._process_group, device):
+                return None
+            g = self._gather_obj = SymmAllGather(self._process_group, device)
+        return g
 
     # ------------------------------------------------------------------ scalar groups
 
