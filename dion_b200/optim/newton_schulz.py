@@ -101,3 +101,36 @@ def newton_schulz(G: Tensor, epsilon: float = 1e-7, coeffs: Sequence[Tuple[float
 def zeropower_via_newtonschulz5(G: Tensor, epsilon: float = 1e-7) -> Tensor:
     """Name-compatible entry point (dion/muon.py:620)."""
     return newton_schulz(G, epsilon)
+
+
+def symmetric_gram(A: Tensor, out: Optional[Tensor] = None) -> Tensor:
+    """``A @ A^T`` for ``A: [m, k]`` or a batch ``[B, m, k]``, computing only the tiles on and above
+    the diagonal and mirroring them (the first product of a Newton-Schulz step; the reference's
+    ``ns_line_1``, dion/newton_schulz_triton.py:134-170).  Output in the dtype of ``A``."""
+    if not A.is_cuda:
+        r = A @ A.mT
+        return r if out is None else out.copy_(r)
+    squeeze = A.dim() == 2
+    A3 = A.unsqueeze(0) if squeeze else A
+    o3 = None if out is None else (out.unsqueeze(0) if squeeze else out)
+    r = ops.gemm(A3, A3.transpose(1, 2), out=o3, symmetric=True)
+    return r[0] if squeeze and out is None else (out if out is not None else r)
+
+
+def symmetric_poly(A: Tensor, alpha: float, beta: float, out: Optional[Tensor] = None) -> Tensor:
+    """``alpha * A @ A^T + beta * A`` for symmetric ``A: [m, m]`` (or a batch), upper-triangular tiles
+    plus mirror with the ``beta * A`` term fused into the epilogue (the second product of a step; the
+    reference's ``ns_line_2``, dion/newton_schulz_triton.py:261-302)."""
+    if not A.is_cuda:
+        r = alpha * (A @ A.mT) + beta * A
+        return r if out is None else out.copy_(r)
+    squeeze = A.dim() == 2
+    A3 = A.unsqueeze(0) if squeeze else A
+    o3 = None if out is None else (out.unsqueeze(0) if squeeze else out)
+    r = ops.gemm(A3, A3.transpose(1, 2), c=A3, out=o3, alpha=float(alpha), beta=float(beta), symmetric=True)
+    return r[0] if squeeze and out is None else (out if out is not None else r)
+
+
+# names of the reference's entry points
+ns_line_1 = symmetric_gram
+ns_line_2 = symmetric_poly
