@@ -1,6 +1,11 @@
 """tcgen05 GEMM front end: ``gemm(a, b)`` computes ``alpha * a @ b (+ beta * c)`` for
 bf16 or fp32 (TF32) operands given as arbitrary row/column-major 2-D or 3-D views.
 
+It carries every matrix product the reference issues through cuBLAS: the power-iteration products
+``M @ Q`` / ``M^T @ P`` (dion/dion.py:801, 839, 921, 951, 1073, 1098), ``foreach_baddbmm_``
+(dion/dion.py:1494-1530), the Newton-Schulz products (dion/newton_schulz_triton.py:336-374) and the
+model's linear layers.
+
 On CPU tensors (tests, host-side logic) the same call runs a plain PyTorch
 implementation of identical semantics, which is also the numerical reference of the
 GPU tests.

@@ -1,4 +1,6 @@
-"""Symmetric-memory arenas and the collectives that run on them.
+"""Symmetric-memory arenas and the collectives that run on them (the transport under the averaged
+all-reduces of the reference's optimizers: ``all_reduce_replicate_mesh``, dion/dion.py:1165-1197, and
+the funcol / DTensor redistributions around the power iteration, dion/dion.py:806-844, 925-960).
 
 One arena per process group: a symmetric allocation (same size on every rank, peers mapped
 over NVLink, optionally bound to an NVSwitch multicast object) with a flag block in front.

@@ -1,4 +1,5 @@
-"""CUDA-event phase timers.  Phases are bracketed by events recorded on the current
+"""CUDA-event phase timers (the reference times its loop with ``time.time()`` around a device
+synchronisation, train.py:825-841).  Phases are bracketed by events recorded on the current
 stream, so measuring adds no synchronisation; `summary()` synchronises once, and
 `max_over_ranks()` reduces with MAX so that multi-GPU numbers are the slowest rank's."""
 
