@@ -49,6 +49,10 @@ _WAIT_NS = int(float(os.environ.get("DION_B200_FSDP_WAIT_S", "30")) * 1e9)
 _MIN_BYTES = 1 << 20
 
 
+def _is_cuda(device) -> bool:
+    return torch.device(device).type == "cuda"
+
+
 def _kernel_dtype(dtype: torch.dtype) -> bool:
     return dtype in (torch.float32, torch.bfloat16)
 
@@ -149,7 +153,7 @@ class SymmReduceScatter(ReduceScatter):
             return torch.empty(tuple(size), dtype=dtype, device=device)
         self._pending_numel = None
         nbytes = n * torch.empty((), dtype=dtype).element_size()
-        if (a is None or not _kernel_dtype(dtype) or torch.device(device).type != "cuda" or n == 0
+        if (a is None or not _kernel_dtype(dtype) or not _is_cuda(device) or n == 0
                 or n % self.world != 0 or (nbytes // self.world) % 16 != 0):
             return torch.empty(tuple(size), dtype=dtype, device=device)
         had = a.arena

@@ -121,3 +121,52 @@ def test_checkpoint_write_is_atomic(tmp_path, monkeypatch):
         torch.testing.assert_close(model.weight.detach(), before)
     finally:
         dist.destroy_process_group()
+
+
+def test_reduce_scatter_hook_hands_out_symmetric_inputs_and_ordinary_outputs(monkeypatch):
+    """Bookkeeping of the FSDP2 reduce-scatter hook, with a stand-in for the symmetric arena: the
+    first buffer FSDP asks for (world * n elements) comes from alternating slots of the arena, the
+    second one (n elements) is ordinary memory that may outlive the call, and requests the kernel
+    cannot serve fall back to ordinary memory as well."""
+    from dion_b200.parallel import fsdp_comm, symm
+
+    class FakeArena:
+        def __init__(self, nbytes):
+            self.buf = torch.zeros(symm._FLAG_BYTES + nbytes, dtype=torch.uint8)
+
+    class FakeSlots:
+        def __init__(self):
+            self.arena, self.slot_bytes, self.grown = None, 0, 0
+
+        def ensure(self, nbytes):
+            if self.arena is None or nbytes > self.slot_bytes:
+                self.slot_bytes = max(1024, nbytes)
+                self.arena = FakeArena(2 * self.slot_bytes)
+                self.grown += 1
+            return True
+
+        def slot_offset(self, index):
+            return symm._FLAG_BYTES + index * self.slot_bytes
+
+    rs = fsdp_comm.SymmReduceScatter.__new__(fsdp_comm.SymmReduceScatter)
+    rs.device, rs.world = torch.device("cpu"), 4
+    rs._slots, rs._next, rs._events, rs._live = FakeSlots(), 0, [None, None], {}
+    rs._pending_numel, rs._generation, rs.kernel_calls, rs.fallback_calls = None, 0, 0, 0
+
+    monkeypatch.setattr(fsdp_comm, "_is_cuda", lambda device: True)   # the stand-in arena lives on the host
+    a_in = rs.allocate((4 * 64,), dtype=torch.float32, device="cpu")
+    a_out_ptr_is_slot = a_in.data_ptr() in rs._live
+    assert a_out_ptr_is_slot and rs._pending_numel == 256
+    base = rs._slots.arena.buf.data_ptr()
+    assert a_in.data_ptr() == base + rs._slots.slot_offset(0)
+    # the output request (pending / world elements) is served from ordinary memory and clears the pending mark
+    out = rs.allocate((64,), dtype=torch.float32, device="cpu")
+    assert rs._pending_numel is None and out.data_ptr() not in rs._live
+    assert not (base <= out.data_ptr() < base + rs._slots.arena.buf.numel())
+    # the next input goes to the other slot
+    b_in = rs.allocate((4 * 64,), dtype=torch.float32, device="cpu")
+    assert b_in.data_ptr() == base + rs._slots.slot_offset(1)
+    rs.allocate((64,), dtype=torch.float32, device="cpu")
+    # a size that is not a multiple of world * 16 bytes is never taken from the arena
+    odd = rs.allocate((4 * 3,), dtype=torch.float32, device="cpu")
+    assert odd.data_ptr() not in rs._live
