@@ -34,18 +34,24 @@ def main():
     ap.add_argument("--fp32_states", action="store_true")
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--layers", type=int, default=12, help="fewer layers for a quick smoke run")
     args = ap.parse_args()
 
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
+    cuda = torch.cuda.is_available()
+    if cuda:
+        torch.cuda.set_device(local)
+    dev = torch.device("cuda", local) if cuda else torch.device("cpu")   # CPUs (gloo) only for smoke runs
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1 or args.mode != "single":
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29555")
         os.environ.setdefault("RANK", "0")
         os.environ.setdefault("WORLD_SIZE", "1")
-        dist.init_process_group("nccl", device_id=dev)
+        if cuda:
+            dist.init_process_group("nccl", device_id=dev)
+        else:
+            dist.init_process_group("gloo")
     rank = dist.get_rank() if dist.is_initialized() else 0
 
     from torch.distributed.device_mesh import init_device_mesh
@@ -53,12 +59,12 @@ def main():
     from dion_b200 import ops
     from dion_b200.training import Hyperparameters, build_model, init_optimizer
 
-    hp = Hyperparameters(model_dim=768, n_layer=12, n_head=12, optimizer=args.optimizer, rank_fraction=args.rank_fraction,
+    hp = Hyperparameters(model_dim=768, n_layer=args.layers, n_head=12, optimizer=args.optimizer, rank_fraction=args.rank_fraction,
                          mixed_precision=not args.fp32_states, replicate_mesh_grad_sync=args.mode == "ddp" or args.compressed,
                          num_iterations=10 ** 6)
     mesh, group = None, None
     if args.mode == "fsdp":
-        mesh = init_device_mesh("cuda", (1, world, 1), mesh_dim_names=("dp", "fs", "tp"))
+        mesh = init_device_mesh("cuda" if cuda else "cpu", (1, world, 1), mesh_dim_names=("dp", "fs", "tp"))
     elif args.mode == "ddp" and world > 1:
         group = dist.group.WORLD
     torch.manual_seed(0)
@@ -67,13 +73,14 @@ def main():
     from dion_b200.models.gpt import parallelize_gpt_model
 
     with torch.device("meta"):
-        model = GPT(GPTConfig(sequence_len=1024, vocab_size=50304, n_layer=12, n_head=12, n_embd=768))
+        model = GPT(GPTConfig(sequence_len=1024, vocab_size=50304, n_layer=args.layers, n_head=12, n_embd=768))
     if mesh is not None:
         parallelize_gpt_model(model, device_mesh=mesh, dp_name=None, fs_name="fs", tp_name="tp")
     model.to_empty(device=dev)
     model.init_weights()
     opt = init_optimizer(model, mesh, group, hp)
     gen = torch.Generator(device=dev).manual_seed(100 + rank)
+    import time
     grads = []
     for p in model.parameters():
         loc = p.to_local() if hasattr(p, "to_local") else p
@@ -91,17 +98,24 @@ def main():
 
     for _ in range(args.warmup):
         step()
-    torch.cuda.synchronize()
+    if cuda:
+        torch.cuda.synchronize()
     if dist.is_initialized():
         dist.barrier()
     n0 = ops.launch_count()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(args.steps):
-        step()
-    b.record()
-    torch.cuda.synchronize()
-    ms = torch.tensor([a.elapsed_time(b) / args.steps], device=dev)
+    if cuda:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            step()
+        b.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([a.elapsed_time(b) / args.steps], device=dev)
+    else:
+        t0 = time.time()
+        for _ in range(args.steps):
+            step()
+        ms = torch.tensor([1000 * (time.time() - t0) / args.steps])
     if dist.is_initialized():
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     ops.check_status()
