@@ -339,6 +339,21 @@ def case_hybrid():
     for (n1, p1), (n2, p2) in zip(model.transformer.h.named_parameters(), ref.transformer.h.named_parameters()):
         optref.state[p2] = {"momentum": torch.zeros_like(p2), "Q": _full(opt.state[p1]["Q"]).clone()}
         optref._get_dion_param_config(p2).is_transposed = opt._param_config[p1].is_transposed
+    # sharding classification (dion/dion.py:498-607): column-parallel weights are Shard(0) over tp and
+    # Shard(1) over fs -> orthogonalise over the tp-sharded dim, not transposed; row-parallel weights
+    # the other way round -> transposed; Q is Shard(0) on the outer and Shard(1) on the inner mesh dim
+    from torch.distributed.tensor import Shard
+
+    blk = model.transformer.h[0]
+    for w, inner_dim, outer_dim, transposed in ((blk.attn.c_q.weight, 0, 1, False), (blk.mlp.c_fc.weight, 0, 1, False),
+                                                (blk.attn.c_proj.weight, 1, 0, True), (blk.mlp.c_proj.weight, 1, 0, True)):
+        c = opt._param_config[w]
+        assert (c.inner_shard_tensor_dim, c.outer_shard_tensor_dim, c.is_transposed) == (inner_dim, outer_dim, transposed), c
+        q = opt.state[w]["Q"]
+        names = q.device_mesh.mesh_dim_names
+        assert q.placements[names.index("fs")] == Shard(0) and q.placements[names.index("tp")] == Shard(1), q.placements
+        m, n = w.shape
+        assert q.shape[0] == (m if transposed else n)
     fs_rank = mesh["fs"].get_local_rank()
     stage("fs x tp: training")
     l1 = _train(model, opt, 3, data_rank=fs_rank, data_world=2)
