@@ -251,6 +251,19 @@ class Muon(Optimizer):
         per = Bp // W if distributed else B                   # matrices owned by each rank
         local_shape = X[0].shape
 
+        if distributed and shard_dim is not None and params[0].size(shard_dim) % W != 0:
+            raise AssertionError(
+                f"Shard dimension {shard_dim} size {params[0].size(shard_dim)} is not divisible by world size {W}.")
+        if distributed and shard_dim is not None and self._fused_exchange_ok(params[0], X[0], shard_dim):
+            # shards travel by peer stores issued from the momentum kernel and from the epilogue of
+            # the last Newton-Schulz product; see _muon_update_class_fused (which gives up, before
+            # it touches the momentum, when the arena cannot hold its buffers yet)
+            try:
+                self._muon_update_class_fused(params, X, G, M, group, shard_dim, per, Bp)
+                return
+            except _ArenaTooSmall:
+                pass  # the arena grows at the next step; this step uses the library collectives
+
         # momentum, Nesterov, bf16 cast and squared norms in one launch (dion/muon.py:525-552)
         U = torch.zeros((Bp, *local_shape), dtype=torch.bfloat16, device=X[0].device) if Bp != B else \
             torch.empty((Bp, *local_shape), dtype=torch.bfloat16, device=X[0].device)
@@ -258,17 +271,6 @@ class Muon(Optimizer):
         sumsq = torch.zeros(Bp, dtype=torch.float32, device=X[0].device) if use_sumsq else None
         ops.muon_momentum(G, M, mu=mu, nesterov=nesterov, U=list(U[:B].unbind(0)), sumsq=sumsq)
 
-        if distributed and shard_dim is not None and params[0].size(shard_dim) % W != 0:
-            raise AssertionError(
-                f"Shard dimension {shard_dim} size {params[0].size(shard_dim)} is not divisible by world size {W}.")
-        if distributed and shard_dim is not None and self._fused_exchange_ok(params[0], X[0], shard_dim):
-            # shards travel by peer stores issued from the momentum kernel and from the epilogue of
-            # the last Newton-Schulz product; see _muon_update_class_fused
-            try:
-                self._muon_update_class_fused(params, X, G, M, group, shard_dim, per, Bp)
-                return
-            except _ArenaTooSmall:
-                pass  # the arena grows at the next step; this step uses the library collectives
         if distributed and shard_dim is not None:
             # shards of the matrices a rank owns travel to it: [W, per, *local] by source rank
             if sumsq is not None:

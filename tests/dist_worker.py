@@ -219,6 +219,12 @@ def case_fsdp():
             # gradient differences flip whole entries by 2 * lr
             loose = "wte" in n1 or "lm_head" in n1
             check(f"fsdp {name} {n1}", _full(p1.detach()), p2.detach(), 6e-2 if (CUDA or loose) else 5e-3)
+        if name == "muon":
+            # the momentum is linear in the gradients, so it pins down that every path (library
+            # all-to-all or peer stores from the momentum kernel) applies it exactly once per step
+            for (n1, p1), (n2, p2) in zip(model.transformer.h.named_parameters(), ref.transformer.h.named_parameters()):
+                check(f"fsdp muon momentum {n1}", _full(opt.state[p1]["momentum"]), optref.state[p2]["momentum"],
+                      5e-2 if CUDA else 2e-3)
     if CUDA and os.environ.get("DION_B200_SYMM", "1") != "0":
         from dion_b200.parallel import fsdp_comm
 
