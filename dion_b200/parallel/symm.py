@@ -78,10 +78,14 @@ class SymmetricArena:
             n *= int(s)
         nbytes = n * torch.empty((), dtype=dtype).element_size()
         start = (self.cursor + _ALIGN - 1) // _ALIGN * _ALIGN
-        self.high_water = max(self.high_water, start + nbytes)
-        if start + nbytes > self.capacity:
-            return None
+        # The cursor also advances for a request that does not fit (every later request of the step
+        # then fails too): the high-water mark is the total need of one step, so that the arena
+        # created at the next step boundary is large enough at once instead of growing by one
+        # buffer per step.
         self.cursor = start + nbytes
+        self.high_water = max(self.high_water, self.cursor)
+        if self.cursor > self.capacity:
+            return None
         off = _FLAG_BYTES + start
         t = self.buf[off:off + nbytes].view(dtype).view(*shape)
         self._views[t.data_ptr()] = off

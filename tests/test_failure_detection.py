@@ -170,3 +170,28 @@ def test_reduce_scatter_hook_hands_out_symmetric_inputs_and_ordinary_outputs(mon
     # a size that is not a multiple of world * 16 bytes is never taken from the arena
     odd = rs.allocate((4 * 3,), dtype=torch.float32, device="cpu")
     assert odd.data_ptr() not in rs._live
+
+
+def test_arena_sizing_converges_in_one_regrowth():
+    """An arena that is too small records the total need of the step, not just the first request
+    that failed, so the next arena fits every buffer of the step."""
+    from dion_b200.parallel import symm
+
+    def fake(capacity):
+        a = symm.SymmetricArena.__new__(symm.SymmetricArena)
+        a.capacity, a.cursor, a.high_water, a._views = capacity, 0, 0, {}
+        a.buf = torch.zeros(symm._FLAG_BYTES + capacity, dtype=torch.uint8)
+        return a
+
+    requests = [((1000,), torch.float32), ((3000,), torch.bfloat16), ((500, 4), torch.float32), ((7,), torch.float32)]
+    small = fake(12000)
+    got = [small.alloc(shape, dt) for shape, dt in requests]
+    assert got[0] is not None and got[1] is not None and got[2] is None and got[3] is None
+    need = small.high_water
+    assert need >= 4000 + 6000 + 8000 + 28
+    big = fake(int(need * 1.25))
+    views = [big.alloc(shape, dt) for shape, dt in requests]
+    assert all(v is not None for v in views)
+    assert all(big.offset_of(v) is not None and big.offset_of(v) % 256 == 0 for v in views)
+    big.reset()
+    assert big.alloc((10,), torch.float32).data_ptr() == views[0].data_ptr()
