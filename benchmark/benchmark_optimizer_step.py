@@ -33,7 +33,7 @@ def main():
     ap.add_argument("--compressed", action="store_true", help="Dion syncs only the low-rank factors over dp")
     ap.add_argument("--fp32_states", action="store_true")
     ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=8, help="the symmetric arenas reach their final size within the first three steps")
     ap.add_argument("--layers", type=int, default=12, help="fewer layers for a quick smoke run")
     args = ap.parse_args()
 
