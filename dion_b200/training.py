@@ -28,6 +28,7 @@ from . import ops
 from .models.data import DistributedDataLoader
 from .models.gpt import GPT, GPTConfig, parallelize_gpt_model
 from .optim import Dion, DionMixedPrecisionConfig, DionReference, DionSimple, Muon, MuonReference
+from .utils.health import StepHeartbeat
 from .utils.timers import PhaseTimers
 
 
@@ -514,59 +515,74 @@ def main(argv=None):
     pbar = tqdm(total=hp.num_iterations, desc="Training", disable=not _MASTER) if tqdm else None
     if pbar:
         pbar.update(start_step)
-    for step in range(start_step, hp.num_iterations + 1):
-        if step == 10:  # the first steps carry one-time set-up cost
-            training_time_ms = 0.0
-            sync()
-            t0 = time.time()
-        timed_steps = (step - 10) if step > 10 else float("nan")
+    # host-side liveness: a rank that leaves says so in the store, and nobody launches the next step
+    # against it (DION_B200_HEARTBEAT=0 turns it off, any other number is the check interval in steps)
+    hb_every = int(os.environ.get("DION_B200_HEARTBEAT", "10"))
+    heartbeat = StepHeartbeat.from_default_group(check_every=hb_every) if hb_every > 0 else None
+    try:
+        for step in range(start_step, hp.num_iterations + 1):
+            if step == 10:  # the first steps carry one-time set-up cost
+                training_time_ms = 0.0
+                sync()
+                t0 = time.time()
+            timed_steps = (step - 10) if step > 10 else float("nan")
 
-        last_step = step == hp.num_iterations
-        if last_step or (hp.val_loss_every > 0 and step % hp.val_loss_every == 0):
-            sync()
-            training_time_ms += 1000 * (time.time() - t0)
-            model.eval()
-            val_loader.reset()
-            val_loss = torch.zeros((), device=device)
-            with torch.no_grad():
-                for _ in range(val_steps):
-                    xv, yv = val_loader.next_batch()
-                    val_loss += model(xv, yv).float()
-            dist.all_reduce(val_loss, op=dist.ReduceOp.SUM)
-            val = val_loss.item() / val_steps / dist.get_world_size()
-            print0(f"step:{step}/{hp.num_iterations} val_loss:{val:.4f} train_time:{training_time_ms:.0f}ms "
-                   f"step_avg:{training_time_ms / timed_steps:.2f}ms")
+            last_step = step == hp.num_iterations
+            if last_step or (hp.val_loss_every > 0 and step % hp.val_loss_every == 0):
+                sync()
+                training_time_ms += 1000 * (time.time() - t0)
+                model.eval()
+                val_loader.reset()
+                val_loss = torch.zeros((), device=device)
+                with torch.no_grad():
+                    for _ in range(val_steps):
+                        xv, yv = val_loader.next_batch()
+                        val_loss += model(xv, yv).float()
+                dist.all_reduce(val_loss, op=dist.ReduceOp.SUM)
+                val = val_loss.item() / val_steps / dist.get_world_size()
+                print0(f"step:{step}/{hp.num_iterations} val_loss:{val:.4f} train_time:{training_time_ms:.0f}ms "
+                       f"step_avg:{training_time_ms / timed_steps:.2f}ms")
+                if _MASTER and use_wandb:
+                    wandb.log({"val/loss": val, "step": step, "time/training_time_ms": training_time_ms})
+                if pbar:
+                    pbar.set_postfix(val_loss=f"{val:.4f}")
+                sync()
+                t0 = time.time()
+            if last_step:
+                break
+
+            if heartbeat is not None:
+                heartbeat.check(step)
+            train_loss = step_fn(train_loader.next_batch() for _ in range(grad_accum))
+            if heartbeat is not None:
+                heartbeat.beat(step)
+            approx_time = training_time_ms + 1000 * (time.time() - t0)
             if _MASTER and use_wandb:
-                wandb.log({"val/loss": val, "step": step, "time/training_time_ms": training_time_ms})
+                grads_norm = float("nan")
+                wandb.log({"train/loss": train_loss.item(), "train/grad_norm": grads_norm, "step": step,
+                           "time/training_time_ms": approx_time})
+            if _MASTER and cli.debug:
+                print0(f"Step {step}: train_loss={train_loss.item():.4f}")
             if pbar:
-                pbar.set_postfix(val_loss=f"{val:.4f}")
-            sync()
-            t0 = time.time()
-        if last_step:
-            break
+                pbar.update(1)
+                pbar.set_postfix(train_loss=f"{train_loss.item():.4f}")
+            if cuda:
+                ops.check_status(device)
 
-        train_loss = step_fn(train_loader.next_batch() for _ in range(grad_accum))
-        approx_time = training_time_ms + 1000 * (time.time() - t0)
-        if _MASTER and use_wandb:
-            grads_norm = float("nan")
-            wandb.log({"train/loss": train_loss.item(), "train/grad_norm": grads_norm, "step": step,
-                       "time/training_time_ms": approx_time})
-        if _MASTER and cli.debug:
-            print0(f"Step {step}: train_loss={train_loss.item():.4f}")
-        if pbar:
-            pbar.update(1)
-            pbar.set_postfix(train_loss=f"{train_loss.item():.4f}")
-        if cuda:
-            ops.check_status(device)
-
-        if hp.checkpoint_freq > 0 and step % hp.checkpoint_freq == 0 and step > 0:
-            sync()
-            training_time_ms += 1000 * (time.time() - t0)  # checkpoints are not training time
-            if hasattr(optimizer, "synchronize_for_checkpoint"):
-                optimizer.synchronize_for_checkpoint()
-            ckpt.save(step=step)
-            sync()
-            t0 = time.time()
+            if hp.checkpoint_freq > 0 and step % hp.checkpoint_freq == 0 and step > 0:
+                sync()
+                training_time_ms += 1000 * (time.time() - t0)  # checkpoints are not training time
+                if hasattr(optimizer, "synchronize_for_checkpoint"):
+                    optimizer.synchronize_for_checkpoint()
+                ckpt.save(step=step)
+                sync()
+                t0 = time.time()
+    except BaseException:
+        if heartbeat is not None:
+            heartbeat.leave()
+        raise
+    if heartbeat is not None:
+        heartbeat.leave()
 
     if pbar:
         pbar.close()

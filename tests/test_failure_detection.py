@@ -195,3 +195,34 @@ def test_arena_sizing_converges_in_one_regrowth():
     assert all(big.offset_of(v) is not None and big.offset_of(v) % 256 == 0 for v in views)
     big.reset()
     assert big.alloc((10,), torch.float32).data_ptr() == views[0].data_ptr()
+
+
+def test_heartbeat_reports_departed_and_stalled_ranks_before_a_step_is_launched():
+    import time
+
+    import torch.distributed as dist
+
+    from dion_b200.utils.health import RankFailure, StepHeartbeat
+
+    store = dist.HashStore()
+    a = StepHeartbeat(store, 0, 3, max_lag=2, stale_after_s=0.05)
+    b = StepHeartbeat(store, 1, 3, max_lag=2, stale_after_s=0.05)
+    c = StepHeartbeat(store, 2, 3, max_lag=2, stale_after_s=0.05)
+    for step in range(3):
+        for hb in (a, b, c):
+            hb.check(step)
+            hb.beat(step)
+    b.leave()                                  # orderly departure between steps
+    with pytest.raises(RankFailure) as e:
+        a.check(3)
+    assert e.value.ranks == [1]
+    # rank 2 stops beating: tolerated while it is within max_lag or its beat is fresh ...
+    store.set("dion_b200/heartbeat/1", f"9:{time.time()}")
+    for step in range(3, 5):
+        a.beat(step)
+    a.check(5)
+    time.sleep(0.08)
+    a.beat(5)
+    with pytest.raises(RankFailure) as e:      # ... and reported once it trails and went silent
+        a.check(6)
+    assert e.value.ranks == [2]
