@@ -86,17 +86,26 @@ class CausalSelfAttention(nn.Module):
         self.c_proj = nn.Linear(self.n_embd, self.n_embd, bias=False)
         self.rotary = Rotary(self.head_dim)
 
-    def forward(self, h: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
-        """h: normalised input [B, T, C]; returns residual + attention output."""
-        B, T, _ = h.shape
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, bt=None) -> torch.Tensor:
+        """h: normalised input [B, T, C]; returns residual + attention output.  With `bt` = (B, T) the
+        model runs sequence-parallel: h and residual are this rank's row block [B * T / tp, C] of the
+        flattened tokens, gathered in front of the q / k / v products and scattered after c_proj."""
         group, _ = _tp_group(self.c_q.weight)
-        if group is not None:
-            h = TP.copy_to_tp_region(h, group)
-        q, k, v = K.linear_fanout(h, _local(self.c_q.weight), _local(self.c_k.weight), _local(self.c_v.weight))
+        if bt is not None:
+            B, T = bt
+            q, k, v = TP.gather_linear(h, group, _local(self.c_q.weight), _local(self.c_k.weight),
+                                       _local(self.c_v.weight))
+        else:
+            B, T, _ = h.shape
+            if group is not None:
+                h = TP.copy_to_tp_region(h, group)
+            q, k, v = K.linear_fanout(h, _local(self.c_q.weight), _local(self.c_k.weight), _local(self.c_v.weight))
         q, k, v = (t.view(B, T, -1, self.head_dim) for t in (q, k, v))
         cos, sin = self.rotary.tables(T, h.device)
         q, k = K.rope_qknorm(q, k, cos, sin)
         y = K.causal_attention(q, k, v)
+        if bt is not None:
+            return TP.linear_scatter(y.reshape(B * T, -1), _local(self.c_proj.weight), group, residual)
         if group is not None:
             return residual + TP.row_parallel_linear(y, _local(self.c_proj.weight), group)
         return K.linear(y, _local(self.c_proj.weight), residual=residual)
@@ -108,8 +117,12 @@ class MLP(nn.Module):
         self.c_fc = nn.Linear(config.n_embd, 4 * config.n_embd, bias=False)
         self.c_proj = nn.Linear(4 * config.n_embd, config.n_embd, bias=False)
 
-    def forward(self, h: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, residual: torch.Tensor, bt=None) -> torch.Tensor:
         group, _ = _tp_group(self.c_fc.weight)
+        if bt is not None:
+            # sequence-parallel: all-gather -> c_fc, c_proj -> reduce-scatter (+ residual) on row blocks
+            (pre,) = TP.gather_linear(h, group, _local(self.c_fc.weight))
+            return TP.linear_scatter(K.relu2(pre), _local(self.c_proj.weight), group, residual)
         if group is not None:
             # column-parallel c_fc (its input gradient is summed over the group by a fused
             # GEMM -> all-reduce), row-parallel c_proj (its output likewise)
@@ -124,11 +137,11 @@ class Block(nn.Module):
         self.attn = CausalSelfAttention(config)
         self.mlp = MLP(config)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, bt=None) -> torch.Tensor:
         x, h = K.norm_branch(x)
-        x = self.attn(h, x)
+        x = self.attn(h, x, bt)
         x, h = K.norm_branch(x)
-        x = self.mlp(h, x)
+        x = self.mlp(h, x, bt)
         return x
 
 
@@ -143,6 +156,8 @@ class GPT(nn.Module):
         self.lm_head = nn.Linear(config.n_embd, config.vocab_size, bias=False)
         # activations: bf16 on GPUs (the kernels' dtype), parameter dtype elsewhere
         self.activation_dtype: Optional[torch.dtype] = None
+        # tensor parallelism with the residual stream sharded over the tokens (set by the TP plan)
+        self.sequence_parallel = False
 
     # -- initialisation (models/gpt_model.py:140-157)
     def init_weights(self):
@@ -167,27 +182,50 @@ class GPT(nn.Module):
 
     # -- forward
     def forward(self, idx, targets=None, return_logits=False):
-        x = self._forward_emb(idx)
-        return self._forward(x, targets, return_logits)
+        bt = self._sequence_parallel_shape(idx)
+        x = self._forward_emb(idx, bt)
+        return self._forward(x, targets, return_logits, bt)
 
-    def _forward_emb(self, idx):
+    def _sequence_parallel_shape(self, idx):
+        """(B, T) when this call runs sequence-parallel: the TP plan asked for it and the flattened
+        tokens split into row blocks of a multiple of 8 rows."""
+        if not self.sequence_parallel:
+            return None
+        group, _ = _tp_group(self.transformer.wte.weight)
+        if group is None:
+            return None
+        world = group.size()
+        n = idx.numel()
+        return tuple(idx.shape) if n % world == 0 and (n // world) % 8 == 0 else None
+
+    def _forward_emb(self, idx, bt=None):
         w = self.transformer.wte.weight
         group, _ = _tp_group(w)
         dtype = self._act_dtype(idx.device)
         if group is not None:
-            return TP.vocab_parallel_embedding(idx, _local(w), group, dtype)
+            return TP.vocab_parallel_embedding(idx, _local(w), group, dtype, scatter_rows=bt is not None)
         return K.embedding(idx, _local(w), dtype)
 
-    def _forward(self, x, targets, return_logits):
+    def _forward(self, x, targets, return_logits, bt=None):
         for block in self.transformer.h:
-            x = block(x)
+            x = block(x, bt) if bt is not None else block(x)
         x = K.rms_norm(x)
         w = self.lm_head.weight
         group, _ = _tp_group(w)
         if targets is not None and not return_logits:
+            if bt is not None:
+                return TP.vocab_parallel_cross_entropy(x, _local(w), targets, group, ignore_index=-1, rows_sharded=True)
             if group is not None:
                 return TP.vocab_parallel_cross_entropy(x, _local(w), targets, group, ignore_index=-1)
             return K.linear_cross_entropy(x, _local(w), targets, ignore_index=-1)
+        if bt is not None:
+            if targets is None and not return_logits:
+                return None
+            # the logits path works on all tokens: gather the row blocks (the backward scatters the sum)
+            x = TP.gather_rows(x, group).view(bt[0], bt[1], -1)
+            if targets is None:
+                x = x[:, [-1], :]
+            return TP.gather_from_tp_region(K.linear(x, _local(w)), group).float()
         if targets is None:
             if not return_logits:
                 return None  # no targets, no logits requested: there is no loss to report
@@ -228,10 +266,12 @@ class GPT(nn.Module):
 
 def parallelize_gpt_model(model: GPT, device_mesh: DeviceMesh, dp_name: Optional[str] = "dp",
                           fs_name: Optional[str] = "fs", tp_name: Optional[str] = "tp",
-                          fsdp_reshard_after_forward: bool = True):
+                          fsdp_reshard_after_forward: bool = True, sequence_parallel: bool = False):
     """Shard `model` in place over the named mesh dimensions: tensor parallel first, then
     FSDP2 over ``fs`` (or over ``(dp, fs)`` as hybrid sharding when ``dp_name`` is given)
-    (models/gpt_model.py:236-288)."""
+    (models/gpt_model.py:236-288).  `sequence_parallel` keeps the residual stream sharded over the
+    tokens between the tensor-parallel products (all-gather -> GEMM, GEMM -> reduce-scatter) instead of
+    all-reducing every row-parallel output."""
     names = [n for n in (dp_name, fs_name, tp_name) if n]
     if not names:
         raise ValueError("At least one of dp_name, fs_name, or tp_name must be provided")
@@ -246,6 +286,7 @@ def parallelize_gpt_model(model: GPT, device_mesh: DeviceMesh, dp_name: Optional
         tp_mesh = device_mesh[tp_name]
         if tp_mesh.size() > 1:
             _apply_tp(model, tp_mesh)
+            model.sequence_parallel = bool(sequence_parallel)
     if fs_name:
         fsdp_mesh = device_mesh[fs_name] if not dp_name else device_mesh[dp_name, fs_name]
         _apply_fsdp(model, fsdp_mesh, fsdp_reshard_after_forward)

@@ -104,13 +104,71 @@ def _tp_comm(group, device):
     return c
 
 
+def _matmul_reduce_scatter(pairs, group, residual=None) -> torch.Tensor:
+    """Row block `rank` of ``sum over ranks r and over i of x_i_r @ w_t_i_r`` (+ `residual`), for
+    ``pairs = [(x_i: [T, K_i], w_t_i: [K_i, N]), ...]``; returns [T / world, N].
+
+    All products but the last accumulate in a local buffer; the last one is a GEMM whose epilogue
+    stores row block k of the partial result straight into rank k's receive buffer (peer stores over
+    NVLink, tile by tile while the remaining tiles are still being multiplied).  After a flag barrier
+    every rank adds up the `world` partial blocks it received (fp32, rank order, so the result does
+    not depend on timing).  Falls back to GEMMs + the process group's reduce-scatter when the shapes
+    or the group do not fit."""
+    x, w_t = pairs[-1]
+    T, N = x.shape[0], w_t.shape[1]
+    comm = _tp_comm(group, x.device) if x.is_cuda else None
+    world = dist.get_world_size(group)
+    ok = (comm is not None and x.dtype == torch.bfloat16 and T % world == 0 and (T // world) % 8 == 0 and N % 8 == 0
+          and comm.recv.ensure(T * N * 2))
+    acc = None
+    for xi, wi in pairs[:-1]:
+        if xi.is_cuda:
+            acc = gemm(xi, wi) if acc is None else gemm(xi, wi, c=acc, out=acc, beta=1.0)
+        else:
+            acc = xi @ wi if acc is None else acc + xi @ wi
+    if not ok:
+        if x.is_cuda:
+            y = gemm(x, w_t) if acc is None else gemm(x, w_t, c=acc, out=acc, beta=1.0)
+        else:
+            y = x @ w_t if acc is None else acc + x @ w_t
+        out = torch.empty(T // world, N, dtype=y.dtype, device=y.device)
+        dist.reduce_scatter_tensor(out, y.contiguous(), group=group)
+        return out if residual is None else out + residual
+    ar = comm.recv.arena
+    comm.calls += 1
+    slot = comm.calls & 1
+    slot_off = comm.recv.slot_offset(slot)
+    rows = T // world
+    block_bytes = rows * N * 2
+    recv = ar.buf[slot_off:slot_off + T * N * 2].view(torch.bfloat16).view(world, rows, N)
+    torch.ops.dion_b200.gemm_scatter(x, w_t, acc, recv[0], comm.ptrs(slot_off, block_bytes), 1, rows, world, 1.0,
+                                     0.0 if acc is None else 1.0, runtime.status_tensor(x.device))
+    ar.barrier()
+    mine = torch.sum(recv, dim=0, dtype=torch.float32)  # fp32 accumulation, fixed order
+    if residual is not None:
+        mine += residual
+    return mine.to(torch.bfloat16)
+
+
+def _gather_rows(x: torch.Tensor, group) -> torch.Tensor:
+    """All-gather of row blocks: [R, ...] on every rank -> [world * R, ...] in rank order (the in-tree
+    all-gather kernel over symmetric memory where it applies, the process group's otherwise)."""
+    world = dist.get_world_size(group)
+    x = x.contiguous()
+    out = x.new_empty((world * x.shape[0],) + tuple(x.shape[1:]))
+    comm = _tp_comm(group, x.device) if x.is_cuda else None
+    if comm is not None:
+        comm.gather(out.view(-1), x.view(-1), group)
+    else:
+        dist.all_gather_into_tensor(out, x, group=group)
+    return out
+
+
 def _matmul_all_reduce(x: torch.Tensor, w_t: torch.Tensor, group) -> torch.Tensor:
     """``sum over ranks of x_r @ w_t_r`` for x: [T, K] bf16 and w_t: [K, N] (a transposed view of the
-    local weight), identical on every rank.  One GEMM whose epilogue stores row block k of the
-    partial product straight into rank k's receive buffer (peer stores over NVLink, tile by tile
-    while the remaining tiles are still being multiplied), a flag barrier, the sum of the `world`
-    partial blocks each rank received, and an all-gather kernel.  Falls back to GEMM + the process
-    group's all-reduce when the shapes or the group do not fit."""
+    local weight), identical on every rank: the GEMM -> reduce-scatter above followed by the
+    all-gather kernel.  Falls back to GEMM + the process group's all-reduce when the shapes or the
+    group do not fit."""
     T, N = x.shape[0], w_t.shape[1]
     comm = _tp_comm(group, x.device) if x.is_cuda else None
     world = dist.get_world_size(group)
@@ -120,17 +178,7 @@ def _matmul_all_reduce(x: torch.Tensor, w_t: torch.Tensor, group) -> torch.Tenso
         y = gemm(x, w_t) if x.is_cuda else x @ w_t
         dist.all_reduce(y, group=group)
         return y
-    ar = comm.recv.arena
-    comm.calls += 1
-    slot = comm.calls & 1
-    slot_off = comm.recv.slot_offset(slot)
-    rows = T // world
-    block_bytes = rows * N * 2
-    recv = ar.buf[slot_off:slot_off + T * N * 2].view(torch.bfloat16).view(world, rows, N)
-    torch.ops.dion_b200.gemm_scatter(x, w_t, None, recv[0], comm.ptrs(slot_off, block_bytes), 1, rows, world, 1.0, 0.0,
-                                     runtime.status_tensor(x.device))
-    ar.barrier()
-    mine = torch.sum(recv, dim=0, dtype=torch.float32).to(torch.bfloat16)  # fp32 accumulation, fixed order
+    mine = _matmul_reduce_scatter([(x, w_t)], group)
     out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
     comm.gather(out.view(-1), mine.view(-1), group)
     return out
@@ -202,6 +250,118 @@ def column_parallel_linear(x: torch.Tensor, weight_local: torch.Tensor, group) -
     return K.linear(copy_to_tp_region(x, group), weight_local)
 
 
+# ------------------------------------------------------------------ sequence-parallel variants
+# The residual stream is kept as row blocks of the flattened token dimension ([B * T / world, C] on
+# every rank, rank order): norms and residual additions touch 1 / world of the tokens, the row-parallel
+# products end in a reduce-scatter instead of an all-reduce, and the column-parallel products start
+# with the all-gather that the all-reduce would have ended with.  The reference's plan keeps the
+# activations replicated (models/gpt_model.py:291-333); the communicated volume is the same.
+
+class _GatherRowsFn(torch.autograd.Function):
+    """All-gather of row blocks forward, reduce-scatter (sum) of the gradient backward."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _gather_rows(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        world = dist.get_world_size(ctx.group)
+        g = g.contiguous()
+        out = g.new_empty((g.shape[0] // world,) + tuple(g.shape[1:]))
+        dist.reduce_scatter_tensor(out, g, group=ctx.group)
+        return out, None
+
+
+class _ScatterSumRowsFn(torch.autograd.Function):
+    """Reduce-scatter (sum) of row blocks forward, all-gather of the gradient backward."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        world = dist.get_world_size(group)
+        x = x.contiguous()
+        out = x.new_empty((x.shape[0] // world,) + tuple(x.shape[1:]))
+        dist.reduce_scatter_tensor(out, x, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return _gather_rows(g, ctx.group), None
+
+
+def gather_rows(x, group):
+    return _GatherRowsFn.apply(x, group)
+
+
+def scatter_sum_rows(x, group):
+    return _ScatterSumRowsFn.apply(x, group)
+
+
+class _GatherLinearFn(torch.autograd.Function):
+    """(xg W_0^T, xg W_1^T, ...) with xg the all-gather of the row block x: [R, K] and column-parallel
+    W_i: [N_i_local, K].  Backward: the input gradient ``sum_i dy_i W_i`` summed over the ranks comes
+    back as this rank's row block through the fused GEMM -> reduce-scatter."""
+
+    @staticmethod
+    def forward(ctx, x, group, *weights):
+        xg = _gather_rows(x, group)
+        ctx.save_for_backward(xg, *weights)
+        ctx.group = group
+        return tuple(gemm(xg, K.bf16_weight(w).t()) for w in weights)
+
+    @staticmethod
+    def backward(ctx, *dys):
+        xg, *weights = ctx.saved_tensors
+        dys = [torch.zeros(xg.shape[0], w.shape[0], dtype=xg.dtype, device=xg.device) if dy is None else dy.contiguous()
+               for dy, w in zip(dys, weights)]
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = _matmul_reduce_scatter([(dy, K.bf16_weight(w)) for dy, w in zip(dys, weights)], ctx.group)
+        dws = [K._weight_grad(dy, xg, w) if ctx.needs_input_grad[2 + i] else None
+               for i, (dy, w) in enumerate(zip(dys, weights))]
+        return (dx, None, *dws)
+
+
+class _LinearScatterFn(torch.autograd.Function):
+    """Row block `rank` of ``sum over ranks of u_r W_r^T`` (+ residual) for a row-parallel
+    W_r: [N, K_local] (fused GEMM -> reduce-scatter); the backward all-gathers the gradient rows."""
+
+    @staticmethod
+    def forward(ctx, u, weight, residual, group):
+        ctx.save_for_backward(u, weight)
+        ctx.group = group
+        ctx.has_residual = residual is not None
+        return _matmul_reduce_scatter([(u, K.bf16_weight(weight).t())], group, residual)
+
+    @staticmethod
+    def backward(ctx, dy):
+        u, weight = ctx.saved_tensors
+        dyg = _gather_rows(dy, ctx.group)
+        du = gemm(dyg, K.bf16_weight(weight)) if ctx.needs_input_grad[0] else None
+        dw = K._weight_grad(dyg, u, weight) if ctx.needs_input_grad[1] else None
+        return du, dw, (dy if ctx.has_residual else None), None
+
+
+def gather_linear(x: torch.Tensor, group, *weights_local: torch.Tensor):
+    """``tuple(all_gather_rows(x) @ w.T for w in weights_local)`` for column-parallel weights and a
+    row-block input x: [R, K]; outputs are [R * world, N_local]."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _GatherLinearFn.apply(x, group, *weights_local)
+    xg = gather_rows(x, group)
+    return tuple(K.linear(xg, w) for w in weights_local)
+
+
+def linear_scatter(u: torch.Tensor, weight_local: torch.Tensor, group, residual=None) -> torch.Tensor:
+    """Row block of the reduced output of a row-parallel layer: u: [T, K_local] -> [T / world, N]
+    (+ `residual`, a row block)."""
+    if u.is_cuda and u.dtype == torch.bfloat16:
+        return _LinearScatterFn.apply(u, weight_local, residual, group)
+    y = scatter_sum_rows(K.linear(u, weight_local), group)
+    return y if residual is None else y + residual
+
+
 def copy_to_tp_region(x, group):
     return _CopyToRegion.apply(x, group)
 
@@ -214,9 +374,11 @@ def gather_from_tp_region(x, group):
     return _GatherFromRegion.apply(x, group)
 
 
-def vocab_parallel_embedding(idx: torch.Tensor, table_local: torch.Tensor, group, out_dtype) -> torch.Tensor:
+def vocab_parallel_embedding(idx: torch.Tensor, table_local: torch.Tensor, group, out_dtype,
+                             scatter_rows: bool = False) -> torch.Tensor:
     """Embedding whose rows are sharded over `group`: look up the locally owned ids, zero the
-    others, all-reduce."""
+    others, all-reduce - or, with `scatter_rows`, reduce-scatter into row blocks of the flattened
+    tokens ([idx.numel() / world, C])."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     rows = table_local.shape[0]
     lo = rank * rows
@@ -224,6 +386,8 @@ def vocab_parallel_embedding(idx: torch.Tensor, table_local: torch.Tensor, group
     local_idx = torch.where(mask, idx - lo, torch.zeros_like(idx))
     out = K.embedding(local_idx, table_local, out_dtype)
     out = out * mask.unsqueeze(-1).to(out.dtype)
+    if scatter_rows:
+        return scatter_sum_rows(out.reshape(-1, out.shape[-1]), group)
     return reduce_from_tp_region(out, group)
 
 
@@ -262,7 +426,12 @@ class _VocabParallelCE(torch.autograd.Function):
 
 
 def vocab_parallel_cross_entropy(x: torch.Tensor, weight_local: torch.Tensor, targets: torch.Tensor, group,
-                                 ignore_index: int = -1) -> torch.Tensor:
+                                 ignore_index: int = -1, rows_sharded: bool = False) -> torch.Tensor:
+    """Mean cross-entropy of ``x @ weight_local.T`` with the vocabulary sharded over `group`.  `x` is
+    replicated, or (`rows_sharded`) this rank's row block of the flattened tokens."""
+    if rows_sharded:
+        (logits,) = gather_linear(x.reshape(-1, x.shape[-1]), group, weight_local)
+        return _VocabParallelCE.apply(logits, targets.reshape(-1), group, ignore_index)
     x2 = copy_to_tp_region(x.reshape(-1, x.shape[-1]), group)
     logits = K.linear(x2, weight_local)
     return _VocabParallelCE.apply(logits, targets.reshape(-1), group, ignore_index)

@@ -76,7 +76,7 @@ def print0(*args, **kwargs):
 
 
 _STORE_TRUE_FLAGS = ("mixed_precision", "replicate_mesh_grad_sync", "fast_fsdp", "no_wandb", "no_compile",
-                     "no_triton", "debug")
+                     "no_triton", "debug", "sequence_parallel")
 
 
 def build_arg_parser() -> argparse.ArgumentParser:
@@ -109,6 +109,8 @@ def build_arg_parser() -> argparse.ArgumentParser:
     p.add_argument("--tp_size", type=int, default=None)
     p.add_argument("--replicate_mesh_grad_sync", action="store_true")
     p.add_argument("--fast_fsdp", action="store_true")
+    p.add_argument("--sequence_parallel", action="store_true",
+                   help="tensor parallelism with the residual stream sharded over the tokens")
     p.add_argument("--debug", action="store_true")
     p.add_argument("--no_compile", action="store_true", help="accepted for compatibility; nothing is compiled")
     p.add_argument("--no_triton", action="store_true", help="accepted for compatibility; no Triton is used")
@@ -381,7 +383,7 @@ class TrainStep:
 
 
 def build_model(hp: Hyperparameters, device_mesh, replicate_mesh_grad_sync: bool, fast_fsdp: bool = False,
-                device: Optional[torch.device] = None, vocab_size: int = 50304):
+                device: Optional[torch.device] = None, vocab_size: int = 50304, sequence_parallel: bool = False):
     """Create the GPT on the meta device, shard it, materialise and initialise it; wrap in DDP
     when there is no mesh but several ranks.  Returns (model, raw_model)."""
     from torch.nn.parallel import DistributedDataParallel as DDP
@@ -394,7 +396,8 @@ def build_model(hp: Hyperparameters, device_mesh, replicate_mesh_grad_sync: bool
         model = GPT(cfg)
     if device_mesh is not None:
         parallelize_gpt_model(model, device_mesh=device_mesh, dp_name=(None if replicate_mesh_grad_sync else "dp"),
-                              fs_name="fs", tp_name="tp", fsdp_reshard_after_forward=not fast_fsdp)
+                              fs_name="fs", tp_name="tp", fsdp_reshard_after_forward=not fast_fsdp,
+                              sequence_parallel=sequence_parallel)
     model.to_empty(device=device)
     model.init_weights()
     raw = model
@@ -447,7 +450,8 @@ def main(argv=None):
                                        hp.sequence_length, dp_rank, dp_world, prefetch=False)
     print0(f"Training DataLoader: {len(train_loader.files)} files; validation DataLoader: {len(val_loader.files)} files")
 
-    model, raw_model = build_model(hp, mesh, hp.replicate_mesh_grad_sync, fast_fsdp=cli.fast_fsdp)
+    model, raw_model = build_model(hp, mesh, hp.replicate_mesh_grad_sync, fast_fsdp=cli.fast_fsdp,
+                                   sequence_parallel=cli.sequence_parallel)
     print0(f"Total parameters: {sum(p.numel() for p in model.parameters())}")
     print0(model)
     print0("=" * 80)

@@ -374,7 +374,13 @@ def case_hybrid():
         check(f"hybrid fs x tp {n1}", _full(p1.detach()), p2.detach(), 6e-2 if (CUDA or loose) else 5e-3)
 
 
-def case_tp():
+def case_tp_sp():
+    """Tensor parallelism with the residual stream sharded over the tokens (all-gather -> GEMM,
+    GEMM -> reduce-scatter) against a single-process run, plus the logits / generation path."""
+    case_tp(sequence_parallel=True)
+
+
+def case_tp(sequence_parallel=False):
     """GPT with tensor parallelism (tp = world): loss and a Dion step (inner mesh) against a
     single-process run."""
     from torch.distributed.device_mesh import init_device_mesh
@@ -385,7 +391,19 @@ def case_tp():
     mesh = init_device_mesh("cuda" if CUDA else "cpu", (1, 1, WORLD), mesh_dim_names=("dp", "fs", "tp"))
     ref = _tiny_gpt().to(DEV)
     model = _tiny_gpt().to(DEV)
-    parallelize_gpt_model(model, mesh, dp_name=None, fs_name="fs", tp_name="tp")
+    parallelize_gpt_model(model, mesh, dp_name=None, fs_name="fs", tp_name="tp", sequence_parallel=sequence_parallel)
+    assert model.sequence_parallel == sequence_parallel
+    if sequence_parallel:
+        torch.manual_seed(5)
+        idx = torch.randint(0, 512, (2, 64), device=DEV)
+        tgt = torch.randint(0, 512, (2, 64), device=DEV)
+        tol = 6e-2 if CUDA else 3e-2     # FSDP's mixed precision runs the forward on bf16 copies of the weights
+        with torch.no_grad():
+            check("tp_sp logits", model(idx, tgt, return_logits=True), ref(idx, tgt, return_logits=True), tol)
+            check("tp_sp last-token logits", model(idx, None, return_logits=True), ref(idx, None, return_logits=True), tol)
+            assert model(idx) is None
+            odd = idx[:, :63]            # 126 tokens do not split into blocks of 8 rows: replicated path
+            check("tp_sp ragged", model(odd, None, return_logits=True), ref(odd, None, return_logits=True), tol)
     mk = lambda m: [dict(params=list(m.transformer.h.parameters())),
                     dict(params=list(m.transformer.wte.parameters()) + list(m.lm_head.parameters()),
                          algorithm="adamw", lr=0.002)]
