@@ -179,6 +179,56 @@ void gemm_scatter(const Tensor& a, const Tensor& b, const std::optional<Tensor>&
   g_launches.fetch_add(1, std::memory_order_relaxed);
 }
 
+// d = gathered(a) @ b with the all-gather of a's row blocks running inside the GEMM kernel:
+// `x_local` [rows, K] are this rank's rows, `a_full` [world * rows, K] receives every rank's rows (it
+// is the GEMM's operand, and stays valid afterwards), `b` is [K, N] K-major, `d` [world * rows, N].
+void gemm_gather(const Tensor& x_local, Tensor a_full, const Tensor& b, Tensor d, at::IntArrayRef peers,
+                 int64_t flag_off, int64_t slot_off, int64_t rank, int64_t epoch, int64_t channel, Tensor counters,
+                 const std::optional<Tensor>& status, int64_t budget_ns) {
+  TORCH_CHECK(x_local.is_cuda() && a_full.is_cuda() && b.is_cuda() && d.is_cuda());
+  TORCH_CHECK(x_local.scalar_type() == at::kBFloat16 && a_full.scalar_type() == at::kBFloat16 &&
+              b.scalar_type() == at::kBFloat16, "gemm_gather operands must be bfloat16");
+  TORCH_CHECK(x_local.dim() == 2 && a_full.dim() == 2 && b.dim() == 2 && d.dim() == 2);
+  TORCH_CHECK(x_local.is_contiguous() && a_full.is_contiguous());
+  const int64_t world = (int64_t)peers.size();
+  TORCH_CHECK(world >= 1 && world <= dion::kGatherMaxPeers && rank >= 0 && rank < world);
+  TORCH_CHECK(a_full.size(0) == x_local.size(0) * world && a_full.size(1) == x_local.size(1),
+              "a_full must hold every rank's rows");
+  TORCH_CHECK(counters.scalar_type() == at::kInt && counters.is_cuda() && counters.is_contiguous());
+  const c10::cuda::CUDAGuard guard(x_local.device());
+  dion::GemmArgs g;
+  g.ab_dtype = dion::kBF16;
+  g.M = (int)a_full.size(0);
+  g.K = (int)a_full.size(1);
+  g.N = (int)b.size(1);
+  TORCH_CHECK(b.size(0) == g.K, "gemm inner dimensions differ");
+  describe_operand(a_full, true, &g.a_major, &g.lda, &g.a_batch_stride, "a_full");
+  describe_operand(b, false, &g.b_major, &g.ldb, &g.b_batch_stride, "b");
+  g.A = a_full.data_ptr();
+  g.B = b.data_ptr();
+  check_out(d, 1, g.M, g.N, "d");
+  g.D = d.data_ptr();
+  g.d_dtype = gemm_dtype(d, "d");
+  g.ldd = d.stride(-2);
+  g.gather.world = (int)world;
+  g.gather.rank = (int)rank;
+  g.gather.rows = (int)x_local.size(0);
+  g.gather.in = x_local.data_ptr();
+  for (int64_t i = 0; i < world; ++i) g.gather.peers[i] = reinterpret_cast<void*>(peers[i]);
+  g.gather.flag_off = flag_off;
+  g.gather.slot_off = slot_off;
+  g.gather.epoch = (unsigned)epoch;
+  g.gather.channel = (int)channel;
+  g.gather.counters = reinterpret_cast<unsigned*>(counters.data_ptr<int>());
+  g.gather.counter_words = (int)counters.numel();
+  g.gather.budget_ns = budget_ns;
+  if (status.has_value()) g.status = status->data_ptr<int>();
+  cudaError_t e = dion::gemm_launch(g, at::cuda::getCurrentCUDAStream());
+  TORCH_CHECK(e == cudaSuccess, "dion_b200 gemm_gather launch failed: ", cudaGetErrorString(e), " ",
+              dion::gemm_last_error());
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
 // ----------------------------------------------------------------------------- multi-tensor helpers
 
 int elem_type(const Tensor& t, const char* what) {
@@ -677,6 +727,9 @@ TORCH_LIBRARY(dion_b200, m) {
   m.def(
       "gemm_scatter(Tensor a, Tensor b, Tensor? c, Tensor block_like, Tensor scatter_ptrs, int mode, int block, "
       "int dests, float alpha, float beta, Tensor? status) -> ()");
+  m.def(
+      "gemm_gather(Tensor x_local, Tensor(a!) a_full, Tensor b, Tensor(b!) d, int[] peers, int flag_off, int slot_off, "
+      "int rank, int epoch, int channel, Tensor(c!) counters, Tensor? status, int budget_ns) -> ()");
   m.def("symm_barrier(Tensor anchor, int[] peers, int flag_off, int channel, int rank, int epoch, Tensor(a!) status) -> ()");
   m.def(
       "symm_all_reduce(Tensor(a!) buf, int[] peers, int flag_off, int data_off, int mc_base, float scale, int rank, "
@@ -746,6 +799,7 @@ TORCH_LIBRARY_IMPL(dion_b200, CUDA, m) {
   m.impl("attn_bwd", &attn_bwd);
   m.impl("refine_prep", &refine_prep);
   m.impl("gemm_scatter", &gemm_scatter);
+  m.impl("gemm_gather", &gemm_gather);
   m.impl("symm_barrier", &symm_barrier);
   m.impl("symm_all_reduce", &symm_all_reduce);
   m.impl("symm_reduce_into", &symm_reduce_into);

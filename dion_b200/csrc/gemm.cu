@@ -2,9 +2,13 @@
 //
 //   warp 0      : TMA producer (one elected lane) - 128B-swizzled tiles of A and B
 //   warp 1      : TMEM allocator + tcgen05.mma issuer (one elected lane)
-//   warps 2..5  : epilogue - tcgen05.ld of the fp32 accumulator, fused
+//   warps 2..9  : epilogue - tcgen05.ld of the fp32 accumulator, fused
 //                 alpha/beta/activation, bf16 or fp32 stores (optionally transposed
 //                 mirror, bf16 shadow copy, or fp32 atomic accumulation for split-K)
+//
+//   warps 10-11 : all-gather variant only (GemmArgs::Gather) - copy the row blocks of A that
+//                 other GPUs produced out of their symmetric-memory slots while the tiles
+//                 of the rows already in place are being multiplied
 //
 // The accumulator is double buffered in TMEM (2 x BLOCK_N columns) so the epilogue
 // of tile i overlaps the main loop of tile i+1.  Operands may be bf16 (kind::f16)
@@ -33,6 +37,27 @@ namespace {
 constexpr int kBlockM = 128;
 constexpr int kNumEpilogueWarps = 8;  // two per TMEM lane quadrant, each takes half of the tile's columns
 constexpr int kNumThreads = 64 + 32 * kNumEpilogueWarps;
+constexpr int kNumGatherThreads = 64;  // two more warps in the all-gather variant (register budget of 384 threads)
+constexpr int kGatherUnitBytes = 64 * 1024;  // what one CTA's copier warps move at a time
+
+// Operand A gathered from the ranks of a group while the product runs (GemmArgs::Gather).
+struct GatherParams {
+  int world, rank, channel;
+  int rows;        // rows per source rank
+  int chunk_rows;  // rows per readiness counter: a multiple of the tile height that divides `rows`
+  int m_rot;       // m-tile the schedule starts with (this rank's first tile)
+  unsigned epoch;
+  long long row_bytes;
+  long long flag_off, slot_off;
+  const char* in;
+  char* out;
+  int units_per_chunk;  // ceil(chunk bytes / kGatherUnitBytes)
+  void* peers[kGatherMaxPeers];
+  unsigned* next_unit;  // work counter of the copier warps
+  unsigned* staged;     // units of this rank's own rows that reached the staging slot
+  unsigned* ready;      // per chunk: units in place; a chunk is complete at units_per_chunk
+  unsigned long long budget_ns;
+};
 
 struct KernelParams {
   int M, N, K, batch, split_k;
@@ -56,6 +81,7 @@ struct KernelParams {
   int vec_c, vec_d, vec_d2;  // 16-byte vector access allowed
   int stage;                 // turn epilogue accesses through shared memory (coalesced)
   int* status;
+  GatherParams g;            // used by the kGather instantiations only
 };
 
 // kPair: two CTAs of a cluster work on one 256 x kBlockN tile (tcgen05 cta_group::2).  Each CTA
@@ -95,6 +121,7 @@ struct TileCoord {
   int batch, split, m_blk, n_blk;
 };
 
+template <bool kGather = false>
 __device__ __forceinline__ TileCoord decode_tile(const KernelParams& p, int tile) {
   TileCoord t;
   const int per_bs = p.tiles_per_batch;
@@ -117,6 +144,12 @@ __device__ __forceinline__ TileCoord decode_tile(const KernelParams& p, int tile
     // n fastest, so that CTAs running together share the same rows of A through L2
     t.m_blk = r / p.tiles_n;
     t.n_blk = r - t.m_blk * p.tiles_n;
+    if constexpr (kGather) {
+      // start with the rows this rank produced itself; the other ranks' rows follow in ring order,
+      // which is also the order in which they are fetched
+      t.m_blk += p.g.m_rot;
+      if (t.m_blk >= p.tiles_m) t.m_blk -= p.tiles_m;
+    }
   }
   return t;
 }
@@ -265,8 +298,39 @@ __device__ __forceinline__ void stage_fetch(uint8_t* st, int lane, int row_first
   for (int i = 0; i < NSEG; ++i) *reinterpret_cast<uint4*>(st + stage_off(i * (32 >> SHIFT) + rsub, seg)) = q[i];
 }
 
-template <bool kTf32, int kAMajor, int kBMajor, int kBlockN, bool kPair>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned ld_acquire_sys_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys_u32(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// orders plain stores / loads of this thread with accesses made through TMA
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// mbarrier wait with a caller-chosen budget (the all-gather variant may wait for another GPU)
+__device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                              unsigned long long budget_ns) {
+  const unsigned long long t0 = global_timer_ns();
+#pragma unroll 1
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 128; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (*abort_flag != 0) return false;
+    if (global_timer_ns() - t0 > budget_ns) return false;
+  }
+}
+
+template <bool kTf32, int kAMajor, int kBMajor, int kBlockN, bool kPair, bool kGather = false>
+__global__ void __launch_bounds__(kNumThreads + (kGather ? kNumGatherThreads : 0), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const KernelParams p) {
   using C = Cfg<kTf32, kAMajor, kBMajor, kBlockN, kPair>;
@@ -281,6 +345,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* gather_word = abort_flag + 1;  // broadcast slot of the copier warps
   uint8_t* stage_area = bar_area + 256;
 
   const int warp = threadIdx.x >> 5;
@@ -321,6 +386,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   const uint32_t tmem_base = *tmem_slot;
 
   const int kb_per_split = p.kblocks_per_split;
+  // every wait inside the pipeline; the all-gather variant allows for the time another GPU may take
+  auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+    if constexpr (kGather) return mbar_wait_for(bar, parity, abort_flag, kWaitBudgetNs + p.g.budget_ns);
+    else return mbar_wait(bar, parity, abort_flag);
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -328,14 +398,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      [[maybe_unused]] int ready_chunk = -1;
       for (int tile = worker; tile < p.total_tiles && ok; tile += num_workers) {
-        const TileCoord t = decode_tile(p, tile);
+        const TileCoord t = decode_tile<kGather>(p, tile);
         const int m0 = t.m_blk * C::TILE_M + (int)cta_rank * kBlockM;
         const int n0 = t.n_blk * kBlockN + (int)cta_rank * (kPair ? C::B_ROWS : 0);
         const int kb0 = t.split * kb_per_split;
         const int kb1 = min(kb0 + kb_per_split, p.kblocks_total);
+        if constexpr (kGather) {
+          // the rows of this tile are in place once every unit of their chunk has been counted
+          const int chunk = m0 / p.g.chunk_rows;
+          if (chunk != ready_chunk) {
+            const unsigned long long t0 = global_timer_ns();
+            while (ld_acquire_gpu_u32(p.g.ready + chunk) < (unsigned)p.g.units_per_chunk) {
+              if (*abort_flag != 0 || global_timer_ns() - t0 > kWaitBudgetNs + p.g.budget_ns) {
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) {
+              *abort_flag = 1;
+              if (p.status) atomicCAS(p.status, 0, kStatusPeerTimeout);
+              break;
+            }
+            fence_proxy_async_all();
+            ready_chunk = chunk;
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_flag)) {
+          if (!wait(&empty_bar[stage], phase ^ 1u)) {
             ok = false;
             *abort_flag = 1;
             if (p.status) atomicCAS(p.status, 0, kStatusProducerTimeout);
@@ -379,12 +470,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       int it = 0;
       bool ok = true;
       for (int tile = worker; tile < p.total_tiles && ok; tile += num_workers, ++it) {
-        const TileCoord t = decode_tile(p, tile);
+        const TileCoord t = decode_tile<kGather>(p, tile);
         const int kb0 = t.split * kb_per_split;
         const int kb1 = min(kb0 + kb_per_split, p.kblocks_total);
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1u, abort_flag)) {
+        if (!wait(&tmem_empty[acc], acc_phase ^ 1u)) {
           ok = false;
           *abort_flag = 1;
           if (p.status) atomicCAS(p.status, 0, kStatusMmaTimeout);
@@ -393,7 +484,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * kBlockN;
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+          if (!wait(&full_bar[stage], phase)) {
             ok = false;
             *abort_flag = 1;
             if (p.status) atomicCAS(p.status, 0, kStatusMmaTimeout);
@@ -423,20 +514,122 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
       }
     }
+  } else if (kGather && warp >= 2 + kNumEpilogueWarps) {
+    // ------------------------------------------------------------------ all-gather of operand A
+    // The copy is cut into units of kGatherUnitBytes, numbered in the order in which the tiles need
+    // them (this rank's rows, then the next ranks' in ring order).  The 64 copier threads of a CTA
+    // take the next unit from a global counter, so the copy advances with whatever CTAs are running
+    // and no CTA ever waits for another one of this launch.
+    const GatherParams& g = p.g;
+    const int ct = (int)threadIdx.x - kNumThreads;
+    const long long chunk_bytes = (long long)g.chunk_rows * g.row_bytes;
+    const int chunks_per_rank = g.rows / g.chunk_rows;
+    const int units_per_chunk = g.units_per_chunk;
+    const int units_per_rank = chunks_per_rank * units_per_chunk;
+    const int total_units = units_per_rank * g.world;
+    auto copier_sync = [] { asm volatile("bar.sync 1, %0;" ::"n"(kNumGatherThreads) : "memory"); };
+    int waited_for = g.rank;  // ranks up to this one (in ring order) have announced their rows
+    for (;;) {
+      if (ct == 0) *gather_word = (int)atomicAdd(g.next_unit, 1u);
+      copier_sync();
+      const int unit = *gather_word;
+      copier_sync();  // everybody has read the word before it is written again
+      if (unit >= total_units) break;
+      const int ring = unit / units_per_rank;
+      const int in_rank = unit - ring * units_per_rank;
+      const int c = in_rank / units_per_chunk;
+      const int u = in_rank - c * units_per_chunk;
+      const int src_rank = (g.rank + ring) % g.world;
+      if (src_rank != waited_for && ring > 0) {
+        if (ct == 0) {
+          const unsigned* f = reinterpret_cast<const unsigned*>(reinterpret_cast<const char*>(g.peers[g.rank]) +
+                                                                g.flag_off) + g.channel * kGatherMaxPeers + src_rank;
+          const unsigned long long t0 = global_timer_ns();
+          int arrived = 1;
+          while ((int)(ld_acquire_sys_u32(f) - g.epoch) < 0) {
+            if (*abort_flag != 0 || global_timer_ns() - t0 > g.budget_ns) {
+              arrived = 0;
+              break;
+            }
+          }
+          if (!arrived) {
+            *abort_flag = 1;
+            if (p.status) atomicCAS(p.status, 0, kStatusPeerTimeout);
+          }
+          *gather_word = arrived;
+        }
+        copier_sync();
+        const bool arrived = *gather_word != 0;
+        copier_sync();
+        if (!arrived) break;
+        waited_for = src_rank;
+      }
+      // bytes [lo, hi) of chunk c of src_rank's rows
+      const long long lo = (long long)u * kGatherUnitBytes;
+      const long long hi = min(lo + (long long)kGatherUnitBytes, chunk_bytes);
+      const long long off = (long long)c * chunk_bytes;
+      const long long nvec = (hi - lo) / 16;
+      const uint4* src;
+      uint4* dst;
+      uint4* dst2 = nullptr;
+      char* block = g.out + (long long)src_rank * g.rows * g.row_bytes;
+      if (ring == 0) {
+        // this rank's rows: into the staging slot the peers read, and into its own block of A
+        src = reinterpret_cast<const uint4*>(g.in + off + lo);
+        dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(g.peers[g.rank]) + g.slot_off + off + lo);
+        if (block != g.in) dst2 = reinterpret_cast<uint4*>(block + off + lo);
+      } else {
+        src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(g.peers[src_rank]) + g.slot_off + off + lo);
+        dst = reinterpret_cast<uint4*>(block + off + lo);
+      }
+      // eight independent 16-byte loads in flight per thread (the sources are mostly peer memory)
+      for (long long v = ct; v < nvec; v += 8 * kNumGatherThreads) {
+        uint4 q[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (v + k * kNumGatherThreads < nvec) q[k] = src[v + k * kNumGatherThreads];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          if (v + k * kNumGatherThreads < nvec) {
+            dst[v + k * kNumGatherThreads] = q[k];
+            if (dst2 != nullptr) dst2[v + k * kNumGatherThreads] = q[k];
+          }
+      }
+      // the unit is visible to every CTA's TMA loads (and, for this rank's rows, to the peers)
+      // before it is counted
+      if (ring == 0) __threadfence_system();
+      else __threadfence();
+      fence_proxy_async_all();
+      copier_sync();
+      if (ct == 0) {
+        atomicAdd(g.ready + src_rank * chunks_per_rank + c, 1u);
+        if (ring == 0) {
+          // whoever stages the last unit of this rank's rows tells every peer that the slot is complete
+          const unsigned prev = atomicAdd(g.staged, 1u);
+          if (prev == (unsigned)units_per_rank - 1) {
+            __threadfence_system();
+            for (int q = 0; q < g.world; ++q) {
+              unsigned* f = reinterpret_cast<unsigned*>(reinterpret_cast<char*>(g.peers[q]) + g.flag_off);
+              st_release_sys_u32(f + g.channel * kGatherMaxPeers + g.rank, g.epoch);
+            }
+          }
+        }
+      }
+    }
   } else {
     // ------------------------------------------------------------------ epilogue
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     int it = 0;
     bool ok = true;
     for (int tile = worker; tile < p.total_tiles && ok; tile += num_workers, ++it) {
-      const TileCoord t = decode_tile(p, tile);
+      const TileCoord t = decode_tile<kGather>(p, tile);
       const int m0 = t.m_blk * C::TILE_M + (int)cta_rank * kBlockM;
       const int n0 = t.n_blk * kBlockN;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const int kb0 = t.split * kb_per_split;
       const bool has_work = kb0 < p.kblocks_total;
-      if (!mbar_wait(&tmem_full[acc], acc_phase, abort_flag)) {
+      if (!wait(&tmem_full[acc], acc_phase)) {
         ok = false;
         *abort_flag = 1;
         if (p.status) atomicCAS(p.status, 0, kStatusEpilogueTimeout);
@@ -716,7 +909,7 @@ int num_sms() {
   return n;
 }
 
-template <bool kTf32, int kAMajor, int kBMajor, int kBlockN, bool kPair = false>
+template <bool kTf32, int kAMajor, int kBMajor, int kBlockN, bool kPair = false, bool kGather = false>
 cudaError_t launch_cfg(const GemmArgs& a, const KernelParams& kp, cudaStream_t stream) {
   using C = Cfg<kTf32, kAMajor, kBMajor, kBlockN, kPair>;
   CUtensorMap ta, tb;
@@ -733,7 +926,8 @@ cudaError_t launch_cfg(const GemmArgs& a, const KernelParams& kp, cudaStream_t s
     ok = make_tmap(&tb, a.B, dt, a.N, a.K, a.batch, a.ldb, a.b_batch_stride, C::CH, C::BK, C::B_ATOM32);
   if (!ok) return cudaErrorInvalidValue;
 
-  auto kernel = gemm_kernel<kTf32, kAMajor, kBMajor, kBlockN, kPair>;
+  auto kernel = gemm_kernel<kTf32, kAMajor, kBMajor, kBlockN, kPair, kGather>;
+  constexpr int kThreads = kNumThreads + (kGather ? kNumGatherThreads : 0);
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
@@ -748,7 +942,7 @@ cudaError_t launch_cfg(const GemmArgs& a, const KernelParams& kp, cudaStream_t s
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(2 * grid, 1, 1);
-    cfg.blockDim = dim3(kNumThreads, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = C::SMEM_BYTES;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -761,7 +955,7 @@ cudaError_t launch_cfg(const GemmArgs& a, const KernelParams& kp, cudaStream_t s
     return cudaLaunchKernelEx(&cfg, kernel, ta, tb, kp);
   } else {
     if (grid > kp.total_tiles) grid = kp.total_tiles;
-    kernel<<<grid, kNumThreads, C::SMEM_BYTES, stream>>>(ta, tb, kp);
+    kernel<<<grid, kThreads, C::SMEM_BYTES, stream>>>(ta, tb, kp);
     return cudaGetLastError();
   }
 }
@@ -919,6 +1113,51 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
     kp.stage = stage_env;
   }
 
+  if (a.gather.world > 0) {
+    // operand A is gathered from the group inside the kernel
+    const GemmArgs::Gather& ga = a.gather;
+    const bool shapes_ok = !tf32 && a.a_major == kMajorK && a.b_major == kMajorK && a.batch == 1 && a.split_k == 1 &&
+                           !a.symmetric && a.lda == a.K && ga.world <= kGatherMaxPeers && ga.rank >= 0 &&
+                           ga.rank < ga.world && ga.rows > 0 && (long long)ga.rows * ga.world == a.M &&
+                           ga.rows % tile_m == 0 && ga.in && ga.counters &&
+                           (reinterpret_cast<uintptr_t>(ga.in) & 15) == 0 && (ga.slot_off & 15) == 0;
+    if (!shapes_ok) {
+      g_last_error = "all-gather variant: bf16 K-major operands, one batch, contiguous A of world * rows rows with "
+                     "rows a multiple of the tile height";
+      return cudaErrorInvalidValue;
+    }
+    if (bn == 64) bn = 128;
+    GatherParams& g = kp.g;
+    g.world = ga.world;
+    g.rank = ga.rank;
+    g.channel = ga.channel;
+    g.rows = ga.rows;
+    int per_chunk = 8;  // tiles per readiness counter: few counters, but work can start early
+    while (per_chunk > 1 && (ga.rows % (tile_m * per_chunk) != 0 || ga.rows / (tile_m * per_chunk) < 4)) per_chunk /= 2;
+    g.chunk_rows = tile_m * per_chunk;
+    g.m_rot = ga.rank * (ga.rows / tile_m);
+    g.epoch = ga.epoch;
+    g.row_bytes = (long long)a.K * 2;
+    g.flag_off = ga.flag_off;
+    g.slot_off = ga.slot_off;
+    g.in = reinterpret_cast<const char*>(ga.in);
+    g.out = reinterpret_cast<char*>(const_cast<void*>(a.A));
+    for (int i = 0; i < kGatherMaxPeers; ++i) g.peers[i] = ga.peers[i];
+    g.units_per_chunk = (int)(((long long)g.chunk_rows * g.row_bytes + kGatherUnitBytes - 1) / kGatherUnitBytes);
+    g.next_unit = ga.counters;
+    g.staged = ga.counters + 1;
+    g.ready = ga.counters + 2;
+    g.budget_ns = (unsigned long long)(ga.budget_ns > 0 ? ga.budget_ns : (long long)kWaitBudgetNs);
+    if (2 + a.M / g.chunk_rows > ga.counter_words) {
+      g_last_error = "all-gather variant: counter buffer too small";
+      return cudaErrorInvalidValue;
+    }
+    cudaError_t e = cudaMemsetAsync(ga.counters, 0, sizeof(unsigned) * (size_t)(2 + a.M / g.chunk_rows), stream);
+    if (e != cudaSuccess) return e;
+    if (pair) return launch_cfg<false, kMajorK, kMajorK, 256, true, true>(a, kp, stream);
+    if (bn == 128) return launch_cfg<false, kMajorK, kMajorK, 128, false, true>(a, kp, stream);
+    return launch_cfg<false, kMajorK, kMajorK, 256, false, true>(a, kp, stream);
+  }
   return tf32 ? launch_major<true>(a, kp, bn, pair, stream) : launch_major<false>(a, kp, bn, pair, stream);
 }
 

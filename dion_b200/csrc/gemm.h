@@ -13,6 +13,8 @@ enum GemmEpilogue : int {
   kEpiStore = 0,      // D = act(alpha * acc) + beta * C
   kEpiAtomicAdd = 1,  // D += alpha * acc   (fp32 D, red.global.add; used with split-K)
 };
+constexpr int kGatherMaxPeers = 8;  // ranks of a symmetric-memory group (width of its flag block)
+
 enum GemmAct : int {
   kActNone = 0,
   kActRelu2 = 1,         // D = relu(alpha * acc)^2 (+ beta * C)
@@ -75,6 +77,29 @@ struct GemmArgs {
   int pair = 0;      // CTA pairs (256-row tiles): 0 = choose automatically, 1 = force (needs block_n 256), -1 = never
 
   int* status = nullptr;  // device int, set to a non-zero code on a device-side failure
+
+  // All-gather of operand A inside the kernel (bf16, K-major A and B, one batch, lda == K): A is
+  // `gather.world` row blocks of `gather.rows` rows, block k produced by rank k.  Two extra warps of
+  // every CTA copy this rank's block from `gather.in` into its staging slot in symmetric memory
+  // (`peers[rank] + slot_off`) and into A, announce it on `channel` of every peer's flag block, and
+  // then pull the other ranks' slots into A with peer loads, in units handed out by a counter, raising
+  // one counter per chunk of rows; the TMA producer waits for the counter of a tile's chunk before it
+  // loads from A, and the tiles are visited starting with this rank's own rows.  `counters`
+  // (`counter_words` >= 2 + M / tile rows unsigned words) is cleared by the launch.  Waits are bounded
+  // by `budget_ns`.
+  struct Gather {
+    int world = 0;  // 0 = off
+    int rank = 0;
+    int rows = 0;
+    const void* in = nullptr;
+    void* peers[kGatherMaxPeers] = {};
+    long long flag_off = 0, slot_off = 0;
+    unsigned epoch = 0;
+    int channel = 0;
+    unsigned* counters = nullptr;
+    int counter_words = 0;
+    long long budget_ns = 0;
+  } gather;
 };
 
 // Returns cudaSuccess or the launch error; argument errors return cudaErrorInvalidValue

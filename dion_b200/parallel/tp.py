@@ -10,6 +10,8 @@ gathered logits: the cross-entropy exchanges only per-token max / sum-exp / targ
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 import torch.nn.functional as F
@@ -78,6 +80,7 @@ class _TPComm:
         self.recv = fsdp_comm._Arena(group, self.device)
         self.gather = fsdp_comm.SymmAllGather(group, self.device)
         self.calls = 0
+        self.fused_gathers = 0
         self._ptr_cache = {}
 
     def ptrs(self, slot_off: int, block_bytes: int) -> torch.Tensor:
@@ -162,6 +165,39 @@ def _gather_rows(x: torch.Tensor, group) -> torch.Tensor:
     else:
         dist.all_gather_into_tensor(out, x, group=group)
     return out
+
+
+# The all-gather inside the GEMM kernel (copier warps pull the peers' rows while the tensor cores work on
+# the rows that are already there) is opt-in until it has been measured against all-gather + GEMM.
+_FUSED_GATHER = os.environ.get("DION_B200_TP_FUSED_GATHER", "0") == "1"
+
+
+def _gather_matmul(x: torch.Tensor, w_t: torch.Tensor, group):
+    """``(xg, xg @ w_t)`` with xg the all-gather of the row block x: [R, K] over `group` and w_t: [K, N]
+    a transposed view of a weight.  With ``DION_B200_TP_FUSED_GATHER=1`` one kernel does both: two extra
+    warps per CTA stage this rank's rows in symmetric memory, announce them, and pull the peers' rows
+    into xg chunk by chunk, while the TMA producer of each tile waits for the chunk counter of its rows
+    (tiles start with this rank's own rows)."""
+    comm = _tp_comm(group, x.device) if x.is_cuda else None
+    R, Kd = x.shape
+    slots = comm.gather._slots if comm is not None else None
+    ok = (_FUSED_GATHER and slots is not None and x.dtype == torch.bfloat16 and w_t.dtype == torch.bfloat16
+          and x.is_contiguous() and R % 256 == 0 and Kd % 8 == 0 and w_t.stride(0) == 1 and w_t.stride(1) == Kd
+          and w_t.data_ptr() % 16 == 0 and slots.ensure(R * Kd * 2))
+    if not ok:
+        xg = _gather_rows(x, group)
+        return xg, (gemm(xg, w_t) if x.is_cuda else xg @ w_t)
+    ar = slots.arena
+    world = ar.world
+    ar.epoch += 1
+    xg = torch.empty(world * R, Kd, dtype=torch.bfloat16, device=x.device)
+    y = torch.empty(world * R, w_t.shape[1], dtype=torch.bfloat16, device=x.device)
+    counters = torch.empty(2 + world * R // 128, dtype=torch.int32, device=x.device)  # cleared by the launch
+    torch.ops.dion_b200.gemm_gather(x, xg, w_t, y, ar.peers, 0, slots.slot_offset(ar.epoch & 1), ar.rank, ar.epoch,
+                                    fsdp_comm._CH_AG, counters, runtime.status_tensor(x.device), fsdp_comm._WAIT_NS)
+    comm.gather.kernel_calls += 1
+    comm.fused_gathers += 1
+    return xg, y
 
 
 def _matmul_all_reduce(x: torch.Tensor, w_t: torch.Tensor, group) -> torch.Tensor:
@@ -306,10 +342,10 @@ class _GatherLinearFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, group, *weights):
-        xg = _gather_rows(x, group)
+        xg, y0 = _gather_matmul(x, K.bf16_weight(weights[0]).t(), group)
         ctx.save_for_backward(xg, *weights)
         ctx.group = group
-        return tuple(gemm(xg, K.bf16_weight(w).t()) for w in weights)
+        return (y0, *(gemm(xg, K.bf16_weight(w).t()) for w in weights[1:]))
 
     @staticmethod
     def backward(ctx, *dys):

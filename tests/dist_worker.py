@@ -374,6 +374,35 @@ def case_hybrid():
         check(f"hybrid fs x tp {n1}", _full(p1.detach()), p2.detach(), 6e-2 if (CUDA or loose) else 5e-3)
 
 
+def case_gemm_gather():
+    """GPUs only: the GEMM that all-gathers the row blocks of its first operand inside the kernel,
+    against the all-gather collective followed by an fp32 product."""
+    if not CUDA:
+        return
+    from dion_b200 import ops
+    from dion_b200.parallel import tp as TP
+
+    g = dist.group.WORLD
+    TP._FUSED_GATHER = True
+    try:
+        for rep, (R, Kd, N) in enumerate([(256, 64, 96), (1024, 768, 1536), (4096, 768, 2304), (1024, 768, 1536)]):
+            gen = torch.Generator(device="cpu").manual_seed(100 * rep + RANK)
+            x = torch.randn(R, Kd, generator=gen).to(DEV).to(torch.bfloat16)
+            w = torch.randn(N, Kd, generator=torch.Generator().manual_seed(7 + rep)).mul_(0.05).to(DEV).to(torch.bfloat16)
+            xg, y = TP._gather_matmul(x, w.t(), g)
+            ref_xg = torch.empty(WORLD * R, Kd, dtype=torch.bfloat16, device=DEV)
+            dist.all_gather_into_tensor(ref_xg, x, group=g)
+            ops.check_status()
+            assert torch.equal(xg, ref_xg), f"gathered operand differs ({R}x{Kd})"
+            check(f"gemm_gather {R}x{Kd}x{N}", y, ref_xg.float() @ w.float().t(), 2e-2)
+            # the unfused all-gather shares the staging slots and epochs with the fused kernel
+            check("gather_rows after gemm_gather", TP._gather_rows(x, g), ref_xg, 1e-6)
+        calls = [c.fused_gathers for c in TP._tp_comms.values()]
+        assert calls and all(c >= 4 for c in calls), f"the all-gather did not run inside the GEMM: {calls}"
+    finally:
+        TP._FUSED_GATHER = False
+
+
 def case_tp_sp():
     """Tensor parallelism with the residual stream sharded over the tokens (all-gather -> GEMM,
     GEMM -> reduce-scatter) against a single-process run, plus the logits / generation path."""

@@ -51,3 +51,13 @@ def test_gpu_ranks(case):
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
     _launch([case], nproc=min(n, 4), force_cpu=False)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(os.environ.get("DION_B200_TP_FUSED_GATHER") != "1",
+                    reason="the all-gather inside the GEMM kernel is opt-in (DION_B200_TP_FUSED_GATHER=1)")
+def test_gpu_gemm_with_fused_all_gather():
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    _launch(["gemm_gather", "tp_sp"], nproc=2, force_cpu=False)
