@@ -427,47 +427,74 @@ def vocab_parallel_embedding(idx: torch.Tensor, table_local: torch.Tensor, group
     return reduce_from_tp_region(out, group)
 
 
-class _VocabParallelCE(torch.autograd.Function):
-    """Mean cross-entropy over logits whose vocabulary dim is sharded: three small
-    all-reduces (max, sum-exp, target logit) instead of gathering the logits."""
+class _VocabParallelLinearCEFn(torch.autograd.Function):
+    """Mean cross-entropy of ``x @ W_local^T`` with the vocabulary rows of W sharded over `group`,
+    without keeping the logits: the tokens are processed in chunks; per chunk the ranks exchange only
+    the per-token max and (sum-exp, target logit), and the chunk's logits are turned into their
+    gradient and contracted into dX (this rank's partial sum over its vocabulary rows) and dW_local
+    right away.  The reference gathers the full logits instead (models/gpt_model.py:296-300)."""
 
     @staticmethod
-    def forward(ctx, logits_local, targets, group, ignore_index):
-        rank = dist.get_rank(group)
-        v_loc = logits_local.shape[-1]
-        lo = rank * v_loc
-        lf = logits_local.float()
-        mx = lf.max(dim=-1).values
-        dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=group)
-        ex = torch.exp(lf - mx.unsqueeze(-1))
-        se = ex.sum(dim=-1)
-        dist.all_reduce(se, group=group)
+    def forward(ctx, x, weight_local, targets, group, ignore_index, chunk_tokens):
+        fast = x.is_cuda and x.dtype == torch.bfloat16
+        wb = K.bf16_weight(weight_local) if fast else weight_local.detach().to(x.dtype)
+        T, Kd = x.shape
+        v_loc = wb.shape[0]
+        lo = dist.get_rank(group) * v_loc
+        need_grad = bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[1])
         valid = targets != ignore_index
-        mine = valid & (targets >= lo) & (targets < lo + v_loc)
-        t_loc = torch.where(mine, targets - lo, torch.zeros_like(targets))
-        tl = torch.where(mine, lf.gather(-1, t_loc.unsqueeze(-1)).squeeze(-1), torch.zeros_like(mx))
-        dist.all_reduce(tl, group=group)
         n_valid = valid.sum().clamp_min(1).float()
-        loss = torch.where(valid, mx + se.log() - tl, torch.zeros_like(mx)).sum() / n_valid
-        probs = ex / se.unsqueeze(-1)
-        probs.scatter_add_(-1, t_loc.unsqueeze(-1), -mine.float().unsqueeze(-1))
-        probs = probs * (valid.float() / n_valid).unsqueeze(-1)
-        ctx.save_for_backward(probs.to(logits_local.dtype))
-        return loss
+        dx = torch.empty_like(x) if need_grad else None
+        dw = torch.zeros(v_loc, Kd, device=x.device, dtype=torch.float32) if need_grad else None
+        loss_sum = torch.zeros((), device=x.device, dtype=torch.float32)
+        chunk = min(chunk_tokens, T)
+        for t0 in range(0, T, chunk):
+            t1 = min(t0 + chunk, T)
+            xc, tc, vc = x[t0:t1], targets[t0:t1], valid[t0:t1]
+            lf = (gemm(xc, wb.t()) if fast else xc @ wb.t()).float()
+            mx = lf.max(dim=-1).values
+            dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=group)
+            ex = lf.sub_(mx.unsqueeze(-1)).exp_()
+            mine = vc & (tc >= lo) & (tc < lo + v_loc)
+            t_loc = torch.where(mine, tc - lo, torch.zeros_like(tc))
+            # exp(target logit - max) of the locally owned targets; its log is the shifted target logit
+            et = torch.where(mine, ex.gather(-1, t_loc.unsqueeze(-1)).squeeze(-1), torch.zeros_like(mx))
+            stats = torch.stack([ex.sum(dim=-1), et])
+            dist.all_reduce(stats, group=group)
+            se, et = stats[0], stats[1]
+            loss_sum += torch.where(vc, se.log() - et.clamp_min(1e-38).log(), torch.zeros_like(se)).sum()
+            if need_grad:
+                probs = ex.div_(se.unsqueeze(-1))
+                probs.scatter_add_(-1, t_loc.unsqueeze(-1), -mine.to(probs.dtype).unsqueeze(-1))
+                probs.mul_((vc.float() / n_valid).unsqueeze(-1))
+                g = probs.to(x.dtype)
+                if fast:
+                    gemm(g, wb, out=dx[t0:t1])
+                    gemm(g.t(), xc, out=dw, accumulate=True, split_k=1)
+                else:
+                    dx[t0:t1] = g @ wb
+                    dw += (g.t() @ xc).float()
+        if need_grad:
+            ctx.save_for_backward(dx, dw)
+            ctx.w_dtype = weight_local.dtype
+        return loss_sum / n_valid
 
     @staticmethod
-    def backward(ctx, g):
-        (grad,) = ctx.saved_tensors
-        return grad * g.to(grad.dtype), None, None, None
+    def backward(ctx, dloss):
+        dx, dw = ctx.saved_tensors
+        dxo = dx * dloss.to(dx.dtype) if ctx.needs_input_grad[0] else None
+        dwo = (dw * dloss).to(ctx.w_dtype) if ctx.needs_input_grad[1] else None
+        return dxo, dwo, None, None, None, None
 
 
 def vocab_parallel_cross_entropy(x: torch.Tensor, weight_local: torch.Tensor, targets: torch.Tensor, group,
-                                 ignore_index: int = -1, rows_sharded: bool = False) -> torch.Tensor:
+                                 ignore_index: int = -1, rows_sharded: bool = False,
+                                 chunk_tokens: int = 8192) -> torch.Tensor:
     """Mean cross-entropy of ``x @ weight_local.T`` with the vocabulary sharded over `group`.  `x` is
     replicated, or (`rows_sharded`) this rank's row block of the flattened tokens."""
-    if rows_sharded:
-        (logits,) = gather_linear(x.reshape(-1, x.shape[-1]), group, weight_local)
-        return _VocabParallelCE.apply(logits, targets.reshape(-1), group, ignore_index)
-    x2 = copy_to_tp_region(x.reshape(-1, x.shape[-1]), group)
-    logits = K.linear(x2, weight_local)
-    return _VocabParallelCE.apply(logits, targets.reshape(-1), group, ignore_index)
+    x2 = x.reshape(-1, x.shape[-1])
+    # every rank contributes the part of dX that comes from its vocabulary rows: summed by the
+    # backward of the region function in front (all-reduce, or reduce-scatter into row blocks)
+    x2 = gather_rows(x2, group) if rows_sharded else copy_to_tp_region(x2, group)
+    return _VocabParallelLinearCEFn.apply(x2.contiguous(), weight_local, targets.reshape(-1).contiguous(), group,
+                                          ignore_index, chunk_tokens)

@@ -403,6 +403,33 @@ def case_gemm_gather():
         TP._FUSED_GATHER = False
 
 
+def _check_vocab_parallel_ce(group):
+    """Chunked vocabulary-parallel lm_head + cross-entropy (several chunks, a ragged last one, ignored
+    targets) against F.cross_entropy on the full logits: loss, dX and dW."""
+    import torch.nn.functional as F
+
+    from dion_b200.parallel import tp as TP
+
+    T, Kd, V = (192 if CUDA else 104), 64, 64 * WORLD
+    gen = torch.Generator().manual_seed(11)
+    dt = torch.bfloat16 if CUDA else torch.float32
+    x = torch.randn(T, Kd, generator=gen).to(DEV).to(dt).requires_grad_()
+    w = (torch.randn(V, Kd, generator=gen) * 0.3).to(DEV).requires_grad_()
+    tgt = torch.randint(0, V, (T,), generator=gen).to(DEV)
+    tgt[::7] = -1
+    v_loc = V // WORLD
+    w_loc = w.detach()[RANK * v_loc:(RANK + 1) * v_loc].clone().requires_grad_()
+    x1 = x.detach().clone().requires_grad_()
+    loss = TP.vocab_parallel_cross_entropy(x1, w_loc, tgt, group, ignore_index=-1, chunk_tokens=64 if CUDA else 32)
+    (loss * 2.0).backward()
+    ref = F.cross_entropy(x.float() @ w.t().float(), tgt, ignore_index=-1)
+    (ref * 2.0).backward()
+    tol = 3e-2 if CUDA else 1e-5
+    check("vocab-parallel CE loss", loss.detach().reshape(1), ref.detach().reshape(1), tol)
+    check("vocab-parallel CE dX", x1.grad, x.grad, tol)
+    check("vocab-parallel CE dW", w_loc.grad, w.grad[RANK * v_loc:(RANK + 1) * v_loc], tol)
+
+
 def case_tp_sp():
     """Tensor parallelism with the residual stream sharded over the tokens (all-gather -> GEMM,
     GEMM -> reduce-scatter) against a single-process run, plus the logits / generation path."""
@@ -418,6 +445,8 @@ def case_tp(sequence_parallel=False):
     from dion_b200.models.gpt import parallelize_gpt_model
 
     mesh = init_device_mesh("cuda" if CUDA else "cpu", (1, 1, WORLD), mesh_dim_names=("dp", "fs", "tp"))
+    if not sequence_parallel:
+        _check_vocab_parallel_ce(mesh.get_group("tp"))
     ref = _tiny_gpt().to(DEV)
     model = _tiny_gpt().to(DEV)
     parallelize_gpt_model(model, mesh, dp_name=None, fs_name="fs", tp_name="tp", sequence_parallel=sequence_parallel)
