@@ -256,7 +256,10 @@ class Dion(Optimizer):
             symm.begin_step(groups, work[0].cls.M.device)
         Scheduler(phase1(), max_in_flight=3).run()
         if work:
-            ortho = orthonormalize_many([w.P for w in work], [w.inner for w in work])
+            # P is the same on every rank of the outer (or else the replicate) group by now: each rank
+            # orthonormalises its share of every batch and the shares are all-gathered
+            ortho = orthonormalize_many([w.P for w in work], [w.inner for w in work],
+                                        shard_groups=[w.outer if w.outer is not None else w.replicate for w in work])
             for w, P in zip(work, ortho):
                 w.P = P
             Scheduler((lambda w=w: self._dion_phase2(w) for w in work), max_in_flight=3).run()

@@ -108,16 +108,68 @@ def _refine(X: Tensor, row_group: Optional[dist.ProcessGroup]) -> Tensor:
     return Xs - Xs @ C.transpose(-1, -2)
 
 
+# Work sharding: a batch that is identical on every rank of a group is split over the group, each rank
+# orthonormalises its share and the shares are all-gathered (the reference hands matrix j of a batch
+# to rank j, dion/dion.py:809-830, 925-946).  DION_B200_SHARD_ORTHO=0 keeps the redundant computation.
+SHARD_WORK = os.environ.get("DION_B200_SHARD_ORTHO", "1") != "0"
+_gatherers = {}
+
+
+def _my_share(X: Tensor, group) -> Tensor:
+    """Matrices [rank * c, (rank + 1) * c) of the batch, c = ceil(B / world); ranks whose range runs
+    past the end repeat the last matrix so that every share has the same shape."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    B = X.shape[0]
+    c = (B + world - 1) // world
+    lo = min(rank * c, B)
+    hi = min(lo + c, B)
+    part = X[lo:hi]
+    if hi - lo < c:
+        part = torch.cat([part, X[B - 1:B].expand(c - (hi - lo), -1, -1)], dim=0)
+    return part
+
+
+def _gather_shares(part: Tensor, group, B: int) -> Tensor:
+    """Inverse of :func:`_my_share`: all-gather the shares and drop the padding."""
+    world = dist.get_world_size(group)
+    part = part.contiguous()
+    out = part.new_empty((world * part.shape[0],) + tuple(part.shape[1:]))
+    gather = None
+    if part.is_cuda:
+        from ..parallel import fsdp_comm
+
+        key = symm._key(group)
+        if key not in _gatherers:
+            _gatherers[key] = (fsdp_comm.SymmAllGather(group, part.device)
+                               if fsdp_comm._usable(group, part.device) else None)
+        gather = _gatherers[key]
+    if gather is not None:
+        gather(out.view(-1), part.view(-1), group)  # in-tree kernel over symmetric memory, or the group's own
+    else:
+        dist.all_gather_into_tensor(out, part, group=group)
+    return out[:B]
+
+
 def orthonormalize_many(Ps, row_groups=None, refine_passes: int = 2,
-                        pivot_floor: float = ops.linalg.DEFAULT_PIVOT_FLOOR):
+                        pivot_floor: float = ops.linalg.DEFAULT_PIVOT_FLOOR, shard_groups=None):
     """Orthonormalise several batches ``P_i: [B_i, a_i, r_i]`` at once.  All Gram matrices of
     the same rank are factorised by a single launch of the Cholesky kernel (one CTA per
     matrix), whatever their row counts; the remaining loss of orthogonality is removed by
     `refine_passes` triangular Newton corrections, which are plain tensor-core GEMMs.
-    ``row_groups[i]`` is the process group sharding the rows of ``P_i`` (or None)."""
+    ``row_groups[i]`` is the process group sharding the rows of ``P_i`` (or None);
+    ``shard_groups[i]`` a group on whose ranks ``P_i`` is identical, which then splits the batch."""
     n = len(Ps)
     if row_groups is None:
         row_groups = [None] * n
+    if shard_groups is None or not SHARD_WORK:
+        shard_groups = [None] * n
+    shard_groups = [g if (g is not None and dist.get_world_size(g) > 1 and P.shape[0] > 1 and rg is None) else None
+                    for g, P, rg in zip(shard_groups, Ps, row_groups)]
+    if any(g is not None for g in shard_groups):
+        parts = [P.float() if g is None else _my_share(P.float(), g) for P, g in zip(Ps, shard_groups)]
+        outs = orthonormalize_many(parts, row_groups, refine_passes, pivot_floor)
+        return [X.to(P.dtype) if g is None else _gather_shares(X, g, P.shape[0]).to(P.dtype)
+                for X, P, g in zip(outs, Ps, shard_groups)]
     dtypes = [P.dtype for P in Ps]
     Xs = [P.float() for P in Ps]
     Gs = [gram(X, g) for X, g in zip(Xs, row_groups)]

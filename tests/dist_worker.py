@@ -103,7 +103,25 @@ def _single_process_dion(rank_fraction, steps):
     return P, opt
 
 
+def _check_sharded_orthonormalisation():
+    """Batches split over the ranks (including one that does not divide evenly and one smaller than
+    the group) give the same result as the redundant computation, identically on every rank."""
+    from dion_b200.optim.orthogonalize import orthonormalize_many
+
+    g = dist.group.WORLD
+    gen = torch.Generator().manual_seed(3)
+    Ps = [torch.randn(b, a, r, generator=gen).to(DEV) for b, a, r in ((2 * WORLD + 1, 96, 32), (1, 64, 32), (WORLD - 1 or 1, 128, 64))]
+    whole = orthonormalize_many(Ps)
+    split = orthonormalize_many(Ps, shard_groups=[g] * len(Ps))
+    for i, (a, b) in enumerate(zip(split, whole)):
+        check(f"sharded orthonormalisation batch {i}", a, b, 1e-5)
+        ref = a.clone()
+        dist.broadcast(ref, src=0)
+        assert torch.equal(a, ref), "ranks hold different orthonormal factors"
+
+
 def case_dion_ddp():
+    _check_sharded_orthonormalisation()
     """Dion with a ProcessGroup replicate mesh, gradient sync owned by the optimizer:
     full-gradient path (rank_fraction 1) and compressed P/R path (rank_fraction 0.25)."""
     from dion_b200 import Dion
