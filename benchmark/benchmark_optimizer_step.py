@@ -57,7 +57,7 @@ def main():
     from torch.distributed.device_mesh import init_device_mesh
 
     from dion_b200 import ops
-    from dion_b200.training import Hyperparameters, build_model, init_optimizer
+    from dion_b200.training import Hyperparameters, init_optimizer
 
     hp = Hyperparameters(model_dim=768, n_layer=args.layers, n_head=12, optimizer=args.optimizer, rank_fraction=args.rank_fraction,
                          mixed_precision=not args.fp32_states, replicate_mesh_grad_sync=args.mode == "ddp" or args.compressed,

@@ -8,7 +8,7 @@ Behavioural reference: dion/opt_utils.py:8-145 and dion/dion.py:1165-1197.
 from __future__ import annotations
 
 from collections import OrderedDict
-from typing import Callable, Dict, Generator, Iterable, Iterator, List, Optional, Sequence, Tuple, Union
+from typing import Callable, Dict, Generator, Iterable, Iterator, List, Optional, Sequence, Union
 
 import torch
 import torch.distributed as dist

@@ -36,7 +36,7 @@ from torch.optim.optimizer import Optimizer, ParamsT
 from .. import ops
 from ..ops import nn as nn_ops
 from ..parallel import symm
-from .common import (Scheduler, all_reduce_, group_of, group_rank, group_size, to_local)
+from .common import Scheduler, all_reduce_, group_of, group_size, to_local
 from .orthogonalize import orthonormalize_many
 
 try:  # pragma: no cover - depends on the torch build

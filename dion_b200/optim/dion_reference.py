@@ -17,7 +17,7 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 from torch.distributed import ProcessGroup
-from torch.distributed.tensor import DeviceMesh, DTensor
+from torch.distributed.tensor import DeviceMesh
 from torch.optim.optimizer import ParamsT
 
 from ..ops import nn as nn_ops

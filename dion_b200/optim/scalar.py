@@ -4,7 +4,6 @@ Math: dion/scalar_opts.py:6-86."""
 
 from __future__ import annotations
 
-import torch
 from torch import Tensor
 
 from .. import ops

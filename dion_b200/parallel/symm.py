@@ -20,7 +20,7 @@ kernels on plain peer loads and stores.
 from __future__ import annotations
 
 import os
-from typing import Dict, Optional, Tuple
+from typing import Dict, Optional
 
 import torch
 import torch.distributed as dist

@@ -14,7 +14,6 @@ import os
 
 import torch
 import torch.distributed as dist
-import torch.nn.functional as F
 
 from ..ops import nn as K
 from ..ops import runtime

@@ -18,7 +18,7 @@ import tempfile
 import time
 from dataclasses import dataclass, fields
 from pathlib import Path
-from typing import Callable, List, Optional, Tuple
+from typing import Callable, List, Optional
 
 import torch
 import torch.distributed as dist

@@ -5,7 +5,6 @@ stream, so measuring adds no synchronisation; `summary()` synchronises once, and
 
 from __future__ import annotations
 
-import time
 from collections import defaultdict
 from typing import Dict, List, Tuple
 

@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-from dion_b200.ops.gemm import gemm, gemm_reference
+from dion_b200.ops.gemm import gemm
 
 
 def _operand(rows, cols, dtype, transposed, batch=None, device="cuda"):

@@ -1,6 +1,4 @@
 """GPT model, data loader and training step on CPU."""
-import os
-import sys
 
 import numpy as np
 import pytest

@@ -3,7 +3,6 @@ import pytest
 import torch
 
 from dion_b200 import ops
-from dion_b200.ops import multi_tensor as mt
 
 SHAPES = [(768, 768), (50, 77), (3, 5), (1, 1), (4099,), (128, 96)]
 
