@@ -267,3 +267,75 @@ def test_muon_custom_newton_schulz_and_flatten():
     p.grad = torch.randn_like(p)
     opt.step()
     assert calls and calls[0][-2:] == (4, 30)
+
+
+def test_scheduler_admits_one_task_per_turn_and_bounds_tasks_in_flight():
+    from dion_b200.optim.common import Scheduler
+
+    log, alive, peak = [], set(), [0]
+
+    def make(i, yields):
+        def gen():
+            alive.add(i)
+            peak[0] = max(peak[0], len(alive))
+            log.append(("start", i))
+            for k in range(yields):
+                yield
+                log.append(("resume", i, k))
+            alive.discard(i)
+            log.append(("end", i))
+        return gen
+
+    Scheduler((make(i, 3) for i in range(6)), max_in_flight=2).run()
+    assert peak[0] == 2
+    assert [e[1] for e in log if e[0] == "start"] == list(range(6))      # tasks are created lazily, in order
+    assert sum(1 for e in log if e[0] == "end") == 6
+    # task 1 starts before task 0 has finished: their steps interleave
+    assert log.index(("start", 1)) < log.index(("end", 0))
+    # a task without any yield finishes inside its admission turn and never counts as in flight
+    log.clear()
+    Scheduler((make(i, 0) for i in range(3)), max_in_flight=1).run()
+    assert [e for e in log if e[0] == "end"] == [("end", 0), ("end", 1), ("end", 2)]
+    with pytest.raises(ValueError):
+        Scheduler(iter(()), max_in_flight=0)
+
+
+def test_muon_keller_jordan_single_rank_step(monkeypatch):
+    from dion_b200.optim.muon_reference import MuonKellerJordan, zeropower_fixed_coeffs
+
+    monkeypatch.setenv("WORLD_SIZE", "1")
+    monkeypatch.setenv("RANK", "0")
+    P = _params([(64, 32), (32, 64)])
+    before = [p.detach().clone() for p in P]
+    for p in P:
+        p.grad = torch.randn_like(p)
+    opt = MuonKellerJordan(P, lr=0.05, momentum=0.9, nesterov=True)
+    opt.step()
+    for p, b in zip(P, before):
+        g = p.grad
+        upd = g + 0.9 * g                       # momentum buffer starts at zero: buf = g, nesterov adds 0.9 * buf
+        u = zeropower_fixed_coeffs(upd, steps=5) * (g.size(0) / g.size(1)) ** 0.5
+        want = b - 0.05 * u.to(torch.bfloat16).to(b.dtype)
+        torch.testing.assert_close(p.detach(), want, rtol=0, atol=1e-6)
+        assert set(opt.state[p].keys()) == {"momentum_buffer"}
+
+
+def test_muon_state_dict_roundtrip_continues_identically():
+    P = _params()
+    opt = Muon([dict(params=P[:3]), dict(params=P[3:], algorithm="adamw", lr=0.01)], lr=0.02, nesterov=True)
+    grads = [[torch.randn_like(p) for p in P] for _ in range(4)]
+    for step in range(2):
+        for p, g in zip(P, grads[step]):
+            p.grad = g.clone()
+        opt.step()
+    Q = _clone(P)
+    opt2 = Muon([dict(params=Q[:3]), dict(params=Q[3:], algorithm="adamw", lr=0.01)], lr=0.02, nesterov=True)
+    opt2.load_state_dict(copy.deepcopy(opt.state_dict()))
+    for step in range(2, 4):
+        for p, q, g in zip(P, Q, grads[step]):
+            p.grad = g.clone()
+            q.grad = g.clone()
+        opt.step()
+        opt2.step()
+    for p, q in zip(P, Q):
+        torch.testing.assert_close(p, q, rtol=0, atol=0)
