@@ -335,7 +335,8 @@ class TrainStep:
     loss (a device tensor; reading it is the caller's synchronisation point)."""
 
     def __init__(self, model, raw_model, optimizer, lr_scheduler=None, grad_accum: int = 1,
-                 optimizer_owns_grad_sync: bool = False, fast_fsdp: bool = False, timers: Optional[PhaseTimers] = None):
+                 optimizer_owns_grad_sync: bool = False, fast_fsdp: bool = False, timers: Optional[PhaseTimers] = None,
+                 track_grad_norm: bool = False):
         from torch.distributed.fsdp import FSDPModule
         from torch.nn.parallel import DistributedDataParallel as DDP
 
@@ -346,6 +347,9 @@ class TrainStep:
         self.optimizer_owns_grad_sync = optimizer_owns_grad_sync
         self.fast_fsdp = fast_fsdp
         self.timers = timers or PhaseTimers(enabled=False)
+        # total gradient norm of the step (train.py:913-916), a device tensor; only when asked for
+        self.track_grad_norm = track_grad_norm
+        self.last_grad_norm: Optional[torch.Tensor] = None
 
     def __call__(self, batches) -> torch.Tensor:
         """`batches`: iterable of ``grad_accum`` (x, y) pairs."""
@@ -374,6 +378,9 @@ class TrainStep:
                 loss.backward()
         t.stop("fwd_bwd")
         t.start("optimizer")
+        if self.track_grad_norm:
+            self.last_grad_norm = torch.nn.utils.get_total_norm(
+                [p.grad for p in self.model.parameters() if p.grad is not None])
         self.optimizer.step()
         if self.lr_scheduler is not None:
             self.lr_scheduler.step()
@@ -507,7 +514,8 @@ def main(argv=None):
         tqdm = None
 
     step_fn = TrainStep(model, raw_model, optimizer, scheduler, grad_accum,
-                        optimizer_owns_grad_sync=hp.replicate_mesh_grad_sync, fast_fsdp=cli.fast_fsdp)
+                        optimizer_owns_grad_sync=hp.replicate_mesh_grad_sync, fast_fsdp=cli.fast_fsdp,
+                        track_grad_norm=use_wandb)
     device = next(raw_model.parameters()).device
     cuda = device.type == "cuda"
     sync = torch.cuda.synchronize if cuda else (lambda: None)
@@ -562,8 +570,10 @@ def main(argv=None):
                 heartbeat.beat(step)
             approx_time = training_time_ms + 1000 * (time.time() - t0)
             if _MASTER and use_wandb:
-                grads_norm = float("nan")
-                wandb.log({"train/loss": train_loss.item(), "train/grad_norm": grads_norm, "step": step,
+                grads_norm = step_fn.last_grad_norm
+                if hasattr(grads_norm, "full_tensor"):
+                    grads_norm = grads_norm.full_tensor()
+                wandb.log({"train/loss": train_loss.item(), "train/grad_norm": float(grads_norm), "step": step,
                            "time/training_time_ms": approx_time})
             if _MASTER and cli.debug:
                 print0(f"Step {step}: train_loss={train_loss.item():.4f}")

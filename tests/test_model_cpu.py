@@ -128,3 +128,19 @@ def test_training_reduces_loss(optimizer):
     losses = [float(step([(x[:2], y[:2]), (x[2:], y[2:])])) for _ in range(8)]
     assert losses[-1] < losses[0] - 0.1, losses
     assert all(p.grad is None for p in m.parameters())
+
+
+def test_train_step_reports_total_gradient_norm():
+    m = _model()
+    hp = Hyperparameters(model_dim=64, n_layer=2, n_head=4, sequence_length=64, optimizer="adamw", lr=0.0,
+                         num_iterations=10)
+    opt = init_optimizer(m, None, None, hp)
+    step = TrainStep(m, m, opt, None, grad_accum=1, track_grad_norm=True)
+    torch.manual_seed(2)
+    x = torch.randint(0, 512, (2, 64))
+    y = torch.randint(0, 512, (2, 64))
+    step([(x, y)])
+    m(x, y).backward()      # lr = 0: the same gradients again
+    want = torch.sqrt(sum((p.grad.float() ** 2).sum() for p in m.parameters()))
+    torch.testing.assert_close(step.last_grad_norm, want, rtol=1e-5, atol=1e-6)
+    assert TrainStep(m, m, opt, None).last_grad_norm is None
