@@ -77,3 +77,19 @@ def test_mesh_training_with_sequence_parallel_tp(tmp_path, shards):
                "--sequence_parallel")
     v = _val_losses(out)
     assert set(v) == {0, 6, 8} and v[8] < v[0], v
+
+
+def test_mesh_benchmark_script_smoke():
+    import json
+
+    env = dict(os.environ)
+    env.update(TORCHDYNAMO_DISABLE="1", OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES="")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(29950 + os.getpid() % 40),
+           os.path.join(ROOT, "benchmark", "benchmark_train_mesh.py"), "--tiny", "--optimizer", "dion", "--dp", "1",
+           "--fs", "1", "--tp", "2", "--sequence_parallel", "--device_batch", "2", "--steps", "2", "--warmup", "3"]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert res.returncode == 0, (res.stdout + res.stderr)[-3000:]
+    line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
+    out = json.loads(line)
+    assert out["n_gpus"] == 2 and out["value"] > 0 and out["config"]["parallelism"].startswith("dp1 x fs1 x tp2")
