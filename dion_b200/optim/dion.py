@@ -37,7 +37,7 @@ from .. import ops
 from ..ops import nn as nn_ops
 from ..parallel import symm
 from .common import Scheduler, all_reduce_, group_of, group_size, to_local
-from .orthogonalize import orthonormalize_many
+from .orthogonalize import SHARD_WORK, orthonormalize_many
 
 try:  # pragma: no cover - depends on the torch build
     from torch.distributed.tensor.placement_types import _StridedShard
@@ -127,7 +127,7 @@ class _PackedClass:
 class _ClassWork:
     """Per-step working set of one parameter class between the two phases of the update."""
 
-    __slots__ = ("cls", "params", "group", "replicate", "outer", "inner", "sync", "compressed", "A", "Qm", "P")
+    __slots__ = ("cls", "params", "group", "replicate", "outer", "inner", "sync", "compressed", "A", "Qm", "P", "P_total")
 
 
 class Dion(Optimizer):
@@ -202,6 +202,8 @@ class Dion(Optimizer):
         self._inner_shard_ranks = (dist.get_process_group_ranks(inner_shard_mesh.get_group())
                                    if inner_shard_mesh is not None else None)
         self._mixed_precision_config = mixed_precision_config or DionMixedPrecisionConfig()
+        # how often P left a reduction as this rank's share of the batch (reduce-scatter instead of all-reduce)
+        self.p_reduce_scatters = 0
         # Q factors are drawn from this generator so that every rank draws the same values
         self._q_seed = 0x0D10
 
@@ -259,7 +261,8 @@ class Dion(Optimizer):
             # P is the same on every rank of the outer (or else the replicate) group by now: each rank
             # orthonormalises its share of every batch and the shares are all-gathered
             ortho = orthonormalize_many([w.P for w in work], [w.inner for w in work],
-                                        shard_groups=[w.outer if w.outer is not None else w.replicate for w in work])
+                                        shard_groups=[w.outer if w.outer is not None else w.replicate for w in work],
+                                        totals=[w.P_total for w in work])
             for w, P in zip(work, ortho):
                 w.P = P
             Scheduler((lambda w=w: self._dion_phase2(w) for w in work), max_in_flight=3).run()
@@ -602,16 +605,36 @@ class Dion(Optimizer):
         # the GEMM writes straight into the symmetric arena of the group that reduces P first
         P = symm.empty(first, (B, a_loc, w.Qm.shape[2]), torch.float32, M.device)
         ops.gemm(w.A, w.Qm, out=P)
-        if w.outer is not None:
-            wait = self._reduce(P, w.outer, average=False)
-            if wait is not None:
-                yield
-                wait()
-        if w.compressed:
-            wait = self._reduce(P, w.replicate, average=True)
-            if wait is not None:
-                yield
-                wait()
+        # The ranks of the first reducing group are the ones that divide the orthonormalisation among
+        # themselves (see step()).  When the batch splits evenly, a reduce-scatter leaves every rank with
+        # exactly the matrices it is going to orthonormalise (dion/dion.py:806-815, 925-929) instead of an
+        # all-reduce of which it would drop all but its share.
+        share_world = dist.get_world_size(first) if first is not None else 1
+        w.P_total = None
+        if (SHARD_WORK and first is not None and w.inner is None and B > 1 and B % share_world == 0
+                and (P[0].numel() * 4) % 16 == 0):
+            w.P_total = B
+            self.p_reduce_scatters += 1
+            share = symm.empty(w.replicate if (w.outer is not None and w.compressed) else None,
+                               (B // share_world, a_loc, w.Qm.shape[2]), torch.float32, M.device)
+            symm.reduce_scatter(P, first, average=w.outer is None, out=share)
+            P = share
+            if w.outer is not None and w.compressed:
+                wait = self._reduce(P, w.replicate, average=True)
+                if wait is not None:
+                    yield
+                    wait()
+        else:
+            if w.outer is not None:
+                wait = self._reduce(P, w.outer, average=False)
+                if wait is not None:
+                    yield
+                    wait()
+            if w.compressed:
+                wait = self._reduce(P, w.replicate, average=True)
+                if wait is not None:
+                    yield
+                    wait()
         w.P = P  # 4. is the joint orthonormalisation in step()
 
     def _dion_phase2(self, w: "_ClassWork") -> Generator[None, None, None]:
@@ -680,7 +703,7 @@ class Dion(Optimizer):
             Qs.copy_(Qn[:, :, i0:i0 + r_loc])
         else:
             Qs.copy_(Qn)
-        w.A = w.Qm = w.P = None
+        w.A = w.Qm = w.P = w.P_total = None
 
     def _apply_update(self, cls: _PackedClass, params: List[Tensor], X: List[Tensor], a_op: Tensor, b_op: Tensor,
                       alpha: float, beta: float) -> None:

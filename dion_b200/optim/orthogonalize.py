@@ -151,25 +151,31 @@ def _gather_shares(part: Tensor, group, B: int) -> Tensor:
 
 
 def orthonormalize_many(Ps, row_groups=None, refine_passes: int = 2,
-                        pivot_floor: float = ops.linalg.DEFAULT_PIVOT_FLOOR, shard_groups=None):
+                        pivot_floor: float = ops.linalg.DEFAULT_PIVOT_FLOOR, shard_groups=None, totals=None):
     """Orthonormalise several batches ``P_i: [B_i, a_i, r_i]`` at once.  All Gram matrices of
     the same rank are factorised by a single launch of the Cholesky kernel (one CTA per
     matrix), whatever their row counts; the remaining loss of orthogonality is removed by
     `refine_passes` triangular Newton corrections, which are plain tensor-core GEMMs.
     ``row_groups[i]`` is the process group sharding the rows of ``P_i`` (or None);
-    ``shard_groups[i]`` a group on whose ranks ``P_i`` is identical, which then splits the batch."""
+    ``shard_groups[i]`` a group on whose ranks ``P_i`` is identical, which then splits the batch.
+    ``totals[i]``, when not None, says that ``P_i`` already is this rank's share (as
+    :func:`_my_share` would cut it) of a batch of that many matrices; the result is the whole batch."""
     n = len(Ps)
     if row_groups is None:
         row_groups = [None] * n
+    if totals is None:
+        totals = [None] * n
     if shard_groups is None or not SHARD_WORK:
+        assert all(t is None for t in totals), "a batch that arrives split needs its group"
         shard_groups = [None] * n
-    shard_groups = [g if (g is not None and dist.get_world_size(g) > 1 and P.shape[0] > 1 and rg is None) else None
-                    for g, P, rg in zip(shard_groups, Ps, row_groups)]
+    shard_groups = [g if (t is not None or (g is not None and dist.get_world_size(g) > 1 and P.shape[0] > 1 and rg is None))
+                    else None for g, P, rg, t in zip(shard_groups, Ps, row_groups, totals)]
     if any(g is not None for g in shard_groups):
-        parts = [P.float() if g is None else _my_share(P.float(), g) for P, g in zip(Ps, shard_groups)]
+        parts = [P.float() if (g is None or t is not None) else _my_share(P.float(), g)
+                 for P, g, t in zip(Ps, shard_groups, totals)]
         outs = orthonormalize_many(parts, row_groups, refine_passes, pivot_floor)
-        return [X.to(P.dtype) if g is None else _gather_shares(X, g, P.shape[0]).to(P.dtype)
-                for X, P, g in zip(outs, Ps, shard_groups)]
+        return [X.to(P.dtype) if g is None else _gather_shares(X, g, P.shape[0] if t is None else t).to(P.dtype)
+                for X, P, g, t in zip(outs, Ps, shard_groups, totals)]
     dtypes = [P.dtype for P in Ps]
     Xs = [P.float() for P in Ps]
     Gs = [gram(X, g) for X, g in zip(Xs, row_groups)]

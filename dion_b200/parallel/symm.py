@@ -30,6 +30,7 @@ from ..ops import runtime
 _FLAG_BYTES = 4096
 _ALIGN = 256
 _MIN_ARENA = 8 << 20
+_RS_WAIT_NS = int(1.5e9)  # bound of the reduce-scatter kernel's waits for its peers
 
 
 def _enabled() -> bool:
@@ -109,6 +110,15 @@ class SymmetricArena:
         torch.ops.dion_b200.symm_all_reduce(t, self.peers, 0, off, self.mc_base,
                                             (1.0 / self.world) if average else 1.0, self.rank, self.epoch,
                                             self.counter, runtime.status_tensor(self.device))
+
+    def reduce_scatter(self, t: torch.Tensor, off: int, out: torch.Tensor, average: bool) -> None:
+        """out = slice `rank` of the sum (mean) of `t` over the group: every rank reads its slice from all
+        peers (or lets the switch add them up, `multimem.ld_reduce`); the kernel retires once every peer
+        has finished reading this rank's `t`."""
+        self.epoch += 1
+        torch.ops.dion_b200.symm_reduce_scatter(t.view(-1), out.view(-1), self.peers, 0, off, self.mc_base,
+                                                (1.0 / self.world) if average else 1.0, self.rank, self.epoch, 0, 1,
+                                                self.counter, runtime.status_tensor(self.device), _RS_WAIT_NS)
 
     def reduce_into(self, src: torch.Tensor, off: int, dst: torch.Tensor, scale: float = 1.0, beta: float = 0.0) -> None:
         self.epoch += 1
@@ -201,6 +211,32 @@ def all_reduce(t: torch.Tensor, group: Optional[dist.ProcessGroup], average: boo
         dist.all_reduce(t, group=group)
         if average:
             t.div_(world)
+
+
+def reduce_scatter(t: torch.Tensor, group: dist.ProcessGroup, average: bool = False,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Slice `rank` of the sum (or mean) of the flat `t` over `group`, blocking in stream order;
+    ``t.numel()`` must be a multiple of the group size.  Buffers in the group's arena go through the
+    in-tree kernel, anything else through the process group."""
+    world = dist.get_world_size(group)
+    n = t.numel() // world
+    if out is None:
+        out = torch.empty(n, dtype=t.dtype, device=t.device)
+    arena = _arenas.get(_key(group)) if t.is_cuda else None
+    if arena is not None:
+        off = arena.offset_of(t)
+        if (off is not None and t.is_contiguous() and out.is_contiguous() and t.dtype in (torch.float32, torch.bfloat16)
+                and (n * t.element_size()) % 16 == 0 and out.data_ptr() % 16 == 0):
+            arena.reduce_scatter(t, off, out, average)
+            return out
+    flat = t.reshape(-1)
+    if average and t.is_cuda and dist.get_backend(group) == "nccl":
+        dist.reduce_scatter_tensor(out.view(-1), flat, op=dist.ReduceOp.AVG, group=group)
+    else:
+        dist.reduce_scatter_tensor(out.view(-1), flat, group=group)
+        if average:
+            out.div_(world)
+    return out
 
 
 def arena_for(group: Optional[dist.ProcessGroup]) -> Optional[SymmetricArena]:

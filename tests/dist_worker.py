@@ -238,6 +238,10 @@ def case_fsdp():
             # gradient differences flip whole entries by 2 * lr
             loose = "wte" in n1 or "lm_head" in n1
             check(f"fsdp {name} {n1}", _full(p1.detach()), p2.detach(), 6e-2 if (CUDA or loose) else 5e-3)
+        if name == "dion":
+            # every class of the 2-layer model has an even number of matrices: P leaves its reduction
+            # over the shard group as this rank's share (reduce-scatter), not as the whole batch
+            assert opt.p_reduce_scatters > 0, "P was all-reduced although the batches split evenly"
         if name == "muon":
             # the momentum is linear in the gradients, so it pins down that every path (library
             # all-to-all or peer stores from the momentum kernel) applies it exactly once per step
