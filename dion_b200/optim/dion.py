@@ -262,7 +262,8 @@ class Dion(Optimizer):
             # orthonormalises its share of every batch and the shares are all-gathered
             ortho = orthonormalize_many([w.P for w in work], [w.inner for w in work],
                                         shard_groups=[w.outer if w.outer is not None else w.replicate for w in work],
-                                        totals=[w.P_total for w in work])
+                                        totals=[w.P_total for w in work],
+                                        out_dtypes=[w.cls.M.dtype for w in work])  # what phase 2 multiplies with
             for w, P in zip(work, ortho):
                 w.P = P
             Scheduler((lambda w=w: self._dion_phase2(w) for w in work), max_in_flight=3).run()

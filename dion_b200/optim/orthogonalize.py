@@ -151,7 +151,8 @@ def _gather_shares(part: Tensor, group, B: int) -> Tensor:
 
 
 def orthonormalize_many(Ps, row_groups=None, refine_passes: int = 2,
-                        pivot_floor: float = ops.linalg.DEFAULT_PIVOT_FLOOR, shard_groups=None, totals=None):
+                        pivot_floor: float = ops.linalg.DEFAULT_PIVOT_FLOOR, shard_groups=None, totals=None,
+                        out_dtypes=None):
     """Orthonormalise several batches ``P_i: [B_i, a_i, r_i]`` at once.  All Gram matrices of
     the same rank are factorised by a single launch of the Cholesky kernel (one CTA per
     matrix), whatever their row counts; the remaining loss of orthogonality is removed by
@@ -159,8 +160,12 @@ def orthonormalize_many(Ps, row_groups=None, refine_passes: int = 2,
     ``row_groups[i]`` is the process group sharding the rows of ``P_i`` (or None);
     ``shard_groups[i]`` a group on whose ranks ``P_i`` is identical, which then splits the batch.
     ``totals[i]``, when not None, says that ``P_i`` already is this rank's share (as
-    :func:`_my_share` would cut it) of a batch of that many matrices; the result is the whole batch."""
+    :func:`_my_share` would cut it) of a batch of that many matrices; the result is the whole batch.
+    ``out_dtypes[i]`` is the dtype of result i (default: the input's); shares are converted before they
+    are exchanged, so a bf16 consumer halves the all-gather."""
     n = len(Ps)
+    if out_dtypes is None:
+        out_dtypes = [P.dtype for P in Ps]
     if row_groups is None:
         row_groups = [None] * n
     if totals is None:
@@ -174,9 +179,9 @@ def orthonormalize_many(Ps, row_groups=None, refine_passes: int = 2,
         parts = [P.float() if (g is None or t is not None) else _my_share(P.float(), g)
                  for P, g, t in zip(Ps, shard_groups, totals)]
         outs = orthonormalize_many(parts, row_groups, refine_passes, pivot_floor)
-        return [X.to(P.dtype) if g is None else _gather_shares(X, g, P.shape[0] if t is None else t).to(P.dtype)
-                for X, P, g, t in zip(outs, Ps, shard_groups, totals)]
-    dtypes = [P.dtype for P in Ps]
+        return [X.to(dt) if g is None else _gather_shares(X.to(dt), g, P.shape[0] if t is None else t)
+                for X, P, g, t, dt in zip(outs, Ps, shard_groups, totals, out_dtypes)]
+    dtypes = out_dtypes
     Xs = [P.float() for P in Ps]
     Gs = [gram(X, g) for X, g in zip(Xs, row_groups)]
     for G, g in zip(Gs, row_groups):
