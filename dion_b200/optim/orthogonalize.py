@@ -129,24 +129,63 @@ def _my_share(X: Tensor, group) -> Tensor:
     return part
 
 
+class _Gatherer:
+    """All-gather callable of one group (None: the process group's own) and whether its first call,
+    which is compared against the process group's result, has happened."""
+
+    def __init__(self, fn):
+        self.fn = fn
+        self.checked = False
+
+
+def _exchange(out: Tensor, part: Tensor, group, state: _Gatherer) -> None:
+    """out = all-gather of `part` over `group`.  The first call through an in-tree kernel also runs the
+    process group's all-gather and compares: if the kernel reports a failure or any rank sees a
+    difference, every rank of the group switches to the process group for good."""
+    if state.fn is None:
+        dist.all_gather_into_tensor(out, part, group=group)
+        return
+    if state.checked:
+        state.fn(out.view(-1), part.view(-1), group)
+        return
+    ref = torch.empty_like(out)
+    dist.all_gather_into_tensor(ref, part, group=group)
+    try:
+        state.fn(out.view(-1), part.view(-1), group)
+        if part.is_cuda:
+            from ..ops import runtime
+
+            runtime.check_status(part.device)
+        ok = torch.equal(out, ref)
+    except Exception as e:  # a kernel-side failure (status word) or a launch error
+        ok = False
+        print(f"[dion_b200] rank {dist.get_rank()}: in-tree all-gather failed on first use ({type(e).__name__}: {e})")
+    verdict = torch.tensor([1 if ok else 0], dtype=torch.int32, device=part.device)
+    dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=group)
+    state.checked = True
+    if int(verdict.item()) == 0:
+        state.fn = None
+        out.copy_(ref)
+        if dist.get_rank() == 0:
+            print("[dion_b200] the in-tree all-gather did not reproduce the process group's on first use; "
+                  "using the process group for the orthonormal factors")
+
+
 def _gather_shares(part: Tensor, group, B: int) -> Tensor:
     """Inverse of :func:`_my_share`: all-gather the shares and drop the padding."""
     world = dist.get_world_size(group)
     part = part.contiguous()
     out = part.new_empty((world * part.shape[0],) + tuple(part.shape[1:]))
-    gather = None
-    if part.is_cuda:
-        from ..parallel import fsdp_comm
+    key = symm._key(group)
+    if key not in _gatherers:
+        fn = None
+        if part.is_cuda:
+            from ..parallel import fsdp_comm
 
-        key = symm._key(group)
-        if key not in _gatherers:
-            _gatherers[key] = (fsdp_comm.SymmAllGather(group, part.device)
-                               if fsdp_comm._usable(group, part.device) else None)
-        gather = _gatherers[key]
-    if gather is not None:
-        gather(out.view(-1), part.view(-1), group)  # in-tree kernel over symmetric memory, or the group's own
-    else:
-        dist.all_gather_into_tensor(out, part, group=group)
+            if fsdp_comm._usable(group, part.device):
+                fn = fsdp_comm.SymmAllGather(group, part.device)  # falls back per call where it does not apply
+        _gatherers[key] = _Gatherer(fn)
+    _exchange(out, part, group, _gatherers[key])
     return out[:B]
 
 

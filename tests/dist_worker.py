@@ -119,6 +119,27 @@ def _check_sharded_orthonormalisation():
         dist.broadcast(ref, src=0)
         if Ps[i].shape[0] > 1:  # gathered: every rank received the same bytes
             assert torch.equal(a, ref), "ranks hold different orthonormal factors"
+    # first-use check of an all-gather kernel: one that works is kept, one that returns something else
+    # than the process group (here: on one rank only) is dropped by every rank, and the result is right
+    from dion_b200.optim import orthogonalize as O
+
+    def good(out, inp, group):
+        dist.all_gather_into_tensor(out, inp, group=group)
+
+    def bad(out, inp, group):
+        dist.all_gather_into_tensor(out, inp, group=group)
+        if RANK == WORLD - 1:
+            out[:1] += 1.0
+
+    part = torch.full((4, 3, 2), float(RANK), device=DEV)
+    want = torch.cat([torch.full((4, 3, 2), float(r), device=DEV) for r in range(WORLD)])
+    for fn, kept in ((good, True), (bad, False)):
+        state = O._Gatherer(fn)
+        for _ in range(2):
+            out = torch.empty(4 * WORLD, 3, 2, device=DEV)
+            O._exchange(out, part, g, state)
+            assert torch.equal(out, want)
+        assert state.checked and (state.fn is not None) == kept
 
 
 def case_dion_ddp():
