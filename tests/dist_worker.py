@@ -429,7 +429,8 @@ def case_gemm_gather():
     g = dist.group.WORLD
     TP._FUSED_GATHER = True
     try:
-        for rep, (R, Kd, N) in enumerate([(256, 64, 96), (1024, 768, 1536), (4096, 768, 2304), (1024, 768, 1536)]):
+        for rep, (R, Kd, N) in enumerate([(256, 64, 96), (1024, 768, 1536), (4096, 768, 2304), (2048, 1024, 4096), (1024, 768, 1536)]):
+            # 128 x 128 tiles, 128 x 256 tiles, CTA pairs with 256 x 256 tiles (K >= 1024), and a repeat
             gen = torch.Generator(device="cpu").manual_seed(100 * rep + RANK)
             x = torch.randn(R, Kd, generator=gen).to(DEV).to(torch.bfloat16)
             w = torch.randn(N, Kd, generator=torch.Generator().manual_seed(7 + rep)).mul_(0.05).to(DEV).to(torch.bfloat16)
@@ -442,7 +443,7 @@ def case_gemm_gather():
             # the unfused all-gather shares the staging slots and epochs with the fused kernel
             check("gather_rows after gemm_gather", TP._gather_rows(x, g), ref_xg, 1e-6)
         calls = [c.fused_gathers for c in TP._tp_comms.values()]
-        assert calls and all(c >= 4 for c in calls), f"the all-gather did not run inside the GEMM: {calls}"
+        assert calls and all(c >= 5 for c in calls), f"the all-gather did not run inside the GEMM: {calls}"
     finally:
         TP._FUSED_GATHER = False
 
