@@ -18,6 +18,23 @@ using at::Tensor;
 std::atomic<long long> g_launches{0};
 int64_t launch_count() { return (int64_t)g_launches.load(); }
 
+// host only: the tiling and copy schedule the all-gather GEMM would use (empty if the shapes do not fit)
+std::vector<int64_t> gemm_gather_plan(int64_t M, int64_t N, int64_t K, int64_t rows, int64_t world, int64_t rank) {
+  dion::GemmArgs g;
+  g.ab_dtype = dion::kBF16;
+  g.M = (int)M;
+  g.N = (int)N;
+  g.K = (int)K;
+  g.lda = K;
+  g.ldb = K;
+  g.gather.world = (int)world;
+  g.gather.rank = (int)rank;
+  g.gather.rows = (int)rows;
+  int out[8];
+  if (!dion::gemm_gather_plan(g, out)) return {};
+  return std::vector<int64_t>(out, out + 8);
+}
+
 int gemm_dtype(const Tensor& t, const char* what) {
   if (t.scalar_type() == at::kBFloat16) return dion::kBF16;
   if (t.scalar_type() == at::kFloat) return dion::kF32;
@@ -777,6 +794,7 @@ TORCH_LIBRARY(dion_b200, m) {
       "Tensor(c!) dk, Tensor(d!) dv, float scale, Tensor(e!) status) -> ()");
   m.def("refine_prep(Tensor G, Tensor(a!) C, Tensor(b!) d) -> ()");
   m.def("launch_count() -> int", &launch_count);
+  m.def("gemm_gather_plan(int M, int N, int K, int rows, int world, int rank) -> int[]", &gemm_gather_plan);
 }
 
 TORCH_LIBRARY_IMPL(dion_b200, CUDA, m) {

@@ -980,6 +980,88 @@ cudaError_t launch_major(const GemmArgs& a, const KernelParams& kp, int bn, bool
   return launch_bn<kTf32, kMajorMN, kMajorMN>(a, kp, bn, pair, s);
 }
 
+struct Tiling {
+  int bn;
+  bool pair;
+  int tile_m;
+};
+
+// Tile width, CTA pairing and tile height for a problem (the heuristics of gemm_launch).
+Tiling choose_tiling(const GemmArgs& a) {
+  int bn = a.block_n;
+  if (a.symmetric) {
+    bn = 128;
+  } else if (bn != 64 && bn != 128 && bn != 256) {
+    // widest tile that still gives every SM work; narrow N picks a narrow tile
+    const long long tm = (a.M + kBlockM - 1) / kBlockM;
+    const long long sms = num_sms();
+    bn = 256;
+    if (a.N <= 64) {
+      bn = 64;
+    } else if (a.N <= 128) {
+      bn = 128;
+    } else {
+      const long long t256 = tm * ((a.N + 255) / 256) * a.batch * a.split_k;
+      if (t256 < sms) bn = 128;
+      if ((a.N % 256) != 0 && (a.N % 256) <= 128 && a.N < 1024) bn = 128;
+    }
+  }
+
+  // CTA pairs (256-row tiles, half the B traffic per CTA) for GEMMs with enough 256 x 256 tiles to
+  // keep every pair busy; DION_B200_GEMM_PAIR=0 turns them off, a.pair = 1 / -1 forces / forbids.
+  static const int pair_env = [] {
+    const char* e = getenv("DION_B200_GEMM_PAIR");
+    return (e && e[0] == '0') ? 0 : 1;
+  }();
+  bool pair = false;
+  if (a.pair > 0 && !a.symmetric) bn = 256;
+  if (!a.symmetric && bn == 256 && a.pair >= 0 && (pair_env || a.pair > 0)) {
+    const long long t = (long long)((a.M + 255) / 256) * ((a.N + 255) / 256) * a.batch * a.split_k;
+    // short-K tiles are bound by the epilogue, which a pair does not speed up
+    pair = a.pair > 0 || (t >= 2 * (num_sms() / 2) && a.K / a.split_k >= 1024);
+  }
+
+  if (a.gather.world > 0 && bn == 64) bn = 128;  // the all-gather variant is built for 128- and 256-wide tiles
+  Tiling t;
+  t.bn = bn;
+  t.pair = pair;
+  t.tile_m = pair ? 2 * kBlockM : kBlockM;
+  return t;
+}
+
+// Parameters of the all-gather variant for a problem and its tiling; false if the shapes do not fit.
+bool plan_gather(const GemmArgs& a, const Tiling& tl, GatherParams* g) {
+  const GemmArgs::Gather& ga = a.gather;
+  const bool tf32 = a.ab_dtype == kF32;
+  const bool shapes_ok = !tf32 && a.a_major == kMajorK && a.b_major == kMajorK && a.batch == 1 && a.split_k == 1 &&
+                         !a.symmetric && a.lda == a.K && ga.world <= kGatherMaxPeers && ga.rank >= 0 &&
+                         ga.rank < ga.world && ga.rows > 0 && (long long)ga.rows * ga.world == a.M &&
+                         ga.rows % tl.tile_m == 0 && (a.K * 2) % 16 == 0;
+  if (!shapes_ok) return false;
+  memset(g, 0, sizeof(*g));
+  g->world = ga.world;
+  g->rank = ga.rank;
+  g->channel = ga.channel;
+  g->rows = ga.rows;
+  int per_chunk = 8;  // tiles per readiness counter: few counters, but work can start early
+  while (per_chunk > 1 && (ga.rows % (tl.tile_m * per_chunk) != 0 || ga.rows / (tl.tile_m * per_chunk) < 4)) per_chunk /= 2;
+  g->chunk_rows = tl.tile_m * per_chunk;
+  g->m_rot = ga.rank * (ga.rows / tl.tile_m);
+  g->epoch = ga.epoch;
+  g->row_bytes = (long long)a.K * 2;
+  g->flag_off = ga.flag_off;
+  g->slot_off = ga.slot_off;
+  g->in = reinterpret_cast<const char*>(ga.in);
+  g->out = reinterpret_cast<char*>(const_cast<void*>(a.A));
+  g->units_per_chunk = (int)(((long long)g->chunk_rows * g->row_bytes + kGatherUnitBytes - 1) / kGatherUnitBytes);
+  for (int i = 0; i < kGatherMaxPeers; ++i) g->peers[i] = ga.peers[i];
+  g->next_unit = ga.counters;
+  g->staged = ga.counters ? ga.counters + 1 : nullptr;
+  g->ready = ga.counters ? ga.counters + 2 : nullptr;
+  g->budget_ns = (unsigned long long)(ga.budget_ns > 0 ? ga.budget_ns : (long long)kWaitBudgetNs);
+  return true;
+}
+
 bool aligned16(const void* p, long long ld, int es) {
   return (reinterpret_cast<uintptr_t>(p) & 15) == 0 && ((ld * es) & 15) == 0;
 }
@@ -987,6 +1069,21 @@ bool aligned16(const void* p, long long ld, int es) {
 }  // namespace
 
 const char* gemm_last_error() { return g_last_error.c_str(); }
+
+bool gemm_gather_plan(const GemmArgs& a, int (&out)[8]) {
+  const Tiling tl = choose_tiling(a);
+  GatherParams g;
+  if (!plan_gather(a, tl, &g)) return false;
+  out[0] = tl.tile_m;
+  out[1] = tl.bn;
+  out[2] = tl.pair ? 1 : 0;
+  out[3] = g.chunk_rows;
+  out[4] = g.units_per_chunk;
+  out[5] = g.m_rot;
+  out[6] = (a.M + tl.tile_m - 1) / tl.tile_m;
+  out[7] = (a.N + tl.bn - 1) / tl.bn;
+  return true;
+}
 
 cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   g_last_error.clear();
@@ -1022,39 +1119,10 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   const int es = tf32 ? 4 : 2;
   const int bk = 128 / es;
 
-  int bn = a.block_n;
-  if (a.symmetric) {
-    bn = 128;
-  } else if (bn != 64 && bn != 128 && bn != 256) {
-    // widest tile that still gives every SM work; narrow N picks a narrow tile
-    const long long tm = (a.M + kBlockM - 1) / kBlockM;
-    const long long sms = num_sms();
-    bn = 256;
-    if (a.N <= 64) {
-      bn = 64;
-    } else if (a.N <= 128) {
-      bn = 128;
-    } else {
-      const long long t256 = tm * ((a.N + 255) / 256) * a.batch * a.split_k;
-      if (t256 < sms) bn = 128;
-      if ((a.N % 256) != 0 && (a.N % 256) <= 128 && a.N < 1024) bn = 128;
-    }
-  }
-
-  // CTA pairs (256-row tiles, half the B traffic per CTA) for GEMMs with enough 256 x 256 tiles to
-  // keep every pair busy; DION_B200_GEMM_PAIR=0 turns them off, a.pair = 1 / -1 forces / forbids.
-  static const int pair_env = [] {
-    const char* e = getenv("DION_B200_GEMM_PAIR");
-    return (e && e[0] == '0') ? 0 : 1;
-  }();
-  bool pair = false;
-  if (a.pair > 0 && !a.symmetric) bn = 256;
-  if (!a.symmetric && bn == 256 && a.pair >= 0 && (pair_env || a.pair > 0)) {
-    const long long t = (long long)((a.M + 255) / 256) * ((a.N + 255) / 256) * a.batch * a.split_k;
-    // short-K tiles are bound by the epilogue, which a pair does not speed up
-    pair = a.pair > 0 || (t >= 2 * (num_sms() / 2) && a.K / a.split_k >= 1024);
-  }
-  const int tile_m = pair ? 2 * kBlockM : kBlockM;
+  const Tiling tiling = choose_tiling(a);
+  const int bn = tiling.bn;
+  const bool pair = tiling.pair;
+  const int tile_m = tiling.tile_m;
 
   KernelParams kp;
   memset(&kp, 0, sizeof(kp));
@@ -1116,43 +1184,18 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   if (a.gather.world > 0) {
     // operand A is gathered from the group inside the kernel
     const GemmArgs::Gather& ga = a.gather;
-    const bool shapes_ok = !tf32 && a.a_major == kMajorK && a.b_major == kMajorK && a.batch == 1 && a.split_k == 1 &&
-                           !a.symmetric && a.lda == a.K && ga.world <= kGatherMaxPeers && ga.rank >= 0 &&
-                           ga.rank < ga.world && ga.rows > 0 && (long long)ga.rows * ga.world == a.M &&
-                           ga.rows % tile_m == 0 && ga.in && ga.counters &&
-                           (reinterpret_cast<uintptr_t>(ga.in) & 15) == 0 && (ga.slot_off & 15) == 0;
-    if (!shapes_ok) {
+    if (!plan_gather(a, tiling, &kp.g) || !ga.in || !ga.counters || (reinterpret_cast<uintptr_t>(ga.in) & 15) != 0 ||
+        (ga.slot_off & 15) != 0) {
       g_last_error = "all-gather variant: bf16 K-major operands, one batch, contiguous A of world * rows rows with "
                      "rows a multiple of the tile height";
       return cudaErrorInvalidValue;
     }
-    if (bn == 64) bn = 128;
-    GatherParams& g = kp.g;
-    g.world = ga.world;
-    g.rank = ga.rank;
-    g.channel = ga.channel;
-    g.rows = ga.rows;
-    int per_chunk = 8;  // tiles per readiness counter: few counters, but work can start early
-    while (per_chunk > 1 && (ga.rows % (tile_m * per_chunk) != 0 || ga.rows / (tile_m * per_chunk) < 4)) per_chunk /= 2;
-    g.chunk_rows = tile_m * per_chunk;
-    g.m_rot = ga.rank * (ga.rows / tile_m);
-    g.epoch = ga.epoch;
-    g.row_bytes = (long long)a.K * 2;
-    g.flag_off = ga.flag_off;
-    g.slot_off = ga.slot_off;
-    g.in = reinterpret_cast<const char*>(ga.in);
-    g.out = reinterpret_cast<char*>(const_cast<void*>(a.A));
-    for (int i = 0; i < kGatherMaxPeers; ++i) g.peers[i] = ga.peers[i];
-    g.units_per_chunk = (int)(((long long)g.chunk_rows * g.row_bytes + kGatherUnitBytes - 1) / kGatherUnitBytes);
-    g.next_unit = ga.counters;
-    g.staged = ga.counters + 1;
-    g.ready = ga.counters + 2;
-    g.budget_ns = (unsigned long long)(ga.budget_ns > 0 ? ga.budget_ns : (long long)kWaitBudgetNs);
-    if (2 + a.M / g.chunk_rows > ga.counter_words) {
+    const int words = 2 + a.M / kp.g.chunk_rows;
+    if (words > ga.counter_words) {
       g_last_error = "all-gather variant: counter buffer too small";
       return cudaErrorInvalidValue;
     }
-    cudaError_t e = cudaMemsetAsync(ga.counters, 0, sizeof(unsigned) * (size_t)(2 + a.M / g.chunk_rows), stream);
+    cudaError_t e = cudaMemsetAsync(ga.counters, 0, sizeof(unsigned) * (size_t)words, stream);
     if (e != cudaSuccess) return e;
     if (pair) return launch_cfg<false, kMajorK, kMajorK, 256, true, true>(a, kp, stream);
     if (bn == 128) return launch_cfg<false, kMajorK, kMajorK, 128, false, true>(a, kp, stream);

@@ -107,4 +107,9 @@ struct GemmArgs {
 cudaError_t gemm_launch(const GemmArgs& args, cudaStream_t stream);
 const char* gemm_last_error();
 
+// Host only, no launch: what the all-gather variant would do for `args` (sizes, majors and the
+// `gather` fields world / rank / rows are read).  out = {tile rows, tile columns, CTA pairs (0 / 1),
+// rows per readiness counter, copy units per counter, first m-tile of the schedule, m-tiles, n-tiles}.
+bool gemm_gather_plan(const GemmArgs& args, int (&out)[8]);
+
 }  // namespace dion

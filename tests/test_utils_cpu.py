@@ -50,3 +50,53 @@ def test_phase_timers_are_inert_without_a_gpu():
     t.start("a")
     t.stop("a")
     assert t.summary() == {} and t.max_over_ranks() == {}
+
+
+@pytest.mark.parametrize("M,N,K,rows,world", [(512, 96, 64, 256, 2), (2048, 1536, 768, 1024, 2), (8192, 2304, 768, 4096, 2),
+                                              (4096, 4096, 1024, 2048, 2), (32768, 1536, 768, 16384, 2),
+                                              (65536, 384, 768, 8192, 8), (32768, 768, 768, 4096, 8)])
+def test_gather_gemm_plan_invariants(M, N, K, rows, world):
+    """Host-side plan of the GEMM that all-gathers its first operand: every tile's rows sit inside one
+    readiness chunk of one source rank, tiles are visited own rows first and then in ring order (the order
+    in which the copier warps fetch), the copy units tile every chunk exactly, and the counter buffer the
+    Python side allocates is large enough."""
+    from dion_b200.ops import _ext
+
+    if not _ext.load(required=False):
+        pytest.skip("extension not built")
+    unit = 64 * 1024
+    for rank in range(world):
+        plan = list(torch.ops.dion_b200.gemm_gather_plan(M, N, K, rows, world, rank))
+        assert plan, "shapes were rejected"
+        tile_m, bn, pair, chunk_rows, units_per_chunk, m_rot, tiles_m, tiles_n = plan
+        assert tile_m == (256 if pair else 128) and bn in (128, 256)
+        assert rows % chunk_rows == 0 and chunk_rows % tile_m == 0 and tiles_m * tile_m == M
+        assert 2 + M // chunk_rows <= 2 + M // 128
+        ring_seen = []
+        for t in range(tiles_m * tiles_n):
+            m_blk = (t // tiles_n + m_rot) % tiles_m
+            row0 = m_blk * tile_m
+            assert row0 % chunk_rows + tile_m <= chunk_rows          # one chunk per tile (both CTAs of a pair)
+            src = row0 // rows
+            assert (row0 + tile_m - 1) // rows == src                # one source rank per tile
+            ring = (src - rank) % world
+            if not ring_seen or ring_seen[-1] != ring:
+                ring_seen.append(ring)
+        assert ring_seen == list(range(world))                       # own rows first, then ring order, each once
+        chunk_bytes = chunk_rows * K * 2
+        assert units_per_chunk == -(-chunk_bytes // unit)
+        covered = 0
+        for u in range(units_per_chunk):
+            lo, hi = u * unit, min((u + 1) * unit, chunk_bytes)
+            assert lo < hi and lo % 16 == 0 and (hi - lo) % 16 == 0
+            covered += hi - lo
+        assert covered == chunk_bytes
+
+
+def test_gather_gemm_plan_rejects_ragged_row_blocks():
+    from dion_b200.ops import _ext
+
+    if not _ext.load(required=False):
+        pytest.skip("extension not built")
+    assert list(torch.ops.dion_b200.gemm_gather_plan(400, 96, 64, 200, 2, 0)) == []      # rows not a multiple of 128
+    assert list(torch.ops.dion_b200.gemm_gather_plan(512, 96, 64, 256, 3, 0)) == []      # world * rows != M
