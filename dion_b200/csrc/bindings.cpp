@@ -690,14 +690,19 @@ void split_tf32(const Tensor& x, Tensor hi, Tensor lo) {
                                           at::cuda::getCurrentCUDAStream()));
 }
 
-void refine_prep(const Tensor& G, Tensor C, Tensor d) {
+void refine_prep(const Tensor& G, Tensor C, Tensor d, double dead_below, const std::optional<Tensor>& skip) {
   const c10::cuda::CUDAGuard guard(G.device());
   TORCH_CHECK(G.scalar_type() == at::kFloat && C.scalar_type() == at::kFloat && d.scalar_type() == at::kFloat);
   TORCH_CHECK(G.dim() == 3 && G.size(1) == G.size(2) && G.is_contiguous() && C.is_contiguous() && d.is_contiguous());
   TORCH_CHECK(C.numel() == G.numel() && d.numel() == G.size(0) * G.size(1));
+  if (skip.has_value())
+    TORCH_CHECK(skip->scalar_type() == at::kInt && skip->is_cuda() && skip->is_contiguous() && skip->numel() == G.size(0),
+                "skip must be one int32 per matrix");
   ++g_launches;
   DION_CUDA_CHECK(dion::refine_prep_launch(G.data_ptr<float>(), C.data_ptr<float>(), d.data_ptr<float>(),
-                                           (int)G.size(0), (int)G.size(1), at::cuda::getCurrentCUDAStream()));
+                                           (int)G.size(0), (int)G.size(1), (float)dead_below,
+                                           skip.has_value() ? skip->data_ptr<int>() : nullptr,
+                                           at::cuda::getCurrentCUDAStream()));
 }
 
 // out (world * n) = concatenation of every rank's `inp` (n), through the staging slot at `slot_off`
@@ -792,7 +797,7 @@ TORCH_LIBRARY(dion_b200, m) {
   m.def(
       "attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, Tensor lse, Tensor(a!) delta, Tensor(b!) dq, "
       "Tensor(c!) dk, Tensor(d!) dv, float scale, Tensor(e!) status) -> ()");
-  m.def("refine_prep(Tensor G, Tensor(a!) C, Tensor(b!) d) -> ()");
+  m.def("refine_prep(Tensor G, Tensor(a!) C, Tensor(b!) d, float dead_below, Tensor? skip) -> ()");
   m.def("launch_count() -> int", &launch_count);
   m.def("gemm_gather_plan(int M, int N, int K, int rows, int world, int rank) -> int[]", &gemm_gather_plan);
 }

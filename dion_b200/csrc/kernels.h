@@ -114,8 +114,10 @@ cudaError_t attn_bwd_launch(const void* q, const void* k, const void* v, const v
                             int D, float scale, int* status, cudaStream_t stream);
 // hi / lo halves of fp32 data for 3xTF32 products; all three pointers 16-byte aligned
 cudaError_t split_tf32_launch(const float* x, float* hi, float* lo, long long numel, cudaStream_t s);
-// d = rsqrt(diag G) (0 where the diagonal vanishes), C = strictly lower part of D G D; contiguous [batch, r, r]
-cudaError_t refine_prep_launch(const float* G, float* C, float* d, int batch, int r, cudaStream_t s);
+// d = rsqrt(diag G) (0 where the diagonal is not above `dead_below`), C = strictly lower part of D G D
+// (all zero for matrices b with skip[b] != 0, `skip` may be null); contiguous [batch, r, r]
+cudaError_t refine_prep_launch(const float* G, float* C, float* d, int batch, int r, float dead_below,
+                               const int* skip, cudaStream_t s);
 
 // ---------------------------------------------------------------------------
 // Collectives over symmetric memory (one arena per process group; the same offset names

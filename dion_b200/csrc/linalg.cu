@@ -6,7 +6,8 @@
 // so that P * Z^T has orthonormal columns.  It is the device-side replacement for the
 // cuSOLVER geqrf / potrf + cuBLAS trsm sequence of the reference
 // (dion/dion.py:1284-1303, 1366-1406).  A pivot that is not safely positive is
-// clamped instead of failing; the count of clamped pivots is reported per matrix.
+// replaced by 1 and its column eliminates nothing (the column is treated as dependent on the earlier
+// ones) instead of failing; the count of such pivots is reported per matrix.
 //
 // Algorithm (right-looking, block size NB): per block column k
 //   1. factor the NB x NB diagonal block in shared memory, invert it (Linv)
@@ -132,17 +133,23 @@ chol_inverse_kernel(const float* __restrict__ Gall, float* __restrict__ Zall, fl
     __syncthreads();
     for (int j = 0; j < nb; ++j) {
       if (tid == 0) {
-        float d = dblk[j * (NB + 1) + j];
+        const float d = dblk[j * (NB + 1) + j];
         if (!(d > pivot_floor)) {
-          d = pivot_floor;
           ++clamp_count;
+          dblk[j * (NB + 1) + j] = -1.f;  // marks the column for the other threads, replaced by 1 below
+        } else {
+          dblk[j * (NB + 1) + j] = sqrtf(d);
         }
-        dblk[j * (NB + 1) + j] = sqrtf(d);
       }
       __syncthreads();
       const float piv = dblk[j * (NB + 1) + j];
-      for (int i = j + 1 + tid; i < nb; i += kCholThreads) dblk[i * (NB + 1) + j] /= piv;
+      // a pivot that is not safely positive belongs to a column that depends on the earlier ones: it
+      // gets a unit pivot and eliminates nothing, so that rounding noise is never divided by a tiny number
+      const bool bad = piv < 0.f;
+      for (int i = j + 1 + tid; i < nb; i += kCholThreads)
+        dblk[i * (NB + 1) + j] = bad ? 0.f : dblk[i * (NB + 1) + j] / piv;
       __syncthreads();
+      if (bad && tid == 0) dblk[j * (NB + 1) + j] = 1.f;
       // rank-1 update of the remaining lower triangle
       const int rem = nb - j - 1;
       for (int e = tid; e < rem * rem; e += kCholThreads) {
@@ -370,13 +377,13 @@ __device__ __forceinline__ int warp_factor_block(const float* dblk, float* linv,
     float aj = 0.f;  // A[lane][j]
 #pragma unroll
     for (int c = 0; c < NB; ++c) aj = (c == j) ? a[c] : aj;
-    float d = __shfl_sync(0xffffffffu, aj, j);
-    if (!(d > pivot_floor)) {
-      d = pivot_floor;
-      if (j < nb) ++clamped;
-    }
-    const float inv_s = rsqrtf(d);
-    const float l = (lane > j) ? aj * inv_s : 0.f;  // L[lane][j] below the diagonal
+    const float d = __shfl_sync(0xffffffffu, aj, j);
+    // a pivot that is not safely positive belongs to a column that depends on the earlier ones: it gets
+    // a unit pivot and eliminates nothing, so that rounding noise is never divided by a tiny number
+    const bool bad = !(d > pivot_floor);
+    if (bad && j < nb) ++clamped;
+    const float inv_s = bad ? 1.f : rsqrtf(d);
+    const float l = (lane > j && !bad) ? aj * inv_s : 0.f;  // L[lane][j] below the diagonal
 #pragma unroll
     for (int c = 0; c < NB; ++c) {
       const float lc = __shfl_sync(0xffffffffu, l, c);
@@ -566,21 +573,24 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float4* __restric
 //   C_ij = i > j ? d_i * G_ij * d_j : 0          (strictly lower part of D G D - I)
 // One block per (row block of 8, batch entry); d is written by the blocks of the first column tile.
 __global__ void __launch_bounds__(256) refine_prep_kernel(const float* __restrict__ G, float* __restrict__ C,
-                                                         float* __restrict__ d, int r) {
+                                                         float* __restrict__ d, int r, float dead_below,
+                                                         const int* __restrict__ skip) {
   const long long b = blockIdx.y;
+  // matrices flagged in `skip` get C = 0: they are only rescaled, not corrected
+  const bool no_correction = skip != nullptr && skip[b] != 0;
   const float* g = G + b * (long long)r * r;
   float* c = C + b * (long long)r * r;
   const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= r) return;
   const int lane = threadIdx.x & 31;
   const float gii = g[(long long)row * r + row];
-  const float di = gii > 1e-30f ? rsqrtf(gii) : 0.f;
+  const float di = gii > dead_below ? rsqrtf(gii) : 0.f;
   if (lane == 0) d[b * r + row] = di;
   for (int j = lane; j < r; j += 32) {
     float v = 0.f;
-    if (j < row) {
+    if (j < row && !no_correction) {
       const float gjj = g[(long long)j * r + j];
-      const float dj = gjj > 1e-30f ? rsqrtf(gjj) : 0.f;
+      const float dj = gjj > dead_below ? rsqrtf(gjj) : 0.f;
       v = di * g[(long long)row * r + j] * dj;
     }
     c[(long long)row * r + j] = v;
@@ -675,10 +685,11 @@ cudaError_t split_tf32_launch(const float* x, float* hi, float* lo, long long nu
   return cudaGetLastError();
 }
 
-cudaError_t refine_prep_launch(const float* G, float* C, float* d, int batch, int r, cudaStream_t s) {
+cudaError_t refine_prep_launch(const float* G, float* C, float* d, int batch, int r, float dead_below,
+                               const int* skip, cudaStream_t s) {
   if (batch == 0 || r == 0) return cudaSuccess;
   if (batch > 65535) return cudaErrorInvalidValue;
-  refine_prep_kernel<<<dim3((r + 7) / 8, batch), 256, 0, s>>>(G, C, d, r);
+  refine_prep_kernel<<<dim3((r + 7) / 8, batch), 256, 0, s>>>(G, C, d, r, dead_below, skip);
   return cudaGetLastError();
 }
 

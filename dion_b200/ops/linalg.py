@@ -16,8 +16,10 @@ MAX_KERNEL_RANK = 1728
 
 
 def chol_inverse_reference(G: torch.Tensor, pivot_floor: float = DEFAULT_PIVOT_FLOOR) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Pure PyTorch version of the kernel: Jacobi scaling, Cholesky with clamped pivots,
-    triangular inverse.  Returns (Z, info) with Z lower triangular, Z @ G @ Z.T ~= I."""
+    """Pure PyTorch version of the kernel: Jacobi scaling, Cholesky, triangular inverse.  A pivot that is
+    not above `pivot_floor` marks a column that (numerically) depends on the earlier ones: it gets a unit
+    pivot and eliminates nothing, so rounding noise is never divided by a tiny number; `info` counts such
+    pivots.  Returns (Z, info) with Z lower triangular, Z @ G @ Z.T ~= I on the independent columns."""
     G = G.float()
     B, r, _ = G.shape
     diag = torch.diagonal(G, dim1=-2, dim2=-1)
@@ -30,10 +32,10 @@ def chol_inverse_reference(G: torch.Tensor, pivot_floor: float = DEFAULT_PIVOT_F
         piv = W[:, j, j]
         bad = ~(piv > pivot_floor)
         info += bad.to(torch.int32)
-        piv = torch.where(bad, torch.full_like(piv, pivot_floor), piv).sqrt()
+        piv = torch.where(bad, torch.ones_like(piv), piv).sqrt()
         L[:, j, j] = piv
         if j + 1 < r:
-            col = W[:, j + 1:, j] / piv.unsqueeze(-1)
+            col = torch.where(bad.unsqueeze(-1), torch.zeros_like(W[:, j + 1:, j]), W[:, j + 1:, j] / piv.unsqueeze(-1))
             L[:, j + 1:, j] = col
             W[:, j + 1:, j + 1:] -= col.unsqueeze(-1) * col.unsqueeze(-2)
     eye = torch.eye(r, dtype=G.dtype, device=G.device).expand(B, r, r)
@@ -100,14 +102,24 @@ def split_tf32(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return hi, x - hi
 
 
-def refine_prep(G: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """From Gram matrices ``G: [B, r, r]``: ``d = rsqrt(diag G)`` (0 where the diagonal vanishes)
-    and ``C = stril(D G D)``, the strictly lower part of the column-scaled Gram matrix."""
+# After a Cholesky-QR pass the squared norm of an independent column is close to 1; one far below that
+# belongs to a column the factorisation gave up on (see chol_inverse_reference) and is dropped.
+DEAD_COLUMN_BELOW = 1e-4
+
+
+def refine_prep(G: torch.Tensor, dead_below: float = 1e-30,
+                skip: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """From Gram matrices ``G: [B, r, r]``: ``d = rsqrt(diag G)`` (0 where the diagonal is not above
+    `dead_below`) and ``C = stril(D G D)``, the strictly lower part of the column-scaled Gram matrix.
+    ``skip`` (int32, one per matrix): C is zero for the matrices where it is non-zero."""
     if runtime.use_cuda_kernels(G) and G.dtype == torch.float32 and G.dim() == 3:
         G = G.contiguous()
         C, d = torch.empty_like(G), torch.empty(G.shape[:-1], dtype=torch.float32, device=G.device)
-        torch.ops.dion_b200.refine_prep(G, C, d)
+        torch.ops.dion_b200.refine_prep(G, C, d, float(dead_below), None if skip is None else skip.contiguous())
         return C, d
     diag = torch.diagonal(G, dim1=-2, dim2=-1)
-    d = torch.where(diag > 1e-30, diag.clamp_min(1e-30).rsqrt(), torch.zeros_like(diag))
-    return torch.tril(G * d.unsqueeze(-1) * d.unsqueeze(-2), diagonal=-1), d
+    d = torch.where(diag > dead_below, diag.clamp_min(1e-30).rsqrt(), torch.zeros_like(diag))
+    C = torch.tril(G * d.unsqueeze(-1) * d.unsqueeze(-2), diagonal=-1)
+    if skip is not None:
+        C = C * (skip == 0).to(C.dtype).view(-1, 1, 1)
+    return C, d

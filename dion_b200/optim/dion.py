@@ -108,6 +108,10 @@ def low_rank_dim(m: int, n: int, rank_fraction: float, rank_multiple_of: int) ->
     return int(min(r, m, n))
 
 
+# steps the shifted two-pass orthonormalisation stays on after the last step that needed it
+ROBUST_STEPS = 20
+
+
 class _PackedClass:
     """All Dion parameters of one (shape, placements, dtype, group) class with their states
     packed into ``M: [B, m_loc, n_loc]`` and ``Q: [B, q_rows_loc, r_loc]``."""
@@ -122,6 +126,11 @@ class _PackedClass:
         self.shadow_ptrs: Optional[Tensor] = None
         self.shadow_ptr_list: Optional[List[int]] = None
         self.nonzero: Optional[Tensor] = None
+        # conditioning of P: steps the ill-conditioned treatment of the orthonormalisation stays on, and
+        # the (asynchronously fetched) count of matrices that asked for it in the last step
+        self.robust_left = 0
+        self.cond_host: Optional[Tensor] = None
+        self.cond_event = None
 
 
 class _ClassWork:
@@ -204,6 +213,8 @@ class Dion(Optimizer):
         self._mixed_precision_config = mixed_precision_config or DionMixedPrecisionConfig()
         # how often P left a reduction as this rank's share of the batch (reduce-scatter instead of all-reduce)
         self.p_reduce_scatters = 0
+        # how often a class of matrices went into the ill-conditioned treatment of the orthonormalisation
+        self.robust_switches = 0
         # Q factors are drawn from this generator so that every rank draws the same values
         self._q_seed = 0x0D10
 
@@ -260,14 +271,44 @@ class Dion(Optimizer):
         if work:
             # P is the same on every rank of the outer (or else the replicate) group by now: each rank
             # orthonormalises its share of every batch and the shares are all-gathered
+            infos: List[Tensor] = []
             ortho = orthonormalize_many([w.P for w in work], [w.inner for w in work],
                                         shard_groups=[w.outer if w.outer is not None else w.replicate for w in work],
                                         totals=[w.P_total for w in work],
-                                        out_dtypes=[w.cls.M.dtype for w in work])  # what phase 2 multiplies with
+                                        out_dtypes=[w.cls.M.dtype for w in work],  # what phase 2 multiplies with
+                                        robust=[w.cls.robust_left > 0 for w in work], infos=infos)
+            for w, info in zip(work, infos):
+                self._note_conditioning(w.cls, info)
             for w, P in zip(work, ortho):
                 w.P = P
             Scheduler((lambda w=w: self._dion_phase2(w) for w in work), max_in_flight=3).run()
         return loss
+
+    def _note_conditioning(self, cls: _PackedClass, info: Tensor) -> None:
+        """Switch the ill-conditioned treatment of a class on for ROBUST_STEPS steps when its
+        factorisation gave up on a pivot (or, while the treatment is on, reports that it still would).
+        On GPUs the count is fetched without waiting: the decision uses the last step whose count has
+        arrived, so the first ill-conditioned step runs the plain path (bounded, columns dropped)."""
+        count = None
+        if not info.is_cuda:
+            count = int(info.sum())
+        else:
+            if cls.cond_event is not None and cls.cond_event.query():
+                count = int(cls.cond_host.item())
+                cls.cond_event = None
+            if cls.cond_event is None:
+                if cls.cond_host is None:
+                    cls.cond_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+                cls.cond_host.copy_(info.sum(dtype=torch.int32).view(1), non_blocking=True)
+                cls.cond_event = torch.cuda.Event()
+                cls.cond_event.record()
+        if count is not None:
+            if count > 0:
+                if cls.robust_left == 0:
+                    self.robust_switches += 1
+                cls.robust_left = ROBUST_STEPS
+            elif cls.robust_left > 0:
+                cls.robust_left -= 1
 
     @torch.no_grad()
     def synchronize_for_checkpoint(self):
@@ -686,6 +727,9 @@ class Dion(Optimizer):
                 yield
                 wait()
         Qn = (R / (ss.sqrt().unsqueeze(1) + eps)).to(M.dtype)
+        # a column of P that the orthonormalisation dropped (P was rank deficient) leaves a zero column
+        # in R: it keeps its previous Q, like a whole matrix whose momentum is zero does
+        Qn = torch.where((ss > 0).unsqueeze(1), Qn, Qm)
 
         # 9. weight decay and update  X = (1 - lr wd) X - lr sqrt(fan_out / fan_in) P Qn^T
         fan_out, fan_in = p0.shape[0], p0.shape[1]

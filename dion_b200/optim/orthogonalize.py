@@ -92,7 +92,7 @@ def orthonormalize_cholqr(P: Tensor, row_group: Optional[dist.ProcessGroup] = No
     return X.to(out_dtype)
 
 
-def _refine(X: Tensor, row_group: Optional[dist.ProcessGroup]) -> Tensor:
+def _refine(X: Tensor, row_group: Optional[dist.ProcessGroup], gave_up: Optional[Tensor] = None) -> Tensor:
     """One triangular Newton correction of an almost orthonormal X: with the column-scaled
     Gram matrix D G D = I + E, the Cholesky factor's inverse is I - stril(E) to first order,
     so X <- (X D) (I - stril(E))^T squares the orthogonality error while keeping the column
@@ -100,7 +100,11 @@ def _refine(X: Tensor, row_group: Optional[dist.ProcessGroup]) -> Tensor:
     G = gram(X, row_group)
     if row_group is not None and dist.get_world_size(row_group) > 1:
         symm.all_reduce(G, row_group)
-    C, d = ops.linalg.refine_prep(G)  # d = rsqrt(diag G), C = stril(D G D) = stril(E)
+    # d = rsqrt(diag G), C = stril(D G D) = stril(E); columns the factorisation gave up on (squared norm
+    # far below 1) are dropped instead of being blown up to unit length
+    # a matrix whose factorisation gave up on some pivot (`gave_up`, int32 per matrix) is far from
+    # orthonormal, where the first-order correction diverges: it is only rescaled
+    C, d = ops.linalg.refine_prep(G, ops.linalg.DEAD_COLUMN_BELOW, gave_up)
     Xs = X * d.unsqueeze(-2)
     if X.is_cuda:
         # the correction term is small, a single tensor-core pass keeps it far below fp32 resolution
@@ -112,6 +116,10 @@ def _refine(X: Tensor, row_group: Optional[dist.ProcessGroup]) -> Tensor:
 # orthonormalises its share and the shares are all-gathered (the reference hands matrix j of a batch
 # to rank j, dion/dion.py:809-830, 925-946).  DION_B200_SHARD_ORTHO=0 keeps the redundant computation.
 SHARD_WORK = os.environ.get("DION_B200_SHARD_ORTHO", "1") != "0"
+# relative rise of the Gram diagonal in the first pass of the ill-conditioned treatment
+ROBUST_SHIFT = 1e-5
+# a batch stays in that treatment while the smallest pivot of its shifted, unit-diagonal Gram matrix is below this
+ROBUST_KEEP_BELOW = 1e-4
 _gatherers = {}
 
 
@@ -191,7 +199,7 @@ def _gather_shares(part: Tensor, group, B: int) -> Tensor:
 
 def orthonormalize_many(Ps, row_groups=None, refine_passes: int = 2,
                         pivot_floor: float = ops.linalg.DEFAULT_PIVOT_FLOOR, shard_groups=None, totals=None,
-                        out_dtypes=None):
+                        out_dtypes=None, robust=None, infos=None):
     """Orthonormalise several batches ``P_i: [B_i, a_i, r_i]`` at once.  All Gram matrices of
     the same rank are factorised by a single launch of the Cholesky kernel (one CTA per
     matrix), whatever their row counts; the remaining loss of orthogonality is removed by
@@ -201,7 +209,13 @@ def orthonormalize_many(Ps, row_groups=None, refine_passes: int = 2,
     ``totals[i]``, when not None, says that ``P_i`` already is this rank's share (as
     :func:`_my_share` would cut it) of a batch of that many matrices; the result is the whole batch.
     ``out_dtypes[i]`` is the dtype of result i (default: the input's); shares are converted before they
-    are exchanged, so a bf16 consumer halves the all-gather."""
+    are exchanged, so a bf16 consumer halves the all-gather.
+    ``robust[i]`` asks for the ill-conditioned treatment of batch i: the first factorisation runs on the
+    Gram matrix with its diagonal raised by ROBUST_SHIFT (always positive definite in fp32) and a second
+    Cholesky-QR pass follows (shifted CholeskyQR3; good up to condition numbers around 1e6, where one pass
+    gives up near 3e3).  ``infos``, if a list, receives per batch the int32 tensor of pivots the (first)
+    factorisation gave up on, per matrix of this rank's share (for a `robust` batch: 1 where the smallest
+    pivot says that the plain factorisation would still give up) - the signal for asking for `robust`."""
     n = len(Ps)
     if out_dtypes is None:
         out_dtypes = [P.dtype for P in Ps]
@@ -214,31 +228,52 @@ def orthonormalize_many(Ps, row_groups=None, refine_passes: int = 2,
         shard_groups = [None] * n
     shard_groups = [g if (t is not None or (g is not None and dist.get_world_size(g) > 1 and P.shape[0] > 1 and rg is None))
                     else None for g, P, rg, t in zip(shard_groups, Ps, row_groups, totals)]
+    if robust is None:
+        robust = [False] * n
     if any(g is not None for g in shard_groups):
         parts = [P.float() if (g is None or t is not None) else _my_share(P.float(), g)
                  for P, g, t in zip(Ps, shard_groups, totals)]
-        outs = orthonormalize_many(parts, row_groups, refine_passes, pivot_floor)
+        outs = orthonormalize_many(parts, row_groups, refine_passes, pivot_floor, robust=robust, infos=infos)
         return [X.to(dt) if g is None else _gather_shares(X.to(dt), g, P.shape[0] if t is None else t)
                 for X, P, g, t, dt in zip(outs, Ps, shard_groups, totals, out_dtypes)]
     dtypes = out_dtypes
     Xs = [P.float() for P in Ps]
-    Gs = [gram(X, g) for X, g in zip(Xs, row_groups)]
-    for G, g in zip(Gs, row_groups):
-        if g is not None and dist.get_world_size(g) > 1:
-            symm.all_reduce(G, g)
-    by_rank = {}
-    for i, G in enumerate(Gs):
-        by_rank.setdefault(G.shape[-1], []).append(i)
-    for r, idxs in by_rank.items():
-        Gcat = Gs[idxs[0]] if len(idxs) == 1 else torch.cat([Gs[i] for i in idxs], dim=0)
-        Z, _ = ops.chol_inverse(Gcat, pivot_floor)
-        off = 0
-        for i in idxs:
-            b = Gs[i].shape[0]
-            Xs[i] = apply_right(Xs[i], Z[off:off + b])
-            off += b
+    first_info = [None] * n
+    last_info = [None] * n  # pivots the last factorisation of each batch gave up on
+    for cholqr_pass in range(2 if any(robust) else 1):
+        todo = [i for i in range(n) if cholqr_pass == 0 or robust[i]]
+        Gs = {i: gram(Xs[i], row_groups[i]) for i in todo}
+        for i in todo:
+            g = row_groups[i]
+            if g is not None and dist.get_world_size(g) > 1:
+                symm.all_reduce(Gs[i], g)
+            if cholqr_pass == 0 and robust[i]:
+                Gs[i].diagonal(dim1=-2, dim2=-1).mul_(1.0 + ROBUST_SHIFT)
+        by_rank = {}
+        for i in todo:
+            by_rank.setdefault(Gs[i].shape[-1], []).append(i)
+        for r, idxs in by_rank.items():
+            Gcat = Gs[idxs[0]] if len(idxs) == 1 else torch.cat([Gs[i] for i in idxs], dim=0)
+            Z, info = ops.chol_inverse(Gcat, pivot_floor)
+            off = 0
+            for i in idxs:
+                b = Gs[i].shape[0]
+                Xs[i] = apply_right(Xs[i], Z[off:off + b])
+                last_info[i] = info[off:off + b]
+                if cholqr_pass == 0 and not robust[i]:
+                    first_info[i] = info[off:off + b]
+                elif cholqr_pass == 0:
+                    # the shifted factorisation never gives up; its smallest pivot, 1 / (G_jj Z_jj^2) in
+                    # the unit-diagonal scaling, says whether the plain one would have
+                    gd = Gs[i].diagonal(dim1=-2, dim2=-1)
+                    zd = Z[off:off + b].diagonal(dim1=-2, dim2=-1)
+                    piv = torch.where(gd > 1e-30, 1.0 / (gd * zd * zd).clamp_min(1e-30), torch.ones_like(gd))
+                    first_info[i] = (piv.amin(dim=-1) < ROBUST_KEEP_BELOW).to(torch.int32)
+                off += b
+    if infos is not None:
+        infos.extend(first_info)
     for _ in range(refine_passes):
-        Xs = [_refine(X, g) for X, g in zip(Xs, row_groups)]
+        Xs = [_refine(X, g, bad) for X, g, bad in zip(Xs, row_groups, last_info)]
     return [X.to(dt) for X, dt in zip(Xs, dtypes)]
 
 

@@ -339,3 +339,72 @@ def test_muon_state_dict_roundtrip_continues_identically():
         opt2.step()
     for p, q in zip(P, Q):
         torch.testing.assert_close(p, q, rtol=0, atol=0)
+
+
+def _with_condition(k, m=192, n=96, batch=2):
+    out = []
+    for _ in range(batch):
+        U = torch.linalg.qr(torch.randn(m, n))[0]
+        V = torch.linalg.qr(torch.randn(n, n))[0]
+        out.append((U * torch.logspace(0, -k, n)) @ V)
+    return torch.stack(out)
+
+
+def _orth_err(X):
+    G = X.transpose(-1, -2) @ X
+    return (G - torch.eye(G.shape[-1])).abs().max().item()
+
+
+def test_orthonormalisation_of_ill_conditioned_batches():
+    from dion_b200.optim.orthogonalize import orthonormalize_many
+
+    torch.manual_seed(0)
+    easy, hard = _with_condition(2), _with_condition(5)
+    # well conditioned: both treatments agree and report nothing
+    infos = []
+    a = orthonormalize_many([easy], infos=infos)[0]
+    assert int(infos[0].sum()) == 0 and _orth_err(a) < 1e-5
+    infos = []
+    b = orthonormalize_many([easy], robust=[True], infos=infos)[0]
+    assert int(infos[0].sum()) == 0
+    torch.testing.assert_close(a, b, rtol=1e-4, atol=1e-5)
+    # condition 1e5: the plain path gives up on pivots, says so, and degrades to unit or dropped columns
+    infos = []
+    c = orthonormalize_many([hard], infos=infos)[0]
+    assert (infos[0] > 0).all()
+    assert torch.isfinite(c).all()
+    norms = c.norm(dim=-2)
+    assert ((norms - 1).abs() < 1e-3).logical_or(norms == 0).all(), norms
+    # ... the shifted two-pass treatment orthonormalises it, and reports that it is still needed
+    infos = []
+    d = orthonormalize_many([hard], robust=[True], infos=infos)[0]
+    assert _orth_err(d) < 1e-4 and (infos[0] > 0).all()
+    Q, _ = torch.linalg.qr(hard.double())
+    assert (d.double().abs() - Q.abs()).abs().max() < 5e-2          # the basis of a QR factorisation, up to signs
+    # mixed request: only the flagged batch takes the second pass, the other result is unchanged
+    e, f = orthonormalize_many([easy, hard], robust=[False, True])
+    torch.testing.assert_close(e, a, rtol=0, atol=0)
+    torch.testing.assert_close(f, d, rtol=0, atol=0)
+
+
+def test_dion_survives_rank_deficient_momentum_and_switches_treatment():
+    torch.manual_seed(0)
+    P = _params([(64, 32), (64, 32), (48, 48)])
+    before = [p.detach().clone() for p in P]
+    opt = Dion(P, lr=0.02, rank_fraction=1.0, weight_decay=0.0)
+    grads = [torch.randn(p.shape[0], 2) @ torch.randn(2, p.shape[1]) for p in P]   # rank 2, every step the same
+    for _ in range(6):
+        for p, g in zip(P, grads):
+            p.grad = g.clone()
+        opt.step()
+        for p in P:
+            assert torch.isfinite(p).all()
+    assert opt.robust_switches >= 1
+    for p, b in zip(P, before):
+        r = min(p.shape)
+        # six steps of at most lr * sqrt(fan_out / fan_in) * ||P Q^T||_F, with unit columns in P and Q
+        bound = 6 * 0.02 * (p.shape[0] / p.shape[1]) ** 0.5 * r
+        assert (p.detach() - b).norm() <= bound
+    for st in opt.state.values():
+        assert torch.isfinite(st["Q"]).all() and torch.isfinite(st["momentum"]).all()
+        assert (st["Q"].norm(dim=0) > 0).all()        # no column of Q has died
