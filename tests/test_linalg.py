@@ -88,3 +88,25 @@ def test_split_tf32_and_refine_prep_match_torch():
     torch.testing.assert_close(d.cpu(), dr, rtol=1e-5, atol=0)
     torch.testing.assert_close(C.cpu(), Cr, rtol=1e-5, atol=1e-7)
     assert d[2, 7] == 0 and C[2, 7].abs().max() == 0 and C[2, :, 7].abs().max() == 0
+
+
+@pytest.mark.gpu
+def test_orthonormalisation_of_ill_conditioned_batch_gpu():
+    """Condition number 1e5: the plain path reports the pivots it gave up on and returns bounded columns,
+    the shifted two-pass treatment orthonormalises."""
+    from dion_b200.optim.orthogonalize import orthonormalize_many
+
+    torch.manual_seed(0)
+    m, n = 512, 256
+    U = torch.linalg.qr(torch.randn(2, m, n, device="cuda"))[0]
+    V = torch.linalg.qr(torch.randn(2, n, n, device="cuda"))[0]
+    P = (U * torch.logspace(0, -5, n, device="cuda")) @ V
+    infos = []
+    X = orthonormalize_many([P], infos=infos)[0]
+    assert (infos[0] > 0).all()
+    assert torch.isfinite(X).all() and X.norm(dim=-2).max() < 1.5
+    infos = []
+    Y = orthonormalize_many([P], robust=[True], infos=infos)[0]
+    eye = torch.eye(n, device="cuda")
+    assert (Y.transpose(-1, -2) @ Y - eye).abs().max() < 1e-3
+    assert (infos[0] > 0).all()
