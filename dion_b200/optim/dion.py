@@ -287,21 +287,23 @@ class Dion(Optimizer):
     def _note_conditioning(self, cls: _PackedClass, info: Tensor) -> None:
         """Switch the ill-conditioned treatment of a class on for ROBUST_STEPS steps when its
         factorisation gave up on a pivot (or, while the treatment is on, reports that it still would).
-        On GPUs the count is fetched without waiting: the decision uses the last step whose count has
-        arrived, so the first ill-conditioned step runs the plain path (bounded, columns dropped)."""
+        On GPUs the count travels to the host asynchronously and is read one step later - by then the
+        copy has long finished, so the read does not stall the GPU, and every rank that factorised the
+        same matrices (the ranks of a tensor-parallel group, whose Gram matrices are all-reduced) takes
+        the same decision at the same step.  The step that discovers the problem runs the plain path
+        (bounded, columns dropped)."""
         count = None
         if not info.is_cuda:
             count = int(info.sum())
         else:
-            if cls.cond_event is not None and cls.cond_event.query():
+            if cls.cond_event is not None:
+                cls.cond_event.synchronize()          # recorded a whole step ago
                 count = int(cls.cond_host.item())
-                cls.cond_event = None
-            if cls.cond_event is None:
-                if cls.cond_host is None:
-                    cls.cond_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
-                cls.cond_host.copy_(info.sum(dtype=torch.int32).view(1), non_blocking=True)
+            if cls.cond_host is None:
+                cls.cond_host = torch.zeros(1, dtype=torch.int32, pin_memory=True)
                 cls.cond_event = torch.cuda.Event()
-                cls.cond_event.record()
+            cls.cond_host.copy_(info.sum(dtype=torch.int32).view(1), non_blocking=True)
+            cls.cond_event.record()
         if count is not None:
             if count > 0:
                 if cls.robust_left == 0:
