@@ -534,6 +534,58 @@ def case_tp(sequence_parallel=False):
             print(f"tp: fused GEMM -> reduce-scatter / all-gather products: {calls}", flush=True)
 
 
+def case_structured():
+    """Periodic token data (low-rank gradients, ill-conditioned P from the first step): Dion under tensor
+    parallelism (row-sharded Gram matrices) and under FSDP2 (P reduce-scattered, work split over the ranks)
+    follows the single-process oracle that orthonormalises with Householder QR."""
+    from torch.distributed.device_mesh import init_device_mesh
+
+    from dion_b200 import Dion, DionReference
+    from dion_b200.models.gpt import parallelize_gpt_model
+
+    def groups(m):
+        return [dict(params=list(m.transformer.h.parameters())),
+                dict(params=list(m.transformer.wte.parameters()) + list(m.lm_head.parameters()), algorithm="lion",
+                     lr=0.002)]
+
+    def batch(step, rank, world):
+        base = (torch.arange(65) * 7) % 23
+        x = torch.stack([(base + i + step) % 23 for i in range(8)])
+        per = 8 // world
+        x = x[rank * per:(rank + 1) * per].to(DEV)
+        return x[:, :-1].contiguous(), x[:, 1:].contiguous()
+
+    def train(m, opt, steps, rank, world):
+        out = []
+        for s in range(steps):
+            x, y = batch(s, rank, world)
+            loss = m(x, y)
+            loss.backward()
+            opt.step()
+            m.zero_grad(set_to_none=True)
+            out.append(loss.detach().float().clone())
+        return torch.stack(out)
+
+    steps = 21
+    ref = _tiny_gpt().to(DEV)
+    want = train(ref, DionReference(groups(ref), lr=0.02, rank_fraction=1.0, qr_method="qr"), steps, 0, 1)
+    kind = "cuda" if CUDA else "cpu"
+    for mode in ("tp", "fsdp"):
+        shape = (1, 1, WORLD) if mode == "tp" else (1, WORLD, 1)
+        mesh = init_device_mesh(kind, shape, mesh_dim_names=("dp", "fs", "tp"))
+        model = _tiny_gpt().to(DEV)
+        parallelize_gpt_model(model, mesh, dp_name=None, fs_name="fs", tp_name="tp")
+        opt = Dion(groups(model), replicate_mesh=mesh["dp"], outer_shard_mesh=mesh["fs"],
+                   inner_shard_mesh=mesh["tp"] if mode == "tp" else None, lr=0.02, rank_fraction=1.0,
+                   rank_multiple_of=WORLD)
+        got = train(model, opt, steps, *((0, 1) if mode == "tp" else (RANK, WORLD)))
+        dist.all_reduce(got)
+        got /= WORLD
+        assert opt.robust_switches >= 1, "the ill-conditioned treatment never came on"
+        assert got[-1] < 0.5 * got[0]
+        check(f"structured {mode} losses", got[4:], want[4:], 0.1 if CUDA else 2e-2)
+
+
 def case_checkpoint():
     """Distributed checkpoint round trip of model + Dion state through CheckpointManager."""
     import tempfile

@@ -28,7 +28,7 @@ def _launch(cases, nproc, force_cpu, timeout=600):
     assert res.returncode == 0 and "ALL OK" in res.stdout, tail
 
 
-@pytest.mark.parametrize("case", ["dion_ddp", "muon_ddp", "fsdp", "fsdp_comm", "tp", "tp_sp", "checkpoint"])
+@pytest.mark.parametrize("case", ["dion_ddp", "muon_ddp", "fsdp", "fsdp_comm", "tp", "tp_sp", "structured", "checkpoint"])
 def test_cpu_two_ranks(case):
     _launch([case], nproc=2, force_cpu=True)
 
