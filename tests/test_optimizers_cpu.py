@@ -410,34 +410,48 @@ def test_dion_survives_rank_deficient_momentum_and_switches_treatment():
         assert (st["Q"].norm(dim=0) > 0).all()        # no column of Q has died
 
 
+def _structured_run(opt_cls, device, steps=24, **kw):
+    from dion_b200.models import GPT, GPTConfig
+
+    torch.manual_seed(0)
+    m = GPT(GPTConfig(sequence_len=64, vocab_size=512, n_layer=2, n_head=4, n_embd=64))
+    m.init_weights()
+    m = m.to(device)
+    groups = [dict(params=list(m.transformer.h.parameters())),
+              dict(params=list(m.transformer.wte.parameters()) + list(m.lm_head.parameters()), algorithm="lion",
+                   lr=0.002)]
+    opt = opt_cls(groups, lr=0.02, rank_fraction=1.0, **kw)
+    base = (torch.arange(65) * 7) % 23
+    losses = []
+    for s in range(steps):
+        x = torch.stack([(base + i + s) % 23 for i in range(8)]).to(device)
+        loss = m(x[:, :-1].contiguous(), x[:, 1:].contiguous())
+        loss.backward()
+        opt.step()
+        m.zero_grad(set_to_none=True)
+        losses.append(loss.item())
+    return losses, opt
+
+
 def test_dion_trains_on_structured_data_like_the_qr_oracle():
     """Periodic token sequences give low-rank gradients, so P = M Q is ill conditioned from the first
     step on - the regime in which a plain Cholesky-QR breaks down.  The loss must follow the oracle that
     orthonormalises with Householder QR."""
-    from dion_b200.models import GPT, GPTConfig
-
-    def run(opt_cls, steps=24, **kw):
-        torch.manual_seed(0)
-        m = GPT(GPTConfig(sequence_len=64, vocab_size=512, n_layer=2, n_head=4, n_embd=64))
-        m.init_weights()
-        groups = [dict(params=list(m.transformer.h.parameters())),
-                  dict(params=list(m.transformer.wte.parameters()) + list(m.lm_head.parameters()), algorithm="lion",
-                       lr=0.002)]
-        opt = opt_cls(groups, lr=0.02, rank_fraction=1.0, **kw)
-        base = (torch.arange(65) * 7) % 23
-        losses = []
-        for s in range(steps):
-            x = torch.stack([(base + i + s) % 23 for i in range(8)])
-            loss = m(x[:, :-1].contiguous(), x[:, 1:].contiguous())
-            loss.backward()
-            opt.step()
-            m.zero_grad(set_to_none=True)
-            losses.append(loss.item())
-        return losses, opt
-
-    ours, opt = run(Dion)
-    oracle, _ = run(DionReference, qr_method="qr")
+    ours, opt = _structured_run(Dion, "cpu")
+    oracle, _ = _structured_run(DionReference, "cpu", qr_method="qr")
     assert opt.robust_switches >= 1
     assert ours[-1] < 0.5 and oracle[-1] < 0.5
     for a, b in zip(ours[4:], oracle[4:]):
         assert abs(a - b) < 0.05 * max(b, 0.1), (ours, oracle)
+
+
+@pytest.mark.gpu
+def test_dion_trains_on_structured_data_gpu():
+    """The same regime through the CUDA kernels (bf16 activations): the ill-conditioned treatment comes
+    on and the loss falls like the oracle's."""
+    ours, opt = _structured_run(Dion, "cuda")
+    oracle, _ = _structured_run(DionReference, "cuda", qr_method="qr")
+    assert opt.robust_switches >= 1
+    assert all(l == l for l in ours)
+    assert ours[-1] < 0.6 and oracle[-1] < 0.6, (ours, oracle)
+    assert abs(ours[-1] - oracle[-1]) < 0.25 * max(oracle[-1], 0.2), (ours, oracle)
