@@ -5,8 +5,9 @@
 Every case allocates well under 4 GB, uses inputs larger than the 126 MB L2 (where the op
 is bandwidth-bound), warms up, then times `iters` launches with CUDA events (L2 flushed in
 between) and prints achieved FLOP/s or bytes/s next to the measured peaks of
-MEASURED_PEAKS.json when that file is present.  Under `ncu -k regex:<kernel> -c 1` the same
-command yields one capture of the named kernel.
+MEASURED_PEAKS.json when that file is present.  Under `ncu --clock-control none -k regex:<kernel> -c 1`
+the same command yields one capture of the named kernel (never profile without `--clock-control none`:
+ncu would lock the GPU's clocks, and that setting outlasts the process).
 
 `--ref` times cuBLAS (torch.matmul / torch.bmm) on the operands of gemm_fwd, gemm_dx, gemm_dw
 and gemm_sym for comparison.

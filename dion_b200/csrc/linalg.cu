@@ -458,7 +458,9 @@ chol_inverse_pair_kernel(const float* __restrict__ Gall, float* __restrict__ Zal
     if (tid < 32) clamp_count += warp_factor_block<NB>(dblk, linv, linv_al, nb, pivot_floor, tid);
     __syncthreads();
 
-    // ---- 2. Z[k,:] = Linv * B[k,:] for columns < k0 + nb (CTA 0 writes it back)
+    // ---- 2. Z[k,:] = Linv * B[k,:] for columns < k0 + nb.  Both CTAs need the old block row, so
+    //         the result stays in `zrow` here; CTA 0 writes it back after the cluster barrier that
+    //         ends the step, when the other CTA can no longer be reading the old values.
     const int zc = k0 + nb;
     for (int c = tid; c < rp; c += kChol2Threads) {
       float bcol[NB];
@@ -477,7 +479,6 @@ chol_inverse_pair_kernel(const float* __restrict__ Gall, float* __restrict__ Zal
           s = fmaf(lv.w, bcol[4 * q + 3], s);
         }
         zrow[(size_t)a * rp + c] = s;
-        if (cta == 0 && a < nb && c < zc) Z[(long long)(k0 + a) * r + c] = s;
       }
     }
     // ---- 3. panel = A[k+1:, k] * Linv^T, stored transposed: panelT[a][i - p0]
@@ -504,11 +505,10 @@ chol_inverse_pair_kernel(const float* __restrict__ Gall, float* __restrict__ Zal
       }
     }
     __syncthreads();
-    if (tr <= 0) break;  // uniform over the cluster
 
     // ---- 4. trailing updates with 128 x 128 tiles, spread over the four 256-thread groups of
     //         the cluster: lower-triangular tiles of the Gram part, then the right-hand side
-    const int nt = (tr + 127) / 128;
+    const int nt = tr > 0 ? (tr + 127) / 128 : 0;
     const int nc = (zc + 127) / 128;
     const int gram_tiles = nt * (nt + 1) / 2;
     const int total_tiles = gram_tiles + nt * nc;
@@ -530,9 +530,18 @@ chol_inverse_pair_kernel(const float* __restrict__ Gall, float* __restrict__ Zal
       }
     }
     chol_cluster_sync();
+    // rows k0 .. k0 + nb of Z: nobody reads them from global memory again before the final scaling,
+    // and every read of their old values (step 2 of both CTAs) lies before the barrier above
+    if (cta == 0) {
+      for (int c = tid; c < zc; c += kChol2Threads)
+        for (int a = 0; a < nb; ++a) Z[(long long)(k0 + a) * r + c] = zrow[(size_t)a * rp + c];
+    }
+    __syncthreads();  // zrow is rewritten by the next step
+    if (tr <= 0) break;  // uniform over the cluster
   }
 
   // undo the Jacobi scaling: G = D^-1 L' L'^T D^-1  =>  L^{-1} = L'^{-1} D, i.e. scale column j by d_j
+  // (the barrier also hands CTA 0's last block row to CTA 1)
   chol_cluster_sync();
   for (int i = cta; i < r; i += 2) {
     for (int j = tid; j < r; j += kChol2Threads) {
@@ -602,6 +611,9 @@ __global__ void __launch_bounds__(256) refine_prep_kernel(const float* __restric
 cudaError_t chol_inverse_launch(const float* G, float* Z, float* work, int* info, int batch, int r, long long ldg,
                                 long long g_batch_stride, float pivot_floor, cudaStream_t s) {
   if (batch == 0 || r == 0) return cudaSuccess;
+  constexpr int kMaxDevices = 64;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
   {
     // cluster-pair kernel (two CTAs per matrix); DION_B200_CHOL_PAIR=0 selects the single-CTA one
     static const int pair_env = [] {
@@ -611,12 +623,13 @@ cudaError_t chol_inverse_launch(const float* G, float* Z, float* work, int* info
     const int rp2 = ((r + 127) / 128) * 128;
     const size_t smem2 = (size_t)(2 * 32 * rp2 + 2 * 32 * 33 + 32 * 32 + rp2 + 4) * sizeof(float);
     if (pair_env && smem2 <= 227 * 1024) {
-      static bool granted = false;
-      if (!granted) {
+      // the attribute belongs to the device that is current, so it is tracked per device
+      static bool granted[kMaxDevices] = {};
+      if (!granted[dev]) {
         cudaError_t e2 = cudaFuncSetAttribute(chol_inverse_pair_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                               227 * 1024);
         if (e2 != cudaSuccess) return e2;
-        granted = true;
+        granted[dev] = true;
       }
       cudaLaunchConfig_t cfg;
       memset(&cfg, 0, sizeof(cfg));
@@ -640,25 +653,25 @@ cudaError_t chol_inverse_launch(const float* G, float* Z, float* work, int* info
   constexpr size_t kMaxSmem = 227 * 1024;
   cudaError_t e;
   if (smem_for(32) <= kMaxSmem) {
-    static size_t granted32 = 48 * 1024;
-    if (smem_for(32) > granted32) {
+    static bool granted32[kMaxDevices] = {};
+    if (smem_for(32) > 48 * 1024 && !granted32[dev]) {
       e = cudaFuncSetAttribute(chol_inverse_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem);
       if (e != cudaSuccess) return e;
-      granted32 = kMaxSmem;
+      granted32[dev] = true;
     }
     chol_inverse_kernel<32><<<batch, kCholThreads, smem_for(32), s>>>(G, Z, work, info, r, ldg, g_batch_stride, rp,
                                                                      pivot_floor);
   } else if (smem_for(16) <= kMaxSmem) {
-    static size_t granted16 = 48 * 1024;
-    if (smem_for(16) > granted16) {
+    static bool granted16[kMaxDevices] = {};
+    if (smem_for(16) > 48 * 1024 && !granted16[dev]) {
       e = cudaFuncSetAttribute(chol_inverse_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kMaxSmem);
       if (e != cudaSuccess) return e;
-      granted16 = kMaxSmem;
+      granted16[dev] = true;
     }
     chol_inverse_kernel<16><<<batch, kCholThreads, smem_for(16), s>>>(G, Z, work, info, r, ldg, g_batch_stride, rp,
                                                                      pivot_floor);
   } else {
-    return cudaErrorInvalidValue;  // caller falls back to the library path for very large ranks
+    return cudaErrorNotSupported;  // rank too large for the kernels' shared memory: the caller falls back
   }
   return cudaGetLastError();
 }

@@ -69,7 +69,7 @@ extern "C" int dion_chol_inverse_noalloc(const float* G, float* Z, int* info, in
   // The kernel writes every element of the working copy it later reads, so stale contents
   // of the shared scratch do not matter.
   e = dion::chol_inverse_launch(G, Z, scratch, info, batch, r, ldg, g_batch_stride, pivot_floor, stream);
-  if (e == cudaErrorInvalidValue) {
+  if (e == cudaErrorNotSupported) {  // the launcher's own size check, nothing was launched
     snprintf(buf, sizeof(buf), "dion_chol_inverse_noalloc: rank %d is larger than the kernel supports", r);
     g_error = buf;
     return 1;

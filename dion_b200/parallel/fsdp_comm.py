@@ -65,27 +65,34 @@ class _Arena:
         self.arena: Optional[symm.SymmetricArena] = None
         self.slot_bytes = 0
         self.calls = 0
+        self.declined = False
 
     def ensure(self, nbytes: int) -> bool:
+        """True when a slot of `nbytes` is available.  `nbytes` is the size of a collective's
+        per-rank input, which FSDP pads to the same value on every rank, so all ranks of the group
+        take the same branch here; the creation itself agrees on size and success across the group
+        (:func:`symm.create_arena`), and a group that could not create its arena stays on the
+        library collectives on every rank."""
+        if self.declined:
+            return False
         if self.arena is not None and nbytes <= self.slot_bytes:
             return True
-        try:
-            if self.arena is not None:
-                # kernels of every rank that still use the old arena must have retired
-                torch.cuda.synchronize(self.device)
-                dist.barrier(self.group)
-            slot = max(_MIN_BYTES, int(nbytes * 1.25))
-            slot = (slot + 255) // 256 * 256
-            self.arena = symm.SymmetricArena(self.group, 2 * slot, self.device)
-            self.slot_bytes = slot
-            self.calls = 0
-            return True
-        except Exception as e:  # pragma: no cover - machine dependent
-            if dist.get_rank() == 0:
-                print(f"[dion_b200] symmetric memory unavailable for FSDP collectives ({type(e).__name__}: {e})")
-            self.arena = None
+        if self.arena is not None:
+            # kernels of every rank that still use the old arena must have retired
+            torch.cuda.synchronize(self.device)
+            dist.barrier(self.group)
+        slot = max(_MIN_BYTES, int(nbytes * 1.25))
+        slot = (slot + 255) // 256 * 256
+        self.arena = symm.create_arena(self.group, 2 * slot, self.device)
+        if self.arena is None:
+            self.declined = True
             self.slot_bytes = 0
+            if dist.get_rank() == 0:
+                print("[dion_b200] symmetric memory unavailable for FSDP collectives; using the library's")
             return False
+        self.slot_bytes = self.arena.capacity // 2 // 256 * 256
+        self.calls = 0
+        return True
 
     def slot_offset(self, index: int) -> int:
         """Byte offset of slot `index` from the arena base (flag block included)."""

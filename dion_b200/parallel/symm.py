@@ -28,6 +28,7 @@ import torch.distributed as dist
 from ..ops import runtime
 
 _FLAG_BYTES = 4096
+_WANT_OFF = 2048  # inside the flag block, far behind the flag words: one fp32 per rank, see post_want()
 _ALIGN = 256
 _MIN_ARENA = 8 << 20
 _RS_WAIT_NS = int(1.5e9)  # bound of the reduce-scatter kernel's waits for its peers
@@ -38,7 +39,11 @@ def _enabled() -> bool:
 
 
 class SymmetricArena:
-    def __init__(self, group: dist.ProcessGroup, nbytes: int, device: torch.device):
+    """Creating one is collective over `group` (rendezvous + barrier) and must be given the same
+    `nbytes` on every rank: use :func:`create_arena`, which agrees on both the size and on whether
+    every rank could allocate, unless the caller has that agreement by other means."""
+
+    def __init__(self, group: dist.ProcessGroup, nbytes: int, device: torch.device, buf: Optional[torch.Tensor] = None):
         import torch.distributed._symmetric_memory as symm_mem
 
         from ..ops import _ext
@@ -47,7 +52,8 @@ class SymmetricArena:
         self.group = group
         self.device = device
         self.capacity = int(nbytes)
-        self.buf = symm_mem.empty(self.capacity + _FLAG_BYTES, dtype=torch.uint8, device=device)
+        self.buf = buf if buf is not None else symm_mem.empty(self.capacity + _FLAG_BYTES, dtype=torch.uint8,
+                                                              device=device)
         self.buf.zero_()
         self.hdl = symm_mem.rendezvous(self.buf, group)
         self.rank = int(self.hdl.rank)
@@ -65,6 +71,11 @@ class SymmetricArena:
         self.cursor = 0
         self.high_water = 0
         self._views: Dict[int, int] = {}  # data_ptr -> byte offset inside the arena (flag block included)
+        # the group's agreement on how much memory a step needs (post_want / agreed_want)
+        self._want_view = self.buf[_WANT_OFF:_WANT_OFF + 4 * self.world].view(torch.float32)
+        self._want_src = torch.zeros(self.world, dtype=torch.float32, pin_memory=True)
+        self._want_host = torch.zeros(self.world, dtype=torch.float32, pin_memory=True)
+        self._want_event: Optional[torch.cuda.Event] = None
         torch.cuda.synchronize(device)
         dist.barrier(group)  # every rank's flag block is zero before anyone signals
 
@@ -104,6 +115,29 @@ class SymmetricArena:
     def peer_address(self, rank: int, t: torch.Tensor) -> int:
         return self.peers[rank] + self._views[t.data_ptr()]
 
+    # -- agreement on the size of the next arena
+    def post_want(self, nbytes: int) -> None:
+        """Tell the group how many bytes this rank's last step asked for.  Every rank puts its figure
+        (in MiB, exact in fp32) into its own element of a vector that the all-reduce kernel sums, and the
+        result travels to pinned host memory asynchronously; :meth:`agreed_want` reads it a step later, by
+        which time the copy has long finished, so the host never waits for the GPU."""
+        self._want_src.zero_()
+        self._want_src[self.rank] = float((int(nbytes) + (1 << 20) - 1) >> 20)
+        self._want_view.copy_(self._want_src, non_blocking=True)
+        self.all_reduce(self._want_view, _WANT_OFF, average=False)
+        self._want_host.copy_(self._want_view, non_blocking=True)
+        if self._want_event is None:
+            self._want_event = torch.cuda.Event()
+        self._want_event.record()
+
+    def agreed_want(self) -> Optional[int]:
+        """Largest request over the ranks of the group as of the last :meth:`post_want` (bytes), the same
+        number on every rank; None before the first one."""
+        if self._want_event is None:
+            return None
+        self._want_event.synchronize()
+        return int(self._want_host.max().item()) << 20
+
     # -- collectives (stream ordered on the current stream)
     def all_reduce(self, t: torch.Tensor, off: int, average: bool) -> None:
         self.epoch += 1
@@ -133,6 +167,8 @@ class SymmetricArena:
 
 _arenas: Dict[str, SymmetricArena] = {}
 _wanted: Dict[str, int] = {}
+_idle: Dict[str, int] = {}
+_declined: set = set()  # groups whose arena could not be created on some rank: library collectives for good
 _failed = False
 
 
@@ -152,33 +188,85 @@ def _usable(group: Optional[dist.ProcessGroup], device: torch.device) -> bool:
     return 1 < w <= 8
 
 
+def create_arena(group: dist.ProcessGroup, nbytes: int, device: torch.device) -> Optional[SymmetricArena]:
+    """Collective creation of an arena of at least `nbytes`.  The ranks first agree on the size (the
+    largest request wins), then each allocates, then they agree on whether every allocation succeeded;
+    only then do they enter the rendezvous.  Every rank therefore gets an arena of the same size or
+    None, never a mixture - a rank that ran out of memory does not leave its peers waiting in the
+    rendezvous, and no rank ends up on the in-tree kernels while another uses the library."""
+    import torch.distributed._symmetric_memory as symm_mem
+
+    size = torch.tensor([int(nbytes)], dtype=torch.int64, device=device)
+    dist.all_reduce(size, op=dist.ReduceOp.MAX, group=group)
+    nbytes = int(size.item())
+    buf, err = None, None
+    try:
+        buf = symm_mem.empty(nbytes + _FLAG_BYTES, dtype=torch.uint8, device=device)
+    except Exception as e:  # pragma: no cover - machine dependent
+        err = e
+    ok = torch.tensor([0 if buf is None else 1], dtype=torch.int32, device=device)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+    if int(ok.item()) == 0:
+        if err is not None:
+            print(f"[dion_b200] rank {dist.get_rank()}: symmetric allocation of {nbytes} bytes failed "
+                  f"({type(err).__name__}: {err})")
+        return None
+    return SymmetricArena(group, nbytes, device, buf=buf)
+
+
 def begin_step(groups, device: torch.device) -> None:
     """Reset (and if necessary create or grow) the arenas of `groups`.  Collective: every rank
-    calls it at the same point of every optimizer step."""
-    global _failed
+    calls it at the same point of every optimizer step with the same groups in the same order.
+
+    Whether an arena is created or replaced is decided from figures the whole group shares, never from
+    this rank's own bookkeeping: a group without an arena agrees on its first size with a (blocking)
+    all-reduce, which happens once or twice in the life of a group; a group with an arena exchanges the
+    ranks' needs through the arena itself every step (:meth:`SymmetricArena.post_want`) and acts on the
+    figure of the previous step, which every rank reads as the same number.  Requests are expected to be
+    the same on every rank of a group (uniform shards): a step that outgrows the arena then overflows to
+    ordinary memory - and the library collectives - on every rank alike."""
     for g in groups:
         if not _usable(g, device):
             continue
         k = _key(g)
+        if k in _declined:
+            continue
         arena = _arenas.get(k)
-        want = max(_wanted.get(k, 0), arena.high_water if arena else 0)
-        if arena is None or want > arena.capacity:
-            size = max(_MIN_ARENA, int(want * 1.25))
-            try:
-                _arenas[k] = SymmetricArena(g, size, device)
-            except Exception as e:  # pragma: no cover - machine dependent
-                _failed = True
-                if dist.get_rank() == 0:
-                    print(f"[dion_b200] symmetric memory unavailable ({type(e).__name__}: {e}); using library collectives")
-                return
+        local = max(_wanted.get(k, 0), arena.high_water if arena else 0)
+        if arena is None:
+            want = torch.tensor([local], dtype=torch.int64, device=device)
+            dist.all_reduce(want, op=dist.ReduceOp.MAX, group=g)
+            agreed = int(want.item())
+            if agreed == 0:
+                # nobody has asked for a buffer of this group yet; a group that stays unused stops asking
+                _idle[k] = _idle.get(k, 0) + 1
+                if _idle[k] >= 3:
+                    _declined.add(k)
+                continue
         else:
-            arena.reset()
+            agreed = arena.agreed_want()
+            if agreed is None or agreed <= arena.capacity:
+                arena.reset()
+                arena.post_want(local)
+                continue
+            # every kernel that uses the old arena has to retire on every rank before it is dropped
+            torch.cuda.synchronize(device)
+        new = create_arena(g, max(_MIN_ARENA, int(agreed * 1.25)), device)
+        if new is None:
+            _declined.add(k)
+            _arenas.pop(k, None)
+            if dist.get_rank() == 0:
+                print("[dion_b200] symmetric memory unavailable on some rank of a group; "
+                      "that group uses the library collectives")
+            continue
+        _arenas[k] = new
+        new.post_want(local)
 
 
 def empty(group: Optional[dist.ProcessGroup], shape, dtype, device) -> torch.Tensor:
     """Buffer that will be reduced over `group`: from the group's arena when it has room."""
     device = torch.device(device)
-    if _usable(group, device):
+    if _usable(group, device) and _key(group) not in _declined:
         arena = _arenas.get(_key(group))
         if arena is not None:
             t = arena.alloc(shape, dtype)

@@ -265,6 +265,7 @@ class CheckpointManager:
     into place by rank 0 (train.py:476-579)."""
 
     DEFAULT_NAME = "checkpoint"
+    OLD_SUFFIX = ".old"  # where save() sets the previous checkpoint aside while the new one takes its name
 
     def __init__(self, checkpoint_dir, model, optimizer, train_loader, val_loader, wandb_id=None):
         self.checkpoint_dir = checkpoint_dir
@@ -299,11 +300,18 @@ class CheckpointManager:
         dcp.save(self._state(), checkpoint_id=tmpdir)
         dist.barrier()
         if dist.get_rank() == 0:
+            # Swap by renames, so that a complete checkpoint exists at every instant: the previous one
+            # is set aside, the new one takes its name, and only then is the previous one deleted.
+            # load() looks at the set-aside copy when the name itself is missing.
+            old = path + self.OLD_SUFFIX
+            if os.path.isdir(old):
+                shutil.rmtree(old, ignore_errors=True)
             if os.path.isfile(path):
                 os.remove(path)
             elif os.path.isdir(path):
-                shutil.rmtree(path, ignore_errors=True)
-            shutil.move(tmpdir, path)
+                os.rename(path, old)
+            os.rename(tmpdir, path)
+            shutil.rmtree(old, ignore_errors=True)
         dist.barrier()
 
     def load(self, name: Optional[str] = None, allow_missing: bool = False):
@@ -312,6 +320,10 @@ class CheckpointManager:
 
         assert self.checkpoint_dir, "Checkpoint directory must be specified"
         path = os.path.join(self.checkpoint_dir, name or self.DEFAULT_NAME)
+        if not os.path.isdir(path) and os.path.isdir(path + self.OLD_SUFFIX):
+            # a writer died between the two renames of save(): the previous checkpoint is intact
+            path = path + self.OLD_SUFFIX
+            print0(f"Checkpoint swap was interrupted; falling back to {path}")
         if not os.path.isdir(path):
             if allow_missing:
                 print0(f"Checkpoint {path} does not exist, skipping load")

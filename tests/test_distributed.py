@@ -11,17 +11,28 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-def _launch(cases, nproc, force_cpu, timeout=600):
+def _free_port() -> int:
+    """A port the kernel just handed out as free (two test processes running side by side cannot be
+    given the same one, unlike a port derived from the process id)."""
+    import socket
+
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _launch(cases, nproc, force_cpu, timeout=600, multicast=False):
     env = dict(os.environ)
     env["DION_TEST_FORCE_CPU"] = "1" if force_cpu else "0"
     env.setdefault("TORCHDYNAMO_DISABLE", "1")
     # in-tree kernels on plain peer loads / stores and NCCL without NVLS: a rank that dies
     # must not leave multicast bindings behind
-    env["DION_B200_MULTICAST"] = "0"
+    env["DION_B200_MULTICAST"] = "1" if multicast else "0"
     env["NCCL_NVLS_ENABLE"] = "0"
+    env["DION_TEST_SOFT_FAIL"] = "1" if multicast else "0"
     env["OMP_NUM_THREADS"] = "2"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-           "--master-addr", "127.0.0.1", "--master-port", str(29600 + (os.getpid() % 300)),
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(HERE, "dist_worker.py"), *cases]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
     tail = (res.stdout[-3000:] + "\n" + res.stderr[-3000:])
@@ -51,6 +62,17 @@ def test_gpu_ranks(case):
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
     _launch([case], nproc=min(n, 4), force_cpu=False)
+
+
+@pytest.mark.gpu
+def test_gpu_symmetric_kernels_with_multimem():
+    """The multimem.ld_reduce / multimem.st instantiations of the collectives (the default outside the
+    tests).  No rank leaves early in this case: failures are recorded, the ranks agree on the verdict,
+    tear down in order and only then exit non-zero."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least 2 GPUs")
+    _launch(["symm_multicast"], nproc=min(n, 4), force_cpu=False, multicast=True)
 
 
 @pytest.mark.gpu

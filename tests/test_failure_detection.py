@@ -123,6 +123,65 @@ def test_checkpoint_write_is_atomic(tmp_path, monkeypatch):
         dist.destroy_process_group()
 
 
+def test_checkpoint_swap_interrupted_between_renames_falls_back_to_previous(tmp_path, monkeypatch):
+    """The writer dies after the previous checkpoint was set aside and before the new one took its
+    name: load() finds the set-aside copy."""
+    import shutil
+
+    import torch.distributed as dist
+
+    from dion_b200 import training
+
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", str(29930 - os.getpid() % 50))
+    if not dist.is_initialized():
+        dist.init_process_group("gloo", rank=0, world_size=1)
+    try:
+        model = torch.nn.Linear(8, 8, bias=False)
+        opt = torch.optim.SGD(model.parameters(), lr=0.1)
+
+        class Loader:
+            def state_dict(self):
+                return {"pos": 3}
+
+            def load_state_dict(self, sd):
+                self.loaded = sd
+
+        mgr = training.CheckpointManager(str(tmp_path), model, opt, Loader(), Loader())
+        mgr.save(step=1)
+        before = model.weight.detach().clone()
+        path = os.path.join(str(tmp_path), mgr.DEFAULT_NAME)
+
+        real_rename = os.rename
+        calls = []
+
+        def dying_rename(src, dst):
+            if path not in (str(src), str(dst)):
+                return real_rename(src, dst)  # the checkpoint writer's own renames inside its directory
+            calls.append((src, dst))
+            if len(calls) == 2:  # the first rename set the old checkpoint aside; the second never happens
+                raise RuntimeError("injected: writer died between the renames")
+            return real_rename(src, dst)
+
+        monkeypatch.setattr(os, "rename", dying_rename)
+        with torch.no_grad():
+            model.weight.add_(1.0)
+        with pytest.raises(RuntimeError, match="injected"):
+            mgr.save(step=2)
+        monkeypatch.setattr(os, "rename", real_rename)
+        assert not os.path.isdir(path) and os.path.isdir(path + mgr.OLD_SUFFIX)
+        with torch.no_grad():
+            model.weight.zero_()
+        mgr.load()
+        torch.testing.assert_close(model.weight.detach(), before)
+        # the next complete save cleans up
+        mgr.save(step=3)
+        assert os.path.isdir(path) and not os.path.isdir(path + mgr.OLD_SUFFIX)
+        shutil.rmtree(path)
+    finally:
+        dist.destroy_process_group()
+
+
 def test_reduce_scatter_hook_hands_out_symmetric_inputs_and_ordinary_outputs(monkeypatch):
     """Bookkeeping of the FSDP2 reduce-scatter hook, with a stand-in for the symmetric arena: the
     first buffer FSDP asks for (world * n elements) comes from alternating slots of the arena, the

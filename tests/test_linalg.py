@@ -50,6 +50,29 @@ def test_chol_inverse_kernel(r):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("r,batch", [(768, 80), (200, 7)])
+def test_chol_inverse_kernel_is_deterministic(r, batch):
+    """The two CTAs that share a matrix exchange their updates through global memory; whichever of them
+    runs ahead, the result must be the same to the last bit.  More matrices than CTA pairs fit on the
+    GPU, a second stream keeping the SMs busy, and a comparison with the single-CTA kernel's accuracy."""
+    P, G = _gram(batch, 2 * r, r, "cuda", cond=1.0)
+    Z0, _ = ops.chol_inverse(G)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    noise = torch.randn(4096, 4096, device="cuda")
+    for _ in range(3):
+        with torch.cuda.stream(side):
+            for _ in range(4):
+                noise = noise @ noise * 1e-3
+        Z, _ = ops.chol_inverse(G)
+        torch.cuda.synchronize()
+        assert torch.equal(Z, Z0)
+    Zr, _ = ops.chol_inverse_reference(G[:2].double())
+    rel = ((Z0[:2].double() - Zr.double()).norm() / Zr.double().norm()).item()
+    assert rel < 1e-2, rel
+
+
+@pytest.mark.gpu
 def test_chol_inverse_kernel_rank_deficient_and_zero():
     P = torch.randn(2, 512, 64, device="cuda")
     P[0, :, 10] = 0          # a zero column

@@ -197,7 +197,7 @@ def test_norm_branch_adds_both_gradients():
     (_ref_rms(xr) * g2.float()).sum().backward()
     _close(x.grad, xr.grad + g1.float(), 2e-2)
     assert torch.equal(xp, x)
-    _close(gx_pass, g1.float() + 0 * xr.grad, 1e-2) if False else None
+    _close(gx_pass, g1.float(), 1e-2)  # the pass-through output alone hands its gradient on unchanged
 
 
 @pytest.mark.gpu
