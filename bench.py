@@ -150,7 +150,8 @@ def emit(args, world, tokens_per_step, dev_ms, e2e_ms, clocks, extra):
             "h2d_bytes_per_step": extra.get("h2d_bytes_per_step"),
             "d2h_bytes_per_step": extra.get("d2h_bytes_per_step"),
         }
-    for k in ("gpu_launches", "optimizer_ms", "fwd_bwd_ms", "peak_mem_mib", "reference_mode"):
+    for k in ("gpu_launches", "optimizer_ms", "fwd_bwd_ms", "peak_mem_mib", "reference_mode", "reference_modes_ms",
+              "comm_paths"):
         if k in extra:
             line[k] = extra[k]
     print(json.dumps(line), flush=True)
@@ -199,6 +200,10 @@ def run_ours(args):
     staged = [loader.next_batch() for _ in range(args.steps)]
     staged = [(x.clone(), y.clone()) for x, y in staged]
     timers.reset()
+    from dion_b200.optim import orthogonalize
+    from dion_b200.parallel import symm
+
+    symm.reset_stats()
     launches0 = ops.launch_count()
     sampler = ClockSampler(gpu_index=local)
     barrier_sync()
@@ -225,6 +230,15 @@ def run_ours(args):
     launches = (ops.launch_count() - launches0) // max(args.steps, 1)
     phases = timers.max_over_ranks()
     ops.check_status()
+    # which implementation carried each kind of collective in the device-timed region (per step), and
+    # whether the all-gather kernel for the orthonormal factors passed its first-use comparison
+    comm_paths = {k: v // max(args.steps, 1) for k, v in sorted(symm.stats.items())}
+    comm_paths["gradient_all_reduce"] = "torch DDP buckets (NCCL), overlapped with backward" if world > 1 else "none (one GPU)"
+    gatherers = list(orthogonalize._gatherers.values())
+    if gatherers:
+        comm_paths["factor_all_gather"] = ("in-tree kernel (first-use comparison passed)"
+                                           if all(g.fn is not None and g.checked for g in gatherers)
+                                           else "process group (kernel unavailable or failed its first-use comparison)")
 
     # ---- end-to-end region: pinned-host batches through the loader, loss read every step
     e2e_ms = None
@@ -243,6 +257,7 @@ def run_ours(args):
         "h2d_bytes_per_step": loader.h2d_bytes_per_batch,
         "d2h_bytes_per_step": 4,
         "peak_mem_mib": torch.cuda.max_memory_allocated() // (1 << 20),
+        "comm_paths": comm_paths,
     }
     if rank == 0:
         emit(args, world, tokens_per_step, dev_ms, e2e_ms, clocks, extra)
@@ -304,8 +319,13 @@ def run_reference(args):
     autocast = torch.amp.autocast(device_type="cuda", dtype=torch.bfloat16)
 
     def build(compiled: bool):
-        """Model, optimizer and step function exactly as the reference trainer sets them up
-        (train.py:674-737, 886-921); `compiled=False` is its --no_compile mode with dynamo off."""
+        """Model, optimizers and step functions exactly as the reference trainer sets them up
+        (train.py:674-737, 886-921); `compiled=False` is its --no_compile mode with dynamo off.
+        Returns {mode name: step function}.  For Dion the reference has two ways of synchronising
+        gradients over the data-parallel replicas, both a matter of one constructor argument / YAML key:
+        `replicate_mesh_grad_sync: true` (its Dion YAMLs; the optimizer all-reduces after a backward
+        pass under DDP.no_sync) and `false` (DDP's bucketed all-reduce overlapped with the backward pass).
+        Both are built on the same model - one optimizer object each - and the faster one is reported."""
         torch.manual_seed(1234)
         cfg = RefCfg(sequence_len=MODEL["sequence_length"], vocab_size=MODEL["vocab_size"], n_layer=args.layers,
                      n_head=MODEL["n_head"], n_embd=MODEL["model_dim"])
@@ -323,45 +343,56 @@ def run_reference(args):
             dict(params=list(raw.lm_head.parameters()), algorithm=HP["scalar_opt"],
                  lr=HP["lr"] / math.sqrt(MODEL["model_dim"]), betas=(0.95, 0.98), weight_decay=0),
         ]
-        sync_in_opt = args.optimizer == "dion"  # replicate_mesh_grad_sync: true in configs/dion_160m.yaml
+        def make_step(opt, sync_in_opt):
+            def step(x, y):
+                model.train()
+                with autocast:
+                    loss = model(x, y)
+                out = loss.detach()
+                if sync_in_opt:
+                    with model.no_sync():
+                        loss.backward()
+                else:
+                    loss.backward()
+                opt.step()
+                model.zero_grad(set_to_none=True)
+                return out
+
+            return step
+
+        def copy_groups():
+            return [dict(g, params=list(g["params"])) for g in groups]
+
         if args.optimizer == "dion":
             mp = None if args.fp32_states else RefMP(momentum_dtype=torch.bfloat16, variance_dtype=torch.bfloat16,
                                                      Q_dtype=torch.bfloat16)
-            opt = RefDion(groups, replicate_mesh=model.process_group, replicate_mesh_grad_sync=True,
-                          rank_fraction=HP["rank_fraction"], lr=HP["lr"], mu=HP["mu"],
-                          weight_decay=HP["weight_decay"], mixed_precision_config=mp)
-        else:
-            opt = RefMuon(groups, distributed_mesh=model.process_group, lr=HP["lr"], mu=HP["mu"],
-                          weight_decay=HP["weight_decay"], nesterov=True, adjust_lr="spectral_norm",
-                          use_triton=compiled)
-
-        def step(x, y):
-            model.train()
-            with autocast:
-                loss = model(x, y)
-            out = loss.detach()
-            if sync_in_opt:
-                with model.no_sync():
-                    loss.backward()
-            else:
-                loss.backward()
-            opt.step()
-            model.zero_grad(set_to_none=True)
-            return out
-
-        return step
+            steps = {}
+            for name, sync_in_opt in (("replicate_mesh_grad_sync=True under DDP.no_sync", True),
+                                      ("replicate_mesh_grad_sync=False, DDP gradient all-reduce", False)):
+                if world == 1 and not sync_in_opt:
+                    continue  # one GPU: there is nothing to synchronise, the two modes are the same program
+                opt = RefDion(copy_groups(), replicate_mesh=model.process_group, replicate_mesh_grad_sync=sync_in_opt,
+                              rank_fraction=HP["rank_fraction"], lr=HP["lr"], mu=HP["mu"],
+                              weight_decay=HP["weight_decay"], mixed_precision_config=mp)
+                steps[name] = make_step(opt, sync_in_opt)
+            return steps
+        opt = RefMuon(groups, distributed_mesh=model.process_group, lr=HP["lr"], mu=HP["mu"],
+                      weight_decay=HP["weight_decay"], nesterov=True, adjust_lr="spectral_norm",
+                      use_triton=compiled)
+        return {"DDP gradient all-reduce": make_step(opt, False)}
 
     tokens_per_step = args.device_batch * MODEL["sequence_length"] * world
-    total_steps = args.warmup + 2 * args.steps + 2
+    total_steps = 2 * args.warmup + 2 * args.steps + 10
     data_dir = make_data(args, rank, world, total_steps)
     loader = RefLoader(os.path.join(data_dir, "fineweb_train_*.bin"), args.device_batch, MODEL["sequence_length"],
                        rank, world)
     mode = "torch.compile (reference default)"
-    step = build(compiled=True)
+    steps = build(compiled=True)
     first = loader.next_batch()
     try:
-        loss = step(*first)
-        float(loss.item())
+        for fn in steps.values():
+            loss = fn(*first)
+            float(loss.item())
     except Exception as e:  # the compiler stack is unusable on this machine: run the reference eagerly
         msg = f"{type(e).__name__}: {str(e).splitlines()[-1] if str(e) else ''}"[:200]
         import traceback
@@ -372,11 +403,28 @@ def run_reference(args):
         torch._dynamo.reset()
         torch._dynamo.config.disable = True
         mode = f"eager, dynamo disabled (torch.compile failed here: {msg})"
-        step = build(compiled=False)
-        loss = step(*first)
-    for _ in range(max(args.warmup - 1, 0)):
-        loss = step(*loader.next_batch())
-    float(loss.item())
+        steps = build(compiled=False)
+        for fn in steps.values():
+            loss = fn(*first)
+    # every mode gets the full warm-up, then a short device-timed trial; the fastest mode is the one measured
+    trial_ms = {}
+    for name, fn in steps.items():
+        for _ in range(max(args.warmup - 1, 0)):
+            loss = fn(*loader.next_batch())
+        float(loss.item())
+        if len(steps) > 1:
+            trial = [loader.next_batch() for _ in range(3)]
+            barrier_sync()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for x, y in trial:
+                loss = fn(x, y)
+            t1.record()
+            barrier_sync()
+            trial_ms[name] = round(max_over_ranks(t0.elapsed_time(t1) / len(trial)), 2)
+    best = min(trial_ms, key=trial_ms.get) if trial_ms else next(iter(steps))
+    step = steps[best]
+    mode = f"{mode}; gradient sync: {best}"
     staged = [loader.next_batch() for _ in range(args.steps)]
     sampler = ClockSampler(gpu_index=local)
     barrier_sync()
@@ -400,6 +448,8 @@ def run_reference(args):
         e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1000.0 / args.steps)
     extra = {"h2d_bytes_per_step": 2 * args.device_batch * MODEL["sequence_length"] * 8, "d2h_bytes_per_step": 4,
              "peak_mem_mib": torch.cuda.max_memory_allocated() // (1 << 20), "reference_mode": mode}
+    if trial_ms:
+        extra["reference_modes_ms"] = trial_ms
     if rank == 0:
         emit(args, world, tokens_per_step, dev_ms, e2e_ms, clocks, extra)
     dist.destroy_process_group()

@@ -6,6 +6,10 @@ kernels (benchmark/benchmark_newton_shultz.py:33-101, 173).
     python benchmark/benchmark_newton_schulz.py --grid            # 512 ... 8192, square
     python benchmark/benchmark_newton_schulz.py --batch_size 12 --m 768 --n 3072
 
+`--triton_ref` adds a third arm: the reference's own Triton kernels (``newton_schulz_triton`` of the
+unmodified reference package installed under baseline/_ref, dion/newton_schulz_triton.py:337-374,
+timed like benchmark/benchmark_newton_shultz.py:49-101 does), on the same inputs and the same box.
+
 FLOPs per iteration are counted as ``4 m^2 n + 2 m^3`` (m <= n), i.e. without crediting the
 symmetric products, so both implementations are measured against the same amount of work.
 Timing: CUDA events on the launching stream, after warm-up, L2 flushed between iterations.
@@ -32,7 +36,40 @@ def ns_flops(m: int, n: int, batch: int = 1, iters: int = len(NS_COEFFS)) -> flo
     return float(batch) * iters * (4.0 * m * m * n + 2.0 * m ** 3)
 
 
-def bench_one(m: int, n: int, batch: int, iters: int = 10):
+_triton_fn = None
+_triton_why = None
+
+
+def reference_triton_newton_schulz():
+    """The reference's ``newton_schulz_triton`` (imported from baseline/_ref, unmodified), or None with
+    the reason in ``_triton_why`` when it cannot be used on this machine."""
+    global _triton_fn, _triton_why
+    if _triton_fn is not None or _triton_why is not None:
+        return _triton_fn
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref_dir = os.path.join(root, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "dion")):
+        _triton_why = "baseline/_ref is not installed"
+        return None
+    # Inductor's host-side code needs a C++ compiler with OpenMP; some images put one first on PATH that lacks it
+    if not os.environ.get("CXX") and os.path.exists("/usr/bin/g++"):
+        os.environ["CXX"] = "/usr/bin/g++"
+    sys.path.insert(0, ref_dir)
+    for name in [m for m in sys.modules if m == "dion" or m.startswith("dion.")]:
+        del sys.modules[name]
+    try:
+        from dion.newton_schulz_triton import newton_schulz_triton
+
+        _triton_fn = newton_schulz_triton
+    except Exception as e:
+        _triton_why = f"import failed: {type(e).__name__}: {e}"[:200]
+    finally:
+        sys.path.remove(ref_dir)
+    return _triton_fn
+
+
+def bench_one(m: int, n: int, batch: int, iters: int = 10, triton_ref: bool = False):
+    global _triton_fn, _triton_why
     shape = (batch, m, n) if batch > 1 else (m, n)
     G = torch.randn(shape, device="cuda", dtype=torch.bfloat16)
     ours = cuda_time_ms(lambda: newton_schulz(G), iters=iters, warmup=3, flush_l2=True)
@@ -40,7 +77,7 @@ def bench_one(m: int, n: int, batch: int, iters: int = 10):
     fl = ns_flops(m, n, batch)
     e = max(m, n) / min(m, n)
     err = (newton_schulz(G).float() - newton_schulz_torch(G).float()).abs().max().item()
-    return {
+    row = {
         "m": m, "n": n, "batch": batch,
         "tcgen05_ms": ours, "tcgen05_tflops": fl / ours / 1e9,
         "torch_ms": ref, "torch_tflops": fl / ref / 1e9,
@@ -48,6 +85,18 @@ def bench_one(m: int, n: int, batch: int, iters: int = 10):
         "max_theoretical_speedup_from_symmetry": (4 * e + 2) / (3 * e + 1),
         "max_abs_diff": err,
     }
+    if triton_ref:
+        fn = reference_triton_newton_schulz()
+        if fn is not None:
+            try:
+                fn(G)  # compile + autotune
+                tri = cuda_time_ms(lambda: fn(G), iters=iters, warmup=3, flush_l2=True)
+                row.update(triton_ref_ms=tri, triton_ref_tflops=fl / tri / 1e9, speedup_vs_triton_ref=tri / ours)
+            except Exception as ex:  # the compiler stack may be unusable on a machine
+                _triton_fn, _triton_why = None, f"{type(ex).__name__}: {str(ex).splitlines()[-1] if str(ex) else ''}"[:200]
+        if _triton_why is not None:
+            row["triton_ref_unavailable"] = _triton_why
+    return row
 
 
 def main():
@@ -59,19 +108,31 @@ def main():
     ap.add_argument("--grid", action="store_true", help="square sizes 512 ... 8192")
     ap.add_argument("--expansion", type=int, default=1, help="n = expansion * m for --grid")
     ap.add_argument("--json", type=str, default=None, help="write the rows to this file")
+    ap.add_argument("--triton_ref", action="store_true", help="also time the reference's Triton kernels (baseline/_ref)")
+    ap.add_argument("--shapes", type=str, default=None,
+                    help="several points in one run: comma-separated batch x m x n, e.g. 1x4096x4096,12x768x3072")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("a CUDA device is required")
     rows = []
-    if a.grid:
+    if a.shapes:
+        for item in a.shapes.split(","):
+            b, m, n = (int(v) for v in item.lower().split("x"))
+            rows.append(bench_one(m, n, b, triton_ref=a.triton_ref))
+    elif a.grid:
         for m in (512, 1024, 2048, 4096, 8192):
-            rows.append(bench_one(m, m * a.expansion, a.batch_size))
+            rows.append(bench_one(m, m * a.expansion, a.batch_size, triton_ref=a.triton_ref))
     else:
-        rows.append(bench_one(a.m, a.n, a.batch_size))
+        rows.append(bench_one(a.m, a.n, a.batch_size, triton_ref=a.triton_ref))
     for r in rows:
+        tri = ""
+        if "triton_ref_ms" in r:
+            tri = f" | reference Triton {r['triton_ref_ms']:8.3f} ms {r['triton_ref_tflops']:7.1f} TF (x{r['speedup_vs_triton_ref']:.2f})"
+        elif "triton_ref_unavailable" in r:
+            tri = f" | reference Triton unavailable: {r['triton_ref_unavailable']}"
         print(f"{r['batch']:3d} x {r['m']:5d} x {r['n']:5d} | tcgen05 {r['tcgen05_ms']:8.3f} ms {r['tcgen05_tflops']:7.1f} TF"
               f" | torch {r['torch_ms']:8.3f} ms {r['torch_tflops']:7.1f} TF | x{r['speedup']:.2f}"
-              f" (symmetry bound x{r['max_theoretical_speedup_from_symmetry']:.2f}) | max diff {r['max_abs_diff']:.3e}")
+              f" (symmetry bound x{r['max_theoretical_speedup_from_symmetry']:.2f}) | max diff {r['max_abs_diff']:.3e}{tri}")
     if a.json:
         with open(a.json, "w") as f:
             json.dump(rows, f, indent=1)

@@ -76,7 +76,7 @@ void gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, Tens
           const std::optional<Tensor>& d2, const std::optional<Tensor>& c_ptrs,
           const std::optional<Tensor>& d_ptrs, const std::optional<Tensor>& d2_ptrs, double alpha, double beta,
           int64_t act, int64_t epilogue, int64_t split_k, bool symmetric, int64_t block_n, int64_t pair,
-          const std::optional<Tensor>& status) {
+          const std::optional<Tensor>& status, int64_t d_dup) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda(), "gemm operands must be CUDA tensors");
   TORCH_CHECK(a.scalar_type() == b.scalar_type(), "gemm operands must share a dtype");
   TORCH_CHECK(a.dim() == b.dim(), "gemm operands must both be 2-D or both 3-D");
@@ -105,9 +105,12 @@ void gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, Tens
   // Per-batch pointer arrays (int64 CUDA tensors) describe outputs that are separate
   // allocations; `d` / `c` then only supply dtype, shape and pitch of one element.
   if (d_ptrs.has_value()) {
-    TORCH_CHECK(d_ptrs->scalar_type() == at::kLong && d_ptrs->is_cuda() && d_ptrs->numel() >= g.batch);
+    TORCH_CHECK(d_dup >= 1 && d_dup <= dion::kMaxPeers, "d_dup out of range");
+    TORCH_CHECK(d_ptrs->scalar_type() == at::kLong && d_ptrs->is_cuda() && d_ptrs->is_contiguous() &&
+                d_ptrs->numel() >= g.batch * d_dup);
     TORCH_CHECK(d.dim() == 2 && d.size(0) == g.M && d.size(1) == g.N && d.stride(1) == 1);
     g.d_ptrs = reinterpret_cast<void* const*>(d_ptrs->data_ptr<int64_t>());
+    g.d_dup = (int)d_dup;
   } else {
     check_out(d, g.batch, g.M, g.N, "d");
     g.d_batch_stride = d.dim() == 3 ? d.stride(0) : 0;
@@ -646,6 +649,161 @@ void symm_reduce_into(const Tensor& src, Tensor dst, at::IntArrayRef peers, int6
                                                 status.data_ptr<int>(), at::cuda::getCurrentCUDAStream()));
 }
 
+// ----------------------------------------------------------------------------- fused reductions of Dion
+
+dion::SlotWait slot_wait(at::IntArrayRef peers, int64_t flag_off, int64_t channel, int64_t rank, int64_t epoch,
+                         int64_t budget_ns) {
+  dion::SlotWait w;
+  memset(&w, 0, sizeof(w));
+  TORCH_CHECK((int)peers.size() <= dion::kMaxPeers, "at most ", dion::kMaxPeers, " peers are supported");
+  for (size_t i = 0; i < peers.size(); ++i) w.peers.ptrs[i] = reinterpret_cast<void*>(peers[i]);
+  w.flag_off = flag_off;
+  w.channel = (int)channel;
+  w.rank = (int)rank;
+  w.world = (int)peers.size();
+  w.epoch = (unsigned)epoch;
+  w.budget_ns = (unsigned long long)budget_ns;
+  return w;
+}
+
+// slots: fp32 [nslots, ...] (a view into this rank's arena); out / hi / lo: fp32 tensors of one slot's size;
+// dests: raw addresses that also receive the sum (peer memory); peers empty = nothing to wait for.
+void slot_reduce(const Tensor& slots, const std::optional<Tensor>& out, const std::optional<Tensor>& hi,
+                 const std::optional<Tensor>& lo, at::IntArrayRef dests, double scale, at::IntArrayRef peers,
+                 int64_t flag_off, int64_t channel, int64_t rank, int64_t epoch, int64_t budget_ns, Tensor status) {
+  const c10::cuda::CUDAGuard guard(slots.device());
+  // slot s may be a leading part of a larger slot (stride(0) is free), but is contiguous in itself
+  TORCH_CHECK(slots.is_cuda() && slots.scalar_type() == at::kFloat && slots.dim() >= 2 && slots.size(0) >= 1 &&
+              (slots.numel() == 0 || slots.select(0, 0).is_contiguous()));
+  dion::SlotReduceArgs a;
+  memset(&a, 0, sizeof(a));
+  a.wait = slot_wait(peers, flag_off, channel, rank, epoch, budget_ns);
+  a.slots = slots.data_ptr<float>();
+  a.nslots = (int)slots.size(0);
+  a.slot_stride = slots.stride(0);
+  a.numel = slots.numel() / slots.size(0);
+  a.scale = (float)scale;
+  auto local = [&](const std::optional<Tensor>& t, const char* what) -> float* {
+    if (!t.has_value()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == a.numel, what,
+                " must be a contiguous fp32 tensor of one slot's size");
+    return t->data_ptr<float>();
+  };
+  a.out = local(out, "out");
+  a.hi = local(hi, "hi");
+  a.lo = local(lo, "lo");
+  TORCH_CHECK((int)dests.size() <= dion::kMaxPeers);
+  a.ndest = (int)dests.size();
+  for (size_t i = 0; i < dests.size(); ++i) a.dest[i] = reinterpret_cast<float*>(dests[i]);
+  a.status = status.data_ptr<int>();
+  ++g_launches;
+  DION_CUDA_CHECK(dion::slot_reduce_launch(a, at::cuda::getCurrentCUDAStream()));
+}
+
+void dion_r_post(const Tensor& slots, double scale, const std::optional<Tensor>& nonzero, const Tensor& Qm,
+                 const std::optional<Tensor>& P, const std::optional<Tensor>& R32, const std::optional<Tensor>& Rm,
+                 const std::optional<Tensor>& ss, bool finish, double eps, const std::optional<Tensor>& Qn,
+                 const std::optional<Tensor>& Qs, int64_t qs_col0, at::IntArrayRef peers, int64_t flag_off,
+                 int64_t channel, int64_t rank, int64_t epoch, int64_t budget_ns, Tensor status) {
+  const c10::cuda::CUDAGuard guard(slots.device());
+  TORCH_CHECK(slots.is_cuda() && slots.scalar_type() == at::kFloat && slots.dim() == 4 && slots.is_contiguous(),
+              "slots must be contiguous fp32 [nslots, B, n, r]");
+  dion::RPostArgs a;
+  memset(&a, 0, sizeof(a));
+  a.wait = slot_wait(peers, flag_off, channel, rank, epoch, budget_ns);
+  a.slots = slots.data_ptr<float>();
+  a.nslots = (int)slots.size(0);
+  a.slot_stride = slots.stride(0);
+  a.scale = (float)scale;
+  a.B = (int)slots.size(1);
+  a.n = (int)slots.size(2);
+  a.r = (int)slots.size(3);
+  const int64_t numel = (int64_t)a.B * a.n * a.r;
+  if (nonzero.has_value()) {
+    TORCH_CHECK(nonzero->scalar_type() == at::kInt && nonzero->numel() >= a.B && nonzero->is_contiguous());
+    a.nonzero = nonzero->data_ptr<int>();
+  }
+  TORCH_CHECK(Qm.dim() == 3 && Qm.size(0) == a.B && Qm.size(1) == a.n && Qm.size(2) == a.r && Qm.stride(2) == 1,
+              "Qm must be [B, n, r] with unit column stride");
+  a.Qm = Qm.data_ptr();
+  a.q_type = elem_type(Qm, "Qm");
+  a.q_ld = Qm.stride(1);
+  a.q_bs = Qm.stride(0);
+  if (P.has_value()) {
+    TORCH_CHECK(P->dim() == 3 && P->size(0) == a.B && P->size(2) == a.r && P->stride(2) == 1,
+                "P must be [B, m, r] with unit column stride");
+    a.P = P->data_ptr();
+    a.p_type = elem_type(*P, "P");
+    a.p_rows = P->size(1);
+    a.p_ld = P->stride(1);
+    a.p_bs = P->stride(0);
+  }
+  if (R32.has_value()) {
+    TORCH_CHECK(R32->scalar_type() == at::kFloat && R32->is_contiguous() && R32->numel() == numel);
+    a.R32 = R32->data_ptr<float>();
+  }
+  if (Rm.has_value()) {
+    TORCH_CHECK(Rm->is_contiguous() && Rm->numel() == numel);
+    a.Rm = Rm->data_ptr();
+    a.rm_type = elem_type(*Rm, "Rm");
+  }
+  if (ss.has_value()) {
+    TORCH_CHECK(ss->scalar_type() == at::kFloat && ss->is_contiguous() && ss->numel() == (int64_t)a.B * a.r);
+    a.ss = ss->data_ptr<float>();
+  }
+  a.finish = finish ? 1 : 0;
+  a.eps = (float)eps;
+  if (Qn.has_value()) {
+    TORCH_CHECK(Qn->is_contiguous() && Qn->numel() == numel);
+    a.Qn = Qn->data_ptr();
+    a.qn_type = elem_type(*Qn, "Qn");
+  }
+  if (Qs.has_value()) {
+    TORCH_CHECK(Qs->dim() == 3 && Qs->is_contiguous() && Qs->size(0) == a.B && Qs->size(1) == a.n);
+    a.Qs = Qs->data_ptr();
+    a.qs_type = elem_type(*Qs, "Qs");
+    a.qs_col0 = (int)qs_col0;
+    a.qs_cols = (int)Qs->size(2);
+  }
+  a.status = status.data_ptr<int>();
+  ++g_launches;
+  DION_CUDA_CHECK(dion::r_post_launch(a, at::cuda::getCurrentCUDAStream()));
+}
+
+void dion_q_norm(const Tensor& R32, const Tensor& ss, const Tensor& Qm, double eps, const std::optional<Tensor>& Qn,
+                 const std::optional<Tensor>& Qs, int64_t qs_col0) {
+  const c10::cuda::CUDAGuard guard(R32.device());
+  TORCH_CHECK(R32.is_cuda() && R32.scalar_type() == at::kFloat && R32.dim() == 3 && R32.is_contiguous());
+  dion::QNormArgs a;
+  memset(&a, 0, sizeof(a));
+  a.R32 = R32.data_ptr<float>();
+  a.B = (int)R32.size(0);
+  a.n = (int)R32.size(1);
+  a.r = (int)R32.size(2);
+  TORCH_CHECK(ss.scalar_type() == at::kFloat && ss.is_contiguous() && ss.numel() == (int64_t)a.B * a.r);
+  a.ss = ss.data_ptr<float>();
+  a.eps = (float)eps;
+  TORCH_CHECK(Qm.dim() == 3 && Qm.size(0) == a.B && Qm.size(1) == a.n && Qm.size(2) == a.r && Qm.stride(2) == 1);
+  a.Qm = Qm.data_ptr();
+  a.q_type = elem_type(Qm, "Qm");
+  a.q_ld = Qm.stride(1);
+  a.q_bs = Qm.stride(0);
+  if (Qn.has_value()) {
+    TORCH_CHECK(Qn->is_contiguous() && Qn->numel() == R32.numel());
+    a.Qn = Qn->data_ptr();
+    a.qn_type = elem_type(*Qn, "Qn");
+  }
+  if (Qs.has_value()) {
+    TORCH_CHECK(Qs->dim() == 3 && Qs->is_contiguous() && Qs->size(0) == a.B && Qs->size(1) == a.n);
+    a.Qs = Qs->data_ptr();
+    a.qs_type = elem_type(*Qs, "Qs");
+    a.qs_col0 = (int)qs_col0;
+    a.qs_cols = (int)Qs->size(2);
+  }
+  ++g_launches;
+  DION_CUDA_CHECK(dion::q_norm_launch(a, at::cuda::getCurrentCUDAStream()));
+}
+
 // q [B, T, H, D], k / v [B, T, Hkv, D] (contiguous bf16) -> out [B, T, H, D], lse [B, H, T]
 void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor out, Tensor lse, double scale, Tensor status) {
   const c10::cuda::CUDAGuard guard(q.device());
@@ -762,7 +920,7 @@ TORCH_LIBRARY(dion_b200, m) {
   m.def(
       "gemm(Tensor a, Tensor b, Tensor? c, Tensor(a!) d, Tensor(b!)? d2, Tensor? c_ptrs, Tensor? d_ptrs, "
       "Tensor? d2_ptrs, float alpha, float beta, int act, int epilogue, int split_k, bool symmetric, "
-      "int block_n, int pair, Tensor? status) -> ()");
+      "int block_n, int pair, Tensor? status, int d_dup=1) -> ()");
   m.def(
       "adamw_multi(Tensor(a!)[] X, Tensor[] G, Tensor(b!)[] M, Tensor(c!)[] V, Tensor(d!)[] shadow, float lr, "
       "float beta1, float beta2, float weight_decay, float eps, int step) -> ()");
@@ -798,6 +956,14 @@ TORCH_LIBRARY(dion_b200, m) {
       "attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, Tensor lse, Tensor(a!) delta, Tensor(b!) dq, "
       "Tensor(c!) dk, Tensor(d!) dv, float scale, Tensor(e!) status) -> ()");
   m.def("refine_prep(Tensor G, Tensor(a!) C, Tensor(b!) d, float dead_below, Tensor? skip) -> ()");
+  m.def(
+      "slot_reduce(Tensor slots, Tensor(a!)? out, Tensor(b!)? hi, Tensor(c!)? lo, int[] dests, float scale, int[] peers, "
+      "int flag_off, int channel, int rank, int epoch, int budget_ns, Tensor(d!) status) -> ()");
+  m.def(
+      "dion_r_post(Tensor slots, float scale, Tensor? nonzero, Tensor Qm, Tensor(a!)? P, Tensor(b!)? R32, Tensor(c!)? Rm, "
+      "Tensor(d!)? ss, bool finish, float eps, Tensor(e!)? Qn, Tensor(f!)? Qs, int qs_col0, int[] peers, int flag_off, "
+      "int channel, int rank, int epoch, int budget_ns, Tensor(g!) status) -> ()");
+  m.def("dion_q_norm(Tensor R32, Tensor ss, Tensor Qm, float eps, Tensor(a!)? Qn, Tensor(b!)? Qs, int qs_col0) -> ()");
   m.def("launch_count() -> int", &launch_count);
   m.def("gemm_gather_plan(int M, int N, int K, int rows, int world, int rank) -> int[]", &gemm_gather_plan);
 }
@@ -821,6 +987,9 @@ TORCH_LIBRARY_IMPL(dion_b200, CUDA, m) {
   m.impl("attn_fwd", &attn_fwd);
   m.impl("attn_bwd", &attn_bwd);
   m.impl("refine_prep", &refine_prep);
+  m.impl("slot_reduce", &slot_reduce);
+  m.impl("dion_r_post", &dion_r_post);
+  m.impl("dion_q_norm", &dion_q_norm);
   m.impl("gemm_scatter", &gemm_scatter);
   m.impl("gemm_gather", &gemm_gather);
   m.impl("symm_barrier", &symm_barrier);

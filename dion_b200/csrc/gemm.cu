@@ -72,6 +72,7 @@ struct KernelParams {
   int d_is_bf16;
   long long ldd, d_batch_stride;
   void* const* d_ptrs;
+  int d_dup;  // destinations per batch element in d_ptrs (>= 1)
   void* D2;
   long long ldd2, d2_batch_stride;
   void* const* d2_ptrs;
@@ -646,9 +647,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         c_base = p.c_ptrs ? reinterpret_cast<const char*>(p.c_ptrs[t.batch])
                           : reinterpret_cast<const char*>(p.C) +
                                 (long long)t.batch * p.c_batch_stride * (p.c_is_bf16 ? 2 : 4);
-      d_base = p.d_ptrs ? reinterpret_cast<char*>(p.d_ptrs[t.batch])
+      d_base = p.d_ptrs ? reinterpret_cast<char*>(p.d_ptrs[(long long)t.batch * p.d_dup])
                         : reinterpret_cast<char*>(p.D) +
                               (long long)t.batch * p.d_batch_stride * (p.d_is_bf16 ? 2 : 4);
+      const int ndup = p.d_ptrs ? p.d_dup : 1;
       if (p.D2 || p.d2_ptrs)
         d2_base = p.d2_ptrs ? reinterpret_cast<char*>(p.d2_ptrs[t.batch])
                             : reinterpret_cast<char*>(p.D2) + (long long)t.batch * p.d2_batch_stride * 2;
@@ -773,32 +775,37 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
           if (stage_d) {
             auto d_row = [&](int grow) { return d_addr(grow, col0); };
-            if (p.d_is_bf16) {
-              stage_put_bf16(st, lane, 0, v);
-              __syncwarp();
-              stage_flush<4>(st, lane, row_first, p.M, d_row);
-            } else {
-              stage_put_f32(st, lane, v);
-              __syncwarp();
-              stage_flush<8>(st, lane, row_first, p.M, d_row);
+            if (p.d_is_bf16) stage_put_bf16(st, lane, 0, v);
+            else stage_put_f32(st, lane, v);
+            __syncwarp();
+            // the staged block goes to every destination of this batch element (d_addr reads d_base)
+            for (int dup = 0; dup < ndup; ++dup) {
+              if (dup > 0) d_base = reinterpret_cast<char*>(p.d_ptrs[(long long)t.batch * p.d_dup + dup]);
+              if (p.d_is_bf16) stage_flush<4>(st, lane, row_first, p.M, d_row);
+              else stage_flush<8>(st, lane, row_first, p.M, d_row);
             }
             __syncwarp();
           } else if (row_ok) {
-            char* dptr = d_addr(row, col0);
-            if (p.d_is_bf16) {
-              store_chunk_bf16(reinterpret_cast<__nv_bfloat16*>(dptr), v, full_cols && p.vec_d, ncols);
-            } else {
-              float* dp = reinterpret_cast<float*>(dptr);
-              if (full_cols && p.vec_d) {
-#pragma unroll
-                for (int i = 0; i < 32; i += 4)
-                  *reinterpret_cast<float4*>(dp + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+            for (int dup = 0; dup < ndup; ++dup) {
+              if (dup > 0) d_base = reinterpret_cast<char*>(p.d_ptrs[(long long)t.batch * p.d_dup + dup]);
+              char* dptr = d_addr(row, col0);
+              if (p.d_is_bf16) {
+                store_chunk_bf16(reinterpret_cast<__nv_bfloat16*>(dptr), v, full_cols && p.vec_d, ncols);
               } else {
-                for (int i = 0; i < 32; ++i)
-                  if (col0 + i < p.N) dp[i] = v[i];
+                float* dp = reinterpret_cast<float*>(dptr);
+                if (full_cols && p.vec_d) {
+#pragma unroll
+                  for (int i = 0; i < 32; i += 4)
+                    *reinterpret_cast<float4*>(dp + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                } else {
+                  for (int i = 0; i < 32; ++i)
+                    if (col0 + i < p.N) dp[i] = v[i];
+                }
               }
             }
           }
+          // later chunks of this tile start from the first destination again
+          if (ndup > 1) d_base = reinterpret_cast<char*>(p.d_ptrs[(long long)t.batch * p.d_dup]);
           if (d2_base != nullptr && !d2_done) emit_d2();
           if (mirror && row_ok) {
             // transposed copy of an off-diagonal tile: D[col, row]; lanes hold
@@ -1107,6 +1114,10 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
     g_last_error = "GEMM output missing";
     return cudaErrorInvalidValue;
   }
+  if (a.d_dup > 1 && (!a.d_ptrs || a.symmetric || a.scatter_mode != 0 || a.epilogue != kEpiStore)) {
+    g_last_error = "several destinations per batch element need d_ptrs and a plain store epilogue";
+    return cudaErrorInvalidValue;
+  }
   if (a.scatter_mode != 0) {
     if (!a.scatter_ptrs || a.scatter_block <= 0 || a.scatter_dests <= 0 || a.symmetric ||
         a.epilogue != kEpiStore || (a.scatter_mode == 2 && a.scatter_block % 32 != 0) ||
@@ -1154,6 +1165,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   kp.ldd = a.ldd;
   kp.d_batch_stride = a.d_batch_stride;
   kp.d_ptrs = a.d_ptrs;
+  kp.d_dup = a.d_dup > 0 ? a.d_dup : 1;
   kp.D2 = a.D2;
   kp.ldd2 = a.ldd2;
   kp.d2_batch_stride = a.d2_batch_stride;

@@ -52,6 +52,9 @@ struct GemmArgs {
   int d_dtype = kF32;
   int64_t ldd = 0, d_batch_stride = 0;
   void* const* d_ptrs = nullptr;  // optional device array of per-batch D pointers
+  // With d_ptrs: every batch element is stored to `d_dup` destinations, d_ptrs[b * d_dup + k] (k < d_dup) -
+  // e.g. the same slot of a symmetric buffer on every rank of a group, written with peer stores.
+  int d_dup = 1;
   // Optional second output: bf16 copy of what was stored to D.
   void* D2 = nullptr;
   int64_t ldd2 = 0, d2_batch_stride = 0;

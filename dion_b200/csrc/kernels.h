@@ -152,4 +152,92 @@ cudaError_t symm_reduce_scatter_launch(const PeerTable& t, long long flag_off, l
                                        unsigned epoch, int ch_start, int ch_end, unsigned* done_counter, int* status,
                                        long long budget_ns, cudaStream_t s);
 
+// ---------------------------------------------------------------------------
+// Reductions over ranks fused with Dion's arithmetic (dion_fused.cu).  A "slot buffer" is
+// `nslots` equally shaped fp32 arrays, `slot_stride` elements apart, in this GPU's part of a
+// symmetric arena: slot s holds what rank s contributed (stored there by that rank's GEMM
+// epilogue or reduction kernel with peer stores).  `SlotWait` describes the flag exchange that
+// tells the consumer the slots are complete (world <= 1: nothing to wait for).
+// ---------------------------------------------------------------------------
+struct SlotWait {
+  PeerTable peers;
+  long long flag_off;
+  int channel, rank, world;
+  unsigned epoch;
+  unsigned long long budget_ns;
+};
+
+// out = scale * (slot 0 + slot 1 + ...), summed in slot order; optionally also its tf32 halves
+// (hi = low 13 mantissa bits cleared, lo = out - hi) and copies to `ndest` further addresses
+// (slots of a second group, for a hierarchical reduction).  numel and slot_stride multiples of 4.
+struct SlotReduceArgs {
+  SlotWait wait;
+  const float* slots;
+  long long slot_stride;
+  int nslots;
+  long long numel;
+  float scale;
+  float* out;  // may be null
+  float* hi;   // both or neither
+  float* lo;
+  int ndest;
+  float* dest[kMaxPeers];
+  int* status;
+};
+cudaError_t slot_reduce_launch(const SlotReduceArgs& a, cudaStream_t s);
+
+// After R = A^T P (contiguous [B][n][r] per slot): R <- scale * sum of slots; for a matrix whose
+// momentum is all zero (nonzero[b] == 0) R <- previous Q and P <- 0, otherwise NaN / inf are
+// replaced in R and P (dion/dion.py:1416-1444); R32 (fp32, optional) and Rm (momentum dtype,
+// optional) receive R, ss[b][j] the column sums of squares.  With `finish` the kernel also writes
+// the new Q = R / (sqrt(ss) + eps) per column (previous Q where ss == 0) to Qn ([B][n][r], optional)
+// and columns [qs_col0, qs_col0 + qs_cols) of it to Qs ([B][n][qs_cols], optional).
+// Qm: previous Q with all r columns, element (b, i, j) at b * q_bs + i * q_ld + j.
+// P: [B][p_rows][r] with pitches p_ld / p_bs, modified in place (may be null).
+struct RPostArgs {
+  SlotWait wait;
+  const float* slots;
+  long long slot_stride;
+  int nslots;
+  float scale;
+  int B, n, r;
+  const int* nonzero;
+  const void* Qm;
+  int q_type;
+  long long q_ld, q_bs;
+  void* P;
+  int p_type;
+  long long p_rows, p_ld, p_bs;
+  float* R32;
+  void* Rm;
+  int rm_type;
+  float* ss;
+  int finish;
+  float eps;
+  void* Qn;
+  int qn_type;
+  void* Qs;
+  int qs_type;
+  int qs_col0, qs_cols;
+  int* status;
+};
+cudaError_t r_post_launch(const RPostArgs& a, cudaStream_t s);
+
+// The column normalisation alone: Qn / Qs from R32 and the (already reduced) ss.
+struct QNormArgs {
+  const float* R32;
+  const float* ss;
+  int B, n, r;
+  float eps;
+  const void* Qm;
+  int q_type;
+  long long q_ld, q_bs;
+  void* Qn;
+  int qn_type;
+  void* Qs;
+  int qs_type;
+  int qs_col0, qs_cols;
+};
+cudaError_t q_norm_launch(const QNormArgs& a, cudaStream_t s);
+
 }  // namespace dion

@@ -20,7 +20,7 @@ _SRC_DIR = _PKG_DIR / "csrc"
 _BUILD_DIR = _PKG_DIR / "_C"
 _LIB_NAME = "dion_b200_C"
 _SOURCES = ["bindings.cpp", "gemm.cu", "optim_kernels.cu", "nn_kernels.cu", "linalg.cu", "comm_kernels.cu",
-            "noalloc.cu", "attention.cu"]
+            "noalloc.cu", "attention.cu", "dion_fused.cu"]
 
 _lock = threading.Lock()
 _loaded: Optional[bool] = None

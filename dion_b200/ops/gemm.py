@@ -76,7 +76,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, c: Optional[torch.Tensor] = None, 
          alpha: float = 1.0, beta: float = 0.0, act: Optional[str] = None, out_dtype: Optional[torch.dtype] = None,
          accumulate: bool = False, split_k: int = 1, symmetric: bool = False, shadow: Optional[torch.Tensor] = None,
          block_n: int = 0, pair: int = 0, out_ptrs: Optional[torch.Tensor] = None, c_ptrs: Optional[torch.Tensor] = None,
-         shadow_ptrs: Optional[torch.Tensor] = None) -> torch.Tensor:
+         shadow_ptrs: Optional[torch.Tensor] = None, out_dup: int = 1) -> torch.Tensor:
     """``out = act(alpha * a @ b + beta * c)``.
 
     a: ``[B,] M, K``; b: ``[B,] K, N``; each may be a transposed view (one unit stride in
@@ -85,6 +85,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, c: Optional[torch.Tensor] = None, 
     result is symmetric (e.g. ``x @ x.T``) and computes only half of the tiles.
     ``shadow`` receives a bf16 copy of ``out``.  ``*_ptrs`` are int64 CUDA tensors with
     one device address per batch element, for outputs that are separate allocations.
+    With ``out_dup = k > 1`` every batch element is stored to k destinations, ``out_ptrs[b * k + j]``
+    (for instance one slot of a symmetric buffer on each rank of a group).
     """
     if a.dim() not in (2, 3) or a.dim() != b.dim():
         raise ValueError("gemm expects two 2-D or two 3-D operands")
@@ -115,5 +117,5 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, c: Optional[torch.Tensor] = None, 
         raise ValueError("split_k > 1 needs accumulate=True")
     torch.ops.dion_b200.gemm(a, b, c, out, shadow, c_ptrs, out_ptrs, shadow_ptrs, float(alpha), float(beta),
                              _ACT[act], 1 if accumulate else 0, int(split_k), bool(symmetric), int(block_n), int(pair),
-                             runtime.status_tensor(a.device))
+                             runtime.status_tensor(a.device), int(out_dup))
     return out

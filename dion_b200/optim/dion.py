@@ -37,7 +37,18 @@ from .. import ops
 from ..ops import nn as nn_ops
 from ..parallel import symm
 from .common import Scheduler, all_reduce_, group_of, group_size, to_local
-from .orthogonalize import SHARD_WORK, orthonormalize_many
+from .orthogonalize import SHARD_WORK, orthonormalize_many, register_split
+
+import os
+
+# The fused paths: partial products pushed into the consumers' symmetric memory by the GEMM epilogue and
+# summed by the kernel that needs them (DION_B200_FUSED_REDUCE=0: GEMM, then a collective kernel), and
+# the guard / norm / new-Q chain after R as one kernel (DION_B200_FUSED_POST=0: element-wise torch ops).
+FUSED_REDUCE = os.environ.get("DION_B200_FUSED_REDUCE", "1") != "0"
+FUSED_POST = os.environ.get("DION_B200_FUSED_POST", "1") != "0"
+# an all-reduce by pushing to every rank costs (world - 1) times the data; beyond this group size the
+# product is reduced by the all-reduce kernel instead
+_MAX_PUSH_WORLD = 4
 
 try:  # pragma: no cover - depends on the torch build
     from torch.distributed.tensor.placement_types import _StridedShard
@@ -126,6 +137,7 @@ class _PackedClass:
         self.shadow_ptrs: Optional[Tensor] = None
         self.shadow_ptr_list: Optional[List[int]] = None
         self.nonzero: Optional[Tensor] = None
+        self.ptr_cache: Dict[tuple, Tensor] = {}  # device tables of push destinations, by buffer placement
         # conditioning of P: steps the ill-conditioned treatment of the orthonormalisation stays on, and
         # the (asynchronously fetched) count of matrices that asked for it in the last step
         self.robust_left = 0
@@ -646,6 +658,15 @@ class Dion(Optimizer):
         w.A = M.transpose(1, 2) if cfg.is_transposed else M
         a_loc = w.A.shape[1]
         first = w.outer if w.outer is not None else (w.replicate if w.compressed else None)
+        w.P_total = None
+        if first is not None and FUSED_REDUCE and M.is_cuda:
+            second = w.replicate if (w.outer is not None and w.compressed) else None
+            P = self._p_pushed(w, first, second, B, a_loc, w.Qm.shape[2])
+            if P is not None:
+                symm.count("dion_p_exchange", True)
+                w.P = P
+                return
+            symm.count("dion_p_exchange", False)
         # the GEMM writes straight into the symmetric arena of the group that reduces P first
         P = symm.empty(first, (B, a_loc, w.Qm.shape[2]), torch.float32, M.device)
         ops.gemm(w.A, w.Qm, out=P)
@@ -654,7 +675,6 @@ class Dion(Optimizer):
         # exactly the matrices it is going to orthonormalise (dion/dion.py:806-815, 925-929) instead of an
         # all-reduce of which it would drop all but its share.
         share_world = dist.get_world_size(first) if first is not None else 1
-        w.P_total = None
         if (SHARD_WORK and first is not None and w.inner is None and B > 1 and B % share_world == 0
                 and (P[0].numel() * 4) % 16 == 0):
             w.P_total = B
@@ -694,7 +714,67 @@ class Dion(Optimizer):
 
         # 5. R = A^T P, partial over the inner mesh
         first = w.inner if w.inner is not None else (w.replicate if w.compressed else None)
-        R = symm.empty(first, (B, A.shape[2], Pm.shape[2]), torch.float32, M.device)
+        n_loc, r = A.shape[2], Pm.shape[2]
+        fan_out, fan_in = p0.shape[0], p0.shape[1]
+        scaled_lr = ((fan_out / fan_in) ** 0.5) * lr
+        alpha = -(1.0 - mu)
+        beta = 1.0 - lr * wd
+        r_loc = Qs.shape[2]
+        i0 = dist.get_rank(w.inner) * r_loc if w.inner is not None else 0
+
+        if M.is_cuda and FUSED_POST:
+            # 5.-8. on GPUs: the partial products go into slots (pushed to the ranks that need the sum where
+            # there are several), and one kernel sums them, applies the all-zero / NaN guard to R and P,
+            # writes R in the momentum dtype, the column sums of squares and - unless those still have to
+            # be completed over the outer mesh - the new Q, including this rank's columns of the Q state
+            slots, scale, wait = None, 1.0, None
+            if first is not None and FUSED_REDUCE:
+                second = w.replicate if (w.inner is not None and w.compressed) else None
+                pushed = self._r_pushed(w, first, second, B, n_loc, r, Pm)
+                symm.count("dion_r_exchange", pushed is not None)
+                if pushed is not None:
+                    slots, scale, wait = pushed
+            if slots is None:
+                R = symm.empty(first, (B, n_loc, r), torch.float32, M.device)
+                ops.gemm(A.transpose(1, 2), Pm, out=R)
+                if w.inner is not None:
+                    wait_fn = self._reduce(R, w.inner, average=False)
+                    if wait_fn is not None:
+                        yield
+                        wait_fn()
+                if w.compressed:
+                    wait_fn = self._reduce(R, w.replicate, average=True)
+                    if wait_fn is not None:
+                        yield
+                        wait_fn()
+                slots = R.unsqueeze(0)
+            finish = w.outer is None
+            Rm = torch.empty((B, n_loc, r), dtype=M.dtype, device=M.device)
+            # the new Q doubles as the Q state when that holds all columns in the dtype the update multiplies with
+            q_is_state = w.inner is None and Qs.dtype == M.dtype
+            Qn = Qs if q_is_state else torch.empty((B, n_loc, r), dtype=M.dtype, device=M.device)
+            ss = symm.empty(w.outer, (B, r), torch.float32, M.device)
+            R32 = None if finish else torch.empty((B, n_loc, r), dtype=torch.float32, device=M.device)
+            ops.dion_r_post(slots, scale, cls.nonzero, Qm, Pm, R32, Rm, ss, finish, eps,
+                            None if q_is_state else Qn, Qs, i0, wait)
+            if not finish:
+                wait_fn = self._reduce(ss, w.outer, average=False)
+                if wait_fn is not None:
+                    yield
+                    wait_fn()
+                ops.dion_q_norm(R32, ss, Qm, eps, None if q_is_state else Qn, Qs, i0)
+            # 7. error feedback  M -= (1 - mu) P R^T, 9. weight decay and update
+            if cfg.is_transposed:
+                ops.gemm(Rm, Pm.transpose(1, 2), c=M, out=M, alpha=alpha, beta=1.0)
+                a_op, b_op = Qn, Pm.transpose(1, 2)
+            else:
+                ops.gemm(Pm, Rm.transpose(1, 2), c=M, out=M, alpha=alpha, beta=1.0)
+                a_op, b_op = Pm, Qn.transpose(1, 2)
+            self._apply_update(cls, params, X, a_op, b_op, -scaled_lr, beta)
+            w.A = w.Qm = w.P = w.P_total = None
+            return
+
+        R = symm.empty(first, (B, n_loc, r), torch.float32, M.device)
         ops.gemm(A.transpose(1, 2), Pm, out=R)
         if w.inner is not None:
             wait = self._reduce(R, w.inner, average=False)
@@ -715,7 +795,6 @@ class Dion(Optimizer):
         Rm = R.to(M.dtype)
 
         # 7. error feedback  M -= (1 - mu) P R^T
-        alpha = -(1.0 - mu)
         if cfg.is_transposed:
             ops.gemm(Rm, Pm.transpose(1, 2), c=M, out=M, alpha=alpha, beta=1.0)
         else:
@@ -734,9 +813,6 @@ class Dion(Optimizer):
         Qn = torch.where((ss > 0).unsqueeze(1), Qn, Qm)
 
         # 9. weight decay and update  X = (1 - lr wd) X - lr sqrt(fan_out / fan_in) P Qn^T
-        fan_out, fan_in = p0.shape[0], p0.shape[1]
-        scaled_lr = ((fan_out / fan_in) ** 0.5) * lr
-        beta = 1.0 - lr * wd
         if cfg.is_transposed:
             a_op, b_op = Qn, Pm.transpose(1, 2)
         else:
@@ -745,12 +821,115 @@ class Dion(Optimizer):
 
         # 10. keep this rank's columns of the new Q (dion.py:1533-1561)
         if w.inner is not None:
-            r_loc = Qs.shape[2]
-            i0 = dist.get_rank(w.inner) * r_loc
             Qs.copy_(Qn[:, :, i0:i0 + r_loc])
         else:
             Qs.copy_(Qn)
         w.A = w.Qm = w.P = w.P_total = None
+
+    # ------------------------------------------------------------------ pushed partial products
+
+    @staticmethod
+    def _ptr_table(cls: _PackedClass, key: tuple, make) -> Tensor:
+        t = cls.ptr_cache.get(key)
+        if t is None:
+            if len(cls.ptr_cache) > 64:  # arenas were replaced: drop tables of buffers that no longer exist
+                cls.ptr_cache.clear()
+            t = cls.ptr_cache[key] = torch.tensor(make(), dtype=torch.int64, device=cls.M.device)
+        return t
+
+    def _p_pushed(self, w: "_ClassWork", first: ProcessGroup, second: Optional[ProcessGroup], B: int, a_loc: int,
+                  r: int) -> Optional[Tensor]:
+        """P = A Q summed over `first` (and then averaged over `second`) without a collective between the
+        product and its consumer (the reduce-scatter / all-reduce of dion/dion.py:806-815, 925-929,
+        1076-1079): the GEMM epilogue stores every tile of this rank's partial product into slot `rank` of
+        a buffer in the memory of the rank(s) that need the sum, while the other tiles are still being
+        multiplied; the next kernel announces that, waits for the other ranks' announcements, adds the
+        slots in rank order and writes P together with the tf32 halves the Gram product needs.
+        When the batch can be split (no tensor-parallel rows), matrix i goes only to rank i // per: every
+        rank receives exactly the matrices it will orthonormalise.  Returns None (nothing launched) when
+        the arenas cannot serve the buffers; sets w.P_total like the unfused path."""
+        cls = w.cls
+        dev = cls.M.device
+        ar1 = symm.arena_for(first)
+        ar2 = symm.arena_for(second) if second is not None else None
+        mat = a_loc * r
+        if ar1 is None or mat % 4 != 0 or (second is not None and ar2 is None):
+            return None
+        W1 = ar1.world
+        split = SHARD_WORK and w.inner is None and B > 1
+        if not split and W1 > _MAX_PUSH_WORLD:
+            return None
+        per = (B + W1 - 1) // W1 if split else B
+        cnt = max(0, min(per, B - ar1.rank * per)) if split else B
+        push2 = ar2 is not None and ar2.world <= _MAX_PUSH_WORLD
+        slots = ar1.alloc_slots((per, a_loc, r))
+        slots2 = ar2.alloc_slots((per, a_loc, r)) if push2 else None
+        if slots is None or (push2 and slots2 is None):
+            return None
+        if split:
+            table = self._ptr_table(cls, ("p_split", ar1.peers[0], ar1.offset_of(slots), B, per, mat), lambda: [
+                ar1.slot_address(i // per, slots, ar1.rank, (i % per) * mat) for i in range(B)])
+            ops.gemm(w.A, w.Qm, out=slots[0, 0], out_ptrs=table)
+            w.P_total = B
+            self.p_reduce_scatters += 1
+        else:
+            table = self._ptr_table(cls, ("p_all", ar1.peers[0], ar1.offset_of(slots), B, mat), lambda: [
+                ar1.slot_address(k, slots, ar1.rank, i * mat) for i in range(B) for k in range(W1)])
+            ops.gemm(w.A, w.Qm, out=slots[0, 0], out_ptrs=table, out_dup=W1)
+        scale1 = 1.0 if w.outer is not None else 1.0 / W1   # a sum over shards, a mean over replicas
+        if ar2 is not None and not push2:
+            # large replicate group: the first sum lands in its arena and the all-reduce kernel averages it
+            share = symm.empty(second, (per, a_loc, r), torch.float32, dev)
+            if cnt < per:
+                share[cnt:].zero_()
+            ops.slot_reduce(slots[:, :cnt], share[:cnt], None, None, [], scale1, ar1.wait_args())
+            wait_fn = self._reduce(share, second, average=True)
+            if wait_fn is not None:
+                wait_fn()
+            return share
+        share = torch.empty((per, a_loc, r), dtype=torch.float32, device=dev)
+        hi, lo = torch.empty_like(share), torch.empty_like(share)
+        if cnt < per:  # shares are padded to equal size with zero matrices, which orthonormalise to zero
+            for t in (share, hi, lo):
+                t[cnt:].zero_()
+        if push2:
+            dests = [ar2.slot_address(q, slots2, ar2.rank) for q in range(ar2.world)]
+            ops.slot_reduce(slots[:, :cnt], None, None, None, dests, scale1, ar1.wait_args())
+            ops.slot_reduce(slots2[:, :cnt], share[:cnt], hi[:cnt], lo[:cnt], [], 1.0 / ar2.world, ar2.wait_args())
+        else:
+            ops.slot_reduce(slots[:, :cnt], share[:cnt], hi[:cnt], lo[:cnt], [], scale1, ar1.wait_args())
+        register_split(share, hi, lo)
+        return share
+
+    def _r_pushed(self, w: "_ClassWork", first: ProcessGroup, second: Optional[ProcessGroup], B: int, n_loc: int,
+                  r: int, Pm: Tensor):
+        """R = A^T P pushed by the GEMM epilogue into slot `rank` of a buffer on every rank of `first`
+        (the all-reduces of dion/dion.py:839-844, 951-960, 1098-1110).  With a `second` group (tensor
+        parallel sum, then mean over the replicas) one reduction kernel adds the slots and hands the sum
+        on to the slots of the second group.  Returns (slots, scale, wait arguments) for the kernel that
+        consumes R, or None (nothing launched) when the arenas cannot serve the buffers."""
+        cls = w.cls
+        ar1 = symm.arena_for(first)
+        ar2 = symm.arena_for(second) if second is not None else None
+        mat = n_loc * r
+        if ar1 is None or mat % 4 != 0 or ar1.world > _MAX_PUSH_WORLD:
+            return None
+        if second is not None and (ar2 is None or ar2.world > _MAX_PUSH_WORLD):
+            return None
+        slots = ar1.alloc_slots((B, n_loc, r))
+        slots2 = ar2.alloc_slots((B, n_loc, r)) if ar2 is not None else None
+        if slots is None or (ar2 is not None and slots2 is None):
+            return None
+        W1 = ar1.world
+        table = self._ptr_table(cls, ("r_all", ar1.peers[0], ar1.offset_of(slots), B, mat), lambda: [
+            ar1.slot_address(k, slots, ar1.rank, i * mat) for i in range(B) for k in range(W1)])
+        ops.gemm(w.A.transpose(1, 2), Pm, out=slots[0, 0], out_ptrs=table, out_dup=W1)
+        scale1 = 1.0 if w.inner is not None else 1.0 / W1
+        if ar2 is None:
+            return slots, scale1, ar1.wait_args()
+        dests = [ar2.slot_address(q, slots2, ar2.rank) for q in range(ar2.world)]
+        ops.slot_reduce(slots, None, None, None, dests, scale1, ar1.wait_args())
+        return slots2, 1.0 / ar2.world, ar2.wait_args()
 
     def _apply_update(self, cls: _PackedClass, params: List[Tensor], X: List[Tensor], a_op: Tensor, b_op: Tensor,
                       alpha: float, beta: float) -> None:

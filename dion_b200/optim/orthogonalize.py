@@ -33,8 +33,22 @@ from ..parallel import symm
 GRAM_PRECISION = os.environ.get("DION_B200_GRAM_PRECISION", "3xtf32")
 
 
+# tf32 halves that a producer already wrote next to its fp32 result (see register_split)
+_presplit = {}
+
+
+def register_split(x: Tensor, hi: Tensor, lo: Tensor) -> None:
+    """Tell the orthonormalisation that the tf32 halves of `x` exist already (the kernel that summed x
+    over the ranks wrote them in the same pass), so that it does not split x again.  Entries live until
+    the end of the next :func:`orthonormalize_many`."""
+    _presplit[(x.data_ptr(), tuple(x.shape))] = (hi, lo)
+
+
 def _split_tf32(x: Tensor):
     """x = hi + lo with hi exactly representable in tf32 (low 13 mantissa bits cleared)."""
+    known = _presplit.get((x.data_ptr(), tuple(x.shape)))
+    if known is not None:
+        return known
     return ops.linalg.split_tf32(x)
 
 
@@ -216,6 +230,14 @@ def orthonormalize_many(Ps, row_groups=None, refine_passes: int = 2,
     gives up near 3e3).  ``infos``, if a list, receives per batch the int32 tensor of pivots the (first)
     factorisation gave up on, per matrix of this rank's share (for a `robust` batch: 1 where the smallest
     pivot says that the plain factorisation would still give up) - the signal for asking for `robust`."""
+    try:
+        return _orthonormalize_many(Ps, row_groups, refine_passes, pivot_floor, shard_groups, totals, out_dtypes,
+                                    robust, infos)
+    finally:
+        _presplit.clear()
+
+
+def _orthonormalize_many(Ps, row_groups, refine_passes, pivot_floor, shard_groups, totals, out_dtypes, robust, infos):
     n = len(Ps)
     if out_dtypes is None:
         out_dtypes = [P.dtype for P in Ps]
@@ -233,7 +255,7 @@ def orthonormalize_many(Ps, row_groups=None, refine_passes: int = 2,
     if any(g is not None for g in shard_groups):
         parts = [P.float() if (g is None or t is not None) else _my_share(P.float(), g)
                  for P, g, t in zip(Ps, shard_groups, totals)]
-        outs = orthonormalize_many(parts, row_groups, refine_passes, pivot_floor, robust=robust, infos=infos)
+        outs = _orthonormalize_many(parts, row_groups, refine_passes, pivot_floor, None, None, None, robust, infos)
         return [X.to(dt) if g is None else _gather_shares(X.to(dt), g, P.shape[0] if t is None else t)
                 for X, P, g, t, dt in zip(outs, Ps, shard_groups, totals, out_dtypes)]
     dtypes = out_dtypes

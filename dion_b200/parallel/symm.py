@@ -32,6 +32,21 @@ _WANT_OFF = 2048  # inside the flag block, far behind the flag words: one fp32 p
 _ALIGN = 256
 _MIN_ARENA = 8 << 20
 _RS_WAIT_NS = int(1.5e9)  # bound of the reduce-scatter kernel's waits for its peers
+_CH_SLOT = 4               # flag channel of the push exchanges (0-3: all-reduce, reduce-into, reduce-scatter)
+_SLOT_WAIT_NS = int(1.5e9)
+
+# How often each kind of collective ran as an in-tree kernel and how often it went to the process group's
+# own implementation since the last reset_stats(); benchmarks report it next to their timings.
+stats: Dict[str, int] = {}
+
+
+def count(kind: str, kernel: bool) -> None:
+    k = f"{kind}.{'kernel' if kernel else 'library'}"
+    stats[k] = stats.get(k, 0) + 1
+
+
+def reset_stats() -> None:
+    stats.clear()
 
 
 def _enabled() -> bool:
@@ -158,6 +173,25 @@ class SymmetricArena:
         self.epoch += 1
         torch.ops.dion_b200.symm_reduce_into(src, dst, self.peers, 0, off, scale, beta, self.rank, self.epoch,
                                              self.counter, runtime.status_tensor(self.device))
+
+    # -- push exchanges: producers store their contribution into slot `rank` of a buffer on the consuming
+    #    ranks, the consumer kernel waits for everybody's announcement and adds the slots up in rank order
+    def alloc_slots(self, shape) -> Optional[torch.Tensor]:
+        """fp32 buffer [world, *shape] in this rank's arena (None when it does not fit): slot s is written
+        by rank s of the group."""
+        return self.alloc((self.world, *shape), torch.float32)
+
+    def slot_address(self, rank: int, slots: torch.Tensor, slot: int, elem: int = 0) -> int:
+        """Address, in the memory of `rank`, of element `elem` of slot `slot` of the buffer that sits where
+        `slots` sits in this rank's arena."""
+        per = slots.numel() // slots.shape[0]
+        return self.peers[rank] + self._views[slots.data_ptr()] + (slot * per + elem) * 4
+
+    def wait_args(self):
+        """Arguments of the flag exchange for the next consumer kernel on this arena (advances the epoch):
+        (peers, flag_off, channel, rank, epoch, budget_ns)."""
+        self.epoch += 1
+        return (self.peers, 0, _CH_SLOT, self.rank, self.epoch, _SLOT_WAIT_NS)
 
     def barrier(self, channel: int = 0) -> None:
         self.epoch += 1
@@ -290,7 +324,9 @@ def all_reduce(t: torch.Tensor, group: Optional[dist.ProcessGroup], average: boo
         off = arena.offset_of(t)
         if off is not None and t.is_contiguous() and t.dtype in (torch.float32, torch.bfloat16):
             arena.all_reduce(t, off, average)
+            count("all_reduce", True)
             return
+    count("all_reduce", False)
     world = dist.get_world_size(group)
     nccl = t.is_cuda and dist.get_backend(group) == "nccl"
     if average and nccl:
@@ -316,7 +352,9 @@ def reduce_scatter(t: torch.Tensor, group: dist.ProcessGroup, average: bool = Fa
         if (off is not None and t.is_contiguous() and out.is_contiguous() and t.dtype in (torch.float32, torch.bfloat16)
                 and (n * t.element_size()) % 16 == 0 and out.data_ptr() % 16 == 0):
             arena.reduce_scatter(t, off, out, average)
+            count("reduce_scatter", True)
             return out
+    count("reduce_scatter", False)
     flat = t.reshape(-1)
     if average and t.is_cuda and dist.get_backend(group) == "nccl":
         dist.reduce_scatter_tensor(out.view(-1), flat, op=dist.ReduceOp.AVG, group=group)

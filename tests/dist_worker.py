@@ -151,6 +151,20 @@ def case_symm_multicast():
     case_symm()
 
 
+def _expect_pushed(*kinds):
+    """On GPUs with symmetric memory on: the partial products of Dion's power iteration went through the
+    GEMM-epilogue push into the consumers' slots (not through a collective kernel or the library)."""
+    if not CUDA or os.environ.get("DION_B200_SYMM", "1") == "0" or os.environ.get("DION_B200_FUSED_REDUCE", "1") == "0":
+        return
+    from dion_b200.parallel import symm
+
+    for kind in kinds:
+        if symm.stats.get(f"{kind}.kernel", 0) <= 0:
+            fail(f"{kind}: never took the pushed path ({dict(symm.stats)})")
+    if RANK == 0:
+        print(f"collective paths so far: {dict(sorted(symm.stats.items()))}", flush=True)
+
+
 def _single_process_dion(rank_fraction, steps):
     from dion_b200 import Dion
 
@@ -228,6 +242,7 @@ def case_dion_ddp():
         for i, (p, q) in enumerate(zip(P, Pref)):
             check(f"dion ddp rf={rf} M[{i}] after synchronize_for_checkpoint", opt.state[p]["momentum"],
                   optref.state[q]["momentum"], 5e-3 if CUDA else 1e-4)
+    _expect_pushed("dion_p_exchange", "dion_r_exchange")  # the compressed run synchronises P and R over the replicas
 
 
 def case_muon_ddp():
@@ -324,6 +339,7 @@ def case_fsdp():
             # every class of the 2-layer model has an even number of matrices: P leaves its reduction
             # over the shard group as this rank's share (reduce-scatter), not as the whole batch
             assert opt.p_reduce_scatters > 0, "P was all-reduced although the batches split evenly"
+            _expect_pushed("dion_p_exchange")
         if name == "muon":
             # the momentum is linear in the gradients, so it pins down that every path (library
             # all-to-all or peer stores from the momentum kernel) applies it exactly once per step
@@ -435,6 +451,7 @@ def case_hybrid():
         check(f"hybrid dp x fs replica consistency {n}", loc, ref, 1e-6)
     st = next(iter(opt.state.values()))
     assert st["momentum"].dtype == torch.bfloat16 and st["Q"].dtype == torch.float32
+    _expect_pushed("dion_p_exchange", "dion_r_exchange")
     # ---- (b)
     stage("fs x tp: building")
     mesh = init_device_mesh(kind, (1, 2, WORLD // 2), mesh_dim_names=("dp", "fs", "tp"))
@@ -473,6 +490,7 @@ def case_hybrid():
     l2 = _train(ref, optref, 3)
     dist.all_reduce(l1, op=dist.ReduceOp.SUM)
     l1 /= WORLD
+    _expect_pushed("dion_p_exchange", "dion_r_exchange")
     check("hybrid fs x tp losses", l1, l2, 3e-2 if CUDA else 2e-3)
     for (n1, p1), (n2, p2) in zip(model.named_parameters(), ref.named_parameters()):
         loose = "wte" in n1 or "lm_head" in n1
