@@ -76,7 +76,8 @@ void gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, Tens
           const std::optional<Tensor>& d2, const std::optional<Tensor>& c_ptrs,
           const std::optional<Tensor>& d_ptrs, const std::optional<Tensor>& d2_ptrs, double alpha, double beta,
           int64_t act, int64_t epilogue, int64_t split_k, bool symmetric, int64_t block_n, int64_t pair,
-          const std::optional<Tensor>& status, int64_t d_dup) {
+          const std::optional<Tensor>& status, int64_t d_dup, const std::optional<Tensor>& a_lo,
+          const std::optional<Tensor>& b_lo, const std::optional<Tensor>& c_col_scale, bool split3) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda(), "gemm operands must be CUDA tensors");
   TORCH_CHECK(a.scalar_type() == b.scalar_type(), "gemm operands must share a dtype");
   TORCH_CHECK(a.dim() == b.dim(), "gemm operands must both be 2-D or both 3-D");
@@ -93,6 +94,19 @@ void gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, Tens
   describe_operand(b, /*contract_last=*/false, &g.b_major, &g.ldb, &g.b_batch_stride, "b");
   g.A = a.data_ptr();
   g.B = b.data_ptr();
+  TORCH_CHECK(a_lo.has_value() == b_lo.has_value(), "hi / lo operands need both low halves");
+  if (split3) {
+    TORCH_CHECK(a.scalar_type() == at::kFloat && !a_lo.has_value(), "split3 takes fp32 operands without low halves");
+    g.split3 = 1;
+  }
+  if (a_lo.has_value()) {
+    TORCH_CHECK(a.scalar_type() == at::kFloat, "hi / lo operands are fp32");
+    TORCH_CHECK(a_lo->is_cuda() && b_lo->is_cuda() && a_lo->scalar_type() == at::kFloat && b_lo->scalar_type() == at::kFloat &&
+                a_lo->sizes() == a.sizes() && a_lo->strides() == a.strides() && b_lo->sizes() == b.sizes() &&
+                b_lo->strides() == b.strides(), "low halves must have the layout of the high halves");
+    g.A_lo = a_lo->data_ptr();
+    g.B_lo = b_lo->data_ptr();
+  }
   g.alpha = (float)alpha;
   g.beta = (float)beta;
   g.act = (int)act;
@@ -130,6 +144,12 @@ void gemm(const Tensor& a, const Tensor& b, const std::optional<Tensor>& c, Tens
     g.C = ct.data_ptr();
     g.c_dtype = gemm_dtype(ct, "c");
     g.ldc = ct.stride(-2);
+  }
+  if (c_col_scale.has_value()) {
+    TORCH_CHECK(c.has_value(), "a column scale needs the addend c");
+    TORCH_CHECK(c_col_scale->is_cuda() && c_col_scale->scalar_type() == at::kFloat && c_col_scale->is_contiguous() &&
+                c_col_scale->numel() == (int64_t)g.batch * g.N, "c_col_scale must be contiguous fp32 [batch, N]");
+    g.c_col_scale = c_col_scale->data_ptr<float>();
   }
   if (d2.has_value()) {
     const Tensor& t = *d2;
@@ -375,6 +395,26 @@ void muon_pre_multi(at::TensorList G, at::TensorList M, at::TensorList U, double
   });
 }
 
+// x, out: contiguous bf16 [B, ...]; sumsq: optional fp32 [B] squared Frobenius norms
+void frob_scale(const Tensor& x, Tensor out, const std::optional<Tensor>& sumsq, double eps) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && out.scalar_type() == at::kBFloat16 && x.dim() >= 2 &&
+              x.is_contiguous() && out.is_contiguous() && out.numel() == x.numel());
+  const int64_t B = x.size(0), per = x.numel() / std::max<int64_t>(B, 1);
+  const float* ss = nullptr;
+  Tensor partial;
+  if (sumsq.has_value()) {
+    TORCH_CHECK(sumsq->scalar_type() == at::kFloat && sumsq->is_contiguous() && sumsq->numel() >= B);
+    ss = sumsq->data_ptr<float>();
+    g_launches += 1;
+  } else {
+    partial = at::empty({B * dion::frob_chunks(per)}, x.options().dtype(at::kFloat));
+    g_launches += 2;
+  }
+  DION_CUDA_CHECK(dion::frob_scale_launch(x.data_ptr(), out.data_ptr(), ss ? nullptr : partial.data_ptr<float>(), ss,
+                                          (float)eps, (int)B, per, at::cuda::getCurrentCUDAStream()));
+}
+
 void muon_post_multi(at::TensorList X, at::TensorList U, at::TensorList shadow, double decay, double step) {
   if (X.empty()) return;
   const c10::cuda::CUDAGuard guard(X[0].device());
@@ -577,7 +617,8 @@ void embedding_bwd(const Tensor& dout, const Tensor& idx, Tensor dtable) {
 
 // ----------------------------------------------------------------------------- linear algebra
 
-void chol_inverse(const Tensor& G, Tensor Z, Tensor work, Tensor info, double pivot_floor) {
+void chol_inverse(const Tensor& G, Tensor Z, Tensor work, Tensor info, double pivot_floor, bool jacobi,
+                  const std::optional<Tensor>& colmask) {
   const c10::cuda::CUDAGuard guard(G.device());
   TORCH_CHECK(G.is_cuda() && G.scalar_type() == at::kFloat && G.dim() == 3 && G.size(1) == G.size(2) &&
               G.stride(2) == 1);
@@ -585,9 +626,14 @@ void chol_inverse(const Tensor& G, Tensor Z, Tensor work, Tensor info, double pi
   TORCH_CHECK(Z.is_contiguous() && Z.scalar_type() == at::kFloat && Z.numel() == (int64_t)batch * r * r);
   TORCH_CHECK(work.is_contiguous() && work.scalar_type() == at::kFloat && work.numel() >= (int64_t)batch * r * r);
   TORCH_CHECK(info.scalar_type() == at::kInt && info.numel() >= batch);
+  float* mask = nullptr;
+  if (colmask.has_value()) {
+    TORCH_CHECK(colmask->scalar_type() == at::kFloat && colmask->is_contiguous() && colmask->numel() == (int64_t)batch * r);
+    mask = colmask->data_ptr<float>();
+  }
   cudaError_t e = dion::chol_inverse_launch(G.data_ptr<float>(), Z.data_ptr<float>(), work.data_ptr<float>(),
                                             info.data_ptr<int>(), batch, r, G.stride(1), G.stride(0),
-                                            (float)pivot_floor, at::cuda::getCurrentCUDAStream());
+                                            (float)pivot_floor, at::cuda::getCurrentCUDAStream(), jacobi, mask);
   TORCH_CHECK(e == cudaSuccess, "chol_inverse launch failed (rank ", r, "): ", cudaGetErrorString(e));
   g_launches.fetch_add(1, std::memory_order_relaxed);
 }
@@ -848,7 +894,20 @@ void split_tf32(const Tensor& x, Tensor hi, Tensor lo) {
                                           at::cuda::getCurrentCUDAStream()));
 }
 
-void refine_prep(const Tensor& G, Tensor C, Tensor d, double dead_below, const std::optional<Tensor>& skip) {
+// x: fp32 [B, rows, cols] view with unit column stride; hi / lo contiguous
+void split_tf32_rows(const Tensor& x, Tensor hi, Tensor lo) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.dim() == 3 && x.stride(2) == 1);
+  TORCH_CHECK(hi.scalar_type() == at::kFloat && lo.scalar_type() == at::kFloat && hi.is_contiguous() &&
+              lo.is_contiguous() && hi.numel() == x.numel() && lo.numel() == x.numel());
+  ++g_launches;
+  DION_CUDA_CHECK(dion::split_tf32_rows_launch(x.data_ptr<float>(), hi.data_ptr<float>(), lo.data_ptr<float>(),
+                                               (int)x.size(0), (int)x.size(1), (int)x.size(2), x.stride(1), x.stride(0),
+                                               at::cuda::getCurrentCUDAStream()));
+}
+
+void refine_prep(const Tensor& G, Tensor C, Tensor d, double dead_below, const std::optional<Tensor>& skip,
+                 bool fold) {
   const c10::cuda::CUDAGuard guard(G.device());
   TORCH_CHECK(G.scalar_type() == at::kFloat && C.scalar_type() == at::kFloat && d.scalar_type() == at::kFloat);
   TORCH_CHECK(G.dim() == 3 && G.size(1) == G.size(2) && G.is_contiguous() && C.is_contiguous() && d.is_contiguous());
@@ -859,7 +918,7 @@ void refine_prep(const Tensor& G, Tensor C, Tensor d, double dead_below, const s
   ++g_launches;
   DION_CUDA_CHECK(dion::refine_prep_launch(G.data_ptr<float>(), C.data_ptr<float>(), d.data_ptr<float>(),
                                            (int)G.size(0), (int)G.size(1), (float)dead_below,
-                                           skip.has_value() ? skip->data_ptr<int>() : nullptr,
+                                           skip.has_value() ? skip->data_ptr<int>() : nullptr, fold,
                                            at::cuda::getCurrentCUDAStream()));
 }
 
@@ -920,7 +979,8 @@ TORCH_LIBRARY(dion_b200, m) {
   m.def(
       "gemm(Tensor a, Tensor b, Tensor? c, Tensor(a!) d, Tensor(b!)? d2, Tensor? c_ptrs, Tensor? d_ptrs, "
       "Tensor? d2_ptrs, float alpha, float beta, int act, int epilogue, int split_k, bool symmetric, "
-      "int block_n, int pair, Tensor? status, int d_dup=1) -> ()");
+      "int block_n, int pair, Tensor? status, int d_dup=1, Tensor? a_lo=None, Tensor? b_lo=None, "
+      "Tensor? c_col_scale=None, bool split3=False) -> ()");
   m.def(
       "adamw_multi(Tensor(a!)[] X, Tensor[] G, Tensor(b!)[] M, Tensor(c!)[] V, Tensor(d!)[] shadow, float lr, "
       "float beta1, float beta2, float weight_decay, float eps, int step) -> ()");
@@ -929,6 +989,7 @@ TORCH_LIBRARY(dion_b200, m) {
       "float beta2, float weight_decay) -> ()");
   m.def("muon_pre_multi(Tensor[] G, Tensor(a!)[] M, Tensor(b!)[] U, float mu, bool nesterov, Tensor(c!)? sumsq) -> ()");
   m.def("muon_post_multi(Tensor(a!)[] X, Tensor[] U, Tensor(b!)[] shadow, float decay, float step) -> ()");
+  m.def("frob_scale(Tensor x, Tensor(a!) out, Tensor? sumsq, float eps) -> ()");
   m.def("dion_accum_multi(Tensor[] G, Tensor(a!)[] M, Tensor(b!)? nonzero) -> ()");
   m.def("cast_multi(Tensor[] src, Tensor(a!)[] dst) -> ()");
   m.def("rmsnorm_fwd(Tensor x, Tensor? residual, Tensor(a!)? x_out, Tensor(b!) y, Tensor(c!) rstd, float eps) -> ()");
@@ -948,14 +1009,17 @@ TORCH_LIBRARY(dion_b200, m) {
       "int ignore_index, bool write_grad) -> ()");
   m.def("embedding_fwd(Tensor table, Tensor idx, Tensor(a!) out) -> ()");
   m.def("embedding_bwd(Tensor dout, Tensor idx, Tensor(a!) dtable) -> ()");
-  m.def("chol_inverse(Tensor G, Tensor(a!) Z, Tensor(b!) work, Tensor(c!) info, float pivot_floor) -> ()");
+  m.def(
+      "chol_inverse(Tensor G, Tensor(a!) Z, Tensor(b!) work, Tensor(c!) info, float pivot_floor, bool jacobi=True, "
+      "Tensor(d!)? colmask=None) -> ()");
+  m.def("split_tf32_rows(Tensor x, Tensor(a!) hi, Tensor(b!) lo) -> ()");
   m.def("col_sumsq(Tensor X, Tensor(a!) out) -> ()");
   m.def("split_tf32(Tensor x, Tensor(a!) hi, Tensor(b!) lo) -> ()");
   m.def("attn_fwd(Tensor q, Tensor k, Tensor v, Tensor(a!) out, Tensor(b!) lse, float scale, Tensor(c!) status) -> ()");
   m.def(
       "attn_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor d_o, Tensor lse, Tensor(a!) delta, Tensor(b!) dq, "
       "Tensor(c!) dk, Tensor(d!) dv, float scale, Tensor(e!) status) -> ()");
-  m.def("refine_prep(Tensor G, Tensor(a!) C, Tensor(b!) d, float dead_below, Tensor? skip) -> ()");
+  m.def("refine_prep(Tensor G, Tensor(a!) C, Tensor(b!) d, float dead_below, Tensor? skip, bool fold=False) -> ()");
   m.def(
       "slot_reduce(Tensor slots, Tensor(a!)? out, Tensor(b!)? hi, Tensor(c!)? lo, int[] dests, float scale, int[] peers, "
       "int flag_off, int channel, int rank, int epoch, int budget_ns, Tensor(d!) status) -> ()");
@@ -970,6 +1034,7 @@ TORCH_LIBRARY(dion_b200, m) {
 
 TORCH_LIBRARY_IMPL(dion_b200, CUDA, m) {
   m.impl("gemm", &gemm);
+  m.impl("frob_scale", &frob_scale);
   m.impl("rmsnorm_fwd", &rmsnorm_fwd);
   m.impl("rmsnorm_bwd", &rmsnorm_bwd);
   m.impl("rope_qknorm_fwd", &rope_qknorm_fwd);
@@ -984,6 +1049,7 @@ TORCH_LIBRARY_IMPL(dion_b200, CUDA, m) {
   m.impl("chol_inverse", &chol_inverse);
   m.impl("col_sumsq", &col_sumsq);
   m.impl("split_tf32", &split_tf32);
+  m.impl("split_tf32_rows", &split_tf32_rows);
   m.impl("attn_fwd", &attn_fwd);
   m.impl("attn_bwd", &attn_bwd);
   m.impl("refine_prep", &refine_prep);

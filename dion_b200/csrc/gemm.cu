@@ -39,6 +39,7 @@ constexpr int kNumEpilogueWarps = 8;  // two per TMEM lane quadrant, each takes 
 constexpr int kNumThreads = 64 + 32 * kNumEpilogueWarps;
 constexpr int kNumGatherThreads = 64;  // two more warps in the all-gather variant (register budget of 384 threads)
 constexpr int kGatherUnitBytes = 64 * 1024;  // what one CTA's copier warps move at a time
+constexpr int kNumSplitThreads = 128;  // four converter warps in the variant that splits fp32 operands in shared memory
 
 // Operand A gathered from the ranks of a group while the product runs (GemmArgs::Gather).
 struct GatherParams {
@@ -63,11 +64,13 @@ struct KernelParams {
   int M, N, K, batch, split_k;
   int tiles_m, tiles_n, tiles_per_batch, total_tiles;
   int kblocks_total, kblocks_per_split;
+  int kblocks_seg;  // k-blocks per operand segment: kblocks_total for a plain product, a third of it for hi / lo operands
   float alpha, beta;
   const void* C;
   int c_is_bf16;
   long long ldc, c_batch_stride;
   const void* const* c_ptrs;
+  const float* c_col_scale;
   void* D;
   int d_is_bf16;
   long long ldd, d_batch_stride;
@@ -88,8 +91,10 @@ struct KernelParams {
 // kPair: two CTAs of a cluster work on one 256 x kBlockN tile (tcgen05 cta_group::2).  Each CTA
 // loads its own 128 rows of A and half of the tile's B rows, so every byte of B is fetched from
 // L2 once per 256 output rows instead of once per 128.
-template <bool kTf32, int kAMajor, int kBMajor, int kBlockN, bool kPair = false>
+// kSplit: fp32 operands are split into tf32 hi / lo halves inside the kernel (see the converter warps).
+template <bool kTf32, int kAMajor, int kBMajor, int kBlockN, bool kPair = false, bool kSplit = false>
 struct Cfg {
+  static_assert(!kSplit || (kTf32 && !kPair && kBlockN <= 128), "in-kernel splitting: fp32 operands, unpaired tiles of up to 128 columns");
   static constexpr int ES = kTf32 ? 4 : 2;
   static constexpr int BK = 128 / ES;      // K elements per stage (one 128B swizzle span)
   static constexpr int CH = 128 / ES;      // M/N elements per 128B chunk (MN-major tiles)
@@ -101,9 +106,18 @@ struct Cfg {
   static constexpr int B_BYTES = B_ROWS * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TX_BYTES = kPair ? 2 * STAGE_BYTES : STAGE_BYTES;  // what one full barrier phase receives
-  static constexpr int STAGES = 196608 / STAGE_BYTES;  // 4 / 6 / 8 stages in 192 KB
-  static constexpr int TMEM_COLS = (2 * kBlockN <= 32) ? 32 : 2 * kBlockN;  // power of two
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + 8 * 32 * 128 /*epilogue staging*/;
+  // kSplit keeps the lo halves of a stage right behind its hi halves (same layout, LO_OFFSET further on)
+  static constexpr int STAGE_STRIDE = kSplit ? 2 * STAGE_BYTES : STAGE_BYTES;
+  static constexpr int LO_OFFSET = STAGE_BYTES;
+  static constexpr int STAGES = 196608 / STAGE_STRIDE;  // 4 / 6 / 8 stages in 192 KB (3 / 4 when splitting)
+  // Two accumulator buffers (the epilogue of one tile overlaps the main loop of the next).  fp32 operands
+  // on tiles up to 128 columns get a second accumulator per buffer, for the small cross terms of a
+  // hi / lo product: added into the large accumulator one by one they would lose their low bits at
+  // every step, summed on their own and added once in the epilogue they do not.
+  static constexpr bool CROSS_ACC = kTf32 && !kPair && kBlockN <= 128;
+  static constexpr int ACC_STRIDE = CROSS_ACC ? 2 * kBlockN : kBlockN;
+  static constexpr int TMEM_COLS = (2 * ACC_STRIDE <= 32) ? 32 : 2 * ACC_STRIDE;  // power of two
+  static constexpr int SMEM_BYTES = STAGES * STAGE_STRIDE + 1024 /*align*/ + 256 /*barriers*/ + 8 * 32 * 128 /*epilogue staging*/;
   // descriptor strides
   static constexpr uint32_t A_LBO = (kAMajor == kMajorK) ? 16u : (uint32_t)BK * 128u;
   static constexpr uint32_t B_LBO = (kBMajor == kMajorK) ? 16u : (uint32_t)BK * 128u;
@@ -330,21 +344,30 @@ __device__ __forceinline__ bool mbar_wait_for(uint64_t* bar, uint32_t parity, vo
   }
 }
 
-template <bool kTf32, int kAMajor, int kBMajor, int kBlockN, bool kPair, bool kGather = false>
-__global__ void __launch_bounds__(kNumThreads + (kGather ? kNumGatherThreads : 0), 1)
+// kSplit (fp32 operands, 3xTF32 accuracy without hi / lo copies in global memory): four more warps
+// take every stage that TMA delivered, clear the low 13 mantissa bits of each fp32 value in place (hi)
+// and write the remainders (lo) LO_OFFSET further on, same layout - an element-wise pass that does not
+// need to know the swizzle.  The MMA warp then issues hi*hi into the main accumulator and lo*hi, hi*lo
+// into the cross-term accumulator for every K-step.  Operand bytes cross L2 once instead of three times.
+template <bool kTf32, int kAMajor, int kBMajor, int kBlockN, bool kPair, bool kGather = false, bool kSplit = false>
+__global__ void __launch_bounds__(kNumThreads + (kGather ? kNumGatherThreads : 0) + (kSplit ? kNumSplitThreads : 0), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+            const __grid_constant__ CUtensorMap tmap_a_lo, const __grid_constant__ CUtensorMap tmap_b_lo,
             const KernelParams p) {
-  using C = Cfg<kTf32, kAMajor, kBMajor, kBlockN, kPair>;
+  static_assert(!(kSplit && kGather), "the converter warps and the copier warps use the same warp slots");
+  using C = Cfg<kTf32, kAMajor, kBMajor, kBlockN, kPair, kSplit>;
   extern __shared__ uint8_t smem_raw[];
   // 128B swizzle atoms need 1024-byte aligned tiles.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* bar_area = smem + C::STAGES * C::STAGE_BYTES;
+  uint8_t* bar_area = smem + C::STAGES * C::STAGE_STRIDE;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bar_area);
   uint64_t* empty_bar = full_bar + C::STAGES;
   uint64_t* tmem_full = empty_bar + C::STAGES;
   uint64_t* tmem_empty = tmem_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* conv_bar = tmem_empty + 2;  // kSplit: stage has been split (one arrival per converter warp)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(conv_bar + (kSplit ? C::STAGES : 0));
+  static_assert((2 * C::STAGES + 4 + (kSplit ? C::STAGES : 0)) * 8 + 16 <= 256, "barrier area");
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* gather_word = abort_flag + 1;  // broadcast slot of the copier warps
   uint8_t* stage_area = bar_area + 256;
@@ -360,9 +383,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if constexpr (kTf32) {
+      if (p.kblocks_seg < p.kblocks_total) {
+        tma_prefetch_desc(&tmap_a_lo);
+        tma_prefetch_desc(&tmap_b_lo);
+      }
+    }
     for (int s = 0; s < C::STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
+      if constexpr (kSplit) mbar_init(&conv_bar[s], kNumSplitThreads / 32);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
@@ -440,20 +470,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             if constexpr (kPair) tma_load_3d_pair(dst, map, bar, c0, c1, t.batch);
             else tma_load_3d(dst, map, &full_bar[stage], c0, c1, t.batch);
           };
-          uint8_t* sa = smem + stage * C::STAGE_BYTES;
+          uint8_t* sa = smem + stage * C::STAGE_STRIDE;
           uint8_t* sb = sa + C::A_BYTES;
-          const int k0 = kb * C::BK;
+          // hi / lo operands: the K range is walked three times, as A B, A_lo B and A B_lo
+          const CUtensorMap* map_a = &tmap_a;
+          const CUtensorMap* map_b = &tmap_b;
+          int kk = kb;
+          if constexpr (kTf32) {
+            if (kb >= p.kblocks_seg) {
+              const int seg = kb / p.kblocks_seg;
+              kk = kb - seg * p.kblocks_seg;
+              if (seg == 1) map_a = &tmap_a_lo;
+              else map_b = &tmap_b_lo;
+            }
+          }
+          const int k0 = kk * C::BK;
           if constexpr (kAMajor == kMajorK) {
-            load(sa, &tmap_a, k0, m0);
+            load(sa, map_a, k0, m0);
           } else {
 #pragma unroll
-            for (int c = 0; c < kBlockM / C::CH; ++c) load(sa + c * (C::BK * 128), &tmap_a, m0 + c * C::CH, k0);
+            for (int c = 0; c < kBlockM / C::CH; ++c) load(sa + c * (C::BK * 128), map_a, m0 + c * C::CH, k0);
           }
           if constexpr (kBMajor == kMajorK) {
-            load(sb, &tmap_b, k0, n0);
+            load(sb, map_b, k0, n0);
           } else {
 #pragma unroll
-            for (int c = 0; c < C::B_ROWS / C::CH; ++c) load(sb + c * (C::BK * 128), &tmap_b, n0 + c * C::CH, k0);
+            for (int c = 0; c < C::B_ROWS / C::CH; ++c) load(sb + c * (C::BK * 128), map_b, n0 + c * C::CH, k0);
           }
           if (++stage == C::STAGES) {
             stage = 0;
@@ -483,23 +525,45 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * kBlockN;
+        const uint32_t d_main = tmem_base + acc * C::ACC_STRIDE;
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!wait(&full_bar[stage], phase)) {
+          // hi / lo operands: the first K-segment (hi * hi) goes to the main accumulator, the two cross
+          // segments to the second one, which starts from zero at the first of them
+          uint32_t d_tmem = d_main;
+          bool fresh = kb == kb0;
+          if constexpr (C::CROSS_ACC) {
+            if (kb >= p.kblocks_seg) {
+              d_tmem = d_main + kBlockN;
+              fresh = kb == p.kblocks_seg;
+            }
+          }
+          // the operands of a stage are ready when TMA delivered them - or, when they are split in
+          // shared memory, when the converter warps are through with the stage
+          if (!wait(kSplit ? &conv_bar[stage] : &full_bar[stage], phase)) {
             ok = false;
             *abort_flag = 1;
             if (p.status) atomicCAS(p.status, 0, kStatusMmaTimeout);
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+          const uint32_t sa = smem_u32(smem + stage * C::STAGE_STRIDE);
           const uint32_t sb = sa + C::A_BYTES;
 #pragma unroll
           for (int j = 0; j < C::KSTEPS; ++j) {
             const uint64_t da = make_smem_desc(sa + j * C::A_KSTEP, C::A_LBO, C::A_SBO, C::A_LAYOUT);
             const uint64_t db = make_smem_desc(sb + j * C::B_KSTEP, C::B_LBO, C::B_SBO, C::B_LAYOUT);
-            if constexpr (kPair) umma_ss_pair<kTf32>(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
-            else umma_ss<kTf32>(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+            if constexpr (kSplit) {
+              const uint64_t da_lo = make_smem_desc(sa + C::LO_OFFSET + j * C::A_KSTEP, C::A_LBO, C::A_SBO, C::A_LAYOUT);
+              const uint64_t db_lo = make_smem_desc(sb + C::LO_OFFSET + j * C::B_KSTEP, C::B_LBO, C::B_SBO, C::B_LAYOUT);
+              const uint32_t first = (!fresh || j > 0) ? 1u : 0u;
+              umma_ss<true>(d_main, da, db, idesc, first);                 // hi * hi
+              umma_ss<true>(d_main + kBlockN, da_lo, db, idesc, first);    // lo * hi
+              umma_ss<true>(d_main + kBlockN, da, db_lo, idesc, 1u);       // hi * lo
+            } else if constexpr (kPair) {
+              umma_ss_pair<kTf32>(d_tmem, da, db, idesc, (!fresh || j > 0) ? 1u : 0u);
+            } else {
+              umma_ss<kTf32>(d_tmem, da, db, idesc, (!fresh || j > 0) ? 1u : 0u);
+            }
           }
           // frees the smem stage (of both CTAs) once these MMAs retire
           if constexpr (kPair) umma_commit_pair(&empty_bar[stage], 3);
@@ -512,6 +576,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (ok) {
           if constexpr (kPair) umma_commit_pair(&tmem_full[acc], 3);
           else umma_commit(&tmem_full[acc]);
+        }
+      }
+    }
+  } else if (kSplit && warp >= 2 + kNumEpilogueWarps) {
+    // ------------------------------------------------------------------ converter: fp32 stage -> tf32 hi / lo
+    const int ct = (int)threadIdx.x - kNumThreads;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = worker; tile < p.total_tiles && ok; tile += num_workers) {
+      const TileCoord t = decode_tile<false>(p, tile);
+      const int kb0 = t.split * kb_per_split;
+      const int kb1 = min(kb0 + kb_per_split, p.kblocks_total);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!wait(&full_bar[stage], phase)) {
+          ok = false;
+          *abort_flag = 1;
+          if (p.status) atomicCAS(p.status, 0, kStatusProducerTimeout);
+          break;
+        }
+        uint8_t* hi = smem + stage * C::STAGE_STRIDE;
+#pragma unroll 4
+        for (int off = ct * 16; off < C::STAGE_BYTES; off += kNumSplitThreads * 16) {
+          const float4 q = *reinterpret_cast<const float4*>(hi + off);
+          float4 h, l;
+          h.x = __int_as_float(__float_as_int(q.x) & 0xffffe000);
+          h.y = __int_as_float(__float_as_int(q.y) & 0xffffe000);
+          h.z = __int_as_float(__float_as_int(q.z) & 0xffffe000);
+          h.w = __int_as_float(__float_as_int(q.w) & 0xffffe000);
+          l.x = q.x - h.x;
+          l.y = q.y - h.y;
+          l.z = q.z - h.z;
+          l.w = q.w - h.w;
+          *reinterpret_cast<float4*>(hi + off) = h;
+          *reinterpret_cast<float4*>(hi + C::LO_OFFSET + off) = l;
+        }
+        // these stores are read by the tensor core (async proxy)
+        fence_proxy_async_all();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&conv_bar[stage]);
+        if (++stage == C::STAGES) {
+          stage = 0;
+          phase ^= 1u;
         }
       }
     }
@@ -695,9 +802,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const int col0 = n0 + c * 32;
         if (col0 >= p.N) break;  // warp-uniform
         float v[32];
-        const uint32_t taddr = tmem_base + acc * kBlockN + c * 32 + ((uint32_t)(quad * 32) << 16);
+        const uint32_t taddr = tmem_base + acc * C::ACC_STRIDE + c * 32 + ((uint32_t)(quad * 32) << 16);
         tmem_ld_32x32(taddr, v);
         tmem_ld_wait();
+        if constexpr (C::CROSS_ACC) {
+          if (kSplit || p.kblocks_total > p.kblocks_seg) {  // hi / lo operands: add the cross terms, summed on their own
+            float x[32];
+            tmem_ld_32x32(taddr + kBlockN, x);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] += x[i];
+          }
+        }
         if (!has_work) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0.f;
@@ -768,6 +884,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             if (p.act == kActMulRelu2Grad) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) v[i] *= 2.f * fmaxf(cv[i], 0.f);
+            } else if (p.c_col_scale != nullptr) {
+              // every lane reads the same 32 factors (a broadcast load per factor)
+              const float* cs = p.c_col_scale + (long long)t.batch * p.N + col0;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] += p.beta * cv[i] * (col0 + i < p.N ? cs[i] : 0.f);
             } else {
 #pragma unroll
               for (int i = 0; i < 32; ++i) v[i] += p.beta * cv[i];
@@ -807,8 +928,36 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           // later chunks of this tile start from the first destination again
           if (ndup > 1) d_base = reinterpret_cast<char*>(p.d_ptrs[(long long)t.batch * p.d_dup]);
           if (d2_base != nullptr && !d2_done) emit_d2();
-          if (mirror && row_ok) {
-            // transposed copy of an off-diagonal tile: D[col, row]; lanes hold
+          if (mirror && p.vec_d && full_cols && row_first + 32 <= p.M) {
+            // Transposed copy of an off-diagonal tile, D[col, row], turned through the staging buffer:
+            // every lane parks its row as a column, then the warp writes the 32 transposed rows with
+            // 16-byte stores (4 instructions for bf16, 8 for fp32) instead of 32 narrow ones.
+            if (p.d_is_bf16) {
+              __nv_bfloat16* tb = reinterpret_cast<__nv_bfloat16*>(st);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) tb[i * 32 + lane] = __float2bfloat16(v[i]);
+              __syncwarp();
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const int cc = (lane >> 2) + 8 * k, seg = lane & 3;
+                const uint4 q = *reinterpret_cast<const uint4*>(st + cc * 64 + seg * 16);
+                *reinterpret_cast<uint4*>(d_base + ((long long)(col0 + cc) * p.ldd + row_first + seg * 8) * 2) = q;
+              }
+            } else {
+              float* tf = reinterpret_cast<float*>(st);
+#pragma unroll
+              for (int i = 0; i < 32; ++i) tf[i * 32 + lane] = v[i];
+              __syncwarp();
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                const int cc = (lane >> 3) + 4 * k, seg = lane & 7;
+                const uint4 q = *reinterpret_cast<const uint4*>(st + cc * 128 + seg * 16);
+                *reinterpret_cast<uint4*>(d_base + ((long long)(col0 + cc) * p.ldd + row_first + seg * 4) * 4) = q;
+              }
+            }
+            __syncwarp();
+          } else if (mirror && row_ok) {
+            // ragged or unaligned tiles: D[col, row] element by element; lanes hold
             // consecutive rows, so each store instruction is contiguous across the warp
             if (p.d_is_bf16) {
               __nv_bfloat16* dt = reinterpret_cast<__nv_bfloat16*>(d_base);
@@ -916,25 +1065,29 @@ int num_sms() {
   return n;
 }
 
-template <bool kTf32, int kAMajor, int kBMajor, int kBlockN, bool kPair = false, bool kGather = false>
+template <bool kTf32, int kAMajor, int kBMajor, int kBlockN, bool kPair = false, bool kGather = false, bool kSplit = false>
 cudaError_t launch_cfg(const GemmArgs& a, const KernelParams& kp, cudaStream_t stream) {
-  using C = Cfg<kTf32, kAMajor, kBMajor, kBlockN, kPair>;
-  CUtensorMap ta, tb;
+  using C = Cfg<kTf32, kAMajor, kBMajor, kBlockN, kPair, kSplit>;
+  CUtensorMap ta, tb, ta_lo, tb_lo;
   const int dt = kTf32 ? kF32 : kBF16;
-  bool ok;
-  if (kAMajor == kMajorK)
-    ok = make_tmap(&ta, a.A, dt, a.K, a.M, a.batch, a.lda, a.a_batch_stride, C::BK, kBlockM, false);
-  else
-    ok = make_tmap(&ta, a.A, dt, a.M, a.K, a.batch, a.lda, a.a_batch_stride, C::CH, C::BK, C::A_ATOM32);
-  if (!ok) return cudaErrorInvalidValue;
-  if (kBMajor == kMajorK)
-    ok = make_tmap(&tb, a.B, dt, a.K, a.N, a.batch, a.ldb, a.b_batch_stride, C::BK, C::B_ROWS, false);
-  else
-    ok = make_tmap(&tb, a.B, dt, a.N, a.K, a.batch, a.ldb, a.b_batch_stride, C::CH, C::BK, C::B_ATOM32);
-  if (!ok) return cudaErrorInvalidValue;
+  auto map_a = [&](CUtensorMap* m, const void* base) {
+    if (kAMajor == kMajorK) return make_tmap(m, base, dt, a.K, a.M, a.batch, a.lda, a.a_batch_stride, C::BK, kBlockM, false);
+    return make_tmap(m, base, dt, a.M, a.K, a.batch, a.lda, a.a_batch_stride, C::CH, C::BK, C::A_ATOM32);
+  };
+  auto map_b = [&](CUtensorMap* m, const void* base) {
+    if (kBMajor == kMajorK) return make_tmap(m, base, dt, a.K, a.N, a.batch, a.ldb, a.b_batch_stride, C::BK, C::B_ROWS, false);
+    return make_tmap(m, base, dt, a.N, a.K, a.batch, a.ldb, a.b_batch_stride, C::CH, C::BK, C::B_ATOM32);
+  };
+  if (!map_a(&ta, a.A) || !map_b(&tb, a.B)) return cudaErrorInvalidValue;
+  if (a.A_lo != nullptr) {
+    if (!map_a(&ta_lo, a.A_lo) || !map_b(&tb_lo, a.B_lo)) return cudaErrorInvalidValue;
+  } else {
+    ta_lo = ta;  // never read
+    tb_lo = tb;
+  }
 
-  auto kernel = gemm_kernel<kTf32, kAMajor, kBMajor, kBlockN, kPair, kGather>;
-  constexpr int kThreads = kNumThreads + (kGather ? kNumGatherThreads : 0);
+  auto kernel = gemm_kernel<kTf32, kAMajor, kBMajor, kBlockN, kPair, kGather, kSplit>;
+  constexpr int kThreads = kNumThreads + (kGather ? kNumGatherThreads : 0) + (kSplit ? kNumSplitThreads : 0);
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
@@ -959,10 +1112,10 @@ cudaError_t launch_cfg(const GemmArgs& a, const KernelParams& kp, cudaStream_t s
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, ta, tb, kp);
+    return cudaLaunchKernelEx(&cfg, kernel, ta, tb, ta_lo, tb_lo, kp);
   } else {
     if (grid > kp.total_tiles) grid = kp.total_tiles;
-    kernel<<<grid, kThreads, C::SMEM_BYTES, stream>>>(ta, tb, kp);
+    kernel<<<grid, kThreads, C::SMEM_BYTES, stream>>>(ta, tb, ta_lo, tb_lo, kp);
     return cudaGetLastError();
   }
 }
@@ -975,6 +1128,22 @@ cudaError_t launch_bn(const GemmArgs& a, const KernelParams& kp, int bn, bool pa
     case 128: return launch_cfg<kTf32, kAMajor, kBMajor, 128>(a, kp, s);
     default: return launch_cfg<kTf32, kAMajor, kBMajor, 256>(a, kp, s);
   }
+}
+
+// fp32 operands split in shared memory: 64- and 128-column tiles
+template <int kAMajor, int kBMajor>
+cudaError_t launch_split_bn(const GemmArgs& a, const KernelParams& kp, int bn, cudaStream_t s) {
+  if (bn == 64) return launch_cfg<true, kAMajor, kBMajor, 64, false, false, true>(a, kp, s);
+  return launch_cfg<true, kAMajor, kBMajor, 128, false, false, true>(a, kp, s);
+}
+
+cudaError_t launch_split(const GemmArgs& a, const KernelParams& kp, int bn, cudaStream_t s) {
+  if (a.a_major == kMajorK) {
+    if (a.b_major == kMajorK) return launch_split_bn<kMajorK, kMajorK>(a, kp, bn, s);
+    return launch_split_bn<kMajorK, kMajorMN>(a, kp, bn, s);
+  }
+  if (a.b_major == kMajorK) return launch_split_bn<kMajorMN, kMajorK>(a, kp, bn, s);
+  return launch_split_bn<kMajorMN, kMajorMN>(a, kp, bn, s);
 }
 
 template <bool kTf32>
@@ -996,8 +1165,20 @@ struct Tiling {
 // Tile width, CTA pairing and tile height for a problem (the heuristics of gemm_launch).
 Tiling choose_tiling(const GemmArgs& a) {
   int bn = a.block_n;
+  // symmetric products with long K and enough 256 x 256 tiles on and above the diagonal run on CTA pairs
+  // as well (half the B traffic per CTA, wide MMAs); short K is bound by the epilogue, where 128-wide
+  // tiles spread the mirrored stores over more CTAs
+  bool sym_pair = false;
   if (a.symmetric) {
-    bn = 128;
+    const long long tn = (a.N + 255) / 256;
+    const long long t = tn * (tn + 1) / 2 * a.batch;
+    static const int sym_pair_env = [] {
+      const char* e = getenv("DION_B200_GEMM_SYM_PAIR");
+      return (e && e[0] == '0') ? 0 : 1;
+    }();
+    sym_pair = sym_pair_env && a.pair >= 0 && a.split_k == 1 && a.K >= 1024 && a.N >= 512 && t >= num_sms() / 2 / 2 &&
+               a.A_lo == nullptr && !a.split3;
+    bn = sym_pair ? 256 : 128;
   } else if (bn != 64 && bn != 128 && bn != 256) {
     // widest tile that still gives every SM work; narrow N picks a narrow tile
     const long long tm = (a.M + kBlockM - 1) / kBlockM;
@@ -1028,6 +1209,11 @@ Tiling choose_tiling(const GemmArgs& a) {
     pair = a.pair > 0 || (t >= 2 * (num_sms() / 2) && a.K / a.split_k >= 1024);
   }
 
+  if (sym_pair) pair = true;
+  if (a.A_lo != nullptr || a.split3) {  // the cross-term accumulator exists on unpaired tiles of up to 128 columns
+    pair = false;
+    if (bn > 128) bn = 128;
+  }
   if (a.gather.world > 0 && bn == 64) bn = 128;  // the all-gather variant is built for 128- and 256-wide tiles
   Tiling t;
   t.bn = bn;
@@ -1106,6 +1292,15 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
     g_last_error = "the atomic-add epilogue needs an fp32 output";
     return cudaErrorInvalidValue;
   }
+  if (a.split3 && (a.ab_dtype != kF32 || a.A_lo != nullptr || a.split_k != 1 || a.gather.world > 0)) {
+    g_last_error = "in-kernel splitting: fp32 operands without separate low halves, no split-K";
+    return cudaErrorInvalidValue;
+  }
+  if ((a.A_lo != nullptr) != (a.B_lo != nullptr) ||
+      (a.A_lo != nullptr && (a.ab_dtype != kF32 || a.split_k != 1 || a.gather.world > 0))) {
+    g_last_error = "hi / lo operands: both low halves, fp32 operands, no split-K";
+    return cudaErrorInvalidValue;
+  }
   if (a.symmetric && a.M != a.N) {
     g_last_error = "symmetric mode needs M == N";
     return cudaErrorInvalidValue;
@@ -1151,7 +1346,8 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
     return cudaErrorInvalidValue;
   }
   kp.total_tiles = (int)total;
-  kp.kblocks_total = (a.K + bk - 1) / bk;
+  kp.kblocks_seg = (a.K + bk - 1) / bk;
+  kp.kblocks_total = a.A_lo != nullptr ? 3 * kp.kblocks_seg : kp.kblocks_seg;
   kp.kblocks_per_split = (kp.kblocks_total + a.split_k - 1) / a.split_k;
   kp.alpha = a.alpha;
   kp.beta = a.beta;
@@ -1160,6 +1356,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   kp.ldc = a.ldc;
   kp.c_batch_stride = a.c_batch_stride;
   kp.c_ptrs = a.c_ptrs;
+  kp.c_col_scale = a.c_col_scale;
   kp.D = a.D;
   kp.d_is_bf16 = a.d_dtype == kBF16;
   kp.ldd = a.ldd;
@@ -1213,6 +1410,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
     if (bn == 128) return launch_cfg<false, kMajorK, kMajorK, 128, false, true>(a, kp, stream);
     return launch_cfg<false, kMajorK, kMajorK, 256, false, true>(a, kp, stream);
   }
+  if (a.split3) return launch_split(a, kp, bn, stream);
   return tf32 ? launch_major<true>(a, kp, bn, pair, stream) : launch_major<false>(a, kp, bn, pair, stream);
 }
 

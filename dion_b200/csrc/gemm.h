@@ -34,6 +34,15 @@ enum GemmAct : int {
 struct GemmArgs {
   const void* A = nullptr;
   const void* B = nullptr;
+  // Optional low halves of fp32 operands that were split as x = hi + lo with hi exactly representable
+  // in tf32 (A and B then hold the hi halves; same shapes, pitches and strides).  The product runs as
+  // three K-segments into one accumulator, A B + A_lo B + A B_lo - a 3xTF32 product (close to fp32
+  // accuracy) in a single launch.  Both or neither; fp32 operands, split_k == 1.
+  const void* A_lo = nullptr;
+  const void* B_lo = nullptr;
+  // fp32 operands multiplied with 3xTF32 accuracy, the hi / lo halves being formed in shared memory by the
+  // kernel itself (no copies in global memory; tiles of up to 128 columns).  Excludes A_lo / B_lo.
+  int split3 = 0;
   int ab_dtype = kBF16;
   int a_major = kMajorK;
   int b_major = kMajorK;
@@ -48,6 +57,9 @@ struct GemmArgs {
   int c_dtype = kF32;
   int64_t ldc = 0, c_batch_stride = 0;
   const void* const* c_ptrs = nullptr;  // optional device array of per-batch C pointers
+  // Optional per-column factor of the addend: D = alpha * acc + beta * C * diag(c_col_scale[b]);
+  // fp32 [batch][N], contiguous.
+  const float* c_col_scale = nullptr;
   void* D = nullptr;
   int d_dtype = kF32;
   int64_t ldd = 0, d_batch_stride = 0;

@@ -52,6 +52,14 @@ cudaError_t cast_multi_launch(const TensorListChunk& tl, int src_type, int dst_t
 
 int multi_tensor_block_elems();
 
+// out[b] = x[b] / (||x[b]||_F + eps) for a contiguous batch of bf16 matrices of `per` elements each (the
+// scaling in front of Newton-Schulz).  With `sumsq` (fp32 [batch], the squared norms) one launch; without,
+// a first launch writes per-chunk partial sums to `partial` (batch * frob_chunks(per) floats), which the
+// scaling launch adds up in a fixed order.
+int frob_chunks(long long per);
+cudaError_t frob_scale_launch(const void* x, void* out, float* partial, const float* sumsq, float eps, int batch,
+                              long long per, cudaStream_t s);
+
 // ---------------------------------------------------------------------------
 // Model kernels (bf16 activations, fp32 math)
 // ---------------------------------------------------------------------------
@@ -96,8 +104,11 @@ cudaError_t embedding_bwd_launch(const void* dout, const long long* idx, float* 
 // pitch ldg): computes the upper Cholesky factor R (G = R^T R) with pivot clamping and
 // writes Rinv = R^{-1} (upper triangular, zeros below the diagonal).
 // `info[b]` counts clamped pivots.  `work` is scratch of batch * r * r floats.
+// `jacobi` = false skips the unit-diagonal scaling (the pivot floor is then absolute); `colmask` (optional,
+// fp32 [batch][r]) receives 1 for every column that was factorised and 0 for every clamped pivot.
 cudaError_t chol_inverse_launch(const float* G, float* Rinv, float* work, int* info, int batch, int r,
-                                long long ldg, long long g_batch_stride, float pivot_floor_rel, cudaStream_t s);
+                                long long ldg, long long g_batch_stride, float pivot_floor_rel, cudaStream_t s,
+                                bool jacobi = true, float* colmask = nullptr);
 
 // Column sums of squares: out[b, j] = sum_i X[b, i, j]^2  (X fp32/bf16, row-major [batch, rows, cols])
 cudaError_t col_sumsq_launch(const void* X, int x_type, float* out, int batch, long long rows, int cols,
@@ -114,10 +125,15 @@ cudaError_t attn_bwd_launch(const void* q, const void* k, const void* v, const v
                             int D, float scale, int* status, cudaStream_t stream);
 // hi / lo halves of fp32 data for 3xTF32 products; all three pointers 16-byte aligned
 cudaError_t split_tf32_launch(const float* x, float* hi, float* lo, long long numel, cudaStream_t s);
+// the same for a strided [batch][rows][cols] source (element (b, i, j) at b * bs + i * ld + j; cols, ld and bs
+// multiples of 4) into contiguous hi / lo
+cudaError_t split_tf32_rows_launch(const float* x, float* hi, float* lo, int batch, int rows, int cols, long long ld,
+                                   long long bs, cudaStream_t s);
 // d = rsqrt(diag G) (0 where the diagonal is not above `dead_below`), C = strictly lower part of D G D
 // (all zero for matrices b with skip[b] != 0, `skip` may be null); contiguous [batch, r, r]
+// With `fold`, column j of C is scaled by d_j once more (see the kernel).
 cudaError_t refine_prep_launch(const float* G, float* C, float* d, int batch, int r, float dead_below,
-                               const int* skip, cudaStream_t s);
+                               const int* skip, bool fold, cudaStream_t s);
 
 // ---------------------------------------------------------------------------
 // Collectives over symmetric memory (one arena per process group; the same offset names

@@ -87,7 +87,7 @@ template <int NB>
 __global__ void __launch_bounds__(kCholThreads, 1)
 chol_inverse_kernel(const float* __restrict__ Gall, float* __restrict__ Zall, float* __restrict__ Wall,
                     int* __restrict__ info, int r, long long ldg, long long g_batch_stride, int rp,
-                    float pivot_floor) {
+                    float pivot_floor, int jacobi, float* __restrict__ colmask) {
   extern __shared__ __align__(16) float sm[];
   // rp = r rounded up to a multiple of 64 (+4 pad keeps rows 16-byte aligned)
   float* panelT = sm;                         // [NB][rp]   panel, transposed
@@ -108,7 +108,7 @@ chol_inverse_kernel(const float* __restrict__ Gall, float* __restrict__ Zall, fl
     float d = 0.f;
     if (i < r) {
       const float g = G[(long long)i * ldg + i];
-      d = (g > 1e-30f) ? rsqrtf(g) : 0.f;
+      d = !jacobi ? 1.f : ((g > 1e-30f) ? rsqrtf(g) : 0.f);
     }
     dscale[i] = d;
   }
@@ -140,6 +140,7 @@ chol_inverse_kernel(const float* __restrict__ Gall, float* __restrict__ Zall, fl
         } else {
           dblk[j * (NB + 1) + j] = sqrtf(d);
         }
+        if (colmask) colmask[(long long)b * r + k0 + j] = (d > pivot_floor) ? 1.f : 0.f;
       }
       __syncthreads();
       const float piv = dblk[j * (NB + 1) + j];
@@ -360,7 +361,7 @@ __device__ __forceinline__ void tile_update128(float* __restrict__ out, long lon
 // Returns the number of clamped pivots (valid in every lane).
 template <int NB>
 __device__ __forceinline__ int warp_factor_block(const float* dblk, float* linv, float* linv_al, int nb,
-                                                 float pivot_floor, int lane) {
+                                                 float pivot_floor, int lane, float* colmask) {
   static_assert(NB <= 32, "one lane per row");
   constexpr int P = NB + 1;
   float a[NB], x[NB];
@@ -382,6 +383,7 @@ __device__ __forceinline__ int warp_factor_block(const float* dblk, float* linv,
     // a unit pivot and eliminates nothing, so that rounding noise is never divided by a tiny number
     const bool bad = !(d > pivot_floor);
     if (bad && j < nb) ++clamped;
+    if (colmask != nullptr && lane == 0 && j < nb) colmask[j] = bad ? 0.f : 1.f;
     const float inv_s = bad ? 1.f : rsqrtf(d);
     const float l = (lane > j && !bad) ? aj * inv_s : 0.f;  // L[lane][j] below the diagonal
 #pragma unroll
@@ -408,7 +410,7 @@ template <int NB>
 __global__ void __launch_bounds__(kChol2Threads, 1)
 chol_inverse_pair_kernel(const float* __restrict__ Gall, float* __restrict__ Zall, float* __restrict__ Wall,
                          int* __restrict__ info, int r, long long ldg, long long g_batch_stride, int rp,
-                         float pivot_floor) {
+                         float pivot_floor, int jacobi, float* __restrict__ colmask) {
   extern __shared__ __align__(16) float sm[];
   // rp = r rounded up to a multiple of 128
   float* panelT = sm;                         // [NB][rp]   panel, transposed
@@ -430,7 +432,7 @@ chol_inverse_pair_kernel(const float* __restrict__ Gall, float* __restrict__ Zal
     float d = 0.f;
     if (i < r) {
       const float g = G[(long long)i * ldg + i];
-      d = (g > 1e-30f) ? rsqrtf(g) : 0.f;
+      d = !jacobi ? 1.f : ((g > 1e-30f) ? rsqrtf(g) : 0.f);
     }
     dscale[i] = d;
   }
@@ -455,7 +457,9 @@ chol_inverse_pair_kernel(const float* __restrict__ Gall, float* __restrict__ Zal
       dblk[i * (NB + 1) + j] = v;
     }
     __syncthreads();
-    if (tid < 32) clamp_count += warp_factor_block<NB>(dblk, linv, linv_al, nb, pivot_floor, tid);
+    if (tid < 32)
+      clamp_count += warp_factor_block<NB>(dblk, linv, linv_al, nb, pivot_floor, tid,
+                                           (colmask != nullptr && cta == 0) ? colmask + (long long)b * r + k0 : nullptr);
     __syncthreads();
 
     // ---- 2. Z[k,:] = Linv * B[k,:] for columns < k0 + nb.  Both CTAs need the old block row, so
@@ -581,9 +585,11 @@ __global__ void __launch_bounds__(256) split_tf32_kernel(const float4* __restric
 //   d_i  = G_ii > tiny ? rsqrt(G_ii) : 0
 //   C_ij = i > j ? d_i * G_ij * d_j : 0          (strictly lower part of D G D - I)
 // One block per (row block of 8, batch entry); d is written by the blocks of the first column tile.
+// With `fold` the columns of C are scaled by d once more (C_ij = d_i G_ij d_j^2), which lets the correction
+// X D (I - C^T) run as one product on the unscaled X: X diag(d) - X (C diag(d))^T.
 __global__ void __launch_bounds__(256) refine_prep_kernel(const float* __restrict__ G, float* __restrict__ C,
                                                          float* __restrict__ d, int r, float dead_below,
-                                                         const int* __restrict__ skip) {
+                                                         const int* __restrict__ skip, int fold) {
   const long long b = blockIdx.y;
   // matrices flagged in `skip` get C = 0: they are only rescaled, not corrected
   const bool no_correction = skip != nullptr && skip[b] != 0;
@@ -601,6 +607,7 @@ __global__ void __launch_bounds__(256) refine_prep_kernel(const float* __restric
       const float gjj = g[(long long)j * r + j];
       const float dj = gjj > dead_below ? rsqrtf(gjj) : 0.f;
       v = di * g[(long long)row * r + j] * dj;
+      if (fold) v *= dj;
     }
     c[(long long)row * r + j] = v;
   }
@@ -609,7 +616,9 @@ __global__ void __launch_bounds__(256) refine_prep_kernel(const float* __restric
 }  // namespace
 
 cudaError_t chol_inverse_launch(const float* G, float* Z, float* work, int* info, int batch, int r, long long ldg,
-                                long long g_batch_stride, float pivot_floor, cudaStream_t s) {
+                                long long g_batch_stride, float pivot_floor, cudaStream_t s, bool jacobi,
+                                float* colmask) {
+  const int jac = jacobi ? 1 : 0;
   if (batch == 0 || r == 0) return cudaSuccess;
   constexpr int kMaxDevices = 64;
   int dev = 0;
@@ -645,7 +654,7 @@ cudaError_t chol_inverse_launch(const float* G, float* Z, float* work, int* info
       cfg.attrs = attr;
       cfg.numAttrs = 1;
       return cudaLaunchKernelEx(&cfg, chol_inverse_pair_kernel<32>, G, Z, work, info, r, ldg, g_batch_stride, rp2,
-                                pivot_floor);
+                                pivot_floor, jac, colmask);
     }
   }
   const int rp = ((r + 63) / 64) * 64;
@@ -660,7 +669,7 @@ cudaError_t chol_inverse_launch(const float* G, float* Z, float* work, int* info
       granted32[dev] = true;
     }
     chol_inverse_kernel<32><<<batch, kCholThreads, smem_for(32), s>>>(G, Z, work, info, r, ldg, g_batch_stride, rp,
-                                                                     pivot_floor);
+                                                                     pivot_floor, jac, colmask);
   } else if (smem_for(16) <= kMaxSmem) {
     static bool granted16[kMaxDevices] = {};
     if (smem_for(16) > 48 * 1024 && !granted16[dev]) {
@@ -669,7 +678,7 @@ cudaError_t chol_inverse_launch(const float* G, float* Z, float* work, int* info
       granted16[dev] = true;
     }
     chol_inverse_kernel<16><<<batch, kCholThreads, smem_for(16), s>>>(G, Z, work, info, r, ldg, g_batch_stride, rp,
-                                                                     pivot_floor);
+                                                                     pivot_floor, jac, colmask);
   } else {
     return cudaErrorNotSupported;  // rank too large for the kernels' shared memory: the caller falls back
   }
@@ -681,6 +690,46 @@ cudaError_t col_sumsq_launch(const void* X, int x_type, float* out, int batch, l
   if (batch == 0 || cols == 0) return cudaSuccess;
   dim3 grid((cols + 31) / 32, batch);
   col_sumsq_kernel<<<grid, 256, 0, s>>>(X, x_type, out, rows, cols, ldx, batch_stride);
+  return cudaGetLastError();
+}
+
+// Rows of a strided [batch][rows][cols] array (element (b, i, j) at b * bs + i * ld + j) into contiguous hi / lo.
+__global__ void __launch_bounds__(256) split_tf32_rows_kernel(const float* __restrict__ x, float* __restrict__ hi,
+                                                             float* __restrict__ lo, long long rows_total, int rows,
+                                                             int cols, long long ld, long long bs) {
+  const int vpr = cols >> 2;  // float4 per row (cols is a multiple of 4)
+  const long long nvec = rows_total * vpr;
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (long long)gridDim.x * blockDim.x) {
+    const long long row = v / vpr;
+    const int c = (int)(v - row * vpr) << 2;
+    const long long b = row / rows;
+    const long long i = row - b * rows;
+    const float4 q = *reinterpret_cast<const float4*>(x + b * bs + i * ld + c);
+    float4 h, l;
+    h.x = __int_as_float(__float_as_int(q.x) & 0xffffe000);
+    h.y = __int_as_float(__float_as_int(q.y) & 0xffffe000);
+    h.z = __int_as_float(__float_as_int(q.z) & 0xffffe000);
+    h.w = __int_as_float(__float_as_int(q.w) & 0xffffe000);
+    l.x = q.x - h.x;
+    l.y = q.y - h.y;
+    l.z = q.z - h.z;
+    l.w = q.w - h.w;
+    reinterpret_cast<float4*>(hi)[v] = h;
+    reinterpret_cast<float4*>(lo)[v] = l;
+  }
+}
+
+cudaError_t split_tf32_rows_launch(const float* x, float* hi, float* lo, int batch, int rows, int cols, long long ld,
+                                   long long bs, cudaStream_t s) {
+  if (batch == 0 || rows == 0 || cols == 0) return cudaSuccess;
+  if ((cols & 3) || (ld & 3) || (bs & 3) ||
+      ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(hi) | reinterpret_cast<uintptr_t>(lo)) & 15))
+    return cudaErrorInvalidValue;
+  const long long rows_total = (long long)batch * rows;
+  const long long nvec = rows_total * (cols >> 2);
+  long long grid = (nvec + 255) / 256;
+  if (grid > 148 * 16) grid = 148 * 16;
+  split_tf32_rows_kernel<<<(int)grid, 256, 0, s>>>(x, hi, lo, rows_total, rows, cols, ld, bs);
   return cudaGetLastError();
 }
 
@@ -699,10 +748,10 @@ cudaError_t split_tf32_launch(const float* x, float* hi, float* lo, long long nu
 }
 
 cudaError_t refine_prep_launch(const float* G, float* C, float* d, int batch, int r, float dead_below,
-                               const int* skip, cudaStream_t s) {
+                               const int* skip, bool fold, cudaStream_t s) {
   if (batch == 0 || r == 0) return cudaSuccess;
   if (batch > 65535) return cudaErrorInvalidValue;
-  refine_prep_kernel<<<dim3((r + 7) / 8, batch), 256, 0, s>>>(G, C, d, r, dead_below, skip);
+  refine_prep_kernel<<<dim3((r + 7) / 8, batch), 256, 0, s>>>(G, C, d, r, dead_below, skip, fold ? 1 : 0);
   return cudaGetLastError();
 }
 

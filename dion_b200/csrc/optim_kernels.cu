@@ -295,11 +295,101 @@ __global__ void __launch_bounds__(kThreads) cast_kernel(const __grid_constant__ 
   });
 }
 
+// ---- Frobenius scaling in front of Newton-Schulz (X / (||X||_F + eps), dion/muon.py:628-631):
+// partial sums of squares per chunk, then every block of the scaling pass adds the partials of its
+// matrix in the same fixed order, so the result does not depend on how the blocks are scheduled.
+constexpr int kFrobChunk = 16384;  // bf16 elements per block
+
+__global__ void __launch_bounds__(kThreads) frob_partial_kernel(const __nv_bfloat16* __restrict__ x,
+                                                               float* __restrict__ partial, long long per, int nchunk) {
+  const long long b = blockIdx.y;
+  const long long lo = (long long)blockIdx.x * kFrobChunk;
+  const long long hi = min(per, lo + (long long)kFrobChunk);
+  const __nv_bfloat16* xb = x + b * per;
+  float acc = 0.f;
+  if (((reinterpret_cast<uintptr_t>(xb) | (uintptr_t)(per * 2)) & 15) == 0) {
+    for (long long i = lo + threadIdx.x * 8; i + 7 < hi; i += kThreads * 8) {
+      const uint4 q = *reinterpret_cast<const uint4*>(xb + i);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc = fmaf(f.x, f.x, acc);
+        acc = fmaf(f.y, f.y, acc);
+      }
+    }
+    for (long long i = lo + ((hi - lo) & ~7LL) + threadIdx.x; i < hi; i += kThreads) {
+      const float f = __bfloat162float(xb[i]);
+      acc = fmaf(f, f, acc);
+    }
+  } else {
+    for (long long i = lo + threadIdx.x; i < hi; i += kThreads) {
+      const float f = __bfloat162float(xb[i]);
+      acc = fmaf(f, f, acc);
+    }
+  }
+  const float s = block_sum(acc);
+  if (threadIdx.x == 0) partial[b * nchunk + blockIdx.x] = s;
+}
+
+__global__ void __launch_bounds__(kThreads) frob_scale_kernel(const __nv_bfloat16* __restrict__ x,
+                                                             __nv_bfloat16* __restrict__ out,
+                                                             const float* __restrict__ partial, int npart,
+                                                             const float* __restrict__ sumsq, float eps, long long per) {
+  __shared__ float scale_s;
+  const long long b = blockIdx.y;
+  float acc = 0.f;
+  if (sumsq == nullptr)
+    for (int i = threadIdx.x; i < npart; i += kThreads) acc += partial[b * npart + i];
+  const float tot = block_sum(acc);
+  if (threadIdx.x == 0) scale_s = 1.f / (sqrtf(sumsq != nullptr ? sumsq[b] : tot) + eps);
+  __syncthreads();
+  const float sc = scale_s;
+  const long long lo = (long long)blockIdx.x * kFrobChunk;
+  const long long hi = min(per, lo + (long long)kFrobChunk);
+  const __nv_bfloat16* xb = x + b * per;
+  __nv_bfloat16* ob = out + b * per;
+  if (((reinterpret_cast<uintptr_t>(xb) | reinterpret_cast<uintptr_t>(ob) | (uintptr_t)(per * 2)) & 15) == 0) {
+    for (long long i = lo + threadIdx.x * 8; i + 7 < hi; i += kThreads * 8) {
+      uint4 q = *reinterpret_cast<const uint4*>(xb + i);
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        h[j] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+      }
+      *reinterpret_cast<uint4*>(ob + i) = q;
+    }
+    for (long long i = lo + ((hi - lo) & ~7LL) + threadIdx.x; i < hi; i += kThreads)
+      ob[i] = __float2bfloat16(__bfloat162float(xb[i]) * sc);
+  } else {
+    for (long long i = lo + threadIdx.x; i < hi; i += kThreads) ob[i] = __float2bfloat16(__bfloat162float(xb[i]) * sc);
+  }
+}
+
 inline int total_blocks(const TensorListChunk& tl) { return tl.block_start[tl.num_tensors]; }
 
 }  // namespace
 
 int multi_tensor_block_elems() { return kBlockElems; }
+
+int frob_chunks(long long per) { return (int)((per + kFrobChunk - 1) / kFrobChunk); }
+
+cudaError_t frob_scale_launch(const void* x, void* out, float* partial, const float* sumsq, float eps, int batch,
+                              long long per, cudaStream_t s) {
+  if (batch == 0 || per == 0) return cudaSuccess;
+  if (batch > 65535 || (sumsq == nullptr && partial == nullptr)) return cudaErrorInvalidValue;
+  const int nchunk = frob_chunks(per);
+  const dim3 grid(nchunk, batch);
+  if (sumsq == nullptr) {
+    frob_partial_kernel<<<grid, kThreads, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), partial, per, nchunk);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  frob_scale_kernel<<<grid, kThreads, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x),
+                                              reinterpret_cast<__nv_bfloat16*>(out), partial, nchunk, sumsq, eps, per);
+  return cudaGetLastError();
+}
 
 cudaError_t adamw_multi_launch(const TensorListChunk& tl, int g_type, int m_type, int v_type, bool has_shadow,
                                const AdamWHyper& h, cudaStream_t s) {

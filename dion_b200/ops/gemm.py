@@ -76,7 +76,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, c: Optional[torch.Tensor] = None, 
          alpha: float = 1.0, beta: float = 0.0, act: Optional[str] = None, out_dtype: Optional[torch.dtype] = None,
          accumulate: bool = False, split_k: int = 1, symmetric: bool = False, shadow: Optional[torch.Tensor] = None,
          block_n: int = 0, pair: int = 0, out_ptrs: Optional[torch.Tensor] = None, c_ptrs: Optional[torch.Tensor] = None,
-         shadow_ptrs: Optional[torch.Tensor] = None, out_dup: int = 1) -> torch.Tensor:
+         shadow_ptrs: Optional[torch.Tensor] = None, out_dup: int = 1, a_lo: Optional[torch.Tensor] = None,
+         b_lo: Optional[torch.Tensor] = None, c_col_scale: Optional[torch.Tensor] = None,
+         split3: bool = False) -> torch.Tensor:
     """``out = act(alpha * a @ b + beta * c)``.
 
     a: ``[B,] M, K``; b: ``[B,] K, N``; each may be a transposed view (one unit stride in
@@ -87,6 +89,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, c: Optional[torch.Tensor] = None, 
     one device address per batch element, for outputs that are separate allocations.
     With ``out_dup = k > 1`` every batch element is stored to k destinations, ``out_ptrs[b * k + j]``
     (for instance one slot of a symmetric buffer on each rank of a group).
+    ``a_lo`` / ``b_lo`` (fp32, laid out like ``a`` / ``b``): ``a`` and ``b`` are then the tf32-exact high
+    halves of split operands and the product is ``a @ b + a_lo @ b + a @ b_lo`` accumulated in one pass
+    over three K-segments - a 3xTF32 product in a single launch.
+    ``c_col_scale`` (fp32 ``[B, N]``) scales the columns of the addend: ``beta * c * diag(c_col_scale)``.
+    ``split3=True`` (fp32 operands): the same 3xTF32 product without any hi / lo tensors - the kernel splits
+    every operand tile in shared memory, so the operands are read once.  On CPU tensors, and for operands
+    the kernel cannot address, the product is taken in plain fp32.
     """
     if a.dim() not in (2, 3) or a.dim() != b.dim():
         raise ValueError("gemm expects two 2-D or two 3-D operands")
@@ -99,6 +108,20 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, c: Optional[torch.Tensor] = None, 
         shape = (*a.shape[:-2], M, N)
         out = torch.empty(shape, dtype=out_dtype or a.dtype, device=a.device)
 
+    if (a_lo is None) != (b_lo is None):
+        raise ValueError("hi / lo operands need both low halves")
+    if split3 and (a_lo is not None or (a.is_cuda and a.dtype != torch.float32)):
+        raise ValueError("split3 takes fp32 operands without separate low halves")
+    if c_col_scale is not None and (c is None or not a.is_cuda):
+        if c is None:
+            raise ValueError("c_col_scale needs the addend c")
+        return gemm(a, b, c=c.float() * c_col_scale.view(*c.shape[:-2], 1, c.shape[-1]), out=out, alpha=alpha,
+                    beta=beta, act=act, out_dtype=out_dtype, a_lo=a_lo, b_lo=b_lo, split3=split3)
+    if a_lo is not None and (not a.is_cuda or a.dtype != torch.float32 or not (_tma_ok(a_lo) and _tma_ok(b_lo))):
+        # no kernel for this case: the same sum from three products
+        out = gemm(a, b, c=c, out=out, alpha=alpha, beta=beta, act=act, out_dtype=out_dtype)
+        gemm(a_lo, b, c=out, out=out, alpha=alpha, beta=1.0)
+        return gemm(a, b_lo, c=out, out=out, alpha=alpha, beta=1.0)
     if not runtime.use_cuda_kernels(a):
         if out_ptrs is not None or c_ptrs is not None or shadow_ptrs is not None:
             raise ValueError("pointer-array outputs need CUDA tensors")
@@ -117,5 +140,5 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, c: Optional[torch.Tensor] = None, 
         raise ValueError("split_k > 1 needs accumulate=True")
     torch.ops.dion_b200.gemm(a, b, c, out, shadow, c_ptrs, out_ptrs, shadow_ptrs, float(alpha), float(beta),
                              _ACT[act], 1 if accumulate else 0, int(split_k), bool(symmetric), int(block_n), int(pair),
-                             runtime.status_tensor(a.device), int(out_dup))
+                             runtime.status_tensor(a.device), int(out_dup), a_lo, b_lo, c_col_scale, bool(split3))
     return out

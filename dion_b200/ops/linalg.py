@@ -3,6 +3,7 @@ column norms.  CUDA tensors use the in-tree kernels, CPU tensors a PyTorch refer
 
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -15,15 +16,20 @@ DEFAULT_PIVOT_FLOOR = 1e-6
 MAX_KERNEL_RANK = 1728
 
 
-def chol_inverse_reference(G: torch.Tensor, pivot_floor: float = DEFAULT_PIVOT_FLOOR) -> Tuple[torch.Tensor, torch.Tensor]:
+def chol_inverse_reference(G: torch.Tensor, pivot_floor: float = DEFAULT_PIVOT_FLOOR, jacobi: bool = True,
+                           colmask: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Pure PyTorch version of the kernel: Jacobi scaling, Cholesky, triangular inverse.  A pivot that is
     not above `pivot_floor` marks a column that (numerically) depends on the earlier ones: it gets a unit
     pivot and eliminates nothing, so rounding noise is never divided by a tiny number; `info` counts such
-    pivots.  Returns (Z, info) with Z lower triangular, Z @ G @ Z.T ~= I on the independent columns."""
+    pivots.  Returns (Z, info) with Z lower triangular, Z @ G @ Z.T ~= I on the independent columns.
+    ``jacobi=False`` skips the scaling (the floor is then absolute); ``colmask`` (``[B, r]``) receives 1
+    for factorised columns and 0 for clamped pivots."""
     G = G.float()
     B, r, _ = G.shape
     diag = torch.diagonal(G, dim1=-2, dim2=-1)
     d = torch.where(diag > 1e-30, diag.clamp_min(1e-30).rsqrt(), torch.zeros_like(diag))
+    if not jacobi:
+        d = torch.ones_like(diag)
     W = G * d.unsqueeze(-1) * d.unsqueeze(-2)
     L = torch.zeros_like(W)
     info = torch.zeros(B, dtype=torch.int32, device=G.device)
@@ -31,6 +37,8 @@ def chol_inverse_reference(G: torch.Tensor, pivot_floor: float = DEFAULT_PIVOT_F
     for j in range(r):
         piv = W[:, j, j]
         bad = ~(piv > pivot_floor)
+        if colmask is not None:
+            colmask[:, j] = (~bad).to(colmask.dtype)
         info += bad.to(torch.int32)
         piv = torch.where(bad, torch.ones_like(piv), piv).sqrt()
         L[:, j, j] = piv
@@ -44,6 +52,92 @@ def chol_inverse_reference(G: torch.Tensor, pivot_floor: float = DEFAULT_PIVOT_F
     return Z, info
 
 
+# Ranks above this are factorised block by block (see chol_inverse_blocked); DION_B200_CHOL_BLOCKED=0
+# keeps the one-launch kernel for every rank it fits.
+BLOCK = 256
+BLOCKED = os.environ.get("DION_B200_CHOL_BLOCKED", "1") != "0"
+
+
+def _split_block(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """tf32 halves (contiguous) of a ``[B, rows, cols]`` block that may be a strided view."""
+    if (runtime.use_cuda_kernels(x) and x.dtype == torch.float32 and x.stride(-1) == 1 and x.shape[-1] % 4 == 0
+            and x.stride(-2) % 4 == 0 and x.stride(0) % 4 == 0 and x.data_ptr() % 16 == 0):
+        hi = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+        lo = torch.empty_like(hi)
+        torch.ops.dion_b200.split_tf32_rows(x, hi, lo)
+        return hi, lo
+    return split_tf32(x.contiguous())
+
+
+def _diag_inverse(D: torch.Tensor, pivot_floor: float):
+    """Inverse Cholesky factor of every diagonal block ``D: [B, nb, nb]`` (a strided view, already in the
+    unit-diagonal scaling of the whole matrix, so no scaling of its own and an absolute pivot floor),
+    the 0 / 1 mask of its clamped pivots and their count."""
+    B, nb, _ = D.shape
+    mask = torch.empty(B, nb, dtype=torch.float32, device=D.device)
+    if runtime.use_cuda_kernels(D):
+        Zd = torch.empty(B, nb, nb, dtype=torch.float32, device=D.device)
+        work = torch.empty_like(Zd)
+        info = torch.empty(B, dtype=torch.int32, device=D.device)
+        torch.ops.dion_b200.chol_inverse(D, Zd, work, info, float(pivot_floor), False, mask)
+        return Zd, mask, info
+    Zd, info = chol_inverse_reference(D, pivot_floor, jacobi=False, colmask=mask)
+    return Zd, mask, info
+
+
+def chol_inverse_blocked(G: torch.Tensor, pivot_floor: float = DEFAULT_PIVOT_FLOOR, block: int = BLOCK,
+                         out: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """:func:`chol_inverse` for larger ranks with the cubic work on the tensor cores: a right-looking
+    block factorisation whose diagonal blocks (``block`` columns) go through the Cholesky-inverse kernel
+    and whose panels, trailing updates and the block-wise inverse are batched 3xTF32 GEMMs
+    (hi / lo operands, one launch per product):
+
+        Z_kk = chol(W_kk)^-1;   L_ik = W_ik Z_kk^T (i > k);   W_ij -= L_ik L_jk^T (i, j > k)
+        Z_ik = -Z_ii (L_i,0:i Z_0:i,0:i)[:, k]               (row blocks of the inverse, top to bottom)
+
+    A clamped pivot has a unit diagonal and eliminates nothing, exactly as in the one-launch kernel: its
+    row of Z_kk is left out of the panel product, which zeroes its column of L below the block."""
+    from .gemm import gemm
+
+    G = G.float()
+    B, r, _ = G.shape
+    diag = torch.diagonal(G, dim1=-2, dim2=-1)
+    d = torch.where(diag > 1e-30, diag.clamp_min(1e-30).rsqrt(), torch.zeros_like(diag))
+    W = G * d.unsqueeze(-1) * d.unsqueeze(-2)
+    Z = out if out is not None else torch.empty_like(W)
+    Z.zero_()
+    info = torch.zeros(B, dtype=torch.int32, device=G.device)
+    edges = list(range(0, r, block)) + [r]
+    zsplit = []
+    for k in range(len(edges) - 1):
+        k0, k1 = edges[k], edges[k + 1]
+        Zd, mask, inf = _diag_inverse(W[:, k0:k1, k0:k1], pivot_floor)
+        info += inf
+        Z[:, k0:k1, k0:k1].copy_(Zd)
+        zsplit.append(split_tf32(Zd))
+        if k1 == r:
+            break
+        zm_hi, zm_lo = split_tf32(Zd * mask.unsqueeze(-1))
+        panel = W[:, k1:, k0:k1]
+        p_hi, p_lo = _split_block(panel)
+        gemm(p_hi, zm_hi.transpose(-1, -2), a_lo=p_lo, b_lo=zm_lo.transpose(-1, -2), out=panel)   # L_ik
+        l_hi, l_lo = _split_block(panel)
+        trail = W[:, k1:, k1:]
+        gemm(l_hi, l_hi.transpose(-1, -2), a_lo=l_lo, b_lo=l_lo.transpose(-1, -2), c=trail, out=trail, alpha=-1.0,
+             beta=1.0)
+    for i in range(1, len(edges) - 1):
+        i0, i1 = edges[i], edges[i + 1]
+        l_hi, l_lo = _split_block(W[:, i0:i1, :i0])
+        z_hi, z_lo = _split_block(Z[:, :i0, :i0])
+        T = gemm(l_hi, z_hi, a_lo=l_lo, b_lo=z_lo)
+        t_hi, t_lo = split_tf32(T)
+        zi_hi, zi_lo = zsplit[i]
+        gemm(zi_hi, t_hi, a_lo=zi_lo, b_lo=t_lo, out=Z[:, i0:i1, :i0], alpha=-1.0)
+    # undo the scaling: L^-1 = L'^-1 D, column j times d_j
+    Z.mul_(d.unsqueeze(-2))
+    return Z, info
+
+
 def chol_inverse(G: torch.Tensor, pivot_floor: float = DEFAULT_PIVOT_FLOOR,
                  out: Optional[torch.Tensor] = None, work: Optional[torch.Tensor] = None,
                  info: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -53,6 +147,13 @@ def chol_inverse(G: torch.Tensor, pivot_floor: float = DEFAULT_PIVOT_FLOOR,
     if G.dim() != 3 or G.shape[-1] != G.shape[-2]:
         raise ValueError("chol_inverse expects [batch, r, r]")
     B, r, _ = G.shape
+    if (BLOCKED and G.is_cuda and G.dtype == torch.float32 and r > BLOCK and r % 4 == 0 and B > 0
+            and (out is None or out.is_contiguous())):
+        Z, inf = chol_inverse_blocked(G, pivot_floor, out=out)
+        if info is not None:
+            info.copy_(inf)
+            inf = info
+        return Z, inf
     if not runtime.use_cuda_kernels(G) or r > MAX_KERNEL_RANK or G.dtype != torch.float32:
         Z, inf = chol_inverse_reference(G, pivot_floor)
         if out is not None:
@@ -107,19 +208,24 @@ def split_tf32(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
 DEAD_COLUMN_BELOW = 1e-4
 
 
-def refine_prep(G: torch.Tensor, dead_below: float = 1e-30,
-                skip: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+def refine_prep(G: torch.Tensor, dead_below: float = 1e-30, skip: Optional[torch.Tensor] = None,
+                fold: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """From Gram matrices ``G: [B, r, r]``: ``d = rsqrt(diag G)`` (0 where the diagonal is not above
     `dead_below`) and ``C = stril(D G D)``, the strictly lower part of the column-scaled Gram matrix.
-    ``skip`` (int32, one per matrix): C is zero for the matrices where it is non-zero."""
+    ``skip`` (int32, one per matrix): C is zero for the matrices where it is non-zero.
+    ``fold``: the columns of C are scaled by d once more (``C diag(d)``), so that the correction
+    ``(X D)(I - C^T)`` can be taken on the unscaled X as ``X diag(d) - X (C diag(d))^T``."""
     if runtime.use_cuda_kernels(G) and G.dtype == torch.float32 and G.dim() == 3:
         G = G.contiguous()
         C, d = torch.empty_like(G), torch.empty(G.shape[:-1], dtype=torch.float32, device=G.device)
-        torch.ops.dion_b200.refine_prep(G, C, d, float(dead_below), None if skip is None else skip.contiguous())
+        torch.ops.dion_b200.refine_prep(G, C, d, float(dead_below), None if skip is None else skip.contiguous(),
+                                        bool(fold))
         return C, d
     diag = torch.diagonal(G, dim1=-2, dim2=-1)
     d = torch.where(diag > dead_below, diag.clamp_min(1e-30).rsqrt(), torch.zeros_like(diag))
     C = torch.tril(G * d.unsqueeze(-1) * d.unsqueeze(-2), diagonal=-1)
     if skip is not None:
         C = C * (skip == 0).to(C.dtype).view(-1, 1, 1)
+    if fold:
+        C = C * d.unsqueeze(-2)
     return C, d

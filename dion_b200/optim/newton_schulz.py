@@ -67,10 +67,11 @@ def newton_schulz(G: Tensor, epsilon: float = 1e-7, coeffs: Sequence[Tuple[float
     X = X.to(torch.bfloat16)
     if not X.is_contiguous():
         X = X.contiguous()
-    if sumsq is None:
-        sumsq = X.float().square().sum(dim=(-2, -1))
-    scale = (1.0 / (sumsq.float().sqrt() + float(epsilon))).view(-1, 1, 1)
-    X = (X.float() * scale).to(torch.bfloat16)
+    # X / (||X||_F + eps) in one pass over X (two when the norms still have to be computed)
+    ops.runtime.use_cuda_kernels(X)  # loads the extension
+    Xs = torch.empty_like(X)
+    torch.ops.dion_b200.frob_scale(X, Xs, None if sumsq is None else sumsq.float().contiguous(), float(epsilon))
+    X = Xs
     Bn, m, n = X.shape
     tall = m > n
     k = n if tall else m

@@ -62,11 +62,9 @@ def gram(P: Tensor, reduce_group=None) -> Tensor:
     if GRAM_PRECISION == "tf32":
         return ops.gemm(Pt, P, out=out, symmetric=True)
     hi, lo = _split_tf32(P)
-    G = ops.gemm(hi.transpose(-1, -2), hi, out=out, symmetric=True)
-    # cross terms lo^T hi + hi^T lo; lo^T lo is below fp32 resolution
-    ops.gemm(lo.transpose(-1, -2), hi, c=G, out=G, beta=1.0)
-    ops.gemm(hi.transpose(-1, -2), lo, c=G, out=G, beta=1.0)
-    return G
+    # hi^T hi and the cross terms lo^T hi + hi^T lo in one launch (three K-segments into one accumulator);
+    # lo^T lo is below fp32 resolution
+    return ops.gemm(hi.transpose(-1, -2), hi, out=out, symmetric=True, a_lo=lo.transpose(-1, -2), b_lo=lo)
 
 
 def apply_right(P: Tensor, Z: Tensor) -> Tensor:
@@ -78,10 +76,7 @@ def apply_right(P: Tensor, Z: Tensor) -> Tensor:
         return ops.gemm(P, Zt)
     p_hi, p_lo = _split_tf32(P)
     z_hi, z_lo = _split_tf32(Z)
-    out = ops.gemm(p_hi, z_hi.transpose(-1, -2))
-    ops.gemm(p_lo, z_hi.transpose(-1, -2), c=out, out=out, beta=1.0)
-    ops.gemm(p_hi, z_lo.transpose(-1, -2), c=out, out=out, beta=1.0)
-    return out
+    return ops.gemm(p_hi, z_hi.transpose(-1, -2), a_lo=p_lo, b_lo=z_lo.transpose(-1, -2))
 
 
 def orthonormalize_cholqr(P: Tensor, row_group: Optional[dist.ProcessGroup] = None, passes: int = 2,
@@ -106,7 +101,8 @@ def orthonormalize_cholqr(P: Tensor, row_group: Optional[dist.ProcessGroup] = No
     return X.to(out_dtype)
 
 
-def _refine(X: Tensor, row_group: Optional[dist.ProcessGroup], gave_up: Optional[Tensor] = None) -> Tensor:
+def _refine(X: Tensor, row_group: Optional[dist.ProcessGroup], gave_up: Optional[Tensor] = None,
+            out_dtype: Optional[torch.dtype] = None) -> Tensor:
     """One triangular Newton correction of an almost orthonormal X: with the column-scaled
     Gram matrix D G D = I + E, the Cholesky factor's inverse is I - stril(E) to first order,
     so X <- (X D) (I - stril(E))^T squares the orthogonality error while keeping the column
@@ -118,12 +114,15 @@ def _refine(X: Tensor, row_group: Optional[dist.ProcessGroup], gave_up: Optional
     # far below 1) are dropped instead of being blown up to unit length
     # a matrix whose factorisation gave up on some pivot (`gave_up`, int32 per matrix) is far from
     # orthonormal, where the first-order correction diverges: it is only rescaled
+    if X.is_cuda:
+        # X D (I - C^T) = X diag(d) - X (C diag(d))^T as one product on the unscaled X: the column scale
+        # rides on the addend in the epilogue; the correction term is small, so a single tensor-core
+        # pass keeps its error far below fp32 resolution
+        C, d = ops.linalg.refine_prep(G, ops.linalg.DEAD_COLUMN_BELOW, gave_up, fold=True)
+        return ops.gemm(X, C.transpose(-1, -2), c=X, alpha=-1.0, beta=1.0, c_col_scale=d, out_dtype=out_dtype)
     C, d = ops.linalg.refine_prep(G, ops.linalg.DEAD_COLUMN_BELOW, gave_up)
     Xs = X * d.unsqueeze(-2)
-    if X.is_cuda:
-        # the correction term is small, a single tensor-core pass keeps it far below fp32 resolution
-        return ops.gemm(Xs, C.transpose(-1, -2), c=Xs, alpha=-1.0, beta=1.0)
-    return Xs - Xs @ C.transpose(-1, -2)
+    return (Xs - Xs @ C.transpose(-1, -2)).to(out_dtype or X.dtype)
 
 
 # Work sharding: a batch that is identical on every rank of a group is split over the group, each rank
@@ -255,7 +254,7 @@ def _orthonormalize_many(Ps, row_groups, refine_passes, pivot_floor, shard_group
     if any(g is not None for g in shard_groups):
         parts = [P.float() if (g is None or t is not None) else _my_share(P.float(), g)
                  for P, g, t in zip(Ps, shard_groups, totals)]
-        outs = _orthonormalize_many(parts, row_groups, refine_passes, pivot_floor, None, None, None, robust, infos)
+        outs = _orthonormalize_many(parts, row_groups, refine_passes, pivot_floor, None, None, out_dtypes, robust, infos)
         return [X.to(dt) if g is None else _gather_shares(X.to(dt), g, P.shape[0] if t is None else t)
                 for X, P, g, t, dt in zip(outs, Ps, shard_groups, totals, out_dtypes)]
     dtypes = out_dtypes
@@ -294,8 +293,10 @@ def _orthonormalize_many(Ps, row_groups, refine_passes, pivot_floor, shard_group
                 off += b
     if infos is not None:
         infos.extend(first_info)
-    for _ in range(refine_passes):
-        Xs = [_refine(X, g, bad) for X, g, bad in zip(Xs, row_groups, last_info)]
+    for k in range(refine_passes):
+        # the last correction writes the result in the dtype its consumer multiplies with
+        last = k == refine_passes - 1
+        Xs = [_refine(X, g, bad, dt if last else None) for X, g, bad, dt in zip(Xs, row_groups, last_info, dtypes)]
     return [X.to(dt) for X, dt in zip(Xs, dtypes)]
 
 

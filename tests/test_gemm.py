@@ -204,3 +204,90 @@ def test_gemm_cta_pair_matches_single_cta_bitwise():
     y1 = gemm(a, b, pair=1)
     y0 = gemm(a, b, pair=-1)
     assert torch.equal(y0, y1)
+
+
+def _split(x):
+    hi = (x.contiguous().view(torch.int32) & -8192).view(torch.float32)
+    return hi, x - hi
+
+
+def test_gemm_hi_lo_operands_and_column_scale_cpu():
+    a, b, c = torch.randn(2, 9, 12), torch.randn(2, 12, 5), torch.randn(2, 9, 5)
+    a_hi, a_lo = _split(a)
+    b_hi, b_lo = _split(b)
+    out = gemm(a_hi, b_hi, a_lo=a_lo, b_lo=b_lo)
+    torch.testing.assert_close(out, a_hi @ b_hi + a_lo @ b_hi + a_hi @ b_lo)
+    s = torch.rand(2, 5)
+    out = gemm(a, b, c=c, alpha=-1.0, beta=1.0, c_col_scale=s)
+    torch.testing.assert_close(out, c * s.unsqueeze(1) - a @ b)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ta", [False, True])
+@pytest.mark.parametrize("tb", [False, True])
+@pytest.mark.parametrize("shape,symmetric", [((384, 200, 328), False), ((512, 512, 1000), False), ((256, 256, 520), True)])
+def test_gemm_hi_lo_operands_reach_fp32_accuracy_in_one_launch(ta, tb, shape, symmetric):
+    """A product of split operands (three K-segments into one accumulator) against fp64: a single tf32
+    pass is about 1e-3 off, the three-segment product is close to fp32 rounding."""
+    M, N, K = shape
+    B = 3
+    if symmetric:
+        if ta != tb:
+            pytest.skip("a symmetric product multiplies an operand with its own transpose")
+        x = _operand(M, K, torch.float32, ta, batch=B)
+        a, b = x, x.transpose(-1, -2)
+    else:
+        a = _operand(M, K, torch.float32, ta, batch=B)
+        b = _operand(K, N, torch.float32, tb, batch=B)
+
+    def split_like(t):  # halves with the memory layout of t
+        base = t.transpose(-1, -2) if t.stride(-1) != 1 else t
+        hi, lo = _split(base)
+        return (hi.transpose(-1, -2), lo.transpose(-1, -2)) if t.stride(-1) != 1 else (hi, lo)
+
+    a_hi, a_lo = split_like(a)
+    b_hi, b_lo = split_like(b)
+    ref = a.double() @ b.double()
+    one = gemm(a_hi, b_hi, symmetric=symmetric)
+    three = gemm(a_hi, b_hi, a_lo=a_lo, b_lo=b_lo, symmetric=symmetric)
+    e1, e3 = _rel_err(one, ref), _rel_err(three, ref)
+    assert e3 < 2e-5, (e1, e3)
+    assert e1 > 10 * e3, (e1, e3)  # the segments really were added
+    if symmetric:
+        # mirrored tiles are exact copies; inside a diagonal tile the two cross terms of an element and of its
+        # mirror image are added in opposite order, which may differ in the last bit
+        torch.testing.assert_close(three, three.transpose(-1, -2), rtol=0, atol=2e-6 * ref.abs().max().item())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+def test_gemm_column_scale_on_the_addend(out_dtype):
+    B, M, N, K = 2, 300, 200, 96
+    a = torch.randn(B, M, K, device="cuda")
+    b = torch.randn(B, K, N, device="cuda") * 0.05
+    c = torch.randn(B, M, N, device="cuda")
+    s = torch.rand(B, N, device="cuda") + 0.5
+    out = gemm(a, b, c=c, alpha=-1.0, beta=1.0, c_col_scale=s, out_dtype=out_dtype)
+    ref = c * s.unsqueeze(1) - a @ b
+    assert _rel_err(out, ref) < (2e-2 if out_dtype == torch.bfloat16 else 3e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n,k,batch", [(1024, 1024, 2), (768, 3072, 6), (520, 1032, 5), (512, 2048, 3)])
+def test_gemm_symmetric_long_k_on_cta_pairs_with_staged_mirror(dtype, n, k, batch):
+    """Symmetric products with K >= 1024 take 256 x 256 tiles on CTA pairs; off-diagonal tiles are stored a
+    second time transposed, through shared memory.  The result must be exactly symmetric and match the
+    plain product, also with an addend (b A + c A A) and ragged edges."""
+    x = torch.randn(batch, n, k, device="cuda").to(dtype) * 0.05
+    out = gemm(x, x.transpose(1, 2), symmetric=True)
+    ref = x.float() @ x.float().transpose(1, 2)
+    tol = 2e-2 if dtype == torch.bfloat16 else 3e-3
+    assert _rel_err(out, ref) < tol
+    assert torch.equal(out, out.transpose(1, 2))
+    a = out.clone()
+    if n * 4 % 16 == 0 and a.shape[-1] >= 1024:
+        poly = gemm(a, a.transpose(1, 2), c=a, alpha=0.5, beta=-1.5, symmetric=True)
+        ref2 = 0.5 * a.float() @ a.float().transpose(1, 2) - 1.5 * a.float()
+        assert _rel_err(poly, ref2) < tol
+        assert torch.equal(poly, poly.transpose(1, 2))

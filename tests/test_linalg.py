@@ -133,3 +133,76 @@ def test_orthonormalisation_of_ill_conditioned_batch_gpu():
     eye = torch.eye(n, device="cuda")
     assert (Y.transpose(-1, -2) @ Y - eye).abs().max() < 1e-3
     assert (infos[0] > 0).all()
+
+
+def _refine_prep_case(device):
+    G = torch.randn(3, 40, 40, device=device)
+    G = G @ G.transpose(-1, -2) + 40 * torch.eye(40, device=device)
+    G[1, 5, 5] = 1e-9      # a dead column: d = 0 there
+    skip = torch.tensor([0, 0, 1], dtype=torch.int32, device=device)
+    C, d = ops.refine_prep(G, 1e-4, skip)
+    C2, d2 = ops.refine_prep(G, 1e-4, skip, fold=True)
+    torch.testing.assert_close(d2, d)
+    torch.testing.assert_close(C2, C * d.unsqueeze(-2))
+    assert d[1, 5] == 0 and (C[2] == 0).all() and torch.equal(C, torch.tril(C, -1))
+    return C, d
+
+
+def test_refine_prep_fold_cpu():
+    _refine_prep_case("cpu")
+
+
+@pytest.mark.gpu
+def test_refine_prep_kernel_with_folded_column_scale():
+    C, d = _refine_prep_case("cuda")
+    Cr, dr = _refine_prep_case("cpu")
+
+
+def _blocked_case(device, r, block):
+    torch.manual_seed(r)
+    P = torch.randn(3, 3 * r, r, device=device) * torch.logspace(0, -1.5, r, device=device)
+    P[0, :, 10] = 0               # a zero column
+    P[0, :, r - 7] = P[0, :, 5]   # a duplicated column, in a later block than its twin
+    P[2] = 0                      # an all-zero matrix
+    G = P.transpose(-1, -2) @ P if device == "cpu" else (P.double().transpose(-1, -2) @ P.double()).float()
+    Zr, info_r = ops.chol_inverse_reference(G.cpu())
+    Zb, info_b = ops.linalg.chol_inverse_blocked(G, block=block)
+    assert torch.equal(Zb, torch.tril(Zb)) and torch.isfinite(Zb).all()
+    if device == "cpu":
+        assert info_b.tolist() == info_r.tolist()
+        rel = ((Zb - Zr).norm() / Zr.norm()).item()
+        assert rel < 1e-5, rel
+    else:
+        # The trailing updates run as 3xTF32 products, whose rounding noise (a few 1e-6 of the unit diagonal)
+        # may leave the twin of a duplicated column a pivot just above the floor: such a column then carries
+        # a bounded noise direction instead of being dropped, and the count is one lower.
+        got, want = info_b.cpu().tolist(), info_r.tolist()
+        assert got[1:] == want[1:] and got[0] in (want[0], want[0] - 1), (got, want)
+        rel = ((Zb[1].cpu() - Zr[1]).norm() / Zr[1].norm()).item()
+        assert rel < 1e-4, rel
+    Q = P[1].double() @ Zb[1].double().T
+    err = (Q.T @ Q - torch.eye(r, device=device, dtype=torch.float64)).abs().max().item()
+    assert err < 1e-4, err
+
+
+@pytest.mark.parametrize("r,block", [(96, 32), (200, 64), (130, 64)])
+def test_chol_inverse_blocked_matches_the_unblocked_reference_cpu(r, block):
+    _blocked_case("cpu", r, block)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("r,block", [(520, 256), (768, 256), (1024, 256), (384, 128)])
+def test_chol_inverse_blocked_kernels(r, block):
+    """Diagonal blocks through the Cholesky-inverse kernel, everything else as 3xTF32 tensor-core products."""
+    _blocked_case("cuda", r, block)
+
+
+@pytest.mark.gpu
+def test_chol_inverse_takes_the_blocked_path_for_large_ranks():
+    P, G = _gram(4, 1536, 768, "cuda", cond=1.5)
+    n0 = ops.launch_count()
+    Z, info = ops.chol_inverse(G)
+    assert ops.launch_count() - n0 > 5            # several kernels, not the one-launch factorisation
+    Zr, _ = ops.chol_inverse_reference(G.double())
+    assert ((Z.double() - Zr.double()).norm() / Zr.double().norm()).item() < 1e-4
+    assert int(info.sum()) == 0
