@@ -274,26 +274,9 @@ def run_reference(args):
         return
     # Inductor compiles small host-side C++ kernels with OpenMP; the first g++ on PATH of
     # some images lacks libgomp.spec, the distribution compiler has it.
-    import shutil
-    import subprocess
+    from dion_b200.utils.compilers import ensure_openmp_cxx
 
-    def can_openmp(cxx: str) -> bool:
-        try:
-            with tempfile.TemporaryDirectory() as d:
-                src = os.path.join(d, "t.cpp")
-                with open(src, "w") as f:
-                    f.write("int main() { return 0; }\n")
-                return subprocess.run([cxx, "-fopenmp", src, "-o", os.path.join(d, "t")],
-                                      capture_output=True, timeout=60).returncode == 0
-        except Exception:
-            return False
-
-    current = os.environ.get("CXX") or shutil.which("g++") or ""
-    if not (current and can_openmp(current)):
-        for cand in ("/usr/bin/g++", "/usr/bin/clang++"):
-            if os.path.exists(cand) and can_openmp(cand):
-                os.environ["CXX"] = cand
-                break
+    ensure_openmp_cxx()
     import torch
     import torch.distributed as dist
 

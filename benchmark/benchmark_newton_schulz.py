@@ -52,8 +52,9 @@ def reference_triton_newton_schulz():
         _triton_why = "baseline/_ref is not installed"
         return None
     # Inductor's host-side code needs a C++ compiler with OpenMP; some images put one first on PATH that lacks it
-    if not os.environ.get("CXX") and os.path.exists("/usr/bin/g++"):
-        os.environ["CXX"] = "/usr/bin/g++"
+    from dion_b200.utils.compilers import ensure_openmp_cxx
+
+    ensure_openmp_cxx()
     sys.path.insert(0, ref_dir)
     for name in [m for m in sys.modules if m == "dion" or m.startswith("dion.")]:
         del sys.modules[name]

@@ -59,8 +59,9 @@ def run_reference(args, dims, mesh, dev, cuda, rank, world):
             print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed on this machine"}))
         dist.destroy_process_group()
         return
-    if not os.environ.get("CXX") and os.path.exists("/usr/bin/g++"):
-        os.environ["CXX"] = "/usr/bin/g++"  # Inductor's host code needs a compiler with OpenMP
+    from dion_b200.utils.compilers import ensure_openmp_cxx
+
+    ensure_openmp_cxx()  # Inductor's host code needs a compiler with OpenMP
     sys.path.insert(0, ref_dir)
     for name in [m for m in sys.modules if m == "dion" or m.startswith("dion.") or m == "models" or m.startswith("models.")]:
         del sys.modules[name]

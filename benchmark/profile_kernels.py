@@ -12,7 +12,7 @@ ncu would lock the GPU's clocks, and that setting outlasts the process).
 `--ref` times cuBLAS (torch.matmul / torch.bmm) on the operands of gemm_fwd, gemm_dx, gemm_dw
 and gemm_sym for comparison.
 
-Cases: gemm_fwd, gemm_dx, gemm_dw, gemm_sym, gemm_tf32_mn, gemm_scatter, chol, cross_entropy,
+Cases: gemm_fwd, gemm_dx, gemm_dw, gemm_sym, gemm_tf32_mn, gram3x, gram3x_k, apply3x, gemm_scatter, chol, cross_entropy,
 rope, rmsnorm, lion, adamw, muon_pre, dion_accum, all_reduce (single rank loop-back over
 symmetric memory).
 """
@@ -94,6 +94,21 @@ def case(name: str, ref: bool = False):
         B, a, b_, rr = 12, 3072, 768, 768
         A, P, R = r(B, a, b_, dt=f32), r(B, a, rr, dt=f32), torch.empty(B, b_, rr, device=dev)
         return (lambda: ops.gemm(A.transpose(1, 2), P, out=R)), 2.0 * B * a * b_ * rr, B * (a * b_ + a * rr + b_ * rr) * 4
+    if name in ("gram3x", "gram3x_k", "apply3x"):
+        # the 3xTF32 products of Dion's orthonormalisation, fp32 operands split inside the kernel:
+        #   gram3x   P^T P (symmetric, both operands MN-major)     gram3x_k  X X^T (symmetric, K-major)
+        #   apply3x  P Z^T (K-major operands)
+        B, a, rr = 64, 768, 768
+        P, Z = r(B, a, rr, dt=f32), r(B, rr, rr, dt=f32)
+        G, X = torch.empty(B, rr, rr, device=dev), torch.empty(B, a, rr, device=dev)
+        if name == "gram3x":
+            fn = lambda: ops.gemm(P.transpose(1, 2), P, out=G, symmetric=True, split3=True)
+            return fn, 3 * 2.0 * B * rr * rr * a / 2, B * (a * rr + rr * rr) * 4
+        if name == "gram3x_k":
+            fn = lambda: ops.gemm(P, P.transpose(1, 2), out=G, symmetric=True, split3=True)
+            return fn, 3 * 2.0 * B * rr * rr * a / 2, B * (a * rr + rr * rr) * 4
+        fn = lambda: ops.gemm(P, Z.transpose(1, 2), out=X, split3=True)
+        return fn, 3 * 2.0 * B * a * rr * rr, B * (2 * a * rr + rr * rr) * 4
     if name == "gemm_scatter":    # last Newton-Schulz product with the scatter epilogue (8 row blocks)
         B, m, n, W = 24, 768, 3072, 8
         bm, x = r(B, m, m), r(B, m, n)

@@ -489,6 +489,62 @@ void rmsnorm_fwd(const Tensor& x, const std::optional<Tensor>& residual, const s
                                            (float)eps, at::cuda::getCurrentCUDAStream()));
 }
 
+void rmsnorm_gain_fwd(const Tensor& x, const Tensor& gain, Tensor y, Tensor rstd, double eps) {
+  check_bf16(x, "x");
+  check_bf16(y, "y");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int dim = (int)x.size(-1);
+  const int64_t rows = x.numel() / dim;
+  TORCH_CHECK(x.is_contiguous() && y.is_contiguous() && gain.is_contiguous() && gain.numel() == dim);
+  TORCH_CHECK(rstd.scalar_type() == at::kFloat && rstd.numel() == rows);
+  ++g_launches;
+  DION_CUDA_CHECK(dion::rmsnorm_gain_fwd_launch(x.data_ptr(), gain.data_ptr(), elem_type(gain, "gain"), y.data_ptr(),
+                                                rstd.data_ptr<float>(), rows, dim, (float)eps,
+                                                at::cuda::getCurrentCUDAStream()));
+}
+
+// returns the per-block partial sums of the gain's gradient, [blocks, dim] fp32
+Tensor rmsnorm_gain_bwd(const Tensor& dy, const Tensor& x, const Tensor& rstd, const Tensor& gain, Tensor dx) {
+  check_bf16(dy, "dy");
+  check_bf16(x, "x");
+  check_bf16(dx, "dx");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int dim = (int)x.size(-1);
+  const int64_t rows = x.numel() / dim;
+  TORCH_CHECK(dy.is_contiguous() && x.is_contiguous() && dx.is_contiguous() && gain.is_contiguous() && gain.numel() == dim);
+  const int blocks = dion::rmsnorm_gain_bwd_blocks(rows);
+  Tensor partial = at::empty({blocks, dim}, x.options().dtype(at::kFloat));
+  ++g_launches;
+  DION_CUDA_CHECK(dion::rmsnorm_gain_bwd_launch(dy.data_ptr(), x.data_ptr(), rstd.data_ptr<float>(), gain.data_ptr(),
+                                                elem_type(gain, "gain"), dx.data_ptr(), partial.data_ptr<float>(), blocks,
+                                                rows, dim, at::cuda::getCurrentCUDAStream()));
+  return partial;
+}
+
+void swiglu_fwd(const Tensor& g, const Tensor& u, Tensor h) {
+  check_bf16(g, "g");
+  check_bf16(u, "u");
+  check_bf16(h, "h");
+  const c10::cuda::CUDAGuard guard(g.device());
+  TORCH_CHECK(g.is_contiguous() && u.is_contiguous() && h.is_contiguous() && u.numel() == g.numel() && h.numel() == g.numel());
+  ++g_launches;
+  DION_CUDA_CHECK(dion::swiglu_fwd_launch(g.data_ptr(), u.data_ptr(), h.data_ptr(), g.numel(), at::cuda::getCurrentCUDAStream()));
+}
+
+void swiglu_bwd(const Tensor& dh, const Tensor& g, const Tensor& u, Tensor dg, Tensor du) {
+  check_bf16(dh, "dh");
+  check_bf16(g, "g");
+  check_bf16(u, "u");
+  check_bf16(dg, "dg");
+  check_bf16(du, "du");
+  const c10::cuda::CUDAGuard guard(g.device());
+  TORCH_CHECK(dh.is_contiguous() && g.is_contiguous() && u.is_contiguous() && dg.is_contiguous() && du.is_contiguous());
+  TORCH_CHECK(dh.numel() == g.numel() && u.numel() == g.numel() && dg.numel() == g.numel() && du.numel() == g.numel());
+  ++g_launches;
+  DION_CUDA_CHECK(dion::swiglu_bwd_launch(dh.data_ptr(), g.data_ptr(), u.data_ptr(), dg.data_ptr(), du.data_ptr(), g.numel(),
+                                          at::cuda::getCurrentCUDAStream()));
+}
+
 void rmsnorm_bwd(const Tensor& dy, const Tensor& x, const Tensor& rstd, const std::optional<Tensor>& dx_add,
                  Tensor dx) {
   check_bf16(dy, "dy");
@@ -994,6 +1050,10 @@ TORCH_LIBRARY(dion_b200, m) {
   m.def("cast_multi(Tensor[] src, Tensor(a!)[] dst) -> ()");
   m.def("rmsnorm_fwd(Tensor x, Tensor? residual, Tensor(a!)? x_out, Tensor(b!) y, Tensor(c!) rstd, float eps) -> ()");
   m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor rstd, Tensor? dx_add, Tensor(a!) dx) -> ()");
+  m.def("rmsnorm_gain_fwd(Tensor x, Tensor gain, Tensor(a!) y, Tensor(b!) rstd, float eps) -> ()");
+  m.def("rmsnorm_gain_bwd(Tensor dy, Tensor x, Tensor rstd, Tensor gain, Tensor(a!) dx) -> Tensor");
+  m.def("swiglu_fwd(Tensor g, Tensor u, Tensor(a!) h) -> ()");
+  m.def("swiglu_bwd(Tensor dh, Tensor g, Tensor u, Tensor(a!) dg, Tensor(b!) du) -> ()");
   m.def(
       "rope_qknorm_fwd(Tensor q, Tensor k, Tensor(a!) q_out, Tensor(b!) k_out, Tensor cos, Tensor sin, int seq_len, "
       "int heads, int head_dim, float eps) -> ()");
@@ -1037,6 +1097,10 @@ TORCH_LIBRARY_IMPL(dion_b200, CUDA, m) {
   m.impl("frob_scale", &frob_scale);
   m.impl("rmsnorm_fwd", &rmsnorm_fwd);
   m.impl("rmsnorm_bwd", &rmsnorm_bwd);
+  m.impl("rmsnorm_gain_fwd", &rmsnorm_gain_fwd);
+  m.impl("rmsnorm_gain_bwd", &rmsnorm_gain_bwd);
+  m.impl("swiglu_fwd", &swiglu_fwd);
+  m.impl("swiglu_bwd", &swiglu_bwd);
   m.impl("rope_qknorm_fwd", &rope_qknorm_fwd);
   m.impl("rope_qknorm_bwd", &rope_qknorm_bwd);
   m.impl("rope_fwd", &rope_fwd);

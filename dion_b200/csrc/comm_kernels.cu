@@ -126,7 +126,12 @@ __global__ void __launch_bounds__(512) all_reduce_kernel(PeerTable t, long long 
   __shared__ int ok_flag;
   if (threadIdx.x == 0) ok_flag = 1;
   __syncthreads();
-  if (threadIdx.x < 32) {
+  // debug build: rank and group size are consistent and the buffer keeps the alignment of the vector accesses
+  if (threadIdx.x == 0 && !DION_DBG_OK(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world && (data_off & 15) == 0 &&
+                                           t.ptrs[rank] != nullptr, status))
+    ok_flag = 0;
+  __syncthreads();
+  if (ok_flag && threadIdx.x < 32) {
     if (blockIdx.x == 0) {
       __threadfence_system();
       signal_peers(t, flag_off, 0, rank, world, epoch, threadIdx.x);

@@ -415,6 +415,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   if constexpr (kPair) cluster_sync_all();  // both CTAs' barriers and TMEM exist before either is used
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // debug build: the allocation lies inside the 512 columns of tensor memory
+  if (threadIdx.x == 0) (void)DION_DBG_OK((tmem_base & 0xffffu) + C::TMEM_COLS <= 512u, p.status);
 
   const int kb_per_split = p.kblocks_per_split;
   // every wait inside the pipeline; the all-gather variant allows for the time another GPU may take
@@ -746,7 +748,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       tc_fence_after();
 
       const int row = m0 + quad * 32 + lane;
-      const bool row_ok = row < p.M;
+      // debug build: the tile lies inside the problem and the output base is 16-byte aligned where vector stores go
+      const bool row_ok = row < p.M && DION_DBG_OK(t.batch < p.batch && m0 < p.M + C::TILE_M && n0 < p.N, p.status);
       const char* c_base = nullptr;
       char* d_base;
       char* d2_base = nullptr;
@@ -784,11 +787,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         long long r = grow;
         int cc = col;
         if (p.scatter_mode == 1) {
-          const int k = grow / p.scatter_block;
+          int k = grow / p.scatter_block;
+          if (!DION_DBG_OK(k < p.scatter_dests, p.status)) k = p.scatter_dests - 1;
           base = reinterpret_cast<char*>(p.scatter_ptrs[(long long)t.batch * p.scatter_dests + k]);
           r = grow - (long long)k * p.scatter_block;
         } else if (p.scatter_mode == 2) {
-          const int k = col / p.scatter_block;
+          int k = col / p.scatter_block;
+          if (!DION_DBG_OK(k < p.scatter_dests, p.status)) k = p.scatter_dests - 1;
           base = reinterpret_cast<char*>(p.scatter_ptrs[(long long)t.batch * p.scatter_dests + k]);
           cc = col - k * p.scatter_block;
         }

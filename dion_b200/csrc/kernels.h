@@ -97,6 +97,19 @@ cudaError_t embedding_fwd_launch(const void* table, int table_type, const long l
 cudaError_t embedding_bwd_launch(const void* dout, const long long* idx, float* dtable, long long tokens, int dim,
                                  cudaStream_t s);
 
+// RMSNorm with a learnable gain (fp32 or bf16 vector of `dim`): y = x * rstd * gain; the backward pass writes
+// dx and per-block partial sums of the gain's gradient, partial[blocks][dim] (fp32), which the caller
+// adds up; `blocks` = rmsnorm_gain_bwd_blocks(rows).  dim a multiple of 8, at most 4096.
+cudaError_t rmsnorm_gain_fwd_launch(const void* x, const void* gain, int gain_type, void* y, float* rstd,
+                                    long long rows, int dim, float eps, cudaStream_t s);
+int rmsnorm_gain_bwd_blocks(long long rows);
+cudaError_t rmsnorm_gain_bwd_launch(const void* dy, const void* x, const float* rstd, const void* gain, int gain_type,
+                                    void* dx, float* partial, int blocks, long long rows, int dim, cudaStream_t s);
+// SwiGLU gate on bf16: h = silu(g) * u;  dg = dh * u * s * (1 + g * (1 - s)), du = dh * g * s, s = sigmoid(g)
+cudaError_t swiglu_fwd_launch(const void* g, const void* u, void* h, long long n, cudaStream_t s);
+cudaError_t swiglu_bwd_launch(const void* dh, const void* g, const void* u, void* dg, void* du, long long n,
+                              cudaStream_t s);
+
 // ---------------------------------------------------------------------------
 // Dense linear algebra on small matrices (one CTA per matrix, fp32)
 // ---------------------------------------------------------------------------

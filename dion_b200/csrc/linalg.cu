@@ -21,6 +21,7 @@
 #include <string.h>
 
 #include "kernels.h"
+#include "umma.cuh"
 
 namespace dion {
 
@@ -447,6 +448,8 @@ chol_inverse_pair_kernel(const float* __restrict__ Gall, float* __restrict__ Zal
   }
   chol_cluster_sync();
 
+  // debug build: the padded rank covers the rank and the shared-memory layout was sized for it
+  if (!DION_DBG_OK(rp >= r && (rp & 127) == 0 && r > 0, nullptr)) return;
   for (int k0 = 0; k0 < r; k0 += NB) {
     const int nb = min(NB, r - k0);
     // ---- 1. diagonal block -> shared, factor and invert it in warp 0

@@ -25,7 +25,18 @@ enum : int {
   kStatusEpilogueTimeout = 3,
   kStatusPeerTimeout = 4,
   kStatusBadArgument = 5,
+  kStatusDebugCheck = 6,  // a bounds / consistency check of the debug build failed
 };
+
+// Debug build (-DDION_B200_DEBUG, `DION_B200_DEBUG=1` when building): index, pointer and resource checks
+// compiled into the kernels.  A failed check records kStatusDebugCheck in the status word and the guarded
+// access is skipped - nothing traps, the kernel runs to its end and the host raises on the next status read.
+// In the regular build the checks compile to nothing and the guarded statement runs unconditionally.
+#ifdef DION_B200_DEBUG
+#define DION_DBG_OK(cond, status) ((cond) ? true : (((status) != nullptr ? (void)atomicCAS((status), 0, ::dion::kStatusDebugCheck) : (void)0), false))
+#else
+#define DION_DBG_OK(cond, status) (true)
+#endif
 
 // Upper bound for any single device-side wait (mbarrier or peer flag).
 static constexpr unsigned long long kWaitBudgetNs = 1500ull * 1000ull * 1000ull;

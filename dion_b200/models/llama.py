@@ -47,7 +47,7 @@ class RMSNormGain(nn.Module):
         self.eps = eps
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return K.rms_norm(x, self.eps) * self.weight.to(x.dtype)
+        return K.rms_norm_gain(x, self.weight, self.eps)
 
 
 class LlamaAttention(nn.Module):
@@ -89,7 +89,7 @@ class LlamaMLP(nn.Module):
     def forward(self, h: torch.Tensor, residual: torch.Tensor) -> torch.Tensor:
         g = K.linear(h, self.w_gate.weight)
         u = K.linear(h, self.w_up.weight)
-        return K.linear(F.silu(g) * u, self.w_down.weight, residual=residual)
+        return K.linear(K.swiglu(g, u), self.w_down.weight, residual=residual)
 
 
 class LlamaBlock(nn.Module):

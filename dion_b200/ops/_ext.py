@@ -17,10 +17,15 @@ import torch
 
 _PKG_DIR = Path(__file__).resolve().parent.parent
 _SRC_DIR = _PKG_DIR / "csrc"
-_BUILD_DIR = _PKG_DIR / "_C"
-_LIB_NAME = "dion_b200_C"
+# DION_B200_DEBUG=1 selects the debug build: the same sources compiled with -DDION_B200_DEBUG, which turns on
+# the bounds / consistency checks of the kernels (they report through the status word, nothing traps).  It
+# lives beside the regular library, so both can exist in one tree; build it with
+# `DION_B200_DEBUG=1 python -c "import __graft_entry__ as g; g.build()"`.
+DEBUG = os.environ.get("DION_B200_DEBUG", "0") == "1"
+_BUILD_DIR = _PKG_DIR / ("_C_debug" if DEBUG else "_C")
+_LIB_NAME = "dion_b200_C_debug" if DEBUG else "dion_b200_C"
 _SOURCES = ["bindings.cpp", "gemm.cu", "optim_kernels.cu", "nn_kernels.cu", "linalg.cu", "comm_kernels.cu",
-            "noalloc.cu", "attention.cu", "dion_fused.cu"]
+            "noalloc.cu", "attention.cu", "dion_fused.cu", "llama_kernels.cu"]
 
 _lock = threading.Lock()
 _loaded: Optional[bool] = None
@@ -60,7 +65,7 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         extra_cuda_cflags=[
             "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
             "--expt-relaxed-constexpr", "-Xptxas", "-v",
-        ],
+        ] + (["-DDION_B200_DEBUG"] if DEBUG else []),
         build_directory=str(_BUILD_DIR),
         is_python_module=False,
         verbose=verbose,

@@ -56,6 +56,8 @@ def chol_inverse_reference(G: torch.Tensor, pivot_floor: float = DEFAULT_PIVOT_F
 # keeps the one-launch kernel for every rank it fits.
 BLOCK = 256
 BLOCKED = os.environ.get("DION_B200_CHOL_BLOCKED", "1") != "0"
+# 3xTF32 products split their fp32 operands inside the GEMM kernel (0: hi / lo tensors from a separate pass)
+SPLIT_IN_KERNEL = os.environ.get("DION_B200_SPLIT_IN_KERNEL", "1") != "0"
 
 
 def _split_block(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -114,19 +116,31 @@ def chol_inverse_blocked(G: torch.Tensor, pivot_floor: float = DEFAULT_PIVOT_FLO
         Zd, mask, inf = _diag_inverse(W[:, k0:k1, k0:k1], pivot_floor)
         info += inf
         Z[:, k0:k1, k0:k1].copy_(Zd)
-        zsplit.append(split_tf32(Zd))
+        zsplit.append(Zd if SPLIT_IN_KERNEL else split_tf32(Zd))
         if k1 == r:
             break
-        zm_hi, zm_lo = split_tf32(Zd * mask.unsqueeze(-1))
+        Zm = Zd * mask.unsqueeze(-1)
         panel = W[:, k1:, k0:k1]
+        trail = W[:, k1:, k1:]
+        if SPLIT_IN_KERNEL:
+            # the products read their operands straight out of W (strided views), splitting them on the fly;
+            # the panel product must not overwrite its own operand, so L_ik lands in a buffer first
+            L = gemm(panel, Zm.transpose(-1, -2), split3=True)
+            panel.copy_(L)
+            gemm(L, L.transpose(-1, -2), c=trail, out=trail, alpha=-1.0, beta=1.0, split3=True)
+            continue
+        zm_hi, zm_lo = split_tf32(Zm)
         p_hi, p_lo = _split_block(panel)
         gemm(p_hi, zm_hi.transpose(-1, -2), a_lo=p_lo, b_lo=zm_lo.transpose(-1, -2), out=panel)   # L_ik
         l_hi, l_lo = _split_block(panel)
-        trail = W[:, k1:, k1:]
         gemm(l_hi, l_hi.transpose(-1, -2), a_lo=l_lo, b_lo=l_lo.transpose(-1, -2), c=trail, out=trail, alpha=-1.0,
              beta=1.0)
     for i in range(1, len(edges) - 1):
         i0, i1 = edges[i], edges[i + 1]
+        if SPLIT_IN_KERNEL:
+            T = gemm(W[:, i0:i1, :i0], Z[:, :i0, :i0], split3=True)
+            gemm(zsplit[i], T, out=Z[:, i0:i1, :i0], alpha=-1.0, split3=True)
+            continue
         l_hi, l_lo = _split_block(W[:, i0:i1, :i0])
         z_hi, z_lo = _split_block(Z[:, :i0, :i0])
         T = gemm(l_hi, z_hi, a_lo=l_lo, b_lo=z_lo)

@@ -333,6 +333,60 @@ def rms_norm(x: torch.Tensor, eps: float = RMS_EPS) -> torch.Tensor:
     return (xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)).to(x.dtype)
 
 
+class _RMSNormGainFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gain, eps):
+        x2 = x.reshape(-1, x.shape[-1])
+        y = torch.empty_like(x2)
+        rstd = torch.empty(x2.shape[0], device=x.device, dtype=torch.float32)
+        torch.ops.dion_b200.rmsnorm_gain_fwd(x2, gain, y, rstd, eps)
+        ctx.save_for_backward(x2, rstd, gain)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, rstd, gain = ctx.saved_tensors
+        dy2 = dy.contiguous().view(x2.shape)
+        dx = torch.empty_like(x2)
+        partial = torch.ops.dion_b200.rmsnorm_gain_bwd(dy2, x2, rstd, gain, dx)
+        return dx.view(dy.shape), partial.sum(dim=0).to(gain.dtype), None
+
+
+def rms_norm_gain(x: torch.Tensor, gain: torch.Tensor, eps: float = RMS_EPS) -> torch.Tensor:
+    """RMSNorm over the last dim with a learnable gain: ``x * rsqrt(mean(x^2) + eps) * gain``.  One kernel
+    each way; the backward kernel also reduces the gain's gradient (per-block partial sums in a fixed
+    order, summed afterwards)."""
+    if (_fast(x) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 4096 and x.is_contiguous() and gain.is_cuda
+            and gain.is_contiguous() and gain.dtype in (torch.float32, torch.bfloat16) and gain.data_ptr() % 16 == 0):
+        return _RMSNormGainFn.apply(x, gain, eps)
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps) * gain.float()).to(x.dtype)
+
+
+class _SwiGLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, g, u):
+        h = torch.empty_like(g)
+        torch.ops.dion_b200.swiglu_fwd(g, u, h)
+        ctx.save_for_backward(g, u)
+        return h
+
+    @staticmethod
+    def backward(ctx, dh):
+        g, u = ctx.saved_tensors
+        dg, du = torch.empty_like(g), torch.empty_like(u)
+        torch.ops.dion_b200.swiglu_bwd(dh.contiguous(), g, u, dg, du)
+        return dg, du
+
+
+def swiglu(g: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
+    """``silu(g) * u``: one kernel forward, one backward (both gradients)."""
+    if (_fast(g) and u.dtype == g.dtype and g.is_contiguous() and u.is_contiguous() and g.numel() % 8 == 0
+            and g.data_ptr() % 16 == 0 and u.data_ptr() % 16 == 0):
+        return _SwiGLUFn.apply(g, u)
+    return torch.nn.functional.silu(g) * u
+
+
 # --------------------------------------------------------------------------- rotary + QK norm
 
 def rotary_tables(seq_len: int, head_dim: int, device, base: float = 10000.0) -> Tuple[torch.Tensor, torch.Tensor]:

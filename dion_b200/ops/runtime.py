@@ -20,6 +20,7 @@ _STATUS_NAMES = {
     3: "epilogue wait timed out",
     4: "peer flag wait timed out",
     5: "bad kernel argument",
+    6: "a bounds check of the debug build failed",
 }
 
 _status: Dict[int, torch.Tensor] = {}

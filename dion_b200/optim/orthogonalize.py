@@ -31,6 +31,9 @@ from ..parallel import symm
 # "3xtf32" splits fp32 operands into two tf32 halves (three tensor-core passes, ~fp32
 # accuracy); "tf32" is a single pass.
 GRAM_PRECISION = os.environ.get("DION_B200_GRAM_PRECISION", "3xtf32")
+# 3xTF32 products split their fp32 operands inside the GEMM kernel (DION_B200_SPLIT_IN_KERNEL=0: hi / lo
+# tensors written by a separate pass, then one launch over three K-segments)
+SPLIT_IN_KERNEL = os.environ.get("DION_B200_SPLIT_IN_KERNEL", "1") != "0"
 
 
 # tf32 halves that a producer already wrote next to its fp32 result (see register_split)
@@ -61,9 +64,12 @@ def gram(P: Tensor, reduce_group=None) -> Tensor:
     out = symm.empty(reduce_group, (P.shape[0], P.shape[2], P.shape[2]), torch.float32, P.device)
     if GRAM_PRECISION == "tf32":
         return ops.gemm(Pt, P, out=out, symmetric=True)
+    if SPLIT_IN_KERNEL:
+        # 3xTF32 with the tf32 halves formed in shared memory: P is read once, nothing is materialised
+        return ops.gemm(Pt, P, out=out, symmetric=True, split3=True)
     hi, lo = _split_tf32(P)
-    # hi^T hi and the cross terms lo^T hi + hi^T lo in one launch (three K-segments into one accumulator);
-    # lo^T lo is below fp32 resolution
+    # hi^T hi and the cross terms lo^T hi + hi^T lo in one launch (three K-segments, the cross terms in an
+    # accumulator of their own); lo^T lo is below fp32 resolution
     return ops.gemm(hi.transpose(-1, -2), hi, out=out, symmetric=True, a_lo=lo.transpose(-1, -2), b_lo=lo)
 
 
@@ -74,6 +80,8 @@ def apply_right(P: Tensor, Z: Tensor) -> Tensor:
         return P @ Zt
     if GRAM_PRECISION == "tf32":
         return ops.gemm(P, Zt)
+    if SPLIT_IN_KERNEL:
+        return ops.gemm(P, Zt, split3=True)
     p_hi, p_lo = _split_tf32(P)
     z_hi, z_lo = _split_tf32(Z)
     return ops.gemm(p_hi, z_hi.transpose(-1, -2), a_lo=p_lo, b_lo=z_lo.transpose(-1, -2))
@@ -293,10 +301,17 @@ def _orthonormalize_many(Ps, row_groups, refine_passes, pivot_floor, shard_group
                 off += b
     if infos is not None:
         infos.extend(first_info)
+    # A batch that went through two Cholesky-QR passes is already orthonormal to about 1e-3 (CholeskyQR2 on a
+    # matrix whose condition number the shifted first pass brought below a few hundred); one correction takes
+    # that to the 1e-6 level.  After a single pass the error can be 1e-1, which takes two corrections.
+    passes = [max(1, refine_passes - 1) if (rb and refine_passes > 0) else refine_passes for rb in robust]
     for k in range(refine_passes):
-        # the last correction writes the result in the dtype its consumer multiplies with
-        last = k == refine_passes - 1
-        Xs = [_refine(X, g, bad, dt if last else None) for X, g, bad, dt in zip(Xs, row_groups, last_info, dtypes)]
+        for i in range(n):
+            if k >= passes[i]:
+                continue
+            # the last correction writes the result in the dtype its consumer multiplies with
+            last = k == passes[i] - 1
+            Xs[i] = _refine(Xs[i], row_groups[i], last_info[i], dtypes[i] if last else None)
     return [X.to(dt) for X, dt in zip(Xs, dtypes)]
 
 

@@ -20,8 +20,8 @@ def _case(device, dtype, B=5, n=70, r=45, m=52, nslots=3, seed=0):
     return slots, Qm, P, nonzero
 
 
-def _run(device, dtype, finish, qs_cols, qs_col0):
-    slots, Qm, P, nonzero = _case(device, dtype)
+def _run(device, dtype, finish, qs_cols, qs_col0, r=45):
+    slots, Qm, P, nonzero = _case(device, dtype, r=r)
     nsl, B, n, r = slots.shape
     scale, eps = 0.5, 1e-8
     Rr, Pr, ssr, Qr = ops.dion_r_post_reference(slots, scale, nonzero, Qm, P.clone(), eps, finish=True)
@@ -62,6 +62,16 @@ def test_r_post_front_end_cpu(finish):
 @pytest.mark.parametrize("finish,qs_cols,qs_col0", [(True, 45, 0), (True, 15, 30), (False, 15, 15), (False, 45, 0)])
 def test_r_post_kernel(dtype, finish, qs_cols, qs_col0):
     _run("cuda", dtype, finish, qs_cols, qs_col0)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("finish,qs_cols,qs_col0,r", [(True, 200, 0, 200), (True, 48, 96, 192), (False, 64, 64, 192),
+                                                      (False, 136, 0, 136), (True, 16, 20, 48)])
+def test_r_post_kernel_wide_strips(dtype, finish, qs_cols, qs_col0, r):
+    """Ranks that are multiples of four take the 128-column strips with 16-byte accesses (several strips,
+    a ragged last one, and a Q slice whose offset is not a multiple of four, which falls back)."""
+    _run("cuda", dtype, finish, qs_cols, qs_col0, r=r)
 
 
 @pytest.mark.gpu

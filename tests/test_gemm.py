@@ -291,3 +291,41 @@ def test_gemm_symmetric_long_k_on_cta_pairs_with_staged_mirror(dtype, n, k, batc
         ref2 = 0.5 * a.float() @ a.float().transpose(1, 2) - 1.5 * a.float()
         assert _rel_err(poly, ref2) < tol
         assert torch.equal(poly, poly.transpose(1, 2))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ta", [False, True])
+@pytest.mark.parametrize("tb", [False, True])
+@pytest.mark.parametrize("shape,symmetric", [((384, 200, 328), False), ((512, 512, 1000), False), ((200, 64, 72), False),
+                                             ((256, 256, 520), True), ((768, 768, 768), True)])
+def test_gemm_split3_splits_fp32_operands_in_shared_memory(ta, tb, shape, symmetric):
+    """3xTF32 product of plain fp32 operands: the kernel forms the tf32 halves of every tile itself.
+    Against fp64, and against the product of operands that were split beforehand."""
+    M, N, K = shape
+    B = 3
+    if symmetric:
+        if ta != tb:
+            pytest.skip("a symmetric product multiplies an operand with its own transpose")
+        x = _operand(M, K, torch.float32, ta, batch=B)
+        a, b = x, x.transpose(-1, -2)
+    else:
+        a = _operand(M, K, torch.float32, ta, batch=B)
+        b = _operand(K, N, torch.float32, tb, batch=B)
+    ref = a.double() @ b.double()
+    one = gemm(a, b, symmetric=symmetric)
+    three = gemm(a, b, symmetric=symmetric, split3=True)
+    e1, e3 = _rel_err(one, ref), _rel_err(three, ref)
+    assert e3 < 2e-5 and e1 > 10 * e3, (e1, e3)
+    # epilogue options ride along: addend with column scale, alpha / beta, strided views as operands
+    c = torch.randn(B, M, N, device="cuda")
+    s = torch.rand(B, N, device="cuda") + 0.5
+    if not symmetric:
+        out = gemm(a, b, c=c, alpha=-1.0, beta=1.0, c_col_scale=s, split3=True)
+        assert _rel_err(out, c.double() * s.unsqueeze(1).double() - ref) < 2e-5
+        big = torch.randn(B, M + 40, K + 24, device="cuda")
+        av = big[:, 8:8 + M, 16:16 + K]
+        out = gemm(av, b, split3=True)
+        assert _rel_err(out, av.double() @ b.double()) < 2e-5
+    from dion_b200 import ops
+
+    ops.check_status()

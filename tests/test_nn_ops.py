@@ -270,3 +270,47 @@ def test_linear_fanout_matches_separate_linears():
     for g, w in zip(got, want):
         err = (g.float() - w.float()).abs().max().item() / w.float().abs().max().item()
         assert err < 1e-2, err
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows,dim", [(300, 768), (64, 4096), (1000, 1024), (5, 256)])
+@pytest.mark.parametrize("gain_dtype", [torch.float32, torch.bfloat16])
+def test_rms_norm_with_gain_kernels(rows, dim, gain_dtype):
+    """RMSNorm with a learnable gain: forward, input gradient and the gain's gradient (per-block partial
+    sums in a fixed order) against fp32 PyTorch; two backward passes give the same bits."""
+    from dion_b200.ops import nn as N
+
+    x = torch.randn(rows, dim, device="cuda").bfloat16().requires_grad_()
+    w = (1 + 0.1 * torch.randn(dim, device="cuda")).to(gain_dtype).requires_grad_()
+    g = torch.randn(rows, dim, device="cuda").bfloat16()
+    y = N.rms_norm_gain(x, w, 1e-5)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    yr = xr * torch.rsqrt(xr.square().mean(-1, keepdim=True) + 1e-5) * wr
+    yr.backward(g.float())
+    _close(y, yr, 2e-2)
+    _close(x.grad, xr.grad, 3e-2)
+    _close(w.grad, wr.grad, 2e-2)
+    first = w.grad.clone()
+    w.grad = None
+    x.grad = None
+    N.rms_norm_gain(x, w, 1e-5).backward(g)
+    assert torch.equal(w.grad, first)
+
+
+@pytest.mark.gpu
+def test_swiglu_kernels():
+    from dion_b200.ops import nn as N
+
+    g = torch.randn(257, 1024, device="cuda").bfloat16().requires_grad_()
+    u = torch.randn(257, 1024, device="cuda").bfloat16().requires_grad_()
+    d = torch.randn(257, 1024, device="cuda").bfloat16()
+    h = N.swiglu(g, u)
+    h.backward(d)
+    gr, ur = g.detach().float().requires_grad_(), u.detach().float().requires_grad_()
+    hr = torch.nn.functional.silu(gr) * ur
+    hr.backward(d.float())
+    _close(h, hr, 2e-2)
+    _close(g.grad, gr.grad, 2e-2)
+    _close(u.grad, ur.grad, 2e-2)
