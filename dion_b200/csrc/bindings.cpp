@@ -802,6 +802,30 @@ void slot_reduce(const Tensor& slots, const std::optional<Tensor>& out, const st
   DION_CUDA_CHECK(dion::slot_reduce_launch(a, at::cuda::getCurrentCUDAStream()));
 }
 
+// slots: bf16 [nslots, ...]; out (and the optional residual): bf16 tensors of one slot's size
+void slot_reduce_bf16(const Tensor& slots, Tensor out, const std::optional<Tensor>& residual, at::IntArrayRef peers,
+                      int64_t flag_off, int64_t channel, int64_t rank, int64_t epoch, int64_t budget_ns, Tensor status) {
+  const c10::cuda::CUDAGuard guard(slots.device());
+  TORCH_CHECK(slots.is_cuda() && slots.scalar_type() == at::kBFloat16 && slots.dim() >= 2 && slots.size(0) >= 1 &&
+              slots.select(0, 0).is_contiguous());
+  dion::SlotReduceBf16Args a;
+  memset(&a, 0, sizeof(a));
+  a.wait = slot_wait(peers, flag_off, channel, rank, epoch, budget_ns);
+  a.slots = slots.data_ptr();
+  a.nslots = (int)slots.size(0);
+  a.slot_stride = slots.stride(0);
+  a.numel = slots.numel() / slots.size(0);
+  TORCH_CHECK(out.scalar_type() == at::kBFloat16 && out.is_contiguous() && out.numel() == a.numel);
+  a.out = out.data_ptr();
+  if (residual.has_value()) {
+    TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->is_contiguous() && residual->numel() == a.numel);
+    a.residual = residual->data_ptr();
+  }
+  a.status = status.data_ptr<int>();
+  ++g_launches;
+  DION_CUDA_CHECK(dion::slot_reduce_bf16_launch(a, at::cuda::getCurrentCUDAStream()));
+}
+
 void dion_r_post(const Tensor& slots, double scale, const std::optional<Tensor>& nonzero, const Tensor& Qm,
                  const std::optional<Tensor>& P, const std::optional<Tensor>& R32, const std::optional<Tensor>& Rm,
                  const std::optional<Tensor>& ss, bool finish, double eps, const std::optional<Tensor>& Qn,
@@ -950,6 +974,31 @@ void split_tf32(const Tensor& x, Tensor hi, Tensor lo) {
                                           at::cuda::getCurrentCUDAStream()));
 }
 
+void jacobi_scale(const Tensor& G, Tensor W, Tensor d) {
+  const c10::cuda::CUDAGuard guard(G.device());
+  TORCH_CHECK(G.is_cuda() && G.scalar_type() == at::kFloat && G.dim() == 3 && G.size(1) == G.size(2) && G.stride(2) == 1);
+  const int64_t B = G.size(0), r = G.size(1);
+  TORCH_CHECK(W.scalar_type() == at::kFloat && W.is_contiguous() && W.numel() == B * r * r);
+  TORCH_CHECK(d.scalar_type() == at::kFloat && d.is_contiguous() && d.numel() == B * r);
+  ++g_launches;
+  DION_CUDA_CHECK(dion::jacobi_scale_launch(G.data_ptr<float>(), W.data_ptr<float>(), d.data_ptr<float>(), (int)B, (int)r,
+                                            G.stride(1), G.stride(0), at::cuda::getCurrentCUDAStream()));
+}
+
+// Z: contiguous [B, r, r]; Zd, Zm: contiguous [B, nb, nb]; mask: [B, nb]
+void place_block(const Tensor& Zd, const Tensor& mask, Tensor Z, Tensor Zm, int64_t k0) {
+  const c10::cuda::CUDAGuard guard(Zd.device());
+  TORCH_CHECK(Zd.is_cuda() && Zd.scalar_type() == at::kFloat && Zd.dim() == 3 && Zd.is_contiguous() && Zd.size(1) == Zd.size(2));
+  const int64_t B = Zd.size(0), nb = Zd.size(1);
+  TORCH_CHECK(Z.scalar_type() == at::kFloat && Z.dim() == 3 && Z.is_contiguous() && Z.size(0) == B && Z.size(1) == Z.size(2));
+  TORCH_CHECK(Zm.scalar_type() == at::kFloat && Zm.is_contiguous() && Zm.numel() == Zd.numel());
+  TORCH_CHECK(mask.scalar_type() == at::kFloat && mask.is_contiguous() && mask.numel() == B * nb);
+  ++g_launches;
+  DION_CUDA_CHECK(dion::place_block_launch(Zd.data_ptr<float>(), mask.data_ptr<float>(), Z.data_ptr<float>(),
+                                           Zm.data_ptr<float>(), (int)B, (int)nb, (int)Z.size(1), (int)k0,
+                                           at::cuda::getCurrentCUDAStream()));
+}
+
 // x: fp32 [B, rows, cols] view with unit column stride; hi / lo contiguous
 void split_tf32_rows(const Tensor& x, Tensor hi, Tensor lo) {
   const c10::cuda::CUDAGuard guard(x.device());
@@ -1073,6 +1122,8 @@ TORCH_LIBRARY(dion_b200, m) {
       "chol_inverse(Tensor G, Tensor(a!) Z, Tensor(b!) work, Tensor(c!) info, float pivot_floor, bool jacobi=True, "
       "Tensor(d!)? colmask=None) -> ()");
   m.def("split_tf32_rows(Tensor x, Tensor(a!) hi, Tensor(b!) lo) -> ()");
+  m.def("jacobi_scale(Tensor G, Tensor(a!) W, Tensor(b!) d) -> ()");
+  m.def("place_block(Tensor Zd, Tensor mask, Tensor(a!) Z, Tensor(b!) Zm, int k0) -> ()");
   m.def("col_sumsq(Tensor X, Tensor(a!) out) -> ()");
   m.def("split_tf32(Tensor x, Tensor(a!) hi, Tensor(b!) lo) -> ()");
   m.def("attn_fwd(Tensor q, Tensor k, Tensor v, Tensor(a!) out, Tensor(b!) lse, float scale, Tensor(c!) status) -> ()");
@@ -1083,6 +1134,9 @@ TORCH_LIBRARY(dion_b200, m) {
   m.def(
       "slot_reduce(Tensor slots, Tensor(a!)? out, Tensor(b!)? hi, Tensor(c!)? lo, int[] dests, float scale, int[] peers, "
       "int flag_off, int channel, int rank, int epoch, int budget_ns, Tensor(d!) status) -> ()");
+  m.def(
+      "slot_reduce_bf16(Tensor slots, Tensor(a!) out, Tensor? residual, int[] peers, int flag_off, int channel, int rank, "
+      "int epoch, int budget_ns, Tensor(b!) status) -> ()");
   m.def(
       "dion_r_post(Tensor slots, float scale, Tensor? nonzero, Tensor Qm, Tensor(a!)? P, Tensor(b!)? R32, Tensor(c!)? Rm, "
       "Tensor(d!)? ss, bool finish, float eps, Tensor(e!)? Qn, Tensor(f!)? Qs, int qs_col0, int[] peers, int flag_off, "
@@ -1114,10 +1168,13 @@ TORCH_LIBRARY_IMPL(dion_b200, CUDA, m) {
   m.impl("col_sumsq", &col_sumsq);
   m.impl("split_tf32", &split_tf32);
   m.impl("split_tf32_rows", &split_tf32_rows);
+  m.impl("jacobi_scale", &jacobi_scale);
+  m.impl("place_block", &place_block);
   m.impl("attn_fwd", &attn_fwd);
   m.impl("attn_bwd", &attn_bwd);
   m.impl("refine_prep", &refine_prep);
   m.impl("slot_reduce", &slot_reduce);
+  m.impl("slot_reduce_bf16", &slot_reduce_bf16);
   m.impl("dion_r_post", &dion_r_post);
   m.impl("dion_q_norm", &dion_q_norm);
   m.impl("gemm_scatter", &gemm_scatter);

@@ -321,14 +321,15 @@ __global__ void __launch_bounds__(512) all_gather_kernel(PeerTable t, long long 
     if (ok_flag) {
       const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(t.ptrs[p]) + slot_off);
       uint4* dst = reinterpret_cast<uint4*>(out + (long long)p * bytes);
-      // four independent 16-byte peer loads in flight per thread
-      for (long long v = tid; v < nvec; v += 4 * nthreads) {
-        uint4 q[4];
+      // eight independent 16-byte peer loads in flight per thread: a load over NVLink takes a few
+      // microseconds, and the bytes in flight have to cover that at link speed
+      for (long long v = tid; v < nvec; v += 8 * nthreads) {
+        uint4 q[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < 8; ++u)
           if (v + u * nthreads < nvec) q[u] = src[v + u * nthreads];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
+        for (int u = 0; u < 8; ++u)
           if (v + u * nthreads < nvec) dst[v + u * nthreads] = q[u];
       }
     }
@@ -487,7 +488,12 @@ cudaError_t symm_all_gather_launch(const PeerTable& t, long long flag_off, long 
       (reinterpret_cast<uintptr_t>(out) & 15))
     return cudaErrorInvalidValue;
   const int threads = 512;
-  const int grid = comm_grid(bytes / 16, threads);
+  // the copies of this kernel are pure loads and stores; with more than two ranks it pays to use most SMs
+  int grid = comm_grid(bytes / 16, threads);
+  if (world > 2) {
+    long long g = (bytes / 16 + threads - 1) / threads;
+    grid = (int)(g < 1 ? 1 : (g > 132 ? 132 : g));
+  }
   all_gather_kernel<<<grid, threads, 0, s>>>(t, flag_off, slot_off, reinterpret_cast<const char*>(in),
                                              reinterpret_cast<char*>(out), bytes, rank, world, epoch, channel,
                                              done_counter, status, (unsigned long long)budget_ns);

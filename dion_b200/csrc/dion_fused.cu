@@ -109,6 +109,56 @@ __global__ void __launch_bounds__(512) slot_reduce_kernel(const SlotReduceArgs a
   }
 }
 
+// bf16 flavour of slot_reduce for activations (tensor-parallel row-parallel products): out = sum of the
+// slots in slot order (fp32 accumulation) + optional residual, bf16 in and out, 16-byte accesses.
+__global__ void __launch_bounds__(512) slot_reduce_bf16_kernel(const SlotReduceBf16Args a) {
+  if (!exchange_ready(a.wait, a.status)) return;
+  const long long nvec = a.numel >> 3;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const uint4* base = reinterpret_cast<const uint4*>(a.slots);
+  const long long sstride = a.slot_stride >> 3;
+  const uint4* res = reinterpret_cast<const uint4*>(a.residual);
+  uint4* out = reinterpret_cast<uint4*>(a.out);
+  for (long long v = (long long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
+    float acc[8];
+    {
+      const uint4 q = base[v];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] = f.x;
+        acc[2 * j + 1] = f.y;
+      }
+    }
+    for (int s = 1; s < a.nslots; ++s) {
+      const uint4 q = base[s * sstride + v];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    if (res != nullptr) {
+      const uint4 q = res[v];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) oh[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    out[v] = o;
+  }
+}
+
 // Four consecutive columns of one row as floats (fp32: one 16-byte access, bf16: one 8-byte access).
 __device__ __forceinline__ float4 load_quad(const void* p, int type, long long i) {
   if (type == kElemF32) return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
@@ -328,6 +378,19 @@ cudaError_t slot_reduce_launch(const SlotReduceArgs& a, cudaStream_t s) {
   if (grid > 2 * 148) grid = 2 * 148;
   if (grid < 1) grid = 1;
   slot_reduce_kernel<<<(int)grid, 512, 0, s>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t slot_reduce_bf16_launch(const SlotReduceBf16Args& a, cudaStream_t s) {
+  if (a.numel == 0 && a.wait.world <= 1) return cudaSuccess;
+  if (!wait_ok(a.wait) || a.nslots < 1 || (a.numel & 7) || (a.slot_stride & 7) || a.out == nullptr ||
+      ((reinterpret_cast<uintptr_t>(a.slots) | reinterpret_cast<uintptr_t>(a.out) | reinterpret_cast<uintptr_t>(a.residual)) & 15))
+    return cudaErrorInvalidValue;
+  const long long nvec = a.numel >> 3;
+  long long grid = (nvec + 512 * 4 - 1) / (512 * 4);
+  if (grid > 2 * 148) grid = 2 * 148;
+  if (grid < 1) grid = 1;
+  slot_reduce_bf16_kernel<<<(int)grid, 512, 0, s>>>(a);
   return cudaGetLastError();
 }
 

@@ -136,6 +136,13 @@ cudaError_t attn_fwd_launch(const void* q, const void* k, const void* v, void* o
 cudaError_t attn_bwd_launch(const void* q, const void* k, const void* v, const void* o, const void* d_o,
                             const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int T, int H, int Hkv,
                             int D, float scale, int* status, cudaStream_t stream);
+// Pieces of the blocked Cholesky-inverse: W = D G D with d = rsqrt(diag G) (contiguous W [batch][r][r], d
+// [batch][r]); and the placement of a diagonal block's inverse factor Zd ([batch][nb][nb]) into Z at (k0, k0)
+// together with its copy Zm whose rows of clamped pivots (mask == 0) are zero.
+cudaError_t jacobi_scale_launch(const float* G, float* W, float* d, int batch, int r, long long ldg,
+                                long long g_batch_stride, cudaStream_t s);
+cudaError_t place_block_launch(const float* Zd, const float* mask, float* Z, float* Zm, int batch, int nb, int r, int k0,
+                               cudaStream_t s);
 // hi / lo halves of fp32 data for 3xTF32 products; all three pointers 16-byte aligned
 cudaError_t split_tf32_launch(const float* x, float* hi, float* lo, long long numel, cudaStream_t s);
 // the same for a strided [batch][rows][cols] source (element (b, i, j) at b * bs + i * ld + j; cols, ld and bs
@@ -214,6 +221,20 @@ struct SlotReduceArgs {
   int* status;
 };
 cudaError_t slot_reduce_launch(const SlotReduceArgs& a, cudaStream_t s);
+
+// The same for bf16 activations: out = slot 0 + slot 1 + ... (+ residual), accumulated in fp32 in slot
+// order; numel and slot_stride multiples of 8, 16-byte aligned pointers.
+struct SlotReduceBf16Args {
+  SlotWait wait;
+  const void* slots;
+  long long slot_stride;
+  int nslots;
+  long long numel;
+  const void* residual;  // may be null
+  void* out;
+  int* status;
+};
+cudaError_t slot_reduce_bf16_launch(const SlotReduceBf16Args& a, cudaStream_t s);
 
 // After R = A^T P (contiguous [B][n][r] per slot): R <- scale * sum of slots; for a matrix whose
 // momentum is all zero (nonzero[b] == 0) R <- previous Q and P <- 0, otherwise NaN / inf are

@@ -722,6 +722,63 @@ __global__ void __launch_bounds__(256) split_tf32_rows_kernel(const float* __res
   }
 }
 
+// Unit-diagonal (Jacobi) scaling of Gram matrices: d_i = rsqrt(G_ii) (0 where G_ii is not positive),
+// W = D G D.  One block per (8 rows, matrix).
+__global__ void __launch_bounds__(256) jacobi_scale_kernel(const float* __restrict__ G, float* __restrict__ W,
+                                                          float* __restrict__ d, int r, long long ldg,
+                                                          long long g_batch_stride) {
+  const long long b = blockIdx.y;
+  const float* g = G + b * g_batch_stride;
+  float* w = W + b * (long long)r * r;
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= r) return;
+  const int lane = threadIdx.x & 31;
+  const float gii = g[(long long)row * ldg + row];
+  const float di = gii > 1e-30f ? rsqrtf(gii) : 0.f;
+  if (lane == 0) d[b * r + row] = di;
+  for (int j = lane; j < r; j += 32) {
+    const float gjj = g[(long long)j * ldg + j];
+    const float dj = gjj > 1e-30f ? rsqrtf(gjj) : 0.f;
+    w[(long long)row * r + j] = g[(long long)row * ldg + j] * di * dj;
+  }
+}
+
+// Zd (contiguous [batch][nb][nb]) into the diagonal block of Z at (k0, k0) (pitch r), and Zm = Zd with the
+// rows of clamped pivots (mask == 0) zeroed.  One block per (8 rows, matrix).
+__global__ void __launch_bounds__(256) place_block_kernel(const float* __restrict__ Zd, const float* __restrict__ mask,
+                                                         float* __restrict__ Z, float* __restrict__ Zm, int nb, int r,
+                                                         int k0) {
+  const long long b = blockIdx.y;
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= nb) return;
+  const int lane = threadIdx.x & 31;
+  const float m = mask[b * nb + row];
+  const float* src = Zd + (b * nb + row) * (long long)nb;
+  float* dst = Z + b * (long long)r * r + (long long)(k0 + row) * r + k0;
+  float* dm = Zm + (b * nb + row) * (long long)nb;
+  for (int j = lane; j < nb; j += 32) {
+    const float v = src[j];
+    dst[j] = v;
+    dm[j] = v * m;
+  }
+}
+
+cudaError_t jacobi_scale_launch(const float* G, float* W, float* d, int batch, int r, long long ldg,
+                                long long g_batch_stride, cudaStream_t s) {
+  if (batch == 0 || r == 0) return cudaSuccess;
+  if (batch > 65535) return cudaErrorInvalidValue;
+  jacobi_scale_kernel<<<dim3((r + 7) / 8, batch), 256, 0, s>>>(G, W, d, r, ldg, g_batch_stride);
+  return cudaGetLastError();
+}
+
+cudaError_t place_block_launch(const float* Zd, const float* mask, float* Z, float* Zm, int batch, int nb, int r, int k0,
+                               cudaStream_t s) {
+  if (batch == 0 || nb == 0) return cudaSuccess;
+  if (batch > 65535 || k0 < 0 || k0 + nb > r) return cudaErrorInvalidValue;
+  place_block_kernel<<<dim3((nb + 7) / 8, batch), 256, 0, s>>>(Zd, mask, Z, Zm, nb, r, k0);
+  return cudaGetLastError();
+}
+
 cudaError_t split_tf32_rows_launch(const float* x, float* hi, float* lo, int batch, int rows, int cols, long long ld,
                                    long long bs, cudaStream_t s) {
   if (batch == 0 || rows == 0 || cols == 0) return cudaSuccess;

@@ -103,11 +103,19 @@ def chol_inverse_blocked(G: torch.Tensor, pivot_floor: float = DEFAULT_PIVOT_FLO
 
     G = G.float()
     B, r, _ = G.shape
-    diag = torch.diagonal(G, dim1=-2, dim2=-1)
-    d = torch.where(diag > 1e-30, diag.clamp_min(1e-30).rsqrt(), torch.zeros_like(diag))
-    W = G * d.unsqueeze(-1) * d.unsqueeze(-2)
+    cuda = runtime.use_cuda_kernels(G) and G.stride(-1) == 1
+    if cuda:
+        W = torch.empty((B, r, r), dtype=torch.float32, device=G.device)
+        d = torch.empty((B, r), dtype=torch.float32, device=G.device)
+        torch.ops.dion_b200.jacobi_scale(G, W, d)
+    else:
+        diag = torch.diagonal(G, dim1=-2, dim2=-1)
+        d = torch.where(diag > 1e-30, diag.clamp_min(1e-30).rsqrt(), torch.zeros_like(diag))
+        W = G * d.unsqueeze(-1) * d.unsqueeze(-2)
     Z = out if out is not None else torch.empty_like(W)
     Z.zero_()
+    # the factor's panels L_ik live in a buffer of their own, so that no product overwrites one of its operands
+    Lbuf = torch.empty_like(W) if (cuda and SPLIT_IN_KERNEL) else W
     info = torch.zeros(B, dtype=torch.int32, device=G.device)
     edges = list(range(0, r, block)) + [r]
     zsplit = []
@@ -115,18 +123,23 @@ def chol_inverse_blocked(G: torch.Tensor, pivot_floor: float = DEFAULT_PIVOT_FLO
         k0, k1 = edges[k], edges[k + 1]
         Zd, mask, inf = _diag_inverse(W[:, k0:k1, k0:k1], pivot_floor)
         info += inf
-        Z[:, k0:k1, k0:k1].copy_(Zd)
+        if cuda and Z.is_contiguous():
+            Zm = torch.empty_like(Zd)
+            torch.ops.dion_b200.place_block(Zd, mask, Z, Zm, k0)   # Z_kk into Z, and its copy without clamped rows
+        else:
+            Z[:, k0:k1, k0:k1].copy_(Zd)
+            Zm = Zd * mask.unsqueeze(-1)
         zsplit.append(Zd if SPLIT_IN_KERNEL else split_tf32(Zd))
         if k1 == r:
             break
-        Zm = Zd * mask.unsqueeze(-1)
         panel = W[:, k1:, k0:k1]
         trail = W[:, k1:, k1:]
         if SPLIT_IN_KERNEL:
-            # the products read their operands straight out of W (strided views), splitting them on the fly;
-            # the panel product must not overwrite its own operand, so L_ik lands in a buffer first
-            L = gemm(panel, Zm.transpose(-1, -2), split3=True)
-            panel.copy_(L)
+            # the products read their operands straight out of W and Lbuf (strided views) and split them on the fly
+            L = Lbuf[:, k1:, k0:k1]
+            gemm(panel, Zm.transpose(-1, -2), out=L, split3=True)
+            if Lbuf is W:  # CPU: the product above was not in place, nothing else to do
+                pass
             gemm(L, L.transpose(-1, -2), c=trail, out=trail, alpha=-1.0, beta=1.0, split3=True)
             continue
         zm_hi, zm_lo = split_tf32(Zm)
@@ -138,7 +151,7 @@ def chol_inverse_blocked(G: torch.Tensor, pivot_floor: float = DEFAULT_PIVOT_FLO
     for i in range(1, len(edges) - 1):
         i0, i1 = edges[i], edges[i + 1]
         if SPLIT_IN_KERNEL:
-            T = gemm(W[:, i0:i1, :i0], Z[:, :i0, :i0], split3=True)
+            T = gemm(Lbuf[:, i0:i1, :i0], Z[:, :i0, :i0], split3=True)
             gemm(zsplit[i], T, out=Z[:, i0:i1, :i0], alpha=-1.0, split3=True)
             continue
         l_hi, l_lo = _split_block(W[:, i0:i1, :i0])

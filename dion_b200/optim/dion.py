@@ -853,7 +853,14 @@ class Dion(Optimizer):
         ar1 = symm.arena_for(first)
         ar2 = symm.arena_for(second) if second is not None else None
         mat = a_loc * r
-        if ar1 is None or mat % 4 != 0 or (second is not None and ar2 is None):
+        if mat % 4 != 0:
+            return None
+        if ar1 is None or (second is not None and ar2 is None):
+            # an arena that does not exist yet is asked for, so that the next step can take this path
+            nbytes = 8 * B * mat * 4
+            symm.request(first, nbytes, dev)
+            if second is not None:
+                symm.request(second, nbytes, dev)
             return None
         W1 = ar1.world
         split = SHARD_WORK and w.inner is None and B > 1
@@ -912,9 +919,15 @@ class Dion(Optimizer):
         ar1 = symm.arena_for(first)
         ar2 = symm.arena_for(second) if second is not None else None
         mat = n_loc * r
-        if ar1 is None or mat % 4 != 0 or ar1.world > _MAX_PUSH_WORLD:
+        if mat % 4 != 0:
             return None
-        if second is not None and (ar2 is None or ar2.world > _MAX_PUSH_WORLD):
+        if ar1 is None or (second is not None and ar2 is None):
+            dev = cls.M.device
+            symm.request(first, 8 * B * mat * 4, dev)
+            if second is not None:
+                symm.request(second, 8 * B * mat * 4, dev)
+            return None
+        if ar1.world > _MAX_PUSH_WORLD or (ar2 is not None and ar2.world > _MAX_PUSH_WORLD):
             return None
         slots = ar1.alloc_slots((B, n_loc, r))
         slots2 = ar2.alloc_slots((B, n_loc, r)) if ar2 is not None else None

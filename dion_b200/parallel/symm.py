@@ -32,6 +32,13 @@ _WANT_OFF = 2048  # inside the flag block, far behind the flag words: one fp32 p
 _ALIGN = 256
 _MIN_ARENA = 8 << 20
 _RS_WAIT_NS = int(1.5e9)  # bound of the reduce-scatter kernel's waits for its peers
+# Debug mode (DION_B200_DEBUG=1, which also selects the kernels' debug build): every buffer handed out by an
+# arena is followed by a guard of _CANARY_BYTES filled with a pattern; begin_step() checks all guards of the
+# step that just ended (a host synchronisation, hence debug only).  A damaged guard means that some kernel -
+# of this rank or, since peers store into this memory, of another one - wrote past the end of a buffer.
+_DEBUG = os.environ.get("DION_B200_DEBUG", "0") == "1"
+_CANARY_BYTES = 256
+_CANARY = 0xA5
 _CH_SLOT = 4               # flag channel of the push exchanges (0-3: all-reduce, reduce-into, reduce-scatter)
 _SLOT_WAIT_NS = int(1.5e9)
 
@@ -86,6 +93,7 @@ class SymmetricArena:
         self.cursor = 0
         self.high_water = 0
         self._views: Dict[int, int] = {}  # data_ptr -> byte offset inside the arena (flag block included)
+        self._guards = []                 # debug mode: (start, nbytes) of every buffer of the current step
         # the group's agreement on how much memory a step needs (post_want / agreed_want)
         self._want_view = self.buf[_WANT_OFF:_WANT_OFF + 4 * self.world].view(torch.float32)
         self._want_src = torch.zeros(self.world, dtype=torch.float32, pin_memory=True)
@@ -96,8 +104,24 @@ class SymmetricArena:
 
     # -- allocation
     def reset(self) -> None:
+        if _DEBUG:
+            self.check_canaries()
         self.cursor = 0
         self._views.clear()
+        self._guards.clear()
+
+    def check_canaries(self) -> None:
+        """Debug mode: raise if the guard behind any buffer of the current step was overwritten."""
+        if not self._guards:
+            return
+        torch.cuda.synchronize(self.device)
+        for index, (start, nbytes) in enumerate(self._guards):
+            guard = self.buf[_FLAG_BYTES + start + nbytes:_FLAG_BYTES + start + nbytes + _CANARY_BYTES]
+            if not bool((guard == _CANARY).all()):
+                bad = int((guard != _CANARY).nonzero()[0])
+                raise runtime.DionKernelError(
+                    f"symmetric arena of rank {self.rank}: the guard behind buffer {index} of this step (offset {start}, "
+                    f"{nbytes} bytes) was overwritten from its byte {bad} on")
 
     def alloc(self, shape, dtype) -> Optional[torch.Tensor]:
         n = 1
@@ -109,13 +133,16 @@ class SymmetricArena:
         # then fails too): the high-water mark is the total need of one step, so that the arena
         # created at the next step boundary is large enough at once instead of growing by one
         # buffer per step.
-        self.cursor = start + nbytes
+        self.cursor = start + nbytes + (_CANARY_BYTES if _DEBUG else 0)
         self.high_water = max(self.high_water, self.cursor)
         if self.cursor > self.capacity:
             return None
         off = _FLAG_BYTES + start
         t = self.buf[off:off + nbytes].view(dtype).view(*shape)
         self._views[t.data_ptr()] = off
+        if _DEBUG:
+            self.buf[off + nbytes:off + nbytes + _CANARY_BYTES].fill_(_CANARY)
+            self._guards.append((start, nbytes))
         return t
 
     def offset_of(self, t: torch.Tensor) -> Optional[int]:
@@ -313,6 +340,14 @@ def empty(group: Optional[dist.ProcessGroup], shape, dtype, device) -> torch.Ten
                 n *= int(s)
             _wanted[_key(group)] = _wanted.get(_key(group), 0) + n * 4 + _ALIGN
     return torch.empty(tuple(shape), dtype=dtype, device=device)
+
+
+def request(group: Optional[dist.ProcessGroup], nbytes: int, device) -> None:
+    """Note that `nbytes` of arena memory of `group` would have been used in this step, so that the next
+    step boundary creates (or grows) the arena: for buffers that are only ever taken from an arena that
+    exists, and would otherwise never cause one to be created."""
+    if _usable(group, torch.device(device)) and _key(group) not in _declined and _key(group) not in _arenas:
+        _wanted[_key(group)] = _wanted.get(_key(group), 0) + int(nbytes) + _ALIGN
 
 
 def all_reduce(t: torch.Tensor, group: Optional[dist.ProcessGroup], average: bool = False) -> None:

@@ -80,6 +80,7 @@ class _TPComm:
         self.gather = fsdp_comm.SymmAllGather(group, self.device)
         self.calls = 0
         self.fused_gathers = 0
+        self.pushed = 0  # all-reduced products that went through the push into every rank's slots
         self._ptr_cache = {}
 
     def ptrs(self, slot_off: int, block_bytes: int) -> torch.Tensor:
@@ -93,6 +94,10 @@ class _TPComm:
         return t
 
 
+# All-reduce of a row-parallel product by pushing the partial result to every rank costs (world - 1) times the
+# data on NVLink; beyond this group size the product is reduce-scattered and all-gathered instead.
+_MAX_PUSH_WORLD = 4
+_PUSH_ALL_REDUCE = os.environ.get("DION_B200_TP_PUSH", "1") != "0"
 _tp_comms = {}
 
 
@@ -207,6 +212,26 @@ def _matmul_all_reduce(x: torch.Tensor, w_t: torch.Tensor, group) -> torch.Tenso
     T, N = x.shape[0], w_t.shape[1]
     comm = _tp_comm(group, x.device) if x.is_cuda else None
     world = dist.get_world_size(group)
+    if (comm is not None and _PUSH_ALL_REDUCE and world <= _MAX_PUSH_WORLD and x.dtype == torch.bfloat16
+            and w_t.dtype == torch.bfloat16 and (T * N) % 8 == 0 and N % 8 == 0 and comm.recv.ensure(world * T * N * 2)):
+        # Small groups: the GEMM epilogue stores every tile of the partial product into slot `rank` of a
+        # receive buffer on every rank of the group (the local copy included) while the other tiles are still
+        # being multiplied; one kernel then waits for the peers' announcements and adds the slots in rank
+        # order.  Two launches, and the NVLink transfer hides behind the product.
+        ar = comm.recv.arena
+        comm.calls += 1
+        slot_off = comm.recv.slot_offset(comm.calls & 1)
+        slots = ar.buf[slot_off:slot_off + world * T * N * 2].view(torch.bfloat16).view(world, T, N)
+        key = ("all", ar.peers[0], slot_off, T, N)
+        table = comm._ptr_cache.get(key)
+        if table is None:
+            table = comm._ptr_cache[key] = torch.tensor([ar.peers[k] + slot_off + ar.rank * T * N * 2 for k in range(world)],
+                                                        dtype=torch.int64, device=x.device)
+        gemm(x, w_t, out=slots[0], out_ptrs=table, out_dup=world)
+        out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+        torch.ops.dion_b200.slot_reduce_bf16(slots, out, None, *ar.wait_args(), runtime.status_tensor(x.device))
+        comm.pushed += 1
+        return out
     ok = (comm is not None and x.dtype == torch.bfloat16 and T % world == 0 and (T // world) % 8 == 0 and N % 8 == 0
           and comm.recv.ensure(T * N * 2))
     if not ok:
