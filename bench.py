@@ -298,7 +298,9 @@ def run_reference(args):
 
     from dion_b200.utils.clocks import ClockSampler
 
-    torch._dynamo.config.cache_size_limit = 100
+    torch._dynamo.config.cache_size_limit = 100  # as the reference's trainer does (train.py:583)
+    if hasattr(torch._dynamo.config, "recompile_limit"):
+        torch._dynamo.config.recompile_limit = 100
     autocast = torch.amp.autocast(device_type="cuda", dtype=torch.bfloat16)
 
     def build(compiled: bool):

@@ -175,6 +175,12 @@ def main():
             del sys.modules[name]
         from dion import Dion as RefDion, Muon as RefMuon
 
+        # the reference's trainer raises dynamo's cache limit because its compiled helpers recompile for
+        # every new shape / hyper-parameter combination (train.py:583); a decoder with seven weight shapes needs it too
+        torch._dynamo.config.cache_size_limit = 100
+        if hasattr(torch._dynamo.config, "recompile_limit"):
+            torch._dynamo.config.recompile_limit = 100
+
         model, groups = build_plain_llama(cfg, mesh["fs"], world, dev)
         if args.optimizer == "dion":
             opt = RefDion(groups, outer_shard_mesh=mesh["fs"] if world > 1 else None, lr=0.01,

@@ -100,6 +100,40 @@ def bench_one(m: int, n: int, batch: int, iters: int = 10, triton_ref: bool = Fa
     return row
 
 
+def write_plot(rows, path: str) -> None:
+    """TFLOPS over the matrix size for every arm, as the reference's `--plot` draws it
+    (benchmark/benchmark_newton_shultz.py:104-170) - written as a plain SVG file, no plotting library needed."""
+    arms = [("tcgen05_tflops", "tcgen05 (this package)", "#d62728"), ("torch_tflops", "PyTorch", "#1f77b4"),
+            ("triton_ref_tflops", "reference Triton", "#2ca02c")]
+    arms = [a for a in arms if any(a[0] in r for r in rows)]
+    xs = [r["m"] for r in rows]
+    top = max(r.get(k, 0.0) for r in rows for k, _, _ in arms) * 1.1 or 1.0
+    W, H, L, B = 640, 400, 70, 50
+    px = lambda i: L + (W - L - 20) * (i / max(len(xs) - 1, 1))
+    py = lambda v: H - B - (H - B - 20) * (v / top)
+    out = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{W}" height="{H}" font-family="sans-serif" font-size="12">',
+           f'<rect width="{W}" height="{H}" fill="white"/>',
+           f'<line x1="{L}" y1="{H - B}" x2="{W - 20}" y2="{H - B}" stroke="black"/>',
+           f'<line x1="{L}" y1="20" x2="{L}" y2="{H - B}" stroke="black"/>',
+           f'<text x="{W / 2}" y="{H - 10}" text-anchor="middle">matrix dimension m (n = expansion x m)</text>',
+           f'<text x="15" y="{H / 2}" transform="rotate(-90 15 {H / 2})" text-anchor="middle">TFLOPS (4 m^2 n + 2 m^3 per step)</text>']
+    for i, x in enumerate(xs):
+        out.append(f'<text x="{px(i)}" y="{H - B + 18}" text-anchor="middle">{x}</text>')
+    for t in range(5):
+        v = top * t / 4
+        out.append(f'<text x="{L - 6}" y="{py(v) + 4}" text-anchor="end">{v:.0f}</text>')
+        out.append(f'<line x1="{L}" y1="{py(v)}" x2="{W - 20}" y2="{py(v)}" stroke="#dddddd"/>')
+    for j, (key, label, colour) in enumerate(arms):
+        pts = " ".join(f"{px(i)},{py(r[key])}" for i, r in enumerate(rows) if key in r)
+        out.append(f'<polyline points="{pts}" fill="none" stroke="{colour}" stroke-width="2"/>')
+        out.append(f'<rect x="{L + 15}" y="{28 + 16 * j}" width="12" height="3" fill="{colour}"/>')
+        out.append(f'<text x="{L + 32}" y="{34 + 16 * j}">{label}</text>')
+    out.append("</svg>")
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    with open(path, "w") as f:
+        f.write("\n".join(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--m", type=int, default=4096)
@@ -110,6 +144,8 @@ def main():
     ap.add_argument("--expansion", type=int, default=1, help="n = expansion * m for --grid")
     ap.add_argument("--json", type=str, default=None, help="write the rows to this file")
     ap.add_argument("--triton_ref", action="store_true", help="also time the reference's Triton kernels (baseline/_ref)")
+    ap.add_argument("--plot", type=str, default=None, metavar="FILE.svg",
+                    help="draw TFLOPS over the size for every arm (use with --grid)")
     ap.add_argument("--shapes", type=str, default=None,
                     help="several points in one run: comma-separated batch x m x n, e.g. 1x4096x4096,12x768x3072")
     a = ap.parse_args()
@@ -137,6 +173,8 @@ def main():
     if a.json:
         with open(a.json, "w") as f:
             json.dump(rows, f, indent=1)
+    if a.plot:
+        write_plot(rows, a.plot)
 
 
 if __name__ == "__main__":

@@ -68,7 +68,9 @@ def run_reference(args, dims, mesh, dev, cuda, rank, world):
     from dion import Dion as RefDion, DionMixedPrecisionConfig as RefMP, Muon as RefMuon
     from models.gpt_model import GPT as RefGPT, GPTConfig as RefCfg, parallelize_gpt_model as ref_parallelize
 
-    torch._dynamo.config.cache_size_limit = 100
+    torch._dynamo.config.cache_size_limit = 100  # as the reference's trainer does (train.py:583)
+    if hasattr(torch._dynamo.config, "recompile_limit"):
+        torch._dynamo.config.recompile_limit = 100
     autocast = torch.amp.autocast(device_type="cuda" if cuda else "cpu", dtype=torch.bfloat16)
 
     def build(compiled: bool):

@@ -615,6 +615,20 @@ class Dion(Optimizer):
             return None
         return all_reduce_(t, group, average=average, async_op=True)
 
+    def _q_gatherer(self, group: ProcessGroup, device):
+        """All-gather object for the columns of Q over the inner (tensor-parallel) group
+        (dion/dion.py:1063-1070 redistributes Q with a DTensor all-gather), or None where the symmetric
+        memory kernels do not apply (CPU tensors, gloo, more than eight ranks)."""
+        if device.type != "cuda":
+            return None
+        key = symm._key(group)
+        cache = self.__dict__.setdefault("_q_gatherers", {})
+        if key not in cache:
+            from ..parallel import fsdp_comm
+
+            cache[key] = fsdp_comm.SymmAllGather(group, device) if fsdp_comm._usable(group, device) else None
+        return cache[key]
+
     def _mesh_dim_group(self, p: Tensor, mesh_dim: Optional[int]) -> Optional[ProcessGroup]:
         if mesh_dim is None or not isinstance(p, DTensor):
             return None
@@ -645,9 +659,17 @@ class Dion(Optimizer):
         if w.inner is not None:
             w_in = dist.get_world_size(w.inner)
             gathered = torch.empty((w_in * B, Qs.shape[1], Qs.shape[2]), dtype=Qs.dtype, device=Qs.device)
-            work = dist.all_gather_into_tensor(gathered, Qs.contiguous(), group=w.inner, async_op=True)
-            yield
-            work.wait()
+            gather = self._q_gatherer(w.inner, Qs.device)
+            if gather is not None:
+                # the all-gather kernel over symmetric memory (it uses the process group by itself for
+                # sizes or alignments it does not cover); blocking in stream order, so nothing to wait for
+                before = gather.kernel_calls
+                gather(gathered.view(-1), Qs.contiguous().view(-1), w.inner)
+                symm.count("dion_q_gather", gather.kernel_calls > before)
+            else:
+                work = dist.all_gather_into_tensor(gathered, Qs.contiguous(), group=w.inner, async_op=True)
+                yield
+                work.wait()
             Q_full = gathered.view(w_in, B, Qs.shape[1], Qs.shape[2]).permute(1, 2, 0, 3).reshape(
                 B, Qs.shape[1], w_in * Qs.shape[2])
         else:

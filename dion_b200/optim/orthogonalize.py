@@ -55,13 +55,16 @@ def _split_tf32(x: Tensor):
     return ops.linalg.split_tf32(x)
 
 
-def gram(P: Tensor, reduce_group=None) -> Tensor:
+def gram(P: Tensor, reduce_group=None, out: Optional[Tensor] = None) -> Tensor:
     """``P^T P`` in fp32 for a batch ``[B, a, r]`` (fp32 input).  When the result will be
-    summed over `reduce_group`, it is produced in that group's symmetric arena."""
+    summed over `reduce_group`, it is produced in that group's symmetric arena; `out` (contiguous
+    ``[B, r, r]``, e.g. a slice of a buffer shared by several batches) receives it otherwise."""
     Pt = P.transpose(-1, -2)
     if not P.is_cuda:
-        return Pt @ P
-    out = symm.empty(reduce_group, (P.shape[0], P.shape[2], P.shape[2]), torch.float32, P.device)
+        res = Pt @ P
+        return res if out is None else out.copy_(res)
+    if out is None:
+        out = symm.empty(reduce_group, (P.shape[0], P.shape[2], P.shape[2]), torch.float32, P.device)
     if GRAM_PRECISION == "tf32":
         return ops.gemm(Pt, P, out=out, symmetric=True)
     if SPLIT_IN_KERNEL:
@@ -271,18 +274,36 @@ def _orthonormalize_many(Ps, row_groups, refine_passes, pivot_floor, shard_group
     last_info = [None] * n  # pivots the last factorisation of each batch gave up on
     for cholqr_pass in range(2 if any(robust) else 1):
         todo = [i for i in range(n) if cholqr_pass == 0 or robust[i]]
-        Gs = {i: gram(Xs[i], row_groups[i]) for i in todo}
-        for i in todo:
-            g = row_groups[i]
-            if g is not None and dist.get_world_size(g) > 1:
-                symm.all_reduce(Gs[i], g)
-            if cholqr_pass == 0 and robust[i]:
-                Gs[i].diagonal(dim1=-2, dim2=-1).mul_(1.0 + ROBUST_SHIFT)
         by_rank = {}
         for i in todo:
-            by_rank.setdefault(Gs[i].shape[-1], []).append(i)
+            by_rank.setdefault(Xs[i].shape[-1], []).append(i)
+        # The Gram matrices of all batches of one rank are factorised together.  Batches whose Gram matrix
+        # is not summed over a row group write theirs straight into one shared buffer; the others are
+        # produced in their group's arena and copied in.
+        Gs, Gcats = {}, {}
         for r, idxs in by_rank.items():
-            Gcat = Gs[idxs[0]] if len(idxs) == 1 else torch.cat([Gs[i] for i in idxs], dim=0)
+            if len(idxs) > 1:
+                total = sum(Xs[i].shape[0] for i in idxs)
+                Gcats[r] = torch.empty((total, r, r), dtype=torch.float32, device=Xs[idxs[0]].device)
+            off = 0
+            for i in idxs:
+                b = Xs[i].shape[0]
+                g = row_groups[i]
+                sharded_rows = g is not None and dist.get_world_size(g) > 1
+                if r in Gcats and not sharded_rows:
+                    Gs[i] = gram(Xs[i], out=Gcats[r][off:off + b])
+                else:
+                    Gs[i] = gram(Xs[i], g)
+                    if sharded_rows:
+                        symm.all_reduce(Gs[i], g)
+                    if r in Gcats:
+                        Gcats[r][off:off + b].copy_(Gs[i])
+                        Gs[i] = Gcats[r][off:off + b]
+                if cholqr_pass == 0 and robust[i]:
+                    Gs[i].diagonal(dim1=-2, dim2=-1).mul_(1.0 + ROBUST_SHIFT)
+                off += b
+        for r, idxs in by_rank.items():
+            Gcat = Gcats[r] if r in Gcats else Gs[idxs[0]]
             Z, info = ops.chol_inverse(Gcat, pivot_floor)
             off = 0
             for i in idxs:
