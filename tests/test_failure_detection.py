@@ -238,7 +238,7 @@ def test_arena_sizing_converges_in_one_regrowth():
 
     def fake(capacity):
         a = symm.SymmetricArena.__new__(symm.SymmetricArena)
-        a.capacity, a.cursor, a.high_water, a._views = capacity, 0, 0, {}
+        a.capacity, a.cursor, a.high_water, a._views, a._guards = capacity, 0, 0, {}, []
         a.buf = torch.zeros(symm._FLAG_BYTES + capacity, dtype=torch.uint8)
         return a
 
