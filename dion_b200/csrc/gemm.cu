@@ -1025,6 +1025,27 @@ EncodeFn get_encode_fn() {
   return fn;
 }
 
+struct TmapKey {
+  const void* base;
+  uint64_t inner, rows, batch, pitch, bstride;
+  uint32_t box_inner, box_rows;
+  int32_t dtype, atom32;
+};
+struct TmapSlot {
+  CUtensorMap map;
+  TmapKey key;
+  bool valid;
+};
+constexpr size_t kTmapSlots = 2048;  // power of two; a GPT-160M step uses about 600 distinct maps
+
+bool tmap_cache_enabled() {  // DION_B200_TMAP_CACHE=0 encodes every map afresh
+  static const bool on = [] {
+    const char* e = getenv("DION_B200_TMAP_CACHE");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+
 // Tensor map over a row-major [batch][rows][inner] array with a [1][box_rows][box_inner] box.
 bool make_tmap(CUtensorMap* map, const void* base, int dtype, uint64_t inner, uint64_t rows, uint64_t batch,
                uint64_t row_pitch_elems, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_rows,
@@ -1045,6 +1066,29 @@ bool make_tmap(CUtensorMap* map, const void* base, int dtype, uint64_t inner, ui
     g_last_error = "GEMM operand must be 16-byte aligned with pitches that are multiples of 16 bytes";
     return false;
   }
+  // A tensor map depends only on the address and the geometry, never on what the memory holds, and a training
+  // step asks for the same few hundred maps again and again: keep them in a direct-mapped per-thread table.
+  TmapSlot* slot = nullptr;
+  if (tmap_cache_enabled()) {
+    TmapKey key;
+    memset(&key, 0, sizeof(key));
+    key.base = base;
+    key.inner = inner; key.rows = rows; key.batch = batch;
+    key.pitch = strides[0]; key.bstride = strides[1];
+    key.box_inner = box_inner; key.box_rows = box_rows;
+    key.dtype = dtype; key.atom32 = atom32 ? 1 : 0;
+    uint64_t h = 1469598103934665603ull;
+    const unsigned char* kb = reinterpret_cast<const unsigned char*>(&key);
+    for (size_t i = 0; i < sizeof(key); ++i) h = (h ^ kb[i]) * 1099511628211ull;
+    static thread_local TmapSlot* table = new TmapSlot[kTmapSlots]();
+    slot = &table[(h ^ (h >> 29)) & (kTmapSlots - 1)];
+    if (slot->valid && memcmp(&slot->key, &key, sizeof(key)) == 0) {
+      memcpy(map, &slot->map, sizeof(CUtensorMap));
+      return true;
+    }
+    slot->valid = false;
+    slot->key = key;
+  }
   CUresult r = fn(map, dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
@@ -1055,6 +1099,10 @@ bool make_tmap(CUtensorMap* map, const void* base, int dtype, uint64_t inner, ui
     snprintf(buf, sizeof(buf), "cuTensorMapEncodeTiled failed with code %d", (int)r);
     g_last_error = buf;
     return false;
+  }
+  if (slot) {
+    memcpy(&slot->map, map, sizeof(CUtensorMap));
+    slot->valid = true;
   }
   return true;
 }

@@ -93,3 +93,22 @@ def test_mesh_benchmark_script_smoke():
     line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
     out = json.loads(line)
     assert out["n_gpus"] == 2 and out["value"] > 0 and out["config"]["parallelism"].startswith("dp1 x fs1 x tp2")
+
+
+def test_loss_curve_script_learns_the_chain(tmp_path):
+    """The loss-curve comparison script: its synthetic Markov-chain tokens are learnable (the loss falls well
+    below the uniform-guess level towards log(fanout)) and its comparison table prints."""
+    import json
+
+    env = dict(os.environ)
+    env.update(OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES="")
+    script = os.path.join(ROOT, "benchmark", "loss_curve.py")
+    out_json = tmp_path / "ours.json"
+    res = subprocess.run([sys.executable, script, "--tiny", "--steps", "30", "--batch", "4", "--states", "64", "--json",
+                          str(out_json)], env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert res.returncode == 0, (res.stdout + res.stderr)[-3000:]
+    rec = json.loads(out_json.read_text())
+    assert len(rec["losses"]) == 30 and rec["losses"][0] > 5.0 and rec["losses"][-1] < 2.5, rec["losses"]
+    res = subprocess.run([sys.executable, script, "--compare", str(out_json), str(out_json)], env=env,
+                         capture_output=True, text=True, timeout=120, cwd=ROOT)
+    assert res.returncode == 0 and "mean of the last 20 steps" in res.stdout, res.stdout + res.stderr
