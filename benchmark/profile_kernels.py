@@ -13,7 +13,7 @@ ncu would lock the GPU's clocks, and that setting outlasts the process).
 and gemm_sym for comparison.
 
 Cases: gemm_fwd, gemm_dx, gemm_dw, gemm_sym, gemm_tf32_mn, gram3x, gram3x_k, apply3x, gemm_scatter, chol, cross_entropy,
-rope, rmsnorm, lion, adamw, muon_pre, dion_accum, all_reduce (single rank loop-back over
+rope, rope_bwd, rmsnorm, lion, adamw, muon_pre, dion_accum, all_reduce (single rank loop-back over
 symmetric memory).
 """
 
@@ -137,6 +137,13 @@ def case(name: str, ref: bool = False):
         cos, sin = K.rotary_tables(1024, Dh, dev)
         fn = lambda: torch.ops.dion_b200.rope_qknorm_fwd(q, k, qo, ko, cos, sin, 1024, H, Dh, K.RMS_EPS)
         return fn, 0.0, T * H * Dh * 2 * 4
+    if name == "rope_bwd":
+        T, H, Dh = 65536, 12, 64
+        q, k, gq, gk = r(T, H * Dh), r(T, H * Dh), r(T, H * Dh), r(T, H * Dh)
+        dq, dk = torch.empty_like(q), torch.empty_like(k)
+        cos, sin = K.rotary_tables(1024, Dh, dev)
+        fn = lambda: torch.ops.dion_b200.rope_qknorm_bwd(gq, gk, q, k, dq, dk, cos, sin, 1024, H, Dh, K.RMS_EPS)
+        return fn, 0.0, T * H * Dh * 2 * 6
     if name == "rmsnorm":
         T, D = 131072, 768
         x, y, rs = r(T, D), torch.empty(T, D, device=dev, dtype=bf), torch.empty(T, device=dev)

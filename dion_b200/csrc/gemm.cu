@@ -231,6 +231,14 @@ __device__ __forceinline__ void load_chunk(const char* base, bool is_bf16, long 
   }
 }
 
+// One special-function instruction instead of the IEEE-rounded sequence of sqrtf(): the operand is a bf16 value and the
+// result scales a gradient that is rounded to bf16 again, 2^-22 of relative error is far below either.
+__device__ __forceinline__ float sqrt_approx(float x) {
+  float y;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // ---- epilogue staging: one warp turns a 32-row block through shared memory.  A buffer holds 32
 // rows of 128 bytes; the 16-byte segment index is XOR-ed with the row so that both the
 // row-per-lane side and the segment-per-lane side are free of bank conflicts.
@@ -739,14 +747,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const uint32_t acc_phase = (it >> 1) & 1;
       const int kb0 = t.split * kb_per_split;
       const bool has_work = kb0 < p.kblocks_total;
-      if (!wait(&tmem_full[acc], acc_phase)) {
-        ok = false;
-        *abort_flag = 1;
-        if (p.status) atomicCAS(p.status, 0, kStatusEpilogueTimeout);
-        break;
-      }
-      tc_fence_after();
-
       const int row = m0 + quad * 32 + lane;
       // debug build: the tile lies inside the problem and the output base is 16-byte aligned where vector stores go
       const bool row_ok = row < p.M && DION_DBG_OK(t.batch < p.batch && m0 < p.M + C::TILE_M && n0 < p.N, p.status);
@@ -774,7 +774,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       const int row_first = m0 + quad * 32;
       const bool full_tile = n0 + kBlockN <= p.N;
       const bool atomic = p.epilogue == kEpiAtomicAdd;
-      const bool use_c = c_base != nullptr && !atomic && (p.beta != 0.f || p.act == kActMulRelu2Grad);
+      const bool use_c = c_base != nullptr && !atomic &&
+                         (p.beta != 0.f || p.act == kActMulRelu2Grad || p.act == kActMulRelu2GradSq);
       const bool stage_c = p.stage && use_c && full_tile && p.vec_c;
       const bool stage_d = p.stage && !atomic && full_tile && p.vec_d;
       const bool stage_d2 = p.stage && d2_base != nullptr && full_tile && p.vec_d2;
@@ -802,6 +803,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
       constexpr int kChunksPerWarp = kBlockN / 32 / (kNumEpilogueWarps / 4);
       const int c_first = ((warp - 2) >> 2) * kChunksPerWarp;
+
+      // A staged bf16 C operand is fetched one chunk ahead: the loads of the first chunk go out before this
+      // warp waits for the accumulator, those of chunk c + 1 while chunk c is converted and stored, so that
+      // their latency does not add to every chunk (with 8 epilogue warps per CTA nothing else hides it).
+      // Same lane mapping as stage_fetch<4>: 4 lanes per row, 8 rows per instruction.
+      const bool prefetch_c = !kSplit && stage_c && p.c_is_bf16;  // the splitting variants have no registers to spare
+      uint4 cq[4];
+      auto c_prefetch = [&](int chunk) {
+        const char* cp = c_base + ((long long)(row_first + (lane >> 2)) * p.ldc + n0 + chunk * 32) * 2 + (lane & 3) * 16;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          cq[i] = make_uint4(0u, 0u, 0u, 0u);
+          if (row_first + i * 8 + (lane >> 2) < p.M) cq[i] = *reinterpret_cast<const uint4*>(cp + (long long)i * 8 * p.ldc * 2);
+        }
+      };
+      if (prefetch_c) c_prefetch(c_first);
+
+      if (!wait(&tmem_full[acc], acc_phase)) {
+        ok = false;
+        *abort_flag = 1;
+        if (p.status) atomicCAS(p.status, 0, kStatusEpilogueTimeout);
+        break;
+      }
+      tc_fence_after();
+
 #pragma unroll 1
       for (int c = c_first; c < c_first + kChunksPerWarp; ++c) {
         const int col0 = n0 + c * 32;
@@ -873,7 +899,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           // C operand: added (beta * C) or, for the ReLU^2 backward, multiplied in as 2 * relu(C)
           if (use_c) {
             float cv[32];
-            if (stage_c) {
+            if (prefetch_c) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(st + stage_off(i * 8 + (lane >> 2), lane & 3)) = cq[i];
+              __syncwarp();
+              stage_get(st, lane, true, cv);
+              __syncwarp();
+              if (c + 1 < c_first + kChunksPerWarp) c_prefetch(c + 1);  // a full tile: every chunk is in range
+            } else if (stage_c) {
               auto c_row = [&](int grow) { return c_base + ((long long)grow * p.ldc + col0) * es_c; };
               if (p.c_is_bf16) stage_fetch<4>(st, lane, row_first, p.M, c_row);
               else stage_fetch<8>(st, lane, row_first, p.M, c_row);
@@ -889,6 +922,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             if (p.act == kActMulRelu2Grad) {
 #pragma unroll
               for (int i = 0; i < 32; ++i) v[i] *= 2.f * fmaxf(cv[i], 0.f);
+            } else if (p.act == kActMulRelu2GradSq) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] *= 2.f * sqrt_approx(fmaxf(cv[i], 0.f));
             } else if (p.c_col_scale != nullptr) {
               // every lane reads the same 32 factors (a broadcast load per factor)
               const float* cs = p.c_col_scale + (long long)t.batch * p.N + col0;

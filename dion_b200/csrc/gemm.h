@@ -20,6 +20,7 @@ enum GemmAct : int {
   kActRelu2 = 1,         // D = relu(alpha * acc)^2 (+ beta * C)
   kActRelu2SavePre = 2,  // as kActRelu2, and D2 receives the pre-activation alpha * acc
   kActMulRelu2Grad = 3,  // D = alpha * acc * 2 * relu(C): backward of ReLU^2 with C the saved pre-activation
+  kActMulRelu2GradSq = 4,  // D = alpha * acc * 2 * sqrt(max(C, 0)): the same with C = relu(pre)^2, the saved activation
 };
 
 // D[b] = alpha * op(A[b]) * op(B[b]) (+ beta * C[b]),  op(A) is M x K, op(B) is K x N.

@@ -4,6 +4,10 @@
 // reference gets from model.compile() (models/gpt_model.py:54-61, 86-89, 106-112,
 // 115-124, 171-179).
 #include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdlib.h>
+
+#include <initializer_list>
 
 #include "kernels.h"
 
@@ -285,6 +289,168 @@ __global__ void __launch_bounds__(256) rope_qknorm_bwd_kernel(const bf16* __rest
   }
 }
 
+// Wide variants (every pointer 16-byte aligned, pitches multiples of 8 elements): HD / 16 lanes share one
+// (token, head); a lane owns eight consecutive rotation pairs - one 16-byte load from each half of the row -
+// of q AND of k, which use the same cos / sin values.  Twice the bytes per load and two independent rows per
+// thread keep more of the memory system busy than the 8-byte kernel above, which stays for unaligned views.
+template <int LPR>
+__device__ __forceinline__ void rope_rotate_norm(const float (&x1)[8], const float (&x2)[8], const float (&c)[8],
+                                                 const float (&sn)[8], float eps, int hd, float (&y1)[8],
+                                                 float (&y2)[8], float& rs) {
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    y1[i] = x1[i] * c[i] + x2[i] * sn[i];
+    y2[i] = x2[i] * c[i] - x1[i] * sn[i];
+    ss += y1[i] * y1[i] + y2[i] * y2[i];
+  }
+  ss = group_sum<LPR>(ss);
+  rs = eps < 0.f ? 1.f : rsqrtf(ss / (float)hd + eps);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(256) rope_qknorm_fwd_wide_kernel(const bf16* __restrict__ q,
+                                                                  const bf16* __restrict__ k, bf16* __restrict__ qo,
+                                                                  bf16* __restrict__ ko,
+                                                                  const bf16* __restrict__ cosb,
+                                                                  const bf16* __restrict__ sinb, long long tokens,
+                                                                  int seq_len, int heads, long long in_pitch,
+                                                                  long long out_pitch, float eps) {
+  constexpr int HALF = HD / 2;
+  constexpr int LPR = HD / 16;  // lanes per (token, head)
+  const long long gid = (long long)blockIdx.x * 256 + threadIdx.x;
+  const long long rid = gid / LPR;
+  const int sub = (int)(gid - rid * LPR);
+  const long long nrows = tokens * heads;
+  const bool live = rid < nrows;  // dead lanes compute on row 0 so that the shuffles stay converged
+  const long long th = live ? rid : 0;
+  const long long tok = th / heads;
+  const int head = (int)(th - tok * heads);
+  const int pos = (int)(tok % seq_len);
+  const int p = sub * 8;
+  const long long in_off = tok * in_pitch + (long long)head * HD + p;
+  const long long out_off = tok * out_pitch + (long long)head * HD + p;
+  // all loads first
+  const uint4 q1 = *reinterpret_cast<const uint4*>(q + in_off);
+  const uint4 q2 = *reinterpret_cast<const uint4*>(q + in_off + HALF);
+  uint4 k1 = make_uint4(0, 0, 0, 0), k2 = k1;
+  if (k) {
+    k1 = *reinterpret_cast<const uint4*>(k + in_off);
+    k2 = *reinterpret_cast<const uint4*>(k + in_off + HALF);
+  }
+  const uint4 cq = *reinterpret_cast<const uint4*>(cosb + (long long)pos * HALF + p);
+  const uint4 sq = *reinterpret_cast<const uint4*>(sinb + (long long)pos * HALF + p);
+  float c[8], sn[8], x1[8], x2[8], y1[8], y2[8], rs;
+  unpack8(cq, c);
+  unpack8(sq, sn);
+  unpack8(q1, x1);
+  unpack8(q2, x2);
+  rope_rotate_norm<LPR>(x1, x2, c, sn, eps, HD, y1, y2, rs);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    y1[i] *= rs;
+    y2[i] *= rs;
+  }
+  if (live) {
+    *reinterpret_cast<uint4*>(qo + out_off) = pack8(y1);
+    *reinterpret_cast<uint4*>(qo + out_off + HALF) = pack8(y2);
+  }
+  if (k) {
+    unpack8(k1, x1);
+    unpack8(k2, x2);
+    rope_rotate_norm<LPR>(x1, x2, c, sn, eps, HD, y1, y2, rs);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      y1[i] *= rs;
+      y2[i] *= rs;
+    }
+    if (live) {
+      *reinterpret_cast<uint4*>(ko + out_off) = pack8(y1);
+      *reinterpret_cast<uint4*>(ko + out_off + HALF) = pack8(y2);
+    }
+  }
+}
+
+template <int LPR>
+__device__ __forceinline__ void rope_backward_row(const uint4& xa, const uint4& xb, const uint4& ga, const uint4& gb,
+                                                  const float (&c)[8], const float (&sn)[8], float eps, int hd,
+                                                  uint4& oa, uint4& ob) {
+  float x1[8], x2[8], g1[8], g2[8], y1[8], y2[8], rs;
+  unpack8(xa, x1);
+  unpack8(xb, x2);
+  unpack8(ga, g1);
+  unpack8(gb, g2);
+  rope_rotate_norm<LPR>(x1, x2, c, sn, eps, hd, y1, y2, rs);
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) dot += g1[i] * y1[i] + g2[i] * y2[i];
+  dot = group_sum<LPR>(dot);
+  const float c3 = eps < 0.f ? 0.f : rs * rs * rs * dot / (float)hd;
+  float o1[8], o2[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float d1 = rs * g1[i] - c3 * y1[i];  // gradient w.r.t. the rotated values
+    const float d2 = rs * g2[i] - c3 * y2[i];
+    o1[i] = d1 * c[i] - d2 * sn[i];
+    o2[i] = d1 * sn[i] + d2 * c[i];
+  }
+  oa = pack8(o1);
+  ob = pack8(o2);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(256) rope_qknorm_bwd_wide_kernel(const bf16* __restrict__ dqo,
+                                                                  const bf16* __restrict__ dko,
+                                                                  const bf16* __restrict__ q,
+                                                                  const bf16* __restrict__ k, bf16* __restrict__ dq,
+                                                                  bf16* __restrict__ dk,
+                                                                  const bf16* __restrict__ cosb,
+                                                                  const bf16* __restrict__ sinb, long long tokens,
+                                                                  int seq_len, int heads, long long in_pitch,
+                                                                  long long out_pitch, float eps) {
+  constexpr int HALF = HD / 2;
+  constexpr int LPR = HD / 16;
+  const long long gid = (long long)blockIdx.x * 256 + threadIdx.x;
+  const long long rid = gid / LPR;
+  const int sub = (int)(gid - rid * LPR);
+  const long long nrows = tokens * heads;
+  const bool live = rid < nrows;
+  const long long th = live ? rid : 0;
+  const long long tok = th / heads;
+  const int head = (int)(th - tok * heads);
+  const int pos = (int)(tok % seq_len);
+  const int p = sub * 8;
+  const long long in_off = tok * in_pitch + (long long)head * HD + p;    // q, k and their gradients
+  const long long out_off = tok * out_pitch + (long long)head * HD + p;  // gradients of the rotated outputs
+  const uint4 q1 = *reinterpret_cast<const uint4*>(q + in_off);
+  const uint4 q2 = *reinterpret_cast<const uint4*>(q + in_off + HALF);
+  const uint4 gq1 = *reinterpret_cast<const uint4*>(dqo + out_off);
+  const uint4 gq2 = *reinterpret_cast<const uint4*>(dqo + out_off + HALF);
+  uint4 k1 = make_uint4(0, 0, 0, 0), k2 = k1, gk1 = k1, gk2 = k1;
+  if (k) {
+    k1 = *reinterpret_cast<const uint4*>(k + in_off);
+    k2 = *reinterpret_cast<const uint4*>(k + in_off + HALF);
+    gk1 = *reinterpret_cast<const uint4*>(dko + out_off);
+    gk2 = *reinterpret_cast<const uint4*>(dko + out_off + HALF);
+  }
+  float c[8], sn[8];
+  unpack8(*reinterpret_cast<const uint4*>(cosb + (long long)pos * HALF + p), c);
+  unpack8(*reinterpret_cast<const uint4*>(sinb + (long long)pos * HALF + p), sn);
+  uint4 oa, ob;
+  rope_backward_row<LPR>(q1, q2, gq1, gq2, c, sn, eps, HD, oa, ob);
+  if (live) {
+    *reinterpret_cast<uint4*>(dq + in_off) = oa;
+    *reinterpret_cast<uint4*>(dq + in_off + HALF) = ob;
+  }
+  if (k) {
+    rope_backward_row<LPR>(k1, k2, gk1, gk2, c, sn, eps, HD, oa, ob);
+    if (live) {
+      *reinterpret_cast<uint4*>(dk + in_off) = oa;
+      *reinterpret_cast<uint4*>(dk + in_off + HALF) = ob;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ ReLU^2
 __global__ void __launch_bounds__(256) relu2_fwd_kernel(const uint4* __restrict__ x, uint4* __restrict__ h,
                                                        long long nvec) {
@@ -467,21 +633,40 @@ cudaError_t rmsnorm_bwd_launch(const void* dy, const void* x, const float* rstd,
   return cudaGetLastError();
 }
 
+// 16-byte accesses need every base pointer on a 16-byte boundary and pitches that keep it there
+static bool rope_wide_ok(std::initializer_list<const void*> ptrs, long long in_pitch, long long out_pitch) {
+  static const bool enabled = [] {  // DION_B200_ROPE_WIDE=0 keeps the 8-byte kernels
+    const char* e = getenv("DION_B200_ROPE_WIDE");
+    return !(e && e[0] == '0');
+  }();
+  if (!enabled) return false;
+  for (const void* p : ptrs)
+    if (reinterpret_cast<uintptr_t>(p) & 15) return false;
+  return in_pitch % 8 == 0 && out_pitch % 8 == 0;
+}
+
 cudaError_t rope_qknorm_fwd_launch(const void* q, const void* k, void* q_out, void* k_out, const void* cos,
                                    const void* sin, long long tokens, int seq_len, int heads, int head_dim,
                                    long long in_pitch, long long out_pitch, float eps, cudaStream_t s) {
   const long long nrows = tokens * heads * (k ? 2 : 1);
   if (nrows == 0) return cudaSuccess;
   if (in_pitch % 4 != 0 || out_pitch % 4 != 0) return cudaErrorInvalidValue;
-  const unsigned grid = (unsigned)((nrows * (head_dim / 8) + 255) / 256);
-#define DION_ROPE_FWD(HD)                                                                                         \
-  rope_qknorm_fwd_kernel<HD><<<grid, 256, 0, s>>>(                                                                \
+  if (head_dim != 64 && head_dim != 128) return cudaErrorInvalidValue;
+  const bool wide = rope_wide_ok({q, k, q_out, k_out, cos, sin}, in_pitch, out_pitch);
+  const unsigned grid = wide ? (unsigned)((tokens * heads * (head_dim / 16) + 255) / 256)
+                             : (unsigned)((nrows * (head_dim / 8) + 255) / 256);
+#define DION_ROPE_FWD(KERNEL, HD)                                                                                 \
+  KERNEL<HD><<<grid, 256, 0, s>>>(                                                                                \
       reinterpret_cast<const bf16*>(q), reinterpret_cast<const bf16*>(k), reinterpret_cast<bf16*>(q_out),         \
       reinterpret_cast<bf16*>(k_out), reinterpret_cast<const bf16*>(cos), reinterpret_cast<const bf16*>(sin),     \
       tokens, seq_len, heads, in_pitch, out_pitch, eps)
-  if (head_dim == 64) DION_ROPE_FWD(64);
-  else if (head_dim == 128) DION_ROPE_FWD(128);
-  else return cudaErrorInvalidValue;
+  if (wide) {
+    if (head_dim == 64) DION_ROPE_FWD(rope_qknorm_fwd_wide_kernel, 64);
+    else DION_ROPE_FWD(rope_qknorm_fwd_wide_kernel, 128);
+  } else {
+    if (head_dim == 64) DION_ROPE_FWD(rope_qknorm_fwd_kernel, 64);
+    else DION_ROPE_FWD(rope_qknorm_fwd_kernel, 128);
+  }
 #undef DION_ROPE_FWD
   return cudaGetLastError();
 }
@@ -492,16 +677,23 @@ cudaError_t rope_qknorm_bwd_launch(const void* dq_out, const void* dk_out, const
   const long long nrows = tokens * heads * (k ? 2 : 1);
   if (nrows == 0) return cudaSuccess;
   if (in_pitch % 4 != 0 || out_pitch % 4 != 0) return cudaErrorInvalidValue;
-  const unsigned grid = (unsigned)((nrows * (head_dim / 8) + 255) / 256);
-#define DION_ROPE_BWD(HD)                                                                                         \
-  rope_qknorm_bwd_kernel<HD><<<grid, 256, 0, s>>>(                                                                \
+  if (head_dim != 64 && head_dim != 128) return cudaErrorInvalidValue;
+  const bool wide = rope_wide_ok({dq_out, dk_out, q, k, dq, dk, cos, sin}, in_pitch, out_pitch);
+  const unsigned grid = wide ? (unsigned)((tokens * heads * (head_dim / 16) + 255) / 256)
+                             : (unsigned)((nrows * (head_dim / 8) + 255) / 256);
+#define DION_ROPE_BWD(KERNEL, HD)                                                                                 \
+  KERNEL<HD><<<grid, 256, 0, s>>>(                                                                                \
       reinterpret_cast<const bf16*>(dq_out), reinterpret_cast<const bf16*>(dk_out),                               \
       reinterpret_cast<const bf16*>(q), reinterpret_cast<const bf16*>(k), reinterpret_cast<bf16*>(dq),            \
       reinterpret_cast<bf16*>(dk), reinterpret_cast<const bf16*>(cos), reinterpret_cast<const bf16*>(sin),        \
       tokens, seq_len, heads, in_pitch, out_pitch, eps)
-  if (head_dim == 64) DION_ROPE_BWD(64);
-  else if (head_dim == 128) DION_ROPE_BWD(128);
-  else return cudaErrorInvalidValue;
+  if (wide) {
+    if (head_dim == 64) DION_ROPE_BWD(rope_qknorm_bwd_wide_kernel, 64);
+    else DION_ROPE_BWD(rope_qknorm_bwd_wide_kernel, 128);
+  } else {
+    if (head_dim == 64) DION_ROPE_BWD(rope_qknorm_bwd_kernel, 64);
+    else DION_ROPE_BWD(rope_qknorm_bwd_kernel, 128);
+  }
 #undef DION_ROPE_BWD
   return cudaGetLastError();
 }

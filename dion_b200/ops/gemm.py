@@ -19,7 +19,7 @@ import torch
 
 from . import runtime
 
-_ACT = {None: 0, "none": 0, "relu2": 1, "relu2_save_pre": 2, "mul_relu2_grad": 3}
+_ACT = {None: 0, "none": 0, "relu2": 1, "relu2_save_pre": 2, "mul_relu2_grad": 3, "mul_relu2_grad_sq": 4}
 
 
 def _apply_act(x: torch.Tensor, act) -> torch.Tensor:
@@ -37,6 +37,8 @@ def gemm_reference(a, b, *, c=None, out=None, alpha=1.0, beta=0.0, act=None, out
     pre = acc
     if act == "mul_relu2_grad":
         res = acc * 2.0 * torch.relu(c.float())
+    elif act == "mul_relu2_grad_sq":
+        res = acc * 2.0 * torch.relu(c.float()).sqrt()
     else:
         res = _apply_act(acc, "relu2" if act == "relu2_save_pre" else act)
         if c is not None and beta != 0.0:

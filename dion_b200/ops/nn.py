@@ -221,29 +221,28 @@ def linear_fanout(x: torch.Tensor, *weights: torch.Tensor):
 
 class _MLPFn(torch.autograd.Function):
     """out = residual + relu(x W_fc^T)^2 W_proj^T with the activation fused into the GEMM
-    epilogues: the forward c_fc product writes both the pre-activation and relu^2 of it, the
-    backward c_proj product multiplies its result by 2 relu(pre) on the way out."""
+    epilogues: the forward c_fc product writes h = relu^2 of its result, the backward c_proj product
+    multiplies its result by 2 relu(pre) = 2 sqrt(h) on the way out - the pre-activation itself is
+    never stored (one [T, 4d] tensor less to write and to keep per layer)."""
 
     @staticmethod
     def forward(ctx, x, w_fc, w_proj, residual):
         fc, pj = bf16_weight(w_fc), bf16_weight(w_proj)
         T = x.shape[0]
-        pre = torch.empty(T, fc.shape[0], device=x.device, dtype=torch.bfloat16)
-        h = torch.empty_like(pre)
-        gemm(x, fc.t(), out=h, shadow=pre, act="relu2_save_pre")
+        h = torch.empty(T, fc.shape[0], device=x.device, dtype=torch.bfloat16)
+        gemm(x, fc.t(), out=h, act="relu2")
         out = torch.empty(T, pj.shape[0], device=x.device, dtype=torch.bfloat16)
         gemm(h, pj.t(), c=residual, beta=1.0, out=out)
-        ctx.save_for_backward(x, w_fc, w_proj, pre, h)
+        ctx.save_for_backward(x, w_fc, w_proj, h)
         return out
 
     @staticmethod
     def backward(ctx, dy):
-        x, w_fc, w_proj, pre, h = ctx.saved_tensors
+        x, w_fc, w_proj, h = ctx.saved_tensors
         fc, pj = bf16_weight(w_fc), bf16_weight(w_proj)
         dy = dy.contiguous()
-        T = x.shape[0]
-        dpre = torch.empty_like(pre)
-        gemm(dy, pj, c=pre, out=dpre, act="mul_relu2_grad")          # (dy W_proj) * 2 relu(pre)
+        dpre = torch.empty_like(h)
+        gemm(dy, pj, c=h, out=dpre, act="mul_relu2_grad_sq")         # (dy W_proj) * 2 sqrt(h)
         dw_proj = _weight_grad(dy, h, w_proj) if ctx.needs_input_grad[2] else None
         dx = None
         if ctx.needs_input_grad[0]:

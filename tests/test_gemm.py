@@ -160,6 +160,10 @@ def test_gemm_relu2_save_pre_and_backward_multiplier():
     gemm(dy, w, c=pre, out=dpre, act="mul_relu2_grad")
     ref = (dy.float() @ w.float()) * 2 * torch.relu(pre.float())
     assert _rel_err(dpre, ref) < 1e-2
+    # the same multiplier recovered from the stored activation h = relu(pre)^2
+    dpre2 = torch.empty_like(dpre)
+    gemm(dy, w, c=h, out=dpre2, act="mul_relu2_grad_sq")
+    assert _rel_err(dpre2, ref) < 1e-2
 
 
 @pytest.mark.gpu

@@ -71,6 +71,50 @@ def test_rope_qknorm_kernel(head_dim):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("head_dim", [64, 128])
+def test_rope_qknorm_kernel_on_views_that_are_only_8_byte_aligned(head_dim):
+    """Inputs that start 8 bytes into an allocation take the kernels with 8-byte accesses; same results."""
+    B, T, H = 2, 40, 3
+    n = B * T * H * head_dim
+    cos, sin = N.rotary_tables(T, head_dim, "cuda")
+    qbuf = torch.randn(n + 4, device="cuda").bfloat16()
+    kbuf = torch.randn(n + 4, device="cuda").bfloat16()
+    q = qbuf[4:].view(B, T, H, head_dim).requires_grad_()
+    k = kbuf[4:].view(B, T, H, head_dim).requires_grad_()
+    assert q.data_ptr() % 16 == 8 and q.is_contiguous()
+    qo, ko = N.rope_qknorm(q, k, cos, sin)
+    gq, gk = torch.randn_like(qo), torch.randn_like(ko)
+    ((qo * gq).sum() + (ko * gk).sum()).backward()
+    qr = q.detach().float().requires_grad_()
+    kr = k.detach().float().requires_grad_()
+    qro, kro = N._rope_qknorm_torch(qr, kr, cos, sin, N.RMS_EPS)
+    ((qro * gq.float()).sum() + (kro * gk.float()).sum()).backward()
+    torch.testing.assert_close(qo.float(), qro, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(ko.float(), kro, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(q.grad.float(), qr.grad, rtol=5e-2, atol=5e-2)
+    torch.testing.assert_close(k.grad.float(), kr.grad, rtol=5e-2, atol=5e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("head_dim", [64, 128])
+def test_rope_alone_kernel(head_dim):
+    """Rotary embedding of one tensor without the norm (the Llama-shaped model's use)."""
+    B, T, H = 2, 33, 5
+    cos, sin = N.rotary_tables(T, head_dim, "cuda")
+    x = torch.randn(B, T, H, head_dim, device="cuda").bfloat16().requires_grad_()
+    y = N.rope(x, cos, sin)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_()
+    d = head_dim // 2
+    c, s_ = cos[None, :T, None, :].float(), sin[None, :T, None, :].float()
+    yr = torch.cat([xr[..., :d] * c + xr[..., d:] * s_, xr[..., d:] * c - xr[..., :d] * s_], dim=-1)
+    yr.backward(g.float())
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.gpu
 def test_relu2_kernel():
     x = torch.randn(64, 3072, device="cuda").bfloat16().requires_grad_()
     h = N.relu2(x)
