@@ -25,6 +25,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <memory>
 #include <mutex>
 #include <string>
 
@@ -1116,7 +1117,7 @@ bool make_tmap(CUtensorMap* map, const void* base, int dtype, uint64_t inner, ui
     uint64_t h = 1469598103934665603ull;
     const unsigned char* kb = reinterpret_cast<const unsigned char*>(&key);
     for (size_t i = 0; i < sizeof(key); ++i) h = (h ^ kb[i]) * 1099511628211ull;
-    static thread_local TmapSlot* table = new TmapSlot[kTmapSlots]();
+    static thread_local std::unique_ptr<TmapSlot[]> table(new TmapSlot[kTmapSlots]());  // freed with the thread
     slot = &table[(h ^ (h >> 29)) & (kTmapSlots - 1)];
     if (slot->valid && memcmp(&slot->key, &key, sizeof(key)) == 0) {
       memcpy(map, &slot->map, sizeof(CUtensorMap));
