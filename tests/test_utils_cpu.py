@@ -100,3 +100,45 @@ def test_gather_gemm_plan_rejects_ragged_row_blocks():
         pytest.skip("extension not built")
     assert list(torch.ops.dion_b200.gemm_gather_plan(400, 96, 64, 200, 2, 0)) == []      # rows not a multiple of 128
     assert list(torch.ops.dion_b200.gemm_gather_plan(512, 96, 64, 256, 3, 0)) == []      # world * rows != M
+
+
+def _load_benchmark_module(name):
+    import importlib.util
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location(name, os.path.join(root, "benchmark", name + ".py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_newton_schulz_benchmark_flop_count_and_plot(tmp_path):
+    """FLOP accounting of the Newton-Schulz benchmark (4 m^2 n + 2 m^3 per step, the smaller dimension as m,
+    as in the reference's script) and its SVG plot writer, which needs no plotting library."""
+    bench = _load_benchmark_module("benchmark_newton_schulz")
+    assert bench.ns_flops(4, 8, iters=1) == 4 * 16 * 8 + 2 * 64
+    assert bench.ns_flops(8, 4, iters=1) == bench.ns_flops(4, 8, iters=1)
+    assert bench.ns_flops(4, 8, batch=3, iters=5) == 15 * bench.ns_flops(4, 8, iters=1)
+    rows = [{"m": 512, "tcgen05_tflops": 100.0, "torch_tflops": 80.0},
+            {"m": 1024, "tcgen05_tflops": 400.0, "torch_tflops": 300.0, "triton_ref_tflops": 350.0}]
+    path = tmp_path / "sub" / "ns.svg"
+    bench.write_plot(rows, str(path))
+    svg = path.read_text()
+    assert svg.startswith("<svg") and svg.rstrip().endswith("</svg>")
+    assert svg.count("<polyline") == 3 and "reference Triton" in svg and ">1024<" in svg
+
+
+def test_loss_curve_markov_batches_are_reproducible_and_follow_the_chain():
+    lc = _load_benchmark_module("loss_curve")
+    a = lc.markov_batches(2, 3, 16, states=8, fanout=2, vocab=50, seed=5)
+    b = lc.markov_batches(2, 3, 16, states=8, fanout=2, vocab=50, seed=5)
+    assert all(torch.equal(x1, x2) and torch.equal(y1, y2) for (x1, y1), (x2, y2) in zip(a, b))
+    x, y = a[0]
+    assert x.shape == (3, 16) and torch.equal(x[:, 1:], y[:, :-1])     # targets are the inputs shifted by one
+    assert len(torch.unique(torch.cat([x.flatten(), y.flatten()]))) <= 8
+    # every token has at most `fanout` distinct successors over all batches
+    succ = {}
+    for x, y in a:
+        for s, t in zip(x.flatten().tolist(), y.flatten().tolist()):
+            succ.setdefault(s, set()).add(t)
+    assert max(len(v) for v in succ.values()) <= 2
