@@ -157,13 +157,15 @@ class Task:
             self.done = True
             return False
 
+    run = advance  # the reference's name for the same step (AsyncTask.run, dion/opt_utils.py:89-98)
+
 
 class Scheduler:
     """Round-robin scheduler over lazily created tasks: at most `max_in_flight` tasks are
     alive; each turn admits one new task and advances every live one by one step, so the
     collectives of one batch overlap the math of the others (dion/opt_utils.py:100-145)."""
 
-    def __init__(self, tasks: Iterable[Callable[[], Generator[None, None, None]]], max_in_flight: int = 3):
+    def __init__(self, tasks: Iterable[Union["Task", Callable[[], Generator[None, None, None]]]], max_in_flight: int = 3):
         if max_in_flight <= 0:
             raise ValueError(f"max_in_flight={max_in_flight} must be positive")
         self._source = iter(tasks)
@@ -177,7 +179,7 @@ class Scheduler:
             if not exhausted and len(live) < self._max:
                 try:
                     make = next(self._source)
-                    t = Task(make())
+                    t = make if isinstance(make, Task) else Task(make())  # a started task or a factory of one
                     if not t.done:
                         nxt.append(t)
                 except StopIteration:

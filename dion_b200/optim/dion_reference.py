@@ -17,7 +17,7 @@ import torch
 import torch.distributed as dist
 from torch import Tensor
 from torch.distributed import ProcessGroup
-from torch.distributed.tensor import DeviceMesh
+from torch.distributed.tensor import DeviceMesh, DTensor
 from torch.optim.optimizer import ParamsT
 
 from ..ops import nn as nn_ops
@@ -66,6 +66,97 @@ def orthogonalize_row_sharded(P: Tensor, qr_method: str, oversample: float, grou
     dist.all_reduce(G, group=group)
     R, _ = torch.linalg.cholesky_ex(G, upper=True)
     return torch.linalg.solve_triangular(R, Q, upper=True, left=False).to(dtype)
+
+
+def power_iteration(B: Tensor, Q_init: Tensor, power_iters: int, qr_method: str, oversample: float,
+                    compressed_all_reduce: bool, replicate_mesh: Union[DeviceMesh, ProcessGroup, None] = None,
+                    inner_shard_mesh_dim: Optional[int] = None, rng: Optional[torch.Generator] = None, *,
+                    row_group: Optional[ProcessGroup] = None,
+                    column_group: Optional[ProcessGroup] = None) -> Tuple[Tensor, Tensor]:
+    """Low-rank factors of ``B ~ P Q^T`` by ``power_iters`` rounds of ``P = orth(B Q)``, ``Q = B^T P``
+    (dion/dion_reference.py:690-730).
+
+    ``B`` and ``Q_init`` are one matrix each, in the same dtype.  Sharding is described either the reference's
+    way - ``B`` a DTensor whose rows are sharded over mesh dimension ``inner_shard_mesh_dim``; P comes back
+    sharded like B's rows and Q replicated - or on local shards with explicit groups: ``row_group`` shards the
+    rows of B (and of P), ``column_group`` its columns (and the rows of Q).  With ``compressed_all_reduce`` the
+    factors are averaged over ``replicate_mesh`` instead of the gradient having been averaged beforehand."""
+    if B.dtype != Q_init.dtype:
+        raise TypeError(f"Expected inputs to have the same dtype, but got {B.dtype} and {Q_init.dtype}.")
+    wrap = None
+    if isinstance(B, DTensor):
+        for i, pl in enumerate(B.placements):
+            if pl.is_partial() or pl.is_shard(1) or (pl.is_shard(0) and i != inner_shard_mesh_dim):
+                raise ValueError("a DTensor B may only have its rows sharded, over inner_shard_mesh_dim")
+        if inner_shard_mesh_dim is not None and B.placements[inner_shard_mesh_dim].is_shard(0):
+            row_group = B.device_mesh.get_group(inner_shard_mesh_dim)
+        wrap = B
+        B, Q_init = B.to_local(), to_local(Q_init)
+    replicate = group_of(replicate_mesh) if compressed_all_reduce else None
+    P, Q = None, Q_init
+    for _ in range(power_iters):
+        P = B @ Q
+        if column_group is not None:
+            dist.all_reduce(P, group=column_group)
+        if replicate is not None:
+            all_reduce_(P, replicate, average=True)
+        P = orthogonalize_row_sharded(P, qr_method, oversample, row_group, rng)
+        Q = B.T @ P
+        if row_group is not None:
+            dist.all_reduce(Q, group=row_group)
+        if replicate is not None:
+            all_reduce_(Q, replicate, average=True)
+    if wrap is not None:
+        from torch.distributed.tensor import Replicate
+
+        P = DTensor.from_local(P, device_mesh=wrap.device_mesh, placements=wrap.placements, run_check=False)
+        Q = DTensor.from_local(Q, device_mesh=wrap.device_mesh, placements=[Replicate()] * wrap.device_mesh.ndim,
+                               run_check=False)
+    return P, Q
+
+
+def dion_update(X: Tensor, G: Tensor, M: Tensor, Q: Tensor, lr, mu, weight_decay, epsilon: float, transpose: bool,
+                power_iters: int, qr_method: str, oversample: float = 1.25, compressed_all_reduce: bool = True,
+                replicate_mesh: Union[DeviceMesh, ProcessGroup, None] = None,
+                inner_shard_mesh_dim: Optional[int] = None, rng: Optional[torch.Generator] = None, *,
+                row_group: Optional[ProcessGroup] = None, column_group: Optional[ProcessGroup] = None,
+                full_shape: Optional[Tuple[int, int]] = None) -> Tensor:
+    """One Dion step on one matrix (dion/dion_reference.py:614-687): momentum accumulation, power iteration,
+    all-zero / NaN guard, error feedback, column-normalised new Q, weight decay and the scaled update.
+    ``X`` and ``M`` are updated in place and the new Q (all columns, in the dtype of M) is returned for the
+    caller to store.
+
+    ``X``, ``G``, ``M`` are local shards and ``Q`` holds all of its columns; ``row_group`` / ``column_group``
+    (keyword only) name the process groups that shard the rows / columns of the matrix the power iteration
+    works on (``M``, or ``M^T`` with ``transpose``), and ``full_shape`` the unsharded (fan_out, fan_in) that
+    scales the learning rate.  ``inner_shard_mesh_dim`` belongs to the reference's DTensor calling convention
+    and is not used on local shards."""
+    del inner_shard_mesh_dim
+    lr, mu, weight_decay = float(lr), float(mu), float(weight_decay)
+    Q_init = Q.to(M.dtype)
+    M.add_(G.to(M.dtype))
+    A = M.T if transpose else M
+    P, R = power_iteration(A, Q_init, power_iters, qr_method, oversample, compressed_all_reduce, replicate_mesh,
+                           rng=rng, row_group=row_group, column_group=column_group)
+    # all-zero momentum shard: no update, keep the previous Q (shard-local check)
+    is_zero = bool((M == 0).all())
+    P = P.nan_to_num() * (0.0 if is_zero else 1.0)
+    R = Q_init.clone() if is_zero else R.nan_to_num()
+
+    M.add_((R @ P.T) if transpose else (P @ R.T), alpha=-(1 - mu))
+
+    R32 = R.float()
+    ss = R32.square().sum(dim=0, keepdim=True)
+    if column_group is not None:
+        dist.all_reduce(ss, group=column_group)
+    Q_new = (R32 / (ss.sqrt() + epsilon)).to(P.dtype)
+
+    X.mul_(1 - lr * weight_decay)
+    fan_out, fan_in = full_shape if full_shape is not None else X.shape
+    scaled_lr = ((fan_out / fan_in) ** 0.5) * lr
+    upd = (Q_new @ P.T) if transpose else (P @ Q_new.T)
+    X.add_(upd.to(X.dtype), alpha=-scaled_lr)
+    return Q_new
 
 
 class DionReference(Dion):
@@ -165,40 +256,9 @@ class DionReference(Dion):
             Q_full = Q_loc
         Q_init = Q_full.to(M.dtype)
 
-        M.add_(grad.to(M.dtype))
-        A = M.T if cfg.is_transposed else M
-        Q = Q_init
-        for _ in range(self._power_iters):
-            P = A @ Q
-            if outer is not None:
-                dist.all_reduce(P, group=outer)
-            if compressed:
-                all_reduce_(P, replicate, average=True)
-            P = orthogonalize_row_sharded(P, qr_method, group["oversample"], inner, self._rng)
-            Q = A.T @ P
-            if inner is not None:
-                dist.all_reduce(Q, group=inner)
-            if compressed:
-                all_reduce_(Q, replicate, average=True)
-        R = Q
-        # all-zero momentum shard: no update, keep the previous Q (shard-local check)
-        is_zero = bool((M == 0).all())
-        P = P.nan_to_num() * (0.0 if is_zero else 1.0)
-        R = Q_init.clone() if is_zero else R.nan_to_num()
-
-        M.add_((R @ P.T) if cfg.is_transposed else (P @ R.T), alpha=-(1 - mu))
-
-        R32 = R.float()
-        ss = R32.square().sum(dim=0, keepdim=True)
-        if outer is not None:
-            dist.all_reduce(ss, group=outer)
-        Q_new = (R32 / (ss.sqrt() + eps)).to(P.dtype)
-
-        X.mul_(1 - lr * wd)
-        fan_out, fan_in = p.shape
-        scaled_lr = ((fan_out / fan_in) ** 0.5) * lr
-        upd = (Q_new @ P.T) if cfg.is_transposed else (P @ Q_new.T)
-        X.add_(upd.to(X.dtype), alpha=-scaled_lr)
+        Q_new = dion_update(X, grad, M, Q_init, lr, mu, wd, eps, cfg.is_transposed, self._power_iters, qr_method,
+                            group["oversample"], compressed, replicate, rng=self._rng, row_group=inner,
+                            column_group=outer, full_shape=tuple(p.shape))
 
         if inner is not None:
             r_loc = Q_loc.shape[1]

@@ -665,6 +665,78 @@ def case_structured():
         check(f"structured {mode} losses", got[4:], want[4:], 0.1 if CUDA else 2e-2)
 
 
+def case_functional():
+    """The free functions that mirror the reference's helpers, on sharded inputs: orthonormalisation of
+    row-sharded matrices (batched Cholesky-QR and the oracle's per-matrix methods), averaged all-reduce, scalar
+    updates behind a gradient all-reduce, and the DTensor sketch."""
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.tensor import DTensor, Replicate, Shard
+
+    from dion_b200 import dion as D
+    from dion_b200 import dion_reference as DR
+
+    mesh = init_device_mesh("cuda" if CUDA else "cpu", (WORLD,), mesh_dim_names=("shard",))
+    g = torch.Generator().manual_seed(7)
+    full = torch.randn(3, 16 * WORLD, 8, generator=g).to(DEV)
+    rows = full.shape[1] // WORLD
+    local = full[:, RANK * rows:(RANK + 1) * rows].contiguous()
+    P = DTensor.from_local(local, device_mesh=mesh, placements=[Shard(1)], run_check=False)
+
+    # batched Cholesky-QR on row shards against the single-process result on the whole matrices
+    out = D.distributed_orthogonalize(P, shard_mesh_dim=0)
+    assert isinstance(out, DTensor) and tuple(out.placements) == (Shard(1),)
+    want = D.orthogonalize(full)
+    check("distributed_orthogonalize (cholesky-qr)", out.to_local(), want[:, RANK * rows:(RANK + 1) * rows], 2e-3 if CUDA else 1e-4)
+    rep = D.distributed_orthogonalize(DTensor.from_local(full, device_mesh=mesh, placements=[Replicate()], run_check=False))
+    check("distributed_orthogonalize (replicated)", rep.to_local(), want, 2e-3 if CUDA else 1e-5)
+
+    # the oracle's per-matrix methods on one row-sharded matrix: orthonormal columns spanning the same space
+    P2 = DTensor.from_local(local[0].contiguous(), device_mesh=mesh, placements=[Shard(0)], run_check=False)
+    for method in ("qr", "cqr", "rcqr"):
+        q = DR.distributed_orthogonalize(P2, qr_method=method, shard_mesh_dim=0)
+        parts = [torch.empty_like(q.to_local()) for _ in range(WORLD)]
+        dist.all_gather(parts, q.to_local().contiguous())
+        Q = torch.cat(parts, dim=0).float()
+        check(f"oracle {method}: Q^T Q = I", Q.T @ Q, torch.eye(8, device=DEV), 1e-3)
+        proj = Q @ (Q.T @ full[0])
+        check(f"oracle {method}: span", proj, full[0], 1e-3)
+
+    # averaged all-reduce of a list, in place and returned
+    grads, mean = rank_grads(3, shapes=[(5, 4), (9,)])
+    got = D.all_reduce_replicate_mesh([t.clone() for t in grads], mesh, return_dtensor=False)
+    for a, b in zip(got, mean):
+        check("all_reduce_replicate_mesh", a, b, 1e-5)
+    assert D.all_reduce_replicate_mesh(grads[0], None) is grads[0]
+
+    # Lion / AdamW behind the gradient all-reduce equal the same update with the mean gradient
+    for algo in ("lion", "adamw"):
+        X = [torch.ones(5, 4, device=DEV), torch.ones(9, device=DEV)]
+        Xw = [x.clone() for x in X]
+        M, Mw = [torch.zeros_like(x) for x in X], [torch.zeros_like(x) for x in X]
+        V, Vw = [torch.zeros_like(x) for x in X], [torch.zeros_like(x) for x in X]
+        G = [t.clone() for t in grads]
+        if algo == "lion":
+            task = D.lion_update_allreduce_grad(X, G, M, 0.01, 0.9, 0.99, 0.1, replicate_mesh=mesh)
+            from dion_b200.scalar_opts import lion_update_foreach
+
+            lion_update_foreach(Xw, mean, Mw, 0.01, 0.9, 0.99, 0.1)
+        else:
+            task = D.adamw_update_allreduce_grad(X, G, M, V, 0.01, 0.9, 0.99, 0.1, 1, 1e-8, replicate_mesh=mesh)
+            from dion_b200.scalar_opts import adamw_update_foreach
+
+            adamw_update_foreach(Xw, mean, Mw, Vw, 0.01, 0.9, 0.99, 0.1, 1, 1e-8)
+        steps = sum(1 for _ in task)
+        assert steps == 1, "one yield while the all-reduce is in flight"
+        for a, b in zip(X, Xw):
+            check(f"{algo}_update_allreduce_grad", a, b, 1e-5)
+
+    # DTensor sketch, sharded along m over the mesh dimension (DTensor random numbers need a CUDA mesh)
+    if CUDA:
+        S = D.generate_random_sketch_matrix(P, 1.25, shard_mesh_dim=0)
+        assert tuple(S.shape) == (3, 128, 16 * WORLD) and tuple(S.to_local().shape) == (3, 128, rows)
+        assert tuple(S.placements) == (Shard(2),)
+
+
 def case_checkpoint():
     """Distributed checkpoint round trip of model + Dion state through CheckpointManager."""
     import tempfile

@@ -39,7 +39,8 @@ def _launch(cases, nproc, force_cpu, timeout=600, multicast=False):
     assert res.returncode == 0 and "ALL OK" in res.stdout, tail
 
 
-@pytest.mark.parametrize("case", ["dion_ddp", "muon_ddp", "fsdp", "fsdp_comm", "tp", "tp_sp", "structured", "checkpoint"])
+@pytest.mark.parametrize("case", ["dion_ddp", "muon_ddp", "fsdp", "fsdp_comm", "tp", "tp_sp", "structured", "checkpoint",
+                                  "functional"])
 def test_cpu_two_ranks(case):
     _launch([case], nproc=2, force_cpu=True)
 
