@@ -277,3 +277,45 @@ def test_power_iteration_and_dion_update_match_the_reference_oracle():
             outs.append((X, M, Q))
         for x, y in zip(outs[0], outs[1]):
             torch.testing.assert_close(x, y, rtol=1e-4, atol=1e-4)
+
+
+def test_model_import_paths_of_the_reference(tmp_path):
+    from dion_b200.models import gpt_model, gpt_utils
+    from dion_b200.models.data import write_datafile
+
+    assert gpt_model.GPT is importlib.import_module("dion_b200.models").GPT
+    for name in ("GPTConfig", "Rotary", "CausalSelfAttention", "MLP", "Block", "parallelize_gpt_model", "_apply_tp",
+                 "_apply_fsdp", "apply_rotary_emb"):
+        assert hasattr(gpt_model, name), name
+    toks = (torch.arange(1000) % 50000).numpy().astype("uint16")
+    path = str(tmp_path / "shard.bin")
+    write_datafile(path, toks)
+    assert gpt_utils._peek_data_shard(path) == 1000
+    assert (gpt_utils._load_data_shard(path) == toks).all()
+
+
+@needs_ref
+def test_apply_rotary_emb_and_shard_readers_match_the_reference(tmp_path):
+    import sys
+
+    from dion_b200.models import gpt_model, gpt_utils
+    from dion_b200.models.data import write_datafile
+
+    ref_root = [p for p in sys.path if p.endswith("_ref") or p == __import__("os").environ.get("DION_REFERENCE_PATH")][0]
+    sys.path.insert(0, ref_root)
+    for m in [k for k in sys.modules if k == "models" or k.startswith("models.")]:
+        del sys.modules[m]
+    ref_model = importlib.import_module("models.gpt_model")
+    ref_utils = importlib.import_module("models.gpt_utils")
+    torch.manual_seed(6)
+    x = torch.randn(2, 9, 3, 16)
+    rot = ref_model.Rotary(16)
+    rot.init_inv_freq()
+    cos, sin = rot(x)
+    torch.testing.assert_close(gpt_model.apply_rotary_emb(x, cos.float(), sin.float()),
+                               ref_model.apply_rotary_emb(x, cos.float(), sin.float()), rtol=1e-5, atol=1e-5)
+    toks = (torch.arange(777) * 13 % 50000).numpy().astype("uint16")
+    path = str(tmp_path / "shard.bin")
+    write_datafile(path, toks)
+    assert gpt_utils._peek_data_shard(path) == ref_utils._peek_data_shard(path)
+    assert (gpt_utils._load_data_shard(path) == ref_utils._load_data_shard(path)).all()
