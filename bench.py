@@ -135,11 +135,13 @@ def emit(args, world, tokens_per_step, dev_ms, e2e_ms, clocks, extra):
             "optimizer": f"{args.optimizer} rank_fraction 1.0 + lion" if args.optimizer == "dion" else "muon + lion",
             "optimizer_state_dtype": "fp32" if args.fp32_states else "bf16",
             "l2": "inputs_exceed_l2 (activations and weights per step are far larger than the 126 MB L2)",
-            "attention": ("reference: F.scaled_dot_product_attention" if args.impl == "reference" else
-                          ("library (F.scaled_dot_product_attention)"
-                           if os.environ.get("DION_B200_ATTENTION", "kernel") == "library"
-                           else "in-tree tcgen05 kernels")),
         },
+        # how the arm computes attention is a property of the implementation, not of the workload: it stays out
+        # of `config`, which is the same dictionary in both arms
+        "attention_impl": ("reference: F.scaled_dot_product_attention" if args.impl == "reference" else
+                           ("library (F.scaled_dot_product_attention)"
+                            if os.environ.get("DION_B200_ATTENTION", "kernel") == "library"
+                            else "in-tree tcgen05 kernels")),
         "clocks": clocks,
     }
     if e2e_ms is not None:
