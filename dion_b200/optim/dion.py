@@ -869,7 +869,14 @@ class Dion(Optimizer):
         slots in rank order and writes P together with the tf32 halves the Gram product needs.
         When the batch can be split (no tensor-parallel rows), matrix i goes only to rank i // per: every
         rank receives exactly the matrices it will orthonormalise.  Returns None (nothing launched) when
-        the arenas cannot serve the buffers; sets w.P_total like the unfused path."""
+        the arenas cannot serve the buffers; sets w.P_total like the unfused path.
+
+        Slot buffers sit at the same arena offsets in every step and no message says that a consumer has
+        finished reading.  Rewriting them a step later is safe because every step passes through at least two
+        synchronising operations on the arena (this exchange, then the R exchange or the all-reduce of the
+        column sums): a rank that is about to push for step n + 1 has completed a consumer kernel that waited
+        for its peers' announcements of the later operation of step n, which those peers launch behind their
+        readers of this buffer (utils/protocol_check.py enumerates the interleavings)."""
         cls = w.cls
         dev = cls.M.device
         ar1 = symm.arena_for(first)
