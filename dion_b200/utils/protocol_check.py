@@ -1,5 +1,6 @@
-"""Exhaustive interleaving check of the push-exchange protocol (csrc/dion_fused.cu, csrc/symm_flags.cuh,
-parallel/symm.py: ``alloc_slots`` / ``wait_args``).
+"""Exhaustive interleaving check of the flag protocols that have no closing barrier: the push exchanges
+(csrc/dion_fused.cu, csrc/symm_flags.cuh, parallel/symm.py: ``alloc_slots`` / ``wait_args``) and the all-gather
+kernel's alternating staging slots (csrc/comm_kernels.cu).
 
 The protocol: every rank's GEMM epilogue stores its partial product into slot ``rank`` of a buffer in the
 memory of each consuming rank; the consumer kernel that follows on the same stream announces "my stores are
@@ -45,6 +46,56 @@ def program(rank: int, world: int, exchanges: Sequence[int]) -> List[Action]:
         for q in range(world):
             acts.append(("read", q, x))        # consumer kernel: read slot q of my buffer
     return acts
+
+
+def program_pull(rank: int, world: int, exchanges: Sequence[int]) -> List[Action]:
+    """Actions of one rank for the all-gather kernel's protocol (csrc/comm_kernels.cu, ``all_gather_kernel``):
+    copy the own shard into the own staging slot, announce it, then pull every peer's slot as soon as that peer
+    has announced.  There is no closing barrier; the slots alternate instead."""
+    acts: List[Action] = []
+    for x, _ in enumerate(exchanges):
+        acts.append(("stage", rank, x))        # write my staging slot (local memory)
+        for d in range(world):
+            acts.append(("announce", d, x))
+        for q in range(world):
+            acts.append(("wait1", q, x))       # flag[rank][q] >= epoch(x)
+            acts.append(("pull", q, x))        # read rank q's staging slot over NVLink
+    return acts
+
+
+def check_pull(world: int, cycles: int, buffers: Sequence[int]) -> Optional[List[Tuple[int, Action]]]:
+    """As :func:`check` for the pull protocol: ``slots[q][b]`` is rank q's staging slot b, written only by q and
+    read by everybody."""
+    exchanges = list(buffers) * cycles
+    nbuf = max(exchanges) + 1
+    progs = [program_pull(r, world, exchanges) for r in range(world)]
+    start = (tuple(0 for _ in range(world)), tuple(-1 for _ in range(world * nbuf)), tuple(0 for _ in range(world * world)))
+    seen = {start}
+    stack = [(start, [])]
+    while stack:
+        (pcs, slots, flags), trail = stack.pop()
+        for r in range(world):
+            if pcs[r] == len(progs[r]):
+                continue
+            kind, peer, x = progs[r][pcs[r]]
+            b = exchanges[x]
+            nslots, nflags = slots, flags
+            if kind == "stage":
+                i = r * nbuf + b
+                nslots = slots[:i] + (x,) + slots[i + 1:]
+            elif kind == "announce":
+                i = peer * world + r
+                nflags = flags[:i] + (x + 1,) + flags[i + 1:]
+            elif kind == "wait1":
+                if flags[r * world + peer] < x + 1:
+                    continue
+            elif slots[peer * nbuf + b] != x:  # pull
+                return trail + [(r, progs[r][pcs[r]])]
+            state = (pcs[:r] + (pcs[r] + 1,) + pcs[r + 1:], nslots, nflags)
+            if state not in seen:
+                seen.add(state)
+                stack.append((state, trail + [(r, progs[r][pcs[r]])]))
+    return None
 
 
 def check(world: int, cycles: int, buffers: Sequence[int]) -> Optional[List[Tuple[int, Action]]]:
@@ -98,10 +149,16 @@ def main() -> None:
     for name, cfg in (("Dion step (P, R)", DION_STEP), ("three ranks", dict(world=3, cycles=2, buffers=(0, 1))),
                       ("lone buffer", LONE_BUFFER)):
         witness = check(**cfg)
-        if witness is None:
-            print(f"{name}: no interleaving reads a wrong slot")
-        else:
-            print(f"{name}: violated after {len(witness)} actions; last: rank {witness[-1][0]} {witness[-1][1]}")
+        report(name, witness)
+    report("all-gather, two alternating staging slots", check_pull(world=3, cycles=2, buffers=(0, 1)))
+    report("all-gather, one staging slot", check_pull(world=2, cycles=2, buffers=(0,)))
+
+
+def report(name: str, witness) -> None:
+    if witness is None:
+        print(f"{name}: no interleaving reads a wrong slot")
+    else:
+        print(f"{name}: violated after {len(witness)} actions; last: rank {witness[-1][0]} {witness[-1][1]}")
 
 
 if __name__ == "__main__":

@@ -28,3 +28,12 @@ def test_the_model_blocks_a_wait_until_every_peer_announced():
     assert kinds == ["push", "push", "announce", "announce", "wait", "read", "read"]
     # a single exchange can never read before both pushes happened: no violation in any interleaving
     assert pc.check(world=2, cycles=1, buffers=(0,)) is None
+
+
+def test_all_gather_staging_slots_must_alternate():
+    """The all-gather kernel has no closing barrier: with two alternating staging slots no interleaving lets a
+    rank overwrite a slot that a peer still pulls; with a single slot one does."""
+    assert pc.check_pull(world=2, cycles=3, buffers=(0, 1)) is None
+    assert pc.check_pull(world=3, cycles=2, buffers=(0, 1)) is None
+    witness = pc.check_pull(world=2, cycles=2, buffers=(0,))
+    assert witness is not None and witness[-1][1][0] == "pull"
