@@ -142,3 +142,20 @@ def test_loss_curve_markov_batches_are_reproducible_and_follow_the_chain():
         for s, t in zip(x.flatten().tolist(), y.flatten().tolist()):
             succ.setdefault(s, set()).add(t)
     assert max(len(v) for v in succ.values()) <= 2
+
+
+def test_openmp_compiler_selection(tmp_path, monkeypatch):
+    """`ensure_openmp_cxx` keeps a compiler that can build OpenMP code and replaces one that cannot."""
+    from dion_b200.utils import compilers
+
+    assert compilers.can_openmp("/nonexistent/compiler") is False
+    broken = tmp_path / "g++"
+    broken.write_text("#!/bin/sh\nexit 1\n")
+    broken.chmod(broken.stat().st_mode | stat.S_IEXEC)
+    assert compilers.can_openmp(str(broken)) is False
+    monkeypatch.setenv("CXX", str(broken))
+    chosen = compilers.ensure_openmp_cxx()
+    if chosen:                                   # a working compiler exists on this machine
+        assert chosen != str(broken) and os.environ["CXX"] == chosen and compilers.can_openmp(chosen)
+        monkeypatch.setenv("CXX", chosen)
+        assert compilers.ensure_openmp_cxx() == chosen
