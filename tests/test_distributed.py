@@ -62,7 +62,8 @@ def test_gpu_ranks(case):
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
-    _launch([case], nproc=min(n, 4), force_cpu=False)
+    # two ranks: the rank count these cases have been run with on GPUs (four ranks: the hybrid case above)
+    _launch([case], nproc=2, force_cpu=False)
 
 
 @pytest.mark.gpu
@@ -73,7 +74,7 @@ def test_gpu_symmetric_kernels_with_multimem():
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
-    _launch(["symm_multicast"], nproc=min(n, 4), force_cpu=False, multicast=True)
+    _launch(["symm_multicast"], nproc=2, force_cpu=False, multicast=True)
 
 
 @pytest.mark.gpu
