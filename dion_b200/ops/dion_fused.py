@@ -9,7 +9,7 @@ contribution has been stored and waits, with a bound, for theirs.
 
 from __future__ import annotations
 
-from typing import Optional, Sequence, Tuple
+from typing import Optional, Sequence
 
 import torch
 
