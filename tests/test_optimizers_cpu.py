@@ -455,3 +455,55 @@ def test_dion_trains_on_structured_data_gpu():
     assert all(l == l for l in ours)
     assert ours[-1] < 0.6 and oracle[-1] < 0.6, (ours, oracle)
     assert abs(ours[-1] - oracle[-1]) < 0.25 * max(oracle[-1], 0.2), (ours, oracle)
+
+
+def _groups(mats, emb, head):
+    return [dict(params=mats),
+            dict(params=[emb], algorithm="lion", lr=0.002, weight_decay=0.0),
+            dict(params=[head], algorithm="adamw", lr=0.003, weight_decay=0.01)]
+
+
+@needs_ref
+@pytest.mark.parametrize("direction", ["reference_to_ours", "ours_to_reference"])
+@pytest.mark.parametrize("kind", ["dion", "muon"])
+def test_optimizer_state_dicts_interchange_with_the_reference(kind, direction):
+    """A state_dict written by the reference's optimizer loads into this package's optimizer (and the other way
+    round) and training continues as if nothing had happened: same keys, same tensors, same group entries."""
+    torch.manual_seed(11)
+    shapes = [(48, 32), (32, 48), (48, 32)]
+    base = [torch.randn(s) for s in shapes] + [torch.randn(50, 16), torch.randn(16, 50)]
+
+    def build(module, which):
+        ps = [torch.nn.Parameter(t.clone()) for t in base]
+        groups = _groups(ps[:3], ps[3], ps[4])
+        if which == "dion":
+            opt = module.Dion(groups, lr=0.02, rank_fraction=0.5, weight_decay=0.05)
+        else:
+            opt = module.Muon(groups, lr=0.02, mu=0.95, weight_decay=0.05, nesterov=True, adjust_lr="spectral_norm")
+        return ps, opt
+
+    def run(ps, opt, steps, seed):
+        g = torch.Generator().manual_seed(seed)
+        for _ in range(steps):
+            for p in ps:
+                p.grad = torch.randn(p.shape, generator=g)
+            opt.step()
+
+    src_mod, dst_mod = (ref, dion_b200) if direction == "reference_to_ours" else (dion_b200, ref)
+    # the writer trains three steps and keeps going; the reader loads the writer's state and takes the same steps
+    ps_w, opt_w = build(src_mod, kind)
+    run(ps_w, opt_w, 3, seed=1)
+    sd = copy.deepcopy(opt_w.state_dict())
+    ps_r, opt_r = build(dst_mod, kind)
+    with torch.no_grad():
+        for a, b in zip(ps_r, ps_w):
+            a.copy_(b)
+    opt_r.load_state_dict(sd)
+    assert opt_r.state_dict()["param_groups"][0].keys() == sd["param_groups"][0].keys()
+    for sw, sr in zip(sd["state"].values(), opt_r.state_dict()["state"].values()):
+        assert sw.keys() == sr.keys()
+    run(ps_w, opt_w, 2, seed=2)
+    run(ps_r, opt_r, 2, seed=2)
+    tol = dict(rtol=2e-3, atol=2e-4) if kind == "dion" else dict(rtol=2e-2, atol=2e-3)   # Muon: bf16 Newton-Schulz
+    for a, b in zip(ps_w, ps_r):
+        torch.testing.assert_close(a, b, **tol)
