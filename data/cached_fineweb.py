@@ -14,11 +14,11 @@ REPOS = {"10B": ("kjj0/fineweb10B-gpt2", "fineweb10B", "fineweb", 103),
          "edu10B": ("kjj0/finewebedu10B-gpt2", "finewebedu10B", "finewebedu", 99)}
 
 
-def main():
+def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--version", default="10B", choices=sorted(REPOS))
     ap.add_argument("num_chunks", nargs="?", type=int, default=None)
-    a = ap.parse_args()
+    a = ap.parse_args(argv)
     from huggingface_hub import hf_hub_download
 
     repo, local, prefix, total = REPOS[a.version]
