@@ -338,7 +338,8 @@ def case_fsdp():
         if name == "dion":
             # every class of the 2-layer model has an even number of matrices: P leaves its reduction
             # over the shard group as this rank's share (reduce-scatter), not as the whole batch
-            assert opt.p_reduce_scatters > 0, "P was all-reduced although the batches split evenly"
+            if WORLD == 2:  # with more ranks the classes of this small model (2, 2 and 8 matrices) do not all split evenly
+                assert opt.p_reduce_scatters > 0, "P was all-reduced although the batches split evenly"
             _expect_pushed("dion_p_exchange")
         if name == "muon":
             # the momentum is linear in the gradients, so it pins down that every path (library

@@ -45,6 +45,13 @@ def test_cpu_two_ranks(case):
     _launch([case], nproc=2, force_cpu=True)
 
 
+@pytest.mark.parametrize("case", ["fsdp", "dion_ddp", "functional"])
+def test_cpu_four_ranks(case):
+    """The same cases with four ranks: batches that do not split evenly over the ranks, shares padded with
+    zero matrices."""
+    _launch([case], nproc=4, force_cpu=True, timeout=900)
+
+
 def test_cpu_four_ranks_hybrid_meshes():
     _launch(["hybrid"], nproc=4, force_cpu=True, timeout=900)
 
