@@ -112,3 +112,20 @@ def test_loss_curve_script_learns_the_chain(tmp_path):
     res = subprocess.run([sys.executable, script, "--compare", str(out_json), str(out_json)], env=env,
                          capture_output=True, text=True, timeout=120, cwd=ROOT)
     assert res.returncode == 0 and "mean of the last 20 steps" in res.stdout, res.stdout + res.stderr
+
+
+def test_training_on_a_dp2_fs2_tp2_mesh_with_compressed_sync(tmp_path, shards):
+    """Eight gloo ranks, all three mesh dimensions active, Dion keeping the replicas in step through the
+    low-rank factors: the layout of the multi-GPU benchmark, run through `train.py`."""
+    env = dict(os.environ)
+    env.update(TORCHDYNAMO_DISABLE="1", OMP_NUM_THREADS="1", CUDA_VISIBLE_DEVICES="")
+    cfg = tmp_path / "c.yaml"
+    cfg.write_text(_YAML.format(iters=6).replace("batch_size: 8", "batch_size: 16") + "replicate_mesh_grad_sync: true\n")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=8", "--master-addr",
+           "127.0.0.1", "--master-port", str(29870 + os.getpid() % 50), os.path.join(ROOT, "train.py"), "--config",
+           str(cfg), "--data_dir", str(shards), "--no_wandb", "--dp_size", "2", "--fs_size", "2", "--tp_size", "2"]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900, cwd=ROOT)
+    out = res.stdout + res.stderr
+    assert res.returncode == 0, out[-4000:]
+    v = _val_losses(out)
+    assert set(v) == {0, 6} and v[6] < v[0], v
