@@ -502,9 +502,12 @@ class Dion(Optimizer):
                 if pl.is_shard():
                     size = mesh.size(mesh_dim)
                     if q_local.size(pl.dim) % size != 0:
+                        hint = ("use rank_multiple_of to round the rank" if pl.dim == 1 else
+                                "the sharded dimension of the weight has to be a multiple of the mesh size "
+                                "(uneven shards are not supported)")
                         raise ValueError(
                             f"Q dimension {pl.dim} of size {q_local.size(pl.dim)} is not divisible by the mesh "
-                            f"size {size}; use rank_multiple_of to round the rank.")
+                            f"size {size}; {hint}.")
                     idx = mesh.get_local_rank(mesh_dim)
                     q_local = q_local.chunk(size, dim=pl.dim)[idx]
             state["Q"] = DTensor.from_local(q_local.contiguous(), device_mesh=mesh, placements=placements,
