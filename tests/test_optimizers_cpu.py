@@ -507,3 +507,58 @@ def test_optimizer_state_dicts_interchange_with_the_reference(kind, direction):
     tol = dict(rtol=2e-3, atol=2e-4) if kind == "dion" else dict(rtol=2e-2, atol=2e-3)   # Muon: bf16 Newton-Schulz
     for a, b in zip(ps_w, ps_r):
         torch.testing.assert_close(a, b, **tol)
+
+
+@needs_ref
+@pytest.mark.parametrize("missing", [False, True])
+def test_dion_edge_cases_follow_the_reference(missing):
+    """Parameters without a gradient in some steps, an all-zero gradient, and groups that override the learning
+    rate, rank fraction and weight decay for matrices of the same shape."""
+    torch.manual_seed(0)
+    P = [torch.nn.Parameter(torch.randn(32, 16)) for _ in range(4)] + [torch.nn.Parameter(torch.randn(16, 32)) for _ in range(2)]
+    A, B = _clone(P), _clone(P)
+    groups = lambda ps: [dict(params=ps[:3]), dict(params=ps[3:], lr=0.005, rank_fraction=0.25, weight_decay=0.0)]
+    oa = Dion(groups(A), lr=0.02, rank_fraction=0.5, rank_multiple_of=1)
+    ob = ref.DionReference(groups(B), lr=0.02, rank_fraction=0.5, rank_multiple_of=1, qr_method="qr")
+    _inject_q(oa, ob, A, B)
+    for step in range(3):
+        gen = torch.Generator().manual_seed(step)
+        for i, (p, q) in enumerate(zip(A, B)):
+            if missing and (i + step) % 3 == 0:
+                p.grad = q.grad = None
+                continue
+            g = torch.zeros(p.shape) if i == 1 else torch.randn(p.shape, generator=gen)
+            p.grad, q.grad = g.clone(), g.clone()
+        oa.step()
+        ob.step()
+    for p, q in zip(A, B):
+        assert torch.isfinite(p).all()
+        torch.testing.assert_close(p, q, rtol=1e-5, atol=1e-6)
+
+
+@needs_ref
+@pytest.mark.parametrize("kw", [dict(nesterov=False, adjust_lr="spectral_norm", flatten=True),
+                                dict(nesterov=True, adjust_lr="rms_norm", flatten=True),
+                                dict(nesterov=True, adjust_lr=None, flatten=False),
+                                dict(nesterov=True, adjust_lr="keller_muon", flatten=True)])
+def test_muon_options_follow_the_reference_on_higher_rank_parameters(kw):
+    """Convolution-shaped (4-D) and batched (3-D) parameters with and without `flatten`, every learning-rate
+    scaling, parameters without a gradient in some steps."""
+    torch.manual_seed(0)
+    P = ([torch.nn.Parameter(torch.randn(32, 16)) for _ in range(3)] + [torch.nn.Parameter(torch.randn(8, 4, 3, 3))]
+         + [torch.nn.Parameter(torch.randn(2, 16, 8))])
+    A, B = _clone(P), _clone(P)
+    oa = Muon(A, lr=0.02, weight_decay=0.05, **kw)
+    ob = ref.Muon(B, lr=0.02, weight_decay=0.05, use_triton=False, **kw)
+    for step in range(3):
+        gen = torch.Generator().manual_seed(step)
+        for i, (p, q) in enumerate(zip(A, B)):
+            if (i + step) % 4 == 0:
+                p.grad = q.grad = None
+                continue
+            g = torch.randn(p.shape, generator=gen)
+            p.grad, q.grad = g.clone(), g.clone()
+        oa.step()
+        ob.step()
+    for p, q in zip(A, B):
+        torch.testing.assert_close(p, q, rtol=2e-3, atol=2e-4)
