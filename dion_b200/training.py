@@ -146,6 +146,11 @@ def override_args_from_cli(hp: Hyperparameters, cli_args: argparse.Namespace) ->
 def init_distributed(dp_size, fs_size, tp_size, backend: Optional[str] = None):
     """DDP process group when no mesh size is given, else a ("dp", "fs", "tp") device mesh."""
     global _MASTER
+    if not any(v in os.environ for v in ("RANK", "LOCAL_RANK", "WORLD_SIZE")):
+        # started as a plain `python train.py ...`: one process, one device (the reference insists on torchrun here)
+        os.environ.update(RANK="0", LOCAL_RANK="0", WORLD_SIZE="1")
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
     assert all(v in os.environ for v in ("RANK", "LOCAL_RANK", "WORLD_SIZE")), \
         "This script must be launched using the 'torchrun' command."
     rank, local_rank, world = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"]), int(os.environ["WORLD_SIZE"])

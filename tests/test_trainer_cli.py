@@ -129,3 +129,26 @@ def test_training_on_a_dp2_fs2_tp2_mesh_with_compressed_sync(tmp_path, shards):
     assert res.returncode == 0, out[-4000:]
     v = _val_losses(out)
     assert set(v) == {0, 6} and v[6] < v[0], v
+
+
+@pytest.mark.parametrize("config", ["dion_160m", "dion_cqr_160m", "muon_160m", "dion_160m_full_rank_ddp"])
+def test_shipped_configs_run_as_a_plain_python_process(tmp_path, shards, config):
+    """Every recipe under configs/ parses and trains (dimensions overridden from the command line so that it runs
+    on a CPU in seconds), started as `python train.py ...` without torchrun: one process, one device."""
+    import yaml
+
+    cfg = yaml.safe_load(open(os.path.join(ROOT, "configs", config + ".yaml")))
+    cfg.update(val_loss_every=4, val_tokens=1024)
+    path = tmp_path / "cfg.yaml"
+    path.write_text(yaml.safe_dump(cfg))
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE")}
+    env.update(TORCHDYNAMO_DISABLE="1", OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES="",
+               MASTER_PORT=str(29600 + os.getpid() % 200))
+    cmd = [sys.executable, os.path.join(ROOT, "train.py"), "--config", str(path), "--data_dir", str(shards), "--no_wandb",
+           "--model_dim", "64", "--n_layer", "2", "--n_head", "4", "--sequence_length", "64", "--batch_size", "4",
+           "--device_batch_size", "2", "--num_iterations", "4"]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    out = res.stdout + res.stderr
+    assert res.returncode == 0, out[-4000:]
+    v = _val_losses(out)
+    assert set(v) == {0, 4} and v[4] < v[0], v
