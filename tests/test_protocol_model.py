@@ -37,3 +37,10 @@ def test_all_gather_staging_slots_must_alternate():
     assert pc.check_pull(world=3, cycles=2, buffers=(0, 1)) is None
     witness = pc.check_pull(world=2, cycles=2, buffers=(0,))
     assert witness is not None and witness[-1][1][0] == "pull"
+
+
+def test_the_rule_is_a_reuse_distance_of_two():
+    """A buffer may be rewritten once one other exchange has passed since it was read: schedules whose every
+    reuse is at least two exchanges apart are safe, a back-to-back reuse anywhere in the cycle is not."""
+    for buffers, safe in (((0, 1, 0, 2), True), ((0, 1, 2), True), ((0, 1, 1), False), ((0, 0, 1), False)):
+        assert (pc.check(world=2, cycles=2, buffers=buffers) is None) == safe, buffers
